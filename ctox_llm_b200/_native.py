@@ -1,0 +1,127 @@
+"""Loads libctox_b200.so and declares the C ABI of include/ctox_b200.h for ctypes.
+
+There is no Python or CPU fallback: if the library cannot be loaded this module raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from . import build as _build
+
+Q2B64, Q4B64, MIXED_Q2Q4B64, F16, F32, BF16 = 0, 1, 2, 3, 4, 5
+ACT_IDENTITY, ACT_SILU = 0, 1
+SCALE_NONE, SCALE_F32, SCALE_F16LE = 0, 1, 2
+KERNEL_AUTO, KERNEL_STREAM, KERNEL_ROWWARP = 0, 1, 2
+PREPARE_KEEP_CANONICAL = 1
+
+ERROR_NAMES = {
+    1: "Shape",
+    2: "InvalidArtifact",
+    3: "UnsupportedDType",
+    4: "UnsupportedOperation",
+    5: "MemoryBudget",
+    6: "InvalidState",
+    7: "Cancelled",
+}
+
+
+class CtoxError(RuntimeError):
+    """Mirror of EngineError (models/qwen38_27b/src/error.rs:5-29)."""
+
+    def __init__(self, code: int, message: str):
+        self.code = code
+        self.kind = ERROR_NAMES.get(code, f"code {code}")
+        super().__init__(f"{self.kind}: {message}")
+
+
+class Segment(C.Structure):
+    """QuantSegment (models/qwen38_27b/src/format.rs:56-64)."""
+
+    _fields_ = [
+        ("group_index", C.c_uint32),
+        ("dtype", C.c_uint32),
+        ("row_start", C.c_uint64),
+        ("row_end", C.c_uint64),
+        ("offset", C.c_uint64),
+        ("length", C.c_uint64),
+    ]
+
+
+class FusedMatVecOp(C.Structure):
+    _fields_ = [
+        ("dtype", C.c_uint32),
+        ("activation", C.c_uint32),
+        ("weights", C.c_void_p),
+        ("weights_len", C.c_uint64),
+        ("segments", C.POINTER(Segment)),
+        ("n_segments", C.c_uint64),
+        ("rows", C.c_uint64),
+        ("columns", C.c_uint64),
+        ("input", C.c_void_p),
+        ("input_len", C.c_uint64),
+        ("s_in_kind", C.c_uint32),
+        ("s_out_kind", C.c_uint32),
+        ("s_in", C.c_void_p),
+        ("s_in_len", C.c_uint64),
+        ("s_out", C.c_void_p),
+        ("s_out_len", C.c_uint64),
+        ("bias", C.c_void_p),
+        ("bias_len", C.c_uint64),
+    ]
+
+
+# name -> (restype, argtypes); every symbol of include/ctox_b200.h
+SIGNATURES = {
+    "ctox_abi_version": (C.c_uint32, []),
+    "ctox_backend_profile": (C.c_char_p, []),
+    "ctox_last_error_message": (C.c_char_p, [C.c_void_p]),
+    "ctox_ctx_create": (C.c_int32, [C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "ctox_ctx_destroy": (C.c_int32, [C.c_void_p]),
+    "ctox_ctx_synchronize": (C.c_int32, [C.c_void_p]),
+    "ctox_ctx_allocated_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "ctox_ctx_device_error": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "ctox_ctx_kernel_timing": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "ctox_ctx_kernel_timing_read": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double),
+                                                C.POINTER(C.c_uint64)]),
+    "ctox_fused_matvec": (C.c_int32, [C.c_void_p, C.POINTER(FusedMatVecOp), C.c_void_p]),
+    "ctox_fused_matvec_fanout": (C.c_int32, [C.c_void_p, C.POINTER(FusedMatVecOp), C.c_uint64,
+                                             C.POINTER(C.c_void_p)]),
+    "ctox_recovered_row": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint64,
+                                       C.c_uint32, C.c_void_p, C.c_uint64, C.c_float, C.c_void_p]),
+    "ctox_recovered_row_matvec": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64,
+                                              C.c_void_p, C.c_uint64, C.c_float,
+                                              C.POINTER(C.c_float)]),
+    "ctox_matvec_prepare": (C.c_int32, [C.c_void_p, C.POINTER(FusedMatVecOp), C.c_uint32,
+                                        C.POINTER(C.c_void_p)]),
+    "ctox_matvec_destroy": (C.c_int32, [C.c_void_p]),
+    "ctox_matvec_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64,
+                                         C.c_void_p, C.c_uint64, C.c_uint32]),
+    "ctox_matvec_dispatch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
+                                              C.c_uint32]),
+    "ctox_matvec_info": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
+                                     C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+}
+
+_lib = None
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load() -> C.CDLL:
+    """Loads the shared library (building it first only if nvcc is present and it is stale)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(_build.LIB_PATH) or (_build.is_stale() and os.path.exists(
+            os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc"))):
+        _build.build()
+    lib = C.CDLL(_build.LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # raises AttributeError if the symbol is missing
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

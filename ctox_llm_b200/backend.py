@@ -1,0 +1,246 @@
+"""Host-side mirror of the reference's per-op API over the C ABI.
+
+``B200Backend`` has the methods of ``trait Backend`` (models/qwen38_27b/src/backend/mod.rs:153-169)
+with the same argument meaning and error kinds as ``CpuBackend`` (backend/cpu.rs). Inputs and
+outputs are numpy arrays in host memory, exactly like the borrowed slices / owned ``Vec``s of the
+trait. ``PreparedMatVec`` is the resident form (``CudaCandidateRuntime::prepare_fused_matvec`` /
+``dispatch_prepared``, backend/cuda_runtime.rs:8341-8382,10560): weights uploaded once, dispatch
+on device pointers or host arrays.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import _native as N
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+@dataclass
+class FusedMatVec:
+    """FusedMatVec<'a> (backend/mod.rs:115-128). A scale given as a ``uint8`` array is
+    ``ScaleSlice::F16Le`` (little-endian f16 bytes); a float array is ``ScaleSlice::F32``."""
+
+    dtype: int
+    weights: np.ndarray
+    rows: int
+    columns: int
+    input: Optional[np.ndarray]
+    segments: Sequence[N.Segment] = field(default_factory=list)
+    s_in: Optional[np.ndarray] = None
+    s_out: Optional[np.ndarray] = None
+    bias: Optional[np.ndarray] = None
+    activation: int = N.ACT_IDENTITY
+
+
+@dataclass
+class RecoveredRow:
+    """RecoveredRow<'a> (backend/mod.rs:131-141)."""
+
+    dtype: int
+    weights: np.ndarray
+    columns: int
+    s_in: np.ndarray
+    s_out: float
+
+
+@dataclass
+class RecoveredRowMatVec:
+    """RecoveredRowMatVec<'a> (backend/mod.rs:143-151)."""
+
+    dtype: int
+    weights: np.ndarray
+    corrected_input: np.ndarray
+    s_out: float
+
+
+def _scale_args(s):
+    if s is None:
+        return N.SCALE_NONE, None, 0, None
+    s = np.asarray(s)
+    if s.dtype == np.uint8:
+        s = np.ascontiguousarray(s)
+        return N.SCALE_F16LE, _ptr(s), s.size // 2, s
+    s = _f32(s)
+    return N.SCALE_F32, _ptr(s), s.size, s
+
+
+def _marshal(op: FusedMatVec):
+    keep = []
+    w = np.ascontiguousarray(op.weights, dtype=np.uint8)
+    x = None if op.input is None else _f32(op.input)
+    seg = None
+    if op.segments:
+        seg = (N.Segment * len(op.segments))(*op.segments)
+    sik, sip, sil, si = _scale_args(op.s_in)
+    sok, sop, sol, so = _scale_args(op.s_out)
+    bias = None if op.bias is None else _f32(op.bias)
+    keep += [w, x, seg, si, so, bias]
+    c = N.FusedMatVecOp(
+        op.dtype, op.activation, _ptr(w), w.size,
+        C.cast(seg, C.POINTER(N.Segment)) if seg is not None else None, len(op.segments),
+        op.rows, op.columns, _ptr(x), 0 if x is None else x.size, sik, sok, sip, sil, sop, sol,
+        _ptr(bias), 0 if bias is None else bias.size)
+    return c, keep
+
+
+class B200Backend:
+    """``impl Backend`` for the B200 library: kind() == Cuda, no CPU fallback."""
+
+    def __init__(self, device: int = 0, stream: Optional[int] = None):
+        self._lib = N.load()
+        handle = C.c_void_p()
+        rc = self._lib.ctox_ctx_create(device, C.c_void_p(stream) if stream else None,
+                                       C.byref(handle))
+        if rc:
+            raise N.CtoxError(rc, self._lib.ctox_last_error_message(None).decode())
+        self._ctx = handle
+        self.device = device
+
+    # -- trait Backend ---------------------------------------------------------------------
+    def kind(self) -> str:
+        return "cuda"
+
+    def promotion_state(self) -> str:
+        return "experimental"
+
+    def profile(self) -> str:
+        return self._lib.ctox_backend_profile().decode()
+
+    def fused_matvec(self, operation: FusedMatVec) -> np.ndarray:
+        c, keep = _marshal(operation)
+        out = np.zeros(max(int(operation.rows), 1), dtype=np.float32)
+        self._check(self._lib.ctox_fused_matvec(self._ctx, C.byref(c), _ptr(out)))
+        return out[: operation.rows]
+
+    def fused_matvec_fanout(self, operations: Sequence[FusedMatVec]) -> list:
+        n = len(operations)
+        arr = (N.FusedMatVecOp * max(n, 1))()
+        keep = []
+        for i, op in enumerate(operations):
+            arr[i], k = _marshal(op)
+            keep.append(k)
+        outs = [np.zeros(int(op.rows), dtype=np.float32) for op in operations]
+        ptrs = (C.c_void_p * max(n, 1))(*[o.ctypes.data for o in outs])
+        self._check(self._lib.ctox_fused_matvec_fanout(self._ctx, arr, n, ptrs))
+        return outs
+
+    def recovered_row(self, operation: RecoveredRow) -> np.ndarray:
+        w = np.ascontiguousarray(operation.weights, dtype=np.uint8)
+        kind, p, n, keep = _scale_args(operation.s_in)
+        out = np.zeros(max(int(operation.columns), 1), dtype=np.float32)
+        self._check(self._lib.ctox_recovered_row(self._ctx, operation.dtype, _ptr(w), w.size,
+                                                 operation.columns, kind, p, n,
+                                                 C.c_float(operation.s_out), _ptr(out)))
+        return out[: operation.columns]
+
+    def recovered_row_matvec(self, operation: RecoveredRowMatVec) -> float:
+        w = np.ascontiguousarray(operation.weights, dtype=np.uint8)
+        x = _f32(operation.corrected_input)
+        out = C.c_float()
+        self._check(self._lib.ctox_recovered_row_matvec(self._ctx, operation.dtype, _ptr(w), w.size,
+                                                        _ptr(x), x.size, C.c_float(operation.s_out),
+                                                        C.byref(out)))
+        return out.value
+
+    # -- resident form ---------------------------------------------------------------------
+    def prepare_fused_matvec(self, operation: FusedMatVec, keep_canonical: bool = False
+                             ) -> "PreparedMatVec":
+        c, keep = _marshal(operation)
+        handle = C.c_void_p()
+        flags = N.PREPARE_KEEP_CANONICAL if keep_canonical else 0
+        self._check(self._lib.ctox_matvec_prepare(self._ctx, C.byref(c), flags, C.byref(handle)))
+        return PreparedMatVec(self, handle, int(operation.rows), int(operation.columns))
+
+    # -- housekeeping ----------------------------------------------------------------------
+    def synchronize(self) -> None:
+        self._check(self._lib.ctox_ctx_synchronize(self._ctx))
+
+    def allocated_bytes(self) -> int:
+        v = C.c_uint64()
+        self._check(self._lib.ctox_ctx_allocated_bytes(self._ctx, C.byref(v)))
+        return v.value
+
+    def device_error(self) -> int:
+        v = C.c_int32()
+        self._check(self._lib.ctox_ctx_device_error(self._ctx, C.byref(v)))
+        return v.value
+
+    def kernel_timing(self, enable: bool) -> None:
+        self._check(self._lib.ctox_ctx_kernel_timing(self._ctx, int(enable)))
+
+    def kernel_timing_read(self):
+        """(total milliseconds, launches) of the dominant kernel since the last read."""
+        ms, n = C.c_double(), C.c_uint64()
+        self._check(self._lib.ctox_ctx_kernel_timing_read(self._ctx, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def close(self) -> None:
+        if getattr(self, "_ctx", None):
+            self._lib.ctox_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int) -> None:
+        if rc:
+            raise N.CtoxError(rc, self._lib.ctox_last_error_message(self._ctx).decode())
+
+
+class PreparedMatVec:
+    """PreparedCudaMatVec (backend/cuda_runtime.rs:8341-8382): device-resident weights."""
+
+    def __init__(self, backend: B200Backend, handle, rows: int, columns: int):
+        self._b = backend
+        self._h = handle
+        self.rows = rows
+        self.columns = columns
+
+    def dispatch_host(self, x, positions: int = 1, kernel: int = N.KERNEL_AUTO) -> np.ndarray:
+        x = _f32(x)
+        if x.size != positions * self.columns:
+            raise N.CtoxError(1, f"input has {x.size}, expected {positions * self.columns} values")
+        y = np.zeros(positions * self.rows, dtype=np.float32)
+        self._b._check(self._b._lib.ctox_matvec_dispatch_host(self._h, _ptr(x), positions, _ptr(y),
+                                                              kernel))
+        return y.reshape(positions, self.rows) if positions > 1 else y
+
+    def dispatch_device(self, x_ptr: int, x_dtype: int, positions: int, x_stride: int, y_ptr: int,
+                        y_stride: int, kernel: int = N.KERNEL_AUTO) -> None:
+        """Enqueue on the context's stream; pointers are raw device addresses."""
+        self._b._check(self._b._lib.ctox_matvec_dispatch(self._h, C.c_void_p(x_ptr), x_dtype,
+                                                         positions, x_stride, C.c_void_p(y_ptr),
+                                                         y_stride, kernel))
+
+    def info(self) -> dict:
+        r, c, p, d = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_uint64()
+        self._b._check(self._b._lib.ctox_matvec_info(self._h, C.byref(r), C.byref(c), C.byref(p),
+                                                     C.byref(d)))
+        return {"rows": r.value, "columns": c.value, "packed_bytes": p.value,
+                "device_bytes": d.value}
+
+    def destroy(self) -> None:
+        if self._h:
+            self._b._lib.ctox_matvec_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            if self._b._ctx:
+                self.destroy()
+        except Exception:
+            pass

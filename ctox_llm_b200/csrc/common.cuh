@@ -1,0 +1,99 @@
+// Shared host-side plumbing of libctox_b200: context object, error reporting,
+// tracked device allocations.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/ctox_b200.h"
+
+struct ctox_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = false;
+    int sm_count = 0;
+    int max_smem_optin = 0;
+    uint64_t allocated = 0;
+    int32_t *dev_error = nullptr;   // device error word (kernels set, host reads)
+    int32_t *host_error = nullptr;  // pinned mirror
+    void *pinned = nullptr;         // pinned staging for the host-form calls
+    size_t pinned_bytes = 0;
+    std::string last_error;
+    // optional per-kernel timing of the dominant kernel (benchmark support)
+    bool timing = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timing_events;
+};
+
+namespace ctox {
+
+extern thread_local std::string g_create_error;
+
+inline ctox_status fail(ctox_ctx *ctx, ctox_status code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    if (ctx)
+        ctx->last_error = buf;
+    else
+        g_create_error = buf;
+    return code;
+}
+
+#define CTOX_CUDA(ctx, expr)                                                              \
+    do {                                                                                  \
+        cudaError_t e_ = (expr);                                                          \
+        if (e_ != cudaSuccess)                                                            \
+            return ctox::fail((ctx), CTOX_INVALID_STATE, "%s failed: %s", #expr,          \
+                              cudaGetErrorString(e_));                                    \
+    } while (0)
+
+// Tracked allocation: every byte is accounted on the context so that a caller
+// can assert "nothing left" after destroying its handles.
+ctox_status dev_alloc(ctox_ctx *ctx, void **ptr, size_t bytes);
+void dev_free(ctox_ctx *ctx, void *ptr, size_t bytes);
+ctox_status ensure_pinned(ctox_ctx *ctx, size_t bytes);
+// When timing is enabled, brackets the next launches with a CUDA event pair on
+// the context's stream; both are no-ops otherwise.
+void timing_begin(ctox_ctx *ctx);
+void timing_end(ctox_ctx *ctx);
+
+// Device error codes written by kernels into ctx->dev_error.
+enum : int32_t {
+    DEV_ERR_NONE = 0,
+    DEV_ERR_WAIT_TIMEOUT = 1,   // a bounded mbarrier wait ran out
+    DEV_ERR_NONFINITE_SCALE = 2,
+    DEV_ERR_NONFINITE_VALUE = 3,
+};
+
+inline float f16_bits_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu, bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else {
+            int shift = 0;
+            while (!(man & 0x400u)) {
+                man <<= 1;
+                shift++;
+            }
+            bits = sign | ((uint32_t)(113 - shift) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 112) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+}  // namespace ctox

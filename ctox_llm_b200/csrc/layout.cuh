@@ -1,0 +1,67 @@
+// Prepared ("streaming") weight layout of the Q2_B64 / Q4_B64 matvec kernels.
+//
+// The canonical CTOXQ payload is row-major blocks of [f16 scale][codes]
+// (34 B for Q4, 18 B for Q2; quant.rs:5-8,117-122,181-186). Neither stride is a
+// multiple of 16 bytes, so a kernel cannot fetch canonical blocks with 128-bit
+// loads or bulk copies. `prepare` therefore repacks once, on the device, into
+// super-tiles of 16 rows x 4 blocks (256 columns) whose bytes are exactly the
+// canonical bytes, regrouped so that one warp reads a super-tile as
+//   [128 B scales][code vectors: 32 lanes x 16 B each]
+// and every lane's 16-byte vector holds the codes it feeds to
+// mma.sync.m16n8k16 (rows g and g+8, 16 consecutive columns of lane quarter t).
+// The size is unchanged: 16*4*34 = 2176 B (Q4), 16*4*18 = 1152 B (Q2); rows pad
+// to 16 and blocks to 4 with zero-scale blocks.
+//
+// Super-tiles are ordered row-tile major, column super-tile minor, so any
+// contiguous range of the work list is one contiguous byte range.
+#pragma once
+#include <cstdint>
+
+namespace ctox {
+
+constexpr int kBlockLen = 64;
+constexpr int kQ2BlockBytes = 18;
+constexpr int kQ4BlockBytes = 34;
+constexpr int kTileRows = 16;
+constexpr int kTileBlocks = 4;
+constexpr int kScaleBytes = 128;  // 16 rows x 4 blocks x f16
+
+template <int DT>
+struct Fmt;
+template <>
+struct Fmt<0> {  // Q2_B64
+    static constexpr int kBlockBytes = kQ2BlockBytes;
+    static constexpr int kCodeBytes = 16;
+    static constexpr int kSuperTileBytes = kScaleBytes + 2 * 512;  // 1152
+    static constexpr int kChunkTiles = 4;                          // super-tiles per bulk copy
+};
+template <>
+struct Fmt<1> {  // Q4_B64
+    static constexpr int kBlockBytes = kQ4BlockBytes;
+    static constexpr int kCodeBytes = 32;
+    static constexpr int kSuperTileBytes = kScaleBytes + 4 * 512;  // 2176
+    static constexpr int kChunkTiles = 2;
+};
+
+// Column order in which a lane's 16 consecutive columns are fed to the four
+// MMAs of a block (two columns per A/B register), and its inverse.
+//   Q4: registers are the nibble pairs (1,5)(2,6)(3,7)(4,0) of each 8-code word.
+//   Q2: registers are the field pairs (2,10)(3,11)...(1,9) of the 16-code word.
+__host__ __device__ inline int inv_perm(int dt, int q) {
+    const int q4[16] = {7, 0, 2, 4, 6, 1, 3, 5, 15, 8, 10, 12, 14, 9, 11, 13};
+    const int q2[16] = {12, 14, 0, 2, 4, 6, 8, 10, 13, 15, 1, 3, 5, 7, 9, 11};
+    return dt ? q4[q] : q2[q];
+}
+
+// The kernels feed the tensor cores fp16 values (bias + code) built by OR-ing
+// an exponent pattern over the code bits; the bias depends only on the column.
+__host__ __device__ inline float code_bias(int dt, int column) {
+    if (dt) return (column & 1) ? 64.0f : 4.0f;
+    const float q2[8] = {64.f, 16.f, 64.f, 16.f, 4.f, 64.f, 16.f, 4.f};
+    return q2[column & 7];
+}
+// value = unit * (code - offset): Q4 (code-7.5)/7.5, Q2 (2*code-3)/3.
+__host__ __device__ inline float code_offset(int dt) { return dt ? 7.5f : 1.5f; }
+__host__ __device__ inline float code_unit(int dt) { return dt ? (1.0f / 7.5f) : (2.0f / 3.0f); }
+
+}  // namespace ctox

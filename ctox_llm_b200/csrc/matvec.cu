@@ -1,0 +1,1156 @@
+// Fused Q2_B64 / Q4_B64 dequantize-matvec for sm_100a, decode (1 position) and
+// verify (2..16 positions) forms.
+//
+//   y[m][r] = act((sum_c W[r][c] * x[m][c] * s_in[c] + bias[r]) * s_out[r])
+//
+// Reference semantics: CpuBackend::fused_matvec (backend/cpu.rs:228-310,432-442),
+// CUDA candidate kernels kernels/cuda/q2q4_fused_matvec_sm86.cu:87-195. The
+// reference kernel is one warp per row with byte loads and scalar FMAs and is
+// instruction-bound; this one is built around HBM bandwidth:
+//
+//  * weights are repacked once (layout.cuh) so that every lane reads its codes
+//    as one 16-byte vector and the bytes of any contiguous work range are one
+//    contiguous byte range;
+//  * each warp owns a private ring of shared-memory stages that it fills with
+//    bulk async copies (cp.async.bulk + mbarrier, no cross-warp barrier in the
+//    steady state), so ~140 KB per SM are in flight;
+//  * the work list (16-row x 256-column super-tiles) is split evenly over all
+//    warps of a persistent grid (stream-K); a row tile cut by a split is summed
+//    from per-piece partials in fixed piece order by whichever warp arrives
+//    last, so the result does not depend on timing;
+//  * codes are turned into fp16 operands with one LOP3 per two codes
+//    ((bits & mask) | exponent = bias + code, exact) and the dot products run
+//    on mma.sync.m16n8k16 with fp32 accumulation. The activation is split into
+//    fp16 hi + lo parts (two B columns per position) after a per-block power
+//    of two normalisation, which keeps ~22 bits of each activation; the bias
+//    terms are removed through the accumulator's initial value.
+#include "common.cuh"
+#include "layout.cuh"
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <vector>
+
+namespace ctox {
+
+constexpr int kWarps = 8;        // consumer warps per CTA (each with a private pipeline)
+constexpr int kStages = 4;       // bulk-copy stages per warp
+constexpr int kMaxPosPerPass = 4;  // positions per pass of the streaming kernel (hi/lo => 8 columns)
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after ~0.3 s so that a lost copy can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < (1 << 22); ++i) {
+        if (mbar_test(bar, parity)) return true;
+        if (i > 64) __nanosleep(64);
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes,
+                                         uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                        uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float2 lds64f(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+    return v;
+}
+
+// ------------------------------------------------------------------ repack
+// One warp per super-tile; lane (g, t) gathers its own code bytes.
+template <int DT>
+__global__ void k_repack(const uint8_t *__restrict__ canon, uint8_t *__restrict__ prep,
+                         uint32_t rows, uint32_t blocks, uint32_t row_tiles, uint32_t kst,
+                         int32_t *error_flag) {
+    using F = Fmt<DT>;
+    const uint64_t s = (uint64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (s >= (uint64_t)row_tiles * kst) return;
+    const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t rt = (uint32_t)(s / kst), ks = (uint32_t)(s % kst);
+    uint8_t *out = prep + s * F::kSuperTileBytes;
+    const uint64_t row_bytes = (uint64_t)blocks * F::kBlockBytes;
+    // scales: lane t == 0 writes the 8 halfs of (row g, row g+8) x 4 blocks
+    if (t == 0) {
+        uint16_t sc[8];
+        for (int hh = 0; hh < 2; ++hh)
+            for (int j = 0; j < 4; ++j) {
+                uint32_t row = rt * 16 + g + 8 * hh, blk = ks * 4 + j;
+                uint16_t v = 0;
+                if (row < rows && blk < blocks) {
+                    const uint8_t *b = canon + row * row_bytes + (uint64_t)blk * F::kBlockBytes;
+                    v = (uint16_t)(b[0] | (b[1] << 8));
+                    if ((v & 0x7c00u) == 0x7c00u) atomicExch(error_flag, DEV_ERR_NONFINITE_SCALE);
+                }
+                sc[hh * 4 + j] = v;
+            }
+        uint4 pk;
+        pk.x = sc[0] | ((uint32_t)sc[1] << 16);
+        pk.y = sc[2] | ((uint32_t)sc[3] << 16);
+        pk.z = sc[4] | ((uint32_t)sc[5] << 16);
+        pk.w = sc[6] | ((uint32_t)sc[7] << 16);
+        *reinterpret_cast<uint4 *>(out + g * 16) = pk;
+    }
+    constexpr int kPerLane = F::kCodeBytes / 4;  // code bytes per (row, block, lane quarter)
+    for (int j = 0; j < 4; ++j) {
+        for (int hh = 0; hh < 2; ++hh) {
+            uint32_t row = rt * 16 + g + 8 * hh, blk = ks * 4 + j;
+            uint8_t bytes[kPerLane];
+            for (int i = 0; i < kPerLane; ++i) bytes[i] = 0;
+            if (row < rows && blk < blocks) {
+                const uint8_t *b =
+                    canon + row * row_bytes + (uint64_t)blk * F::kBlockBytes + 2 + t * kPerLane;
+                for (int i = 0; i < kPerLane; ++i) bytes[i] = b[i];
+            }
+            uint8_t *dst;
+            if (DT == 1)  // Q4: one 16 B vector per block: [row g: 8 B][row g+8: 8 B]
+                dst = out + kScaleBytes + j * 512 + lane * 16 + hh * 8;
+            else  // Q2: one vector per block pair: [g,b0][g+8,b0][g,b1][g+8,b1], 4 B each
+                dst = out + kScaleBytes + (j >> 1) * 512 + lane * 16 + (j & 1) * 8 + hh * 4;
+            for (int i = 0; i < kPerLane; ++i) dst[i] = bytes[i];
+        }
+    }
+}
+
+// ------------------------------------------------------------------ activation preparation
+// Turns positions x columns activations into the B-operand fragments of the
+// streaming kernel: x' = x * s_in, per 64-column block scaled by a power of two
+// so that the block maximum lies in [2^14, 2^15), split as fp16 hi + lo.
+// Layout per block: [half 0|1][column n = 2*pos + (hi|lo)][lane quarter t][8 fp16].
+// meta[block][pos] = (-(sum over the block of (bias+offset) * x~), unit / scale factor).
+__global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_stride,
+                         const float *__restrict__ s_in, int columns, int blocks_padded, int npos,
+                         int dt, uint8_t *__restrict__ xfrag, float2 *__restrict__ meta) {
+    const int gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int i = threadIdx.x & 15;
+    if (gid >= blocks_padded * npos) return;  // whole 16-lane groups leave together
+    const int b = gid / npos, m = gid % npos;
+    const int nc = 2 * npos;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int k = b * 64 + i * 4 + j;
+        float xv = 0.f;
+        if (k < columns) {
+            if (x_is_bf16)
+                xv = __bfloat162float(((const __nv_bfloat16 *)x)[(long long)m * x_stride + k]);
+            else
+                xv = ((const float *)x)[(long long)m * x_stride + k];
+            if (s_in) xv *= s_in[k];
+        }
+        v[j] = xv;
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    // the 16 lanes of a group are lanes 0-15 or 16-31 of a warp
+    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+    int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;
+    if (!(amax > 0.f) || e > 127) e = 14;  // zero block or non-finite input: factor 1
+    e = max(e, -100);
+    const float f = __uint_as_float((uint32_t)(14 - e + 127) << 23);
+    const float inv = __uint_as_float((uint32_t)(e - 14 + 127) << 23);
+    float corr = 0.f;
+    uint8_t *base = xfrag + (size_t)b * nc * 128;
+    const int t = i >> 2;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int q = (i & 3) * 4 + j;
+        const float sv = v[j] * f;
+        const __half hi = __float2half_rn(sv);
+        const __half lo = __float2half_rn(sv - __half2float(hi));
+        const float xt = __half2float(hi) + __half2float(lo);
+        corr += (code_bias(dt, q) + code_offset(dt)) * xt;
+        const int pos = inv_perm(dt, q);
+        uint8_t *p = base + (pos >> 3) * (nc * 64) + t * 16 + (pos & 7) * 2;
+        *reinterpret_cast<__half *>(p + (2 * m) * 64) = hi;
+        *reinterpret_cast<__half *>(p + (2 * m + 1) * 64) = lo;
+    }
+#pragma unroll
+    for (int o = 1; o < 16; o <<= 1) corr += __shfl_xor_sync(gmask, corr, o);
+    if (i == 0) meta[b * npos + m] = make_float2(-corr, inv * code_unit(dt));
+}
+
+// ------------------------------------------------------------------ streaming kernel
+struct StreamParams {
+    const uint8_t *wprep;
+    const uint8_t *xfrag;   // prepared activations (k_prep_x)
+    const float2 *meta;
+    const float *s_out;     // [rows] or null
+    const float *bias;      // [rows] or null
+    float *y;               // [npos][y_stride]
+    float *partial;         // [row_tiles][max_pieces][16][kMaxPosPerPass]
+    unsigned *counters;     // [row_tiles], zero between launches
+    int32_t *error_flag;
+    long long y_stride;
+    uint32_t rows, row_tiles, kst, npos, activation, max_pieces;
+    uint32_t total_warps;   // warps that take work (<= super-tiles)
+    uint32_t xfrag_bytes, meta_bytes;
+};
+
+__device__ __forceinline__ float finish_value(float v, uint32_t row, const StreamParams &p) {
+    if (p.bias) v += p.bias[row];
+    if (p.s_out) v *= p.s_out[row];
+    if (p.activation == CTOX_ACT_SILU) v = v / (1.0f + expf(-v));
+    return v;
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kWarps * 32, 1) k_matvec_stream(const StreamParams p) {
+    using F = Fmt<DT>;
+    constexpr uint32_t kChunkBytes = F::kChunkTiles * F::kSuperTileBytes;
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t nc = 2 * p.npos;
+
+    uint8_t *stages = smem;
+    uint8_t *xs = smem + kWarps * kStages * kChunkBytes;
+    uint8_t *ms = xs + p.xfrag_bytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ms + ((p.meta_bytes + 15) & ~15u));
+    const uint32_t xbar = smem_u32(&bars[kWarps * kStages]);
+    const uint32_t my_bars = smem_u32(&bars[warp * kStages]);
+    const uint32_t my_stage = smem_u32(stages + warp * kStages * kChunkBytes);
+
+    // work range of this warp: super-tiles [beg, end)
+    const uint64_t total = (uint64_t)p.row_tiles * p.kst;
+    const uint32_t gw = blockIdx.x * kWarps + warp;
+    const bool active = gw < p.total_warps;
+    uint64_t beg = 0, end = 0;
+    if (active) {
+        beg = ((uint64_t)gw * total) / p.total_warps;
+        end = ((uint64_t)(gw + 1) * total) / p.total_warps;
+    }
+    const uint32_t nchunks = (uint32_t)((end - beg + F::kChunkTiles - 1) / F::kChunkTiles);
+
+    if (threadIdx.x == 0) mbar_init(xbar, 1);
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(my_bars + 8 * s, 1);
+        fence_barrier_init();
+        fence_proxy_async();
+        // weights do not depend on the activations: start streaming at once
+        for (uint32_t c = 0; c < (uint32_t)kStages && c < nchunks; ++c) {
+            uint64_t s0 = beg + (uint64_t)c * F::kChunkTiles;
+            uint32_t n = (uint32_t)min((uint64_t)F::kChunkTiles, end - s0);
+            mbar_expect_tx(my_bars + 8 * c, n * F::kSuperTileBytes);
+            bulk_g2s(my_stage + c * kChunkBytes, p.wprep + s0 * F::kSuperTileBytes,
+                     n * F::kSuperTileBytes, my_bars + 8 * c);
+        }
+    }
+    __syncthreads();  // xbar initialised
+    if (threadIdx.x == 0) {
+        fence_proxy_async();
+        mbar_expect_tx(xbar, p.xfrag_bytes + p.meta_bytes);
+        uint32_t off = 0;
+        while (off < p.xfrag_bytes) {
+            uint32_t n = min(p.xfrag_bytes - off, 32768u);
+            bulk_g2s(smem_u32(xs) + off, p.xfrag + off, n, xbar);
+            off += n;
+        }
+        bulk_g2s(smem_u32(ms), p.meta, p.meta_bytes, xbar);
+    }
+    if (!active || nchunks == 0) {
+        // still hold the CTA until the activation copy has landed in our shared memory
+        if (warp == 0 && !mbar_wait(xbar, 0) && lane == 0) atomicExch(p.error_flag, DEV_ERR_WAIT_TIMEOUT);
+        return;
+    }
+    bool ok = mbar_wait(xbar, 0);
+
+    const uint32_t xs_a = smem_u32(xs), ms_a = smem_u32(ms);
+    const bool has_b = g < nc;
+    const bool has_m = t < p.npos;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t cur_rt = (uint32_t)(beg / p.kst);
+
+    auto flush = [&](uint32_t rt) {
+        // pieces of this row tile = consecutive warps whose ranges intersect it
+        const uint64_t s_first = (uint64_t)rt * p.kst, s_last = s_first + p.kst - 1;
+        const uint32_t w_first = (uint32_t)(((s_first + 1) * p.total_warps + total - 1) / total - 1);
+        const uint32_t w_last = (uint32_t)(((s_last + 1) * p.total_warps + total - 1) / total - 1);
+        const uint32_t pieces = w_last - w_first + 1;
+        float v0 = acc[0] + acc[1], v1 = acc[2] + acc[3];  // hi + lo columns of position t
+        const uint32_t r0 = rt * 16 + g, r1 = r0 + 8;
+        if (pieces > 1) {
+            float *slot = p.partial + ((size_t)rt * p.max_pieces + (gw - w_first)) * (16 * kMaxPosPerPass);
+            if (has_m) {
+                __stcg(slot + g * kMaxPosPerPass + t, v0);
+                __stcg(slot + (g + 8) * kMaxPosPerPass + t, v1);
+            }
+            __threadfence();
+            __syncwarp();
+            unsigned old = 0;
+            if (lane == 0) old = atomicAdd(p.counters + rt, 1u);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old != pieces - 1) return;
+            __threadfence();
+            v0 = 0.f;
+            v1 = 0.f;
+            if (has_m) {
+                const float *base = p.partial + (size_t)rt * p.max_pieces * (16 * kMaxPosPerPass);
+                for (uint32_t q = 0; q < pieces; ++q) {  // fixed order: deterministic sum
+                    v0 += __ldcg(base + q * (16 * kMaxPosPerPass) + g * kMaxPosPerPass + t);
+                    v1 += __ldcg(base + q * (16 * kMaxPosPerPass) + (g + 8) * kMaxPosPerPass + t);
+                }
+            }
+            if (lane == 0) p.counters[rt] = 0;  // ready for the next launch
+        }
+        if (has_m) {
+            if (r0 < p.rows) p.y[(long long)t * p.y_stride + r0] = finish_value(v0, r0, p);
+            if (r1 < p.rows) p.y[(long long)t * p.y_stride + r1] = finish_value(v1, r1, p);
+        }
+    };
+
+    uint32_t waited = 0;  // chunks whose barrier we have passed (for the drain on failure)
+    for (uint32_t c = 0; c < nchunks && ok; ++c) {
+        const uint32_t st = c % kStages, parity = (c / kStages) & 1;
+        ok = mbar_wait(my_bars + 8 * st, parity);
+        if (!ok) break;
+        waited = c + 1;
+        const uint64_t s0 = beg + (uint64_t)c * F::kChunkTiles;
+        const uint32_t n = (uint32_t)min((uint64_t)F::kChunkTiles, end - s0);
+        for (uint32_t i = 0; i < n; ++i) {
+            const uint64_t s = s0 + i;
+            const uint32_t rt = (uint32_t)(s / p.kst), ks = (uint32_t)(s % p.kst);
+            if (rt != cur_rt) {
+                flush(cur_rt);
+                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+                cur_rt = rt;
+            }
+            const uint32_t tile = my_stage + st * kChunkBytes + i * F::kSuperTileBytes;
+            const uint4 sv = lds128(tile + g * 16);
+            const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
+            const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.y));
+            const float2 u01 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.z));
+            const float2 u23 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.w));
+            const float sg[4] = {s01.x, s01.y, s23.x, s23.y};   // row g, blocks 0..3
+            const float sg8[4] = {u01.x, u01.y, u23.x, u23.y};  // row g+8
+            uint4 cw2 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t b = ks * 4 + j;
+                uint4 bA = make_uint4(0, 0, 0, 0), bB = make_uint4(0, 0, 0, 0);
+                if (has_b) {
+                    bA = lds128(xs_a + b * nc * 128 + lane * 16);
+                    bB = lds128(xs_a + b * nc * 128 + nc * 64 + lane * 16);
+                }
+                float2 mt = make_float2(0.f, 0.f);
+                if (has_m) mt = lds64f(ms_a + (b * p.npos + t) * 8);
+                float c4[4] = {mt.x, 0.f, mt.x, 0.f};
+                if (DT == 1) {
+                    const uint4 cw = lds128(tile + kScaleBytes + j * 512 + lane * 16);
+                    {
+                        const uint32_t w = cw.x, w8 = cw.z;
+                        const uint32_t r = __funnelshift_r(w, w, 8), r8 = __funnelshift_r(w8, w8, 8);
+                        mma_f16(c4, (w & 0x00f000f0u) | 0x54005400u, (w8 & 0x00f000f0u) | 0x54005400u,
+                                (w & 0x0f000f00u) | 0x44004400u, (w8 & 0x0f000f00u) | 0x44004400u,
+                                bA.x, bA.y);
+                        mma_f16(c4, (r & 0x00f000f0u) | 0x54005400u, (r8 & 0x00f000f0u) | 0x54005400u,
+                                (r & 0x0f000f00u) | 0x44004400u, (r8 & 0x0f000f00u) | 0x44004400u,
+                                bA.z, bA.w);
+                    }
+                    {
+                        const uint32_t w = cw.y, w8 = cw.w;
+                        const uint32_t r = __funnelshift_r(w, w, 8), r8 = __funnelshift_r(w8, w8, 8);
+                        mma_f16(c4, (w & 0x00f000f0u) | 0x54005400u, (w8 & 0x00f000f0u) | 0x54005400u,
+                                (w & 0x0f000f00u) | 0x44004400u, (w8 & 0x0f000f00u) | 0x44004400u,
+                                bB.x, bB.y);
+                        mma_f16(c4, (r & 0x00f000f0u) | 0x54005400u, (r8 & 0x00f000f0u) | 0x54005400u,
+                                (r & 0x0f000f00u) | 0x44004400u, (r8 & 0x0f000f00u) | 0x44004400u,
+                                bB.z, bB.w);
+                    }
+                } else {
+                    if ((j & 1) == 0) cw2 = lds128(tile + kScaleBytes + (j >> 1) * 512 + lane * 16);
+                    const uint32_t w = (j & 1) ? cw2.z : cw2.x, w8 = (j & 1) ? cw2.w : cw2.y;
+                    const uint32_t a = w >> 6, a8 = w8 >> 6, l = w << 4, l8 = w8 << 4;
+                    mma_f16(c4, (w & 0x00300030u) | 0x54005400u, (w8 & 0x00300030u) | 0x54005400u,
+                            (w & 0x00c000c0u) | 0x4c004c00u, (w8 & 0x00c000c0u) | 0x4c004c00u, bA.x, bA.y);
+                    mma_f16(c4, (w & 0x03000300u) | 0x44004400u, (w8 & 0x03000300u) | 0x44004400u,
+                            (a & 0x00300030u) | 0x54005400u, (a8 & 0x00300030u) | 0x54005400u, bA.z, bA.w);
+                    mma_f16(c4, (a & 0x00c000c0u) | 0x4c004c00u, (a8 & 0x00c000c0u) | 0x4c004c00u,
+                            (a & 0x03000300u) | 0x44004400u, (a8 & 0x03000300u) | 0x44004400u, bB.x, bB.y);
+                    mma_f16(c4, (l & 0x00300030u) | 0x54005400u, (l8 & 0x00300030u) | 0x54005400u,
+                            (l & 0x00c000c0u) | 0x4c004c00u, (l8 & 0x00c000c0u) | 0x4c004c00u, bB.z, bB.w);
+                }
+                const float f0 = sg[j] * mt.y, f1 = sg8[j] * mt.y;
+                acc[0] = fmaf(f0, c4[0], acc[0]);
+                acc[1] = fmaf(f0, c4[1], acc[1]);
+                acc[2] = fmaf(f1, c4[2], acc[2]);
+                acc[3] = fmaf(f1, c4[3], acc[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && c + kStages < nchunks) {
+            // refill the stage we just drained
+            const uint32_t cn = c + kStages;
+            const uint64_t sn = beg + (uint64_t)cn * F::kChunkTiles;
+            const uint32_t nn = (uint32_t)min((uint64_t)F::kChunkTiles, end - sn);
+            fence_proxy_async();
+            mbar_expect_tx(my_bars + 8 * st, nn * F::kSuperTileBytes);
+            bulk_g2s(my_stage + st * kChunkBytes, p.wprep + sn * F::kSuperTileBytes,
+                     nn * F::kSuperTileBytes, my_bars + 8 * st);
+        }
+    }
+    if (!ok) {
+        if (lane == 0) atomicExch(p.error_flag, DEV_ERR_WAIT_TIMEOUT);
+        // let copies already issued into our stages land before the CTA can retire
+        const uint32_t issued = min(nchunks, waited + (uint32_t)kStages);
+        for (uint32_t c = waited; c < issued; ++c)
+            mbar_wait(my_bars + 8 * (c % kStages), (c / kStages) & 1);
+        return;
+    }
+    flush(cur_rt);
+}
+
+// ------------------------------------------------------------------ row-per-warp kernel
+// One warp per row over the canonical bytes, scalar fp32 FMAs, shuffle
+// reduction: the shape of the reference's sm_86 kernel
+// (kernels/cuda/q2q4_fused_matvec_sm86.cu:87-195). Kept as the comparison
+// point for the streaming kernel and for operations that keep canonical bytes.
+template <int DT>
+__global__ void k_matvec_rowwarp(const uint8_t *__restrict__ canon, const float *__restrict__ x,
+                                 const float *__restrict__ s_in, const float *__restrict__ s_out,
+                                 const float *__restrict__ bias, float *__restrict__ y,
+                                 uint32_t rows, uint32_t blocks, uint32_t activation) {
+    using F = Fmt<DT>;
+    const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const uint32_t lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const uint8_t *rp = canon + (uint64_t)row * blocks * F::kBlockBytes;
+    float sum = 0.f;
+    for (uint32_t b = lane; b < blocks; b += 32) {
+        const uint16_t *bp = reinterpret_cast<const uint16_t *>(rp + (uint64_t)b * F::kBlockBytes);
+        const float scale = __half2float(__ushort_as_half(bp[0]));
+        float part = 0.f;
+        const float *xb = x + b * 64;
+        const float *sb = s_in ? s_in + b * 64 : nullptr;
+#pragma unroll 4
+        for (int h = 0; h < F::kCodeBytes / 2; ++h) {
+            const uint32_t w = bp[1 + h];
+            if (DT == 1) {
+#pragma unroll
+                for (int n = 0; n < 4; ++n) {
+                    const int k = h * 4 + n;
+                    const float xv = sb ? xb[k] * sb[k] : xb[k];
+                    part = fmaf(((float)((w >> (4 * n)) & 15u) - 7.5f) * (1.0f / 7.5f), xv, part);
+                }
+            } else {
+#pragma unroll
+                for (int n = 0; n < 8; ++n) {
+                    const int k = h * 8 + n;
+                    const float xv = sb ? xb[k] * sb[k] : xb[k];
+                    part = fmaf((2.0f * (float)((w >> (2 * n)) & 3u) - 3.0f) * (1.0f / 3.0f), xv, part);
+                }
+            }
+        }
+        sum = fmaf(scale, part, sum);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) {
+        if (bias) sum += bias[row];
+        if (s_out) sum *= s_out[row];
+        if (activation == CTOX_ACT_SILU) sum = sum / (1.0f + expf(-sum));
+        y[row] = sum;
+    }
+}
+
+// Embedding-row decode: out[i][c] = scale * norm(code) * s_in[c] * s_out_i for the
+// rows picked by row_ids (backend/cpu.rs:312-370; CUDA candidate
+// kernels/cuda/q2q4_fused_matvec_sm86.cu:711-830). One thread per two columns.
+template <int DT>
+__global__ void k_recovered_rows(const uint8_t *__restrict__ canon, const uint32_t *__restrict__ row_ids,
+                                 const float *__restrict__ s_in, const float *__restrict__ s_out,
+                                 float s_out_scalar, float *__restrict__ out, uint32_t columns,
+                                 uint32_t n_rows, uint32_t matrix_rows, int32_t *error_flag) {
+    using F = Fmt<DT>;
+    const uint32_t i = blockIdx.y;
+    const uint32_t c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n_rows || c >= columns) return;
+    const uint32_t row = row_ids ? row_ids[i] : i;
+    if (row >= matrix_rows) {
+        atomicExch(error_flag, DEV_ERR_NONFINITE_VALUE);
+        return;
+    }
+    const uint32_t blocks = columns / 64;
+    const uint8_t *bp = canon + ((uint64_t)row * blocks + c / 64) * F::kBlockBytes;
+    const float scale = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(bp)));
+    const uint32_t lc = c & 63;
+    float n0, n1;
+    if (DT == 1) {
+        const uint32_t byte = bp[2 + lc / 2];
+        n0 = ((float)(byte & 15u) - 7.5f) / 7.5f;
+        n1 = ((float)(byte >> 4) - 7.5f) / 7.5f;
+    } else {
+        const uint32_t byte = bp[2 + lc / 4] >> ((lc & 3) * 2);
+        const float cb[4] = {-1.0f, -1.0f / 3.0f, 1.0f / 3.0f, 1.0f};
+        n0 = cb[byte & 3u];
+        n1 = cb[(byte >> 2) & 3u];
+    }
+    const float so = s_out ? s_out[row] : s_out_scalar;
+    const float a = s_in ? s_in[c] : 1.0f, b = s_in ? s_in[c + 1] : 1.0f;
+    out[(size_t)i * columns + c] = scale * n0 * a * so;
+    out[(size_t)i * columns + c + 1] = scale * n1 * b * so;
+}
+
+__global__ void k_bf16_to_f32(const __nv_bfloat16 *in, float *out, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = __bfloat162float(in[i]);
+}
+
+}  // namespace ctox
+
+using namespace ctox;
+
+// ------------------------------------------------------------------ host objects
+struct MatvecPart {
+    int dt = 0;  // 0 Q2, 1 Q4
+    uint64_t row_start = 0, rows = 0;
+    uint32_t row_tiles = 0, kst = 0;
+    uint8_t *prep = nullptr;
+    size_t prep_bytes = 0;
+    uint8_t *canon = nullptr;
+    size_t canon_bytes = 0;
+    float *partial = nullptr;
+    size_t partial_bytes = 0;
+    unsigned *counters = nullptr;
+    size_t counters_bytes = 0;
+    uint32_t max_pieces = 1, total_warps = 1, grid = 1;
+};
+
+struct ctox_matvec {
+    ctox_ctx *ctx = nullptr;
+    uint64_t rows = 0, columns = 0, packed_bytes = 0;
+    uint32_t blocks = 0, blocks_padded = 0, activation = 0;
+    std::vector<MatvecPart> parts;
+    float *s_in = nullptr, *s_out = nullptr, *bias = nullptr;
+    uint8_t *xfrag = nullptr;  // [blocks_padded][2*kMaxPosPerPass][128]
+    size_t xfrag_bytes = 0;
+    float2 *meta = nullptr;
+    size_t meta_bytes = 0;
+    float *xtmp = nullptr;  // f32 staging (bf16 input to the row-warp kernel, host form)
+    size_t xtmp_bytes = 0;
+    float *ytmp = nullptr;
+    size_t ytmp_bytes = 0;
+    uint64_t device_bytes = 0;
+};
+
+namespace {
+
+// backend/cpu.rs:41-173
+ctox_status validate_op(ctox_ctx *ctx, const ctox_fused_matvec_op *op, bool need_input) {
+    if (!op) return fail(ctx, CTOX_SHAPE, "operation is NULL");
+    if (op->columns == 0 || op->rows == 0 || op->columns % kBlockLen)
+        return fail(ctx, CTOX_SHAPE,
+                    "Q2/Q4 fused matvec dimensions must be non-zero and columns divisible by 64");
+    if (need_input && (!op->input || op->input_len != op->columns))
+        return fail(ctx, CTOX_SHAPE, "input has %llu, expected %llu values",
+                    (unsigned long long)op->input_len, (unsigned long long)op->columns);
+    if (op->s_in_kind != CTOX_SCALE_NONE && op->s_in_len != op->columns)
+        return fail(ctx, CTOX_SHAPE, "s_in length differs from columns");
+    if (op->s_out_kind != CTOX_SCALE_NONE && op->s_out_len != op->rows)
+        return fail(ctx, CTOX_SHAPE, "s_out length differs from rows");
+    if (op->bias && op->bias_len != op->rows)
+        return fail(ctx, CTOX_SHAPE, "bias length differs from rows");
+    if (op->s_in_kind > CTOX_SCALE_F16LE || op->s_out_kind > CTOX_SCALE_F16LE)
+        return fail(ctx, CTOX_SHAPE, "unknown scale slice kind");
+    if (op->activation > CTOX_ACT_SILU) return fail(ctx, CTOX_SHAPE, "unknown activation");
+    const uint64_t bpr = op->columns / kBlockLen;
+    uint64_t bb = 0;
+    if (op->dtype == CTOX_Q2B64)
+        bb = kQ2BlockBytes;
+    else if (op->dtype == CTOX_Q4B64)
+        bb = kQ4BlockBytes;
+    else if (op->dtype != CTOX_MIXED_Q2Q4B64)
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "dtype %u", op->dtype);
+    if (op->rows > 0x7fffffffull || op->columns > 0x7fffffffull)
+        return fail(ctx, CTOX_SHAPE, "matrix dimension exceeds the device index range");
+    if (bb) {
+        if (op->n_segments)
+            return fail(ctx, CTOX_INVALID_ARTIFACT, "pure Q2/Q4 operation declares mixed row segments");
+        uint64_t blocks, expected;
+        if (__builtin_mul_overflow(op->rows, bpr, &blocks) || __builtin_mul_overflow(blocks, bb, &expected))
+            return fail(ctx, CTOX_SHAPE, "weight buffer size overflows");
+        if (op->weights_len != expected || !op->weights)
+            return fail(ctx, CTOX_SHAPE, "weight buffer has %llu bytes, expected %llu",
+                        (unsigned long long)op->weights_len, (unsigned long long)expected);
+        return CTOX_OK;
+    }
+    if (op->n_segments == 0 || !op->segments)
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "mixed Q2/Q4 operation has no row segments");
+    uint64_t expected_row = 0, expected_offset = 0;
+    for (uint64_t gidx = 0; gidx < op->n_segments; ++gidx) {
+        const ctox_segment &s = op->segments[gidx];
+        if (s.group_index != gidx || s.row_start != expected_row || s.row_end <= s.row_start ||
+            s.row_end > op->rows || s.offset != expected_offset)
+            return fail(ctx, CTOX_INVALID_ARTIFACT, "mixed Q2/Q4 operation has non-contiguous segment %u",
+                        s.group_index);
+        uint64_t sbb;
+        if (s.dtype == CTOX_Q2B64)
+            sbb = kQ2BlockBytes;
+        else if (s.dtype == CTOX_Q4B64)
+            sbb = kQ4BlockBytes;
+        else
+            return fail(ctx, CTOX_INVALID_ARTIFACT, "mixed Q2/Q4 segment %u has invalid dtype %u",
+                        s.group_index, s.dtype);
+        uint64_t blocks, expected_length;
+        if (__builtin_mul_overflow(s.row_end - s.row_start, bpr, &blocks) ||
+            __builtin_mul_overflow(blocks, sbb, &expected_length))
+            return fail(ctx, CTOX_SHAPE, "mixed segment size overflows");
+        if (s.length != expected_length)
+            return fail(ctx, CTOX_INVALID_ARTIFACT, "mixed Q2/Q4 segment %u has %llu bytes, expected %llu",
+                        s.group_index, (unsigned long long)s.length, (unsigned long long)expected_length);
+        expected_row = s.row_end;
+        if (__builtin_add_overflow(expected_offset, s.length, &expected_offset))
+            return fail(ctx, CTOX_SHAPE, "mixed weight buffer size overflows");
+    }
+    if (expected_row != op->rows || expected_offset != op->weights_len || !op->weights)
+        return fail(ctx, CTOX_SHAPE, "mixed segments cover %llu/%llu rows and %llu/%llu bytes",
+                    (unsigned long long)expected_row, (unsigned long long)op->rows,
+                    (unsigned long long)expected_offset, (unsigned long long)op->weights_len);
+    return CTOX_OK;
+}
+
+// backend/mod.rs:91-111: widen a recovery-scale slice, rejecting non-finite values.
+ctox_status widen_scales(ctox_ctx *ctx, uint32_t kind, const void *data, uint64_t n,
+                         std::vector<float> &out) {
+    out.resize(n);
+    for (uint64_t i = 0; i < n; ++i) {
+        float v;
+        if (kind == CTOX_SCALE_F32) {
+            v = ((const float *)data)[i];
+        } else {
+            const uint8_t *b = (const uint8_t *)data + 2 * i;
+            v = f16_bits_to_f32((uint16_t)(b[0] | (b[1] << 8)));
+        }
+        if (!std::isfinite(v))
+            return fail(ctx, CTOX_INVALID_ARTIFACT, "recovery scale %llu is non-finite",
+                        (unsigned long long)i);
+        out[i] = v;
+    }
+    return CTOX_OK;
+}
+
+ctox_status upload_f32(ctox_ctx *ctx, const float *src, uint64_t n, float **dst, ctox_matvec *mv) {
+    ctox_status rc = dev_alloc(ctx, (void **)dst, n * sizeof(float));
+    if (rc) return rc;
+    mv->device_bytes += n * sizeof(float);
+    CTOX_CUDA(ctx, cudaMemcpyAsync(*dst, src, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // src may be a temporary
+    return CTOX_OK;
+}
+
+template <int DT>
+size_t stream_smem_bytes(uint32_t blocks_padded, uint32_t npos) {
+    using F = Fmt<DT>;
+    size_t stage = (size_t)kWarps * kStages * F::kChunkTiles * F::kSuperTileBytes;
+    size_t xfrag = (size_t)blocks_padded * 2 * npos * 128;
+    size_t meta = ((size_t)blocks_padded * npos * 8 + 15) & ~(size_t)15;
+    return stage + xfrag + meta + (kWarps * kStages + 1) * 8;
+}
+
+size_t stream_smem_bytes(int dt, uint32_t blocks_padded, uint32_t npos) {
+    return dt ? stream_smem_bytes<1>(blocks_padded, npos) : stream_smem_bytes<0>(blocks_padded, npos);
+}
+
+void free_matvec(ctox_matvec *mv) {
+    ctox_ctx *ctx = mv->ctx;
+    for (auto &p : mv->parts) {
+        dev_free(ctx, p.prep, p.prep_bytes);
+        dev_free(ctx, p.canon, p.canon_bytes);
+        dev_free(ctx, p.partial, p.partial_bytes);
+        dev_free(ctx, p.counters, p.counters_bytes);
+    }
+    dev_free(ctx, mv->s_in, mv->columns * sizeof(float));
+    dev_free(ctx, mv->s_out, mv->rows * sizeof(float));
+    dev_free(ctx, mv->bias, mv->rows * sizeof(float));
+    dev_free(ctx, mv->xfrag, mv->xfrag_bytes);
+    dev_free(ctx, mv->meta, mv->meta_bytes);
+    dev_free(ctx, mv->xtmp, mv->xtmp_bytes);
+    dev_free(ctx, mv->ytmp, mv->ytmp_bytes);
+    delete mv;
+}
+
+ctox_status prepare_part(ctox_ctx *ctx, ctox_matvec *mv, MatvecPart &part, const uint8_t *host_bytes,
+                         size_t nbytes, uint32_t flags) {
+    const int bb = part.dt ? kQ4BlockBytes : kQ2BlockBytes;
+    const int stb = part.dt ? Fmt<1>::kSuperTileBytes : Fmt<0>::kSuperTileBytes;
+    part.row_tiles = (uint32_t)((part.rows + kTileRows - 1) / kTileRows);
+    part.kst = mv->blocks_padded / kTileBlocks;
+    part.canon_bytes = nbytes;
+    (void)bb;
+    ctox_status rc = dev_alloc(ctx, (void **)&part.canon, nbytes);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemcpyAsync(part.canon, host_bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    part.prep_bytes = (size_t)part.row_tiles * part.kst * stb;
+    rc = dev_alloc(ctx, (void **)&part.prep, part.prep_bytes);
+    if (rc) return rc;
+    const uint64_t total = (uint64_t)part.row_tiles * part.kst;
+    const uint32_t grid = (uint32_t)((total + 3) / 4);
+    if (part.dt)
+        k_repack<1><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
+                                                   part.row_tiles, part.kst, ctx->dev_error);
+    else
+        k_repack<0><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
+                                                   part.row_tiles, part.kst, ctx->dev_error);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    // work split of the streaming kernel
+    uint32_t nw = (uint32_t)ctx->sm_count * kWarps;
+    if ((uint64_t)nw > total) nw = (uint32_t)total;
+    part.total_warps = nw;
+    part.grid = (nw + kWarps - 1) / kWarps;
+    const uint64_t per_warp = total / nw;  // >= 1
+    uint64_t mp = (part.kst + per_warp - 1) / per_warp + 1;
+    if (mp > part.kst) mp = part.kst;
+    if (mp > nw) mp = nw;
+    part.max_pieces = (uint32_t)mp;
+    part.partial_bytes = (size_t)part.row_tiles * part.max_pieces * 16 * kMaxPosPerPass * sizeof(float);
+    rc = dev_alloc(ctx, (void **)&part.partial, part.partial_bytes);
+    if (rc) return rc;
+    part.counters_bytes = (size_t)part.row_tiles * sizeof(unsigned);
+    rc = dev_alloc(ctx, (void **)&part.counters, part.counters_bytes);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemsetAsync(part.counters, 0, part.counters_bytes, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (!(flags & CTOX_PREPARE_KEEP_CANONICAL)) {
+        dev_free(ctx, part.canon, part.canon_bytes);
+        part.canon = nullptr;
+        part.canon_bytes = 0;
+    }
+    mv->device_bytes += part.prep_bytes + part.canon_bytes + part.partial_bytes + part.counters_bytes;
+    return CTOX_OK;
+}
+
+ctox_status set_smem_attr(ctox_ctx *ctx) {
+    static thread_local int done_device = -1;
+    if (done_device == ctx->device) return CTOX_OK;
+    CTOX_CUDA(ctx, cudaFuncSetAttribute(k_matvec_stream<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ctx->max_smem_optin));
+    CTOX_CUDA(ctx, cudaFuncSetAttribute(k_matvec_stream<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        ctx->max_smem_optin));
+    done_device = ctx->device;
+    return CTOX_OK;
+}
+
+ctox_status check_device_error(ctox_ctx *ctx, const char *what) {
+    int32_t code = 0;
+    ctox_status rc = ctox_ctx_device_error(ctx, &code);
+    if (rc) return rc;
+    if (code == DEV_ERR_NONFINITE_SCALE)
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "%s: block scale is non-finite", what);
+    if (code == DEV_ERR_WAIT_TIMEOUT)
+        return fail(ctx, CTOX_INVALID_STATE, "%s: a bounded device wait ran out", what);
+    if (code) return fail(ctx, CTOX_INVALID_STATE, "%s: device error %d", what, code);
+    return CTOX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_matvec_prepare(ctox_ctx *ctx, const ctox_fused_matvec_op *op, uint32_t flags,
+                                ctox_matvec **out) {
+    if (!ctx || !out) return CTOX_INVALID_STATE;
+    *out = nullptr;
+    ctox_status rc = validate_op(ctx, op, false);
+    if (rc) return rc;
+    std::vector<float> s_in, s_out;
+    if (op->s_in_kind != CTOX_SCALE_NONE) {
+        rc = widen_scales(ctx, op->s_in_kind, op->s_in, op->s_in_len, s_in);
+        if (rc) return rc;
+    }
+    if (op->s_out_kind != CTOX_SCALE_NONE) {
+        rc = widen_scales(ctx, op->s_out_kind, op->s_out, op->s_out_len, s_out);
+        if (rc) return rc;
+    }
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    rc = set_smem_attr(ctx);
+    if (rc) return rc;
+    ctox_matvec *mv = new ctox_matvec();
+    mv->ctx = ctx;
+    mv->rows = op->rows;
+    mv->columns = op->columns;
+    mv->packed_bytes = op->weights_len;
+    mv->blocks = (uint32_t)(op->columns / kBlockLen);
+    mv->blocks_padded = (mv->blocks + kTileBlocks - 1) / kTileBlocks * kTileBlocks;
+    mv->activation = op->activation;
+#define PREP_TRY(expr)          \
+    do {                        \
+        rc = (expr);            \
+        if (rc) {               \
+            free_matvec(mv);    \
+            return rc;          \
+        }                       \
+    } while (0)
+    if (!s_in.empty()) PREP_TRY(upload_f32(ctx, s_in.data(), s_in.size(), &mv->s_in, mv));
+    if (!s_out.empty()) PREP_TRY(upload_f32(ctx, s_out.data(), s_out.size(), &mv->s_out, mv));
+    if (op->bias) PREP_TRY(upload_f32(ctx, op->bias, op->rows, &mv->bias, mv));
+    if (op->dtype == CTOX_MIXED_Q2Q4B64) {
+        for (uint64_t i = 0; i < op->n_segments; ++i) {
+            const ctox_segment &s = op->segments[i];
+            MatvecPart part;
+            part.dt = s.dtype == CTOX_Q4B64;
+            part.row_start = s.row_start;
+            part.rows = s.row_end - s.row_start;
+            mv->parts.push_back(part);
+            PREP_TRY(prepare_part(ctx, mv, mv->parts.back(), op->weights + s.offset, s.length, flags));
+        }
+    } else {
+        MatvecPart part;
+        part.dt = op->dtype == CTOX_Q4B64;
+        part.rows = op->rows;
+        mv->parts.push_back(part);
+        PREP_TRY(prepare_part(ctx, mv, mv->parts.back(), op->weights, op->weights_len, flags));
+    }
+    mv->xfrag_bytes = (size_t)mv->blocks_padded * 2 * kMaxPosPerPass * 128;
+    PREP_TRY(dev_alloc(ctx, (void **)&mv->xfrag, mv->xfrag_bytes));
+    mv->meta_bytes = (size_t)mv->blocks_padded * kMaxPosPerPass * sizeof(float2);
+    PREP_TRY(dev_alloc(ctx, (void **)&mv->meta, mv->meta_bytes));
+    mv->device_bytes += mv->xfrag_bytes + mv->meta_bytes;
+    PREP_TRY(check_device_error(ctx, "prepare"));
+#undef PREP_TRY
+    *out = mv;
+    return CTOX_OK;
+}
+
+ctox_status ctox_matvec_destroy(ctox_matvec *mv) {
+    if (!mv) return CTOX_OK;
+    cudaSetDevice(mv->ctx->device);
+    cudaStreamSynchronize(mv->ctx->stream);
+    free_matvec(mv);
+    return CTOX_OK;
+}
+
+ctox_status ctox_matvec_info(const ctox_matvec *mv, uint64_t *rows, uint64_t *columns,
+                             uint64_t *packed_bytes, uint64_t *device_bytes) {
+    if (!mv) return CTOX_INVALID_STATE;
+    if (rows) *rows = mv->rows;
+    if (columns) *columns = mv->columns;
+    if (packed_bytes) *packed_bytes = mv->packed_bytes;
+    if (device_bytes) *device_bytes = mv->device_bytes;
+    return CTOX_OK;
+}
+
+ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_dtype,
+                                 uint32_t positions, uint64_t x_stride, float *y_dev,
+                                 uint64_t y_stride, uint32_t kernel) {
+    if (!mv) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = mv->ctx;
+    if (!x_dev || !y_dev) return fail(ctx, CTOX_SHAPE, "dispatch: null device pointer");
+    if (positions == 0 || positions > 16)
+        return fail(ctx, CTOX_SHAPE, "dispatch: positions must be 1..16, got %u", positions);
+    if (x_dtype != CTOX_F32 && x_dtype != CTOX_BF16)
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "dispatch: activation dtype %u", x_dtype);
+    if (x_stride < mv->columns || y_stride < mv->rows)
+        return fail(ctx, CTOX_SHAPE, "dispatch: stride shorter than a row");
+    if (kernel == CTOX_KERNEL_AUTO) kernel = CTOX_KERNEL_STREAM;
+    cudaStream_t st = ctx->stream;
+
+    if (kernel == CTOX_KERNEL_ROWWARP) {
+        const float *xf = (const float *)x_dev;
+        if (x_dtype == CTOX_BF16) {
+            size_t need = (size_t)positions * x_stride * sizeof(float);
+            if (need > mv->xtmp_bytes) {
+                dev_free(ctx, mv->xtmp, mv->xtmp_bytes);
+                mv->xtmp = nullptr;
+                mv->xtmp_bytes = 0;
+                ctox_status rc = dev_alloc(ctx, (void **)&mv->xtmp, need);
+                if (rc) return rc;
+                mv->xtmp_bytes = need;
+            }
+            long long n = (long long)positions * x_stride;
+            k_bf16_to_f32<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const __nv_bfloat16 *)x_dev,
+                                                                       mv->xtmp, n);
+            xf = mv->xtmp;
+        }
+        for (auto &p : mv->parts) {
+            if (!p.canon)
+                return fail(ctx, CTOX_UNSUPPORTED_OPERATION,
+                            "row-warp kernel needs CTOX_PREPARE_KEEP_CANONICAL at prepare");
+            for (uint32_t m = 0; m < positions; ++m) {
+                const unsigned grid = (unsigned)((p.rows + 3) / 4);
+                const float *so = mv->s_out ? mv->s_out + p.row_start : nullptr;
+                const float *bi = mv->bias ? mv->bias + p.row_start : nullptr;
+                float *yy = y_dev + m * y_stride + p.row_start;
+                timing_begin(ctx);
+                if (p.dt)
+                    k_matvec_rowwarp<1><<<grid, 128, 0, st>>>(p.canon, xf + m * x_stride, mv->s_in, so, bi,
+                                                              yy, (uint32_t)p.rows, mv->blocks, mv->activation);
+                else
+                    k_matvec_rowwarp<0><<<grid, 128, 0, st>>>(p.canon, xf + m * x_stride, mv->s_in, so, bi,
+                                                              yy, (uint32_t)p.rows, mv->blocks, mv->activation);
+                timing_end(ctx);
+            }
+        }
+        CTOX_CUDA(ctx, cudaGetLastError());
+        return CTOX_OK;
+    }
+    if (kernel != CTOX_KERNEL_STREAM) return fail(ctx, CTOX_SHAPE, "dispatch: unknown kernel %u", kernel);
+
+    // positions per pass: limited by the hi/lo column count (8) and by shared memory
+    uint32_t per_pass = kMaxPosPerPass;
+    int worst_dt = 0;
+    for (auto &p : mv->parts) worst_dt |= p.dt;
+    while (per_pass > 1 && stream_smem_bytes(worst_dt, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
+        --per_pass;
+    if (stream_smem_bytes(worst_dt, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
+        return fail(ctx, CTOX_MEMORY_BUDGET, "columns %llu exceed the shared-memory budget of the streaming kernel",
+                    (unsigned long long)mv->columns);
+    const size_t esz = x_dtype == CTOX_BF16 ? 2 : 4;
+    for (uint32_t m0 = 0; m0 < positions; m0 += per_pass) {
+        const uint32_t npos = positions - m0 < per_pass ? positions - m0 : per_pass;
+        const uint8_t *xp = (const uint8_t *)x_dev + (size_t)m0 * x_stride * esz;
+        for (auto &p : mv->parts) {
+            // the activation fragments depend on the code format (bias pattern)
+            const int groups = (int)(mv->blocks_padded * npos);
+            k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, st>>>(xp, x_dtype == CTOX_BF16, (long long)x_stride,
+                                                               mv->s_in, (int)mv->columns,
+                                                               (int)mv->blocks_padded, (int)npos, p.dt,
+                                                               mv->xfrag, mv->meta);
+            StreamParams sp;
+            sp.wprep = p.prep;
+            sp.xfrag = mv->xfrag;
+            sp.meta = mv->meta;
+            sp.s_out = mv->s_out ? mv->s_out + p.row_start : nullptr;
+            sp.bias = mv->bias ? mv->bias + p.row_start : nullptr;
+            sp.y = y_dev + (size_t)m0 * y_stride + p.row_start;
+            sp.partial = p.partial;
+            sp.counters = p.counters;
+            sp.error_flag = ctx->dev_error;
+            sp.y_stride = (long long)y_stride;
+            sp.rows = (uint32_t)p.rows;
+            sp.row_tiles = p.row_tiles;
+            sp.kst = p.kst;
+            sp.npos = npos;
+            sp.activation = mv->activation;
+            sp.max_pieces = p.max_pieces;
+            sp.total_warps = p.total_warps;
+            sp.xfrag_bytes = mv->blocks_padded * 2 * npos * 128;
+            sp.meta_bytes = mv->blocks_padded * npos * 8;
+            const size_t smem = stream_smem_bytes(p.dt, mv->blocks_padded, npos);
+            timing_begin(ctx);
+            if (p.dt)
+                k_matvec_stream<1><<<p.grid, kWarps * 32, smem, st>>>(sp);
+            else
+                k_matvec_stream<0><<<p.grid, kWarps * 32, smem, st>>>(sp);
+            timing_end(ctx);
+        }
+    }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status ctox_matvec_dispatch_host(ctox_matvec *mv, const float *x_host, uint32_t positions,
+                                      float *y_host, uint32_t kernel) {
+    if (!mv) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = mv->ctx;
+    if (!x_host || !y_host) return fail(ctx, CTOX_SHAPE, "dispatch_host: null pointer");
+    if (positions == 0 || positions > 16)
+        return fail(ctx, CTOX_SHAPE, "dispatch_host: positions must be 1..16, got %u", positions);
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    const size_t xb = (size_t)positions * mv->columns * sizeof(float);
+    const size_t yb = (size_t)positions * mv->rows * sizeof(float);
+    ctox_status rc = ensure_pinned(ctx, xb + yb);
+    if (rc) return rc;
+    if (xb > mv->xtmp_bytes) {
+        dev_free(ctx, mv->xtmp, mv->xtmp_bytes);
+        mv->xtmp = nullptr;
+        mv->xtmp_bytes = 0;
+        rc = dev_alloc(ctx, (void **)&mv->xtmp, xb);
+        if (rc) return rc;
+        mv->xtmp_bytes = xb;
+    }
+    if (yb > mv->ytmp_bytes) {
+        dev_free(ctx, mv->ytmp, mv->ytmp_bytes);
+        mv->ytmp = nullptr;
+        mv->ytmp_bytes = 0;
+        rc = dev_alloc(ctx, (void **)&mv->ytmp, yb);
+        if (rc) return rc;
+        mv->ytmp_bytes = yb;
+    }
+    float *px = (float *)ctx->pinned;
+    float *py = (float *)((uint8_t *)ctx->pinned + xb);
+    memcpy(px, x_host, xb);
+    CTOX_CUDA(ctx, cudaMemcpyAsync(mv->xtmp, px, xb, cudaMemcpyHostToDevice, ctx->stream));
+    rc = ctox_matvec_dispatch(mv, mv->xtmp, CTOX_F32, positions, mv->columns, mv->ytmp, mv->rows, kernel);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemcpyAsync(py, mv->ytmp, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->host_error, ctx->dev_error, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                   ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*ctx->host_error) {
+        rc = check_device_error(ctx, "dispatch");
+        if (rc) return rc;
+    }
+    memcpy(y_host, py, yb);
+    return CTOX_OK;
+}
+
+ctox_status ctox_fused_matvec(ctox_ctx *ctx, const ctox_fused_matvec_op *op, float *out) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    ctox_status rc = validate_op(ctx, op, true);
+    if (rc) return rc;
+    if (!out) return fail(ctx, CTOX_SHAPE, "output is NULL");
+    ctox_matvec *mv = nullptr;
+    rc = ctox_matvec_prepare(ctx, op, 0, &mv);
+    if (rc) return rc;
+    rc = ctox_matvec_dispatch_host(mv, op->input, 1, out, CTOX_KERNEL_AUTO);
+    ctox_matvec_destroy(mv);
+    if (rc) return rc;
+    // a non-finite output is an invalid state, as in backend/cuda_runtime.rs:10626-10630
+    for (uint64_t i = 0; i < op->rows; ++i)
+        if (!std::isfinite(out[i]))
+            return fail(ctx, CTOX_INVALID_STATE, "fused matvec produced a non-finite output at row %llu",
+                        (unsigned long long)i);
+    return CTOX_OK;
+}
+
+ctox_status ctox_fused_matvec_fanout(ctox_ctx *ctx, const ctox_fused_matvec_op *ops, uint64_t n,
+                                     float *const *outs) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    if (n == 0 || !ops || !outs) return fail(ctx, CTOX_SHAPE, "fan-out requires at least one projection");
+    for (uint64_t i = 0; i < n; ++i) {
+        ctox_status rc = validate_op(ctx, &ops[i], true);
+        if (rc) return rc;
+    }
+    for (uint64_t i = 0; i < n; ++i) {
+        ctox_status rc = ctox_fused_matvec(ctx, &ops[i], outs[i]);
+        if (rc) return rc;
+    }
+    return CTOX_OK;
+}
+
+ctox_status ctox_recovered_row(ctox_ctx *ctx, uint32_t dtype, const uint8_t *weights,
+                               uint64_t weights_len, uint64_t columns, uint32_t s_in_kind,
+                               const void *s_in, uint64_t s_in_len, float s_out, float *out) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    // backend/cpu.rs:313-338
+    if (columns == 0 || columns % kBlockLen)
+        return fail(ctx, CTOX_SHAPE, "recovered row columns must be non-zero and divisible by 64");
+    if (s_in_kind == CTOX_SCALE_NONE || s_in_kind > CTOX_SCALE_F16LE || s_in_len != columns ||
+        !std::isfinite(s_out))
+        return fail(ctx, CTOX_SHAPE, "recovered row scale contract differs");
+    uint64_t bb;
+    if (dtype == CTOX_Q2B64)
+        bb = kQ2BlockBytes;
+    else if (dtype == CTOX_Q4B64)
+        bb = kQ4BlockBytes;
+    else
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "dtype %u", dtype);
+    const uint64_t expected = columns / kBlockLen * bb;
+    if (weights_len != expected || !weights || !out)
+        return fail(ctx, CTOX_SHAPE, "recovered row has %llu packed bytes, expected %llu",
+                    (unsigned long long)weights_len, (unsigned long long)expected);
+    for (uint64_t b = 0; b < columns / kBlockLen; ++b) {
+        const uint8_t *blk = weights + b * bb;
+        if (!std::isfinite(f16_bits_to_f32((uint16_t)(blk[0] | (blk[1] << 8)))))
+            return fail(ctx, CTOX_INVALID_ARTIFACT, "recovered row block scale is non-finite");
+    }
+    std::vector<float> si;
+    ctox_status rc = widen_scales(ctx, s_in_kind, s_in, s_in_len, si);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    uint8_t *dw = nullptr;
+    float *dsi = nullptr, *dout = nullptr;
+    const size_t fb = columns * sizeof(float);
+    rc = dev_alloc(ctx, (void **)&dw, weights_len);
+    if (!rc) rc = dev_alloc(ctx, (void **)&dsi, fb);
+    if (!rc) rc = dev_alloc(ctx, (void **)&dout, fb);
+    if (!rc) rc = ensure_pinned(ctx, fb);
+    cudaError_t e = cudaSuccess;
+    if (!rc) {
+        e = cudaMemcpyAsync(dw, weights, weights_len, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(dsi, si.data(), fb, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) {
+            dim3 grid((unsigned)((columns / 2 + 127) / 128), 1);
+            if (dtype == CTOX_Q4B64)
+                k_recovered_rows<1><<<grid, 128, 0, ctx->stream>>>(dw, nullptr, dsi, nullptr, s_out, dout,
+                                                                   (uint32_t)columns, 1, 1, ctx->dev_error);
+            else
+                k_recovered_rows<0><<<grid, 128, 0, ctx->stream>>>(dw, nullptr, dsi, nullptr, s_out, dout,
+                                                                   (uint32_t)columns, 1, 1, ctx->dev_error);
+            e = cudaGetLastError();
+        }
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(ctx->pinned, dout, fb, cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e == cudaSuccess) memcpy(out, ctx->pinned, fb);
+    }
+    dev_free(ctx, dw, weights_len);
+    dev_free(ctx, dsi, fb);
+    dev_free(ctx, dout, fb);
+    if (rc) return rc;
+    if (e != cudaSuccess) return fail(ctx, CTOX_INVALID_STATE, "recovered row: %s", cudaGetErrorString(e));
+    return CTOX_OK;
+}
+
+ctox_status ctox_recovered_row_matvec(ctox_ctx *ctx, uint32_t dtype, const uint8_t *weights,
+                                      uint64_t weights_len, const float *corrected_input,
+                                      uint64_t columns, float s_out, float *out) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    // backend/cpu.rs:478-497
+    bool bad = columns == 0 || columns % kBlockLen || !std::isfinite(s_out) || !corrected_input || !out;
+    for (uint64_t i = 0; !bad && i < columns; ++i) bad = !std::isfinite(corrected_input[i]);
+    if (bad) return fail(ctx, CTOX_SHAPE, "recovered row matvec input or output scale is invalid");
+    if (dtype != CTOX_Q2B64 && dtype != CTOX_Q4B64) return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "dtype %u", dtype);
+    ctox_fused_matvec_op op;
+    memset(&op, 0, sizeof op);
+    op.dtype = dtype;
+    op.weights = weights;
+    op.weights_len = weights_len;
+    op.rows = 1;
+    op.columns = columns;
+    op.input = corrected_input;
+    op.input_len = columns;
+    op.s_out_kind = CTOX_SCALE_F32;
+    op.s_out = &s_out;
+    op.s_out_len = 1;
+    return ctox_fused_matvec(ctx, &op, out);
+}
+
+}  // extern "C"

@@ -1,0 +1,180 @@
+/*
+ * libctox_b200 — C ABI of the B200 (sm_100a) decode hot path for CTOX-LLM's
+ * Qwen3.8-27B integration.
+ *
+ * Every entry point is what a foreign-function binding of the reference crate
+ * (models/qwen38_27b/src/) would bind for this path; the reference interface
+ * each one replaces is cited as file:line relative to that directory.
+ *
+ * Conventions
+ *  - All functions return a ctox_status; 0 is success. Codes map 1:1 to the
+ *    variants of EngineError (error.rs:5-29). ctox_last_error_message() gives
+ *    the text of the last failure on a context.
+ *  - Host pointers are borrowed for the duration of the call. `*_prepare`
+ *    copies what it needs into library-owned device memory.
+ *  - Device pointers passed in are borrowed and must belong to the context's
+ *    device. Work is enqueued on the context's stream; functions documented as
+ *    "host form" synchronise before returning.
+ *  - A context and everything created from it are thread-affine, like the
+ *    reference's CudaCandidateRuntime (backend/cuda_runtime.rs:298-300): call
+ *    from one thread at a time. There is no CPU fallback: without a usable
+ *    CUDA device every call fails with CTOX_UNSUPPORTED_OPERATION.
+ */
+#ifndef CTOX_B200_H
+#define CTOX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef int32_t ctox_status;
+
+/* error.rs:5-29 */
+enum {
+    CTOX_OK = 0,
+    CTOX_SHAPE = 1,
+    CTOX_INVALID_ARTIFACT = 2,
+    CTOX_UNSUPPORTED_DTYPE = 3,
+    CTOX_UNSUPPORTED_OPERATION = 4,
+    CTOX_MEMORY_BUDGET = 5,
+    CTOX_INVALID_STATE = 6,
+    CTOX_CANCELLED = 7
+};
+
+/* format.rs:26-32 (TensorDType) plus the activation element types the device
+ * entry points accept. */
+enum {
+    CTOX_Q2B64 = 0,
+    CTOX_Q4B64 = 1,
+    CTOX_MIXED_Q2Q4B64 = 2,
+    CTOX_F16 = 3,
+    CTOX_F32 = 4,
+    CTOX_BF16 = 5
+};
+
+/* backend/mod.rs:54-57 (Activation); the kernel ABI uses the same codes
+ * (backend/cuda_runtime.rs:8370-8373). */
+enum { CTOX_ACT_IDENTITY = 0, CTOX_ACT_SILU = 1 };
+
+/* backend/mod.rs:74-77 (ScaleSlice) */
+enum { CTOX_SCALE_NONE = 0, CTOX_SCALE_F32 = 1, CTOX_SCALE_F16LE = 2 };
+
+/* Kernel choice for ctox_matvec_dispatch. AUTO is the production path. */
+enum {
+    CTOX_KERNEL_AUTO = 0,
+    CTOX_KERNEL_STREAM = 1, /* bulk-copy staged, tensor-core dot products, repacked weights */
+    CTOX_KERNEL_ROWWARP = 2 /* one warp per row over canonical bytes, fp32 FMA */
+};
+
+/* ctox_matvec_prepare flags */
+enum {
+    CTOX_PREPARE_KEEP_CANONICAL = 1u /* keep the canonical bytes resident (row gathers, ROWWARP) */
+};
+
+typedef struct ctox_ctx ctox_ctx;
+typedef struct ctox_matvec ctox_matvec;
+
+/* format.rs:56-64 (QuantSegment) */
+typedef struct {
+    uint32_t group_index;
+    uint32_t dtype;
+    uint64_t row_start;
+    uint64_t row_end;
+    uint64_t offset;
+    uint64_t length;
+} ctox_segment;
+
+/* backend/mod.rs:115-128 (FusedMatVec<'a>) with host slices as pointer+length. */
+typedef struct {
+    uint32_t dtype;
+    uint32_t activation;
+    const uint8_t *weights;
+    uint64_t weights_len;
+    const ctox_segment *segments;
+    uint64_t n_segments;
+    uint64_t rows;
+    uint64_t columns;
+    const float *input;
+    uint64_t input_len;
+    uint32_t s_in_kind;
+    uint32_t s_out_kind;
+    const void *s_in;
+    uint64_t s_in_len; /* values, not bytes */
+    const void *s_out;
+    uint64_t s_out_len;
+    const float *bias;
+    uint64_t bias_len;
+} ctox_fused_matvec_op;
+
+/* ---- context (backend/cuda_runtime.rs:352-417: private context + one stream) ---- */
+
+/* `stream` is a cudaStream_t to borrow, or NULL to let the context own one. */
+ctox_status ctox_ctx_create(int32_t device, void *stream, ctox_ctx **out);
+ctox_status ctox_ctx_destroy(ctox_ctx *ctx);
+ctox_status ctox_ctx_synchronize(ctox_ctx *ctx);
+/* Never NULL; empty when no call has failed. ctx may be NULL (creation errors). */
+const char *ctox_last_error_message(const ctox_ctx *ctx);
+/* Bytes of device memory currently owned through this context
+ * (engine.rs:46-74 AllocationSnapshot; must be 0 after everything is destroyed,
+ * engine.rs:818-824). */
+ctox_status ctox_ctx_allocated_bytes(const ctox_ctx *ctx, uint64_t *bytes);
+/* Returns (and clears) the device-side error word: 0 = none. Kernels set it
+ * instead of trapping, e.g. when a bounded wait ran out. */
+ctox_status ctox_ctx_device_error(ctox_ctx *ctx, int32_t *code);
+/* Benchmark support (the reference's verify/bench binaries time dispatches the
+ * same way, src/bin/cuda_bench.rs): when enabled, every launch of a dominant
+ * kernel (the streaming matvec, the recurrence, the fused head) is bracketed by
+ * a CUDA event pair on the context's stream. _read synchronises, returns the
+ * summed duration and the number of launches since the last read, and clears. */
+ctox_status ctox_ctx_kernel_timing(ctox_ctx *ctx, int32_t enable);
+ctox_status ctox_ctx_kernel_timing_read(ctox_ctx *ctx, double *total_ms, uint64_t *launches);
+/* backend/mod.rs:153-156: kind()/promotion_state()/profile() */
+const char *ctox_backend_profile(void);
+uint32_t ctox_abi_version(void);
+
+/* ---- Backend trait, host form (backend/mod.rs:153-169; CPU implementation
+ * backend/cpu.rs:432-497). Inputs and outputs are host memory; the call
+ * uploads, runs on the GPU, downloads and synchronises. Validation and error
+ * kinds follow backend/cpu.rs:41-173. ---- */
+ctox_status ctox_fused_matvec(ctox_ctx *ctx, const ctox_fused_matvec_op *op, float *out);
+ctox_status ctox_fused_matvec_fanout(ctox_ctx *ctx, const ctox_fused_matvec_op *ops, uint64_t n,
+                                     float *const *outs);
+/* RecoveredRow (backend/mod.rs:131-141, backend/cpu.rs:312-370) */
+ctox_status ctox_recovered_row(ctox_ctx *ctx, uint32_t dtype, const uint8_t *weights,
+                               uint64_t weights_len, uint64_t columns, uint32_t s_in_kind,
+                               const void *s_in, uint64_t s_in_len, float s_out, float *out);
+/* RecoveredRowMatVec (backend/mod.rs:143-151, backend/cpu.rs:478-497) */
+ctox_status ctox_recovered_row_matvec(ctox_ctx *ctx, uint32_t dtype, const uint8_t *weights,
+                                      uint64_t weights_len, const float *corrected_input,
+                                      uint64_t columns, float s_out, float *out);
+
+/* ---- resident form (backend/cuda_runtime.rs:8341-8382 prepare_fused_matvec,
+ * :10560 dispatch_prepared*, :423-468 device views) ---- */
+
+/* Validates like ctox_fused_matvec (op->input may be NULL), uploads weights and
+ * scales once and repacks them for the streaming kernel. */
+ctox_status ctox_matvec_prepare(ctox_ctx *ctx, const ctox_fused_matvec_op *op, uint32_t flags,
+                                ctox_matvec **out);
+ctox_status ctox_matvec_destroy(ctox_matvec *mv);
+/* Y[m][r] = act((sum_c W[r][c] * X[m][c] * s_in[c] + bias[r]) * s_out[r]) for
+ * m < positions. x_dev: positions rows of `columns` elements (CTOX_F32 or
+ * CTOX_BF16), row stride x_stride elements; y_dev: float, row stride y_stride.
+ * positions = 1 is the decode matvec (kernel ABI backend/cuda.rs:73-122); 2..16
+ * is the verify-batched projection (backend/cuda_runtime.rs:9764-9816). */
+ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_dtype,
+                                 uint32_t positions, uint64_t x_stride, float *y_dev,
+                                 uint64_t y_stride, uint32_t kernel);
+/* Same, with host x and y (pinned staging inside the library); synchronises. */
+ctox_status ctox_matvec_dispatch_host(ctox_matvec *mv, const float *x_host, uint32_t positions,
+                                      float *y_host, uint32_t kernel);
+/* Geometry of the prepared operation. */
+ctox_status ctox_matvec_info(const ctox_matvec *mv, uint64_t *rows, uint64_t *columns,
+                             uint64_t *packed_bytes, uint64_t *device_bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
