@@ -45,18 +45,20 @@ struct Fmt<1> {  // Q4_B64
 
 // Column order in which a lane's 16 consecutive columns are fed to the four
 // MMAs of a block (two columns per A/B register), and its inverse.
-//   Q4: registers are the nibble pairs (1,5)(2,6)(3,7)(4,0) of each 8-code word.
+//   Q4: registers are the nibble pairs (0,4)(1,5)(2,6)(3,7) of each 8-code word.
 //   Q2: registers are the field pairs (2,10)(3,11)...(1,9) of the 16-code word.
 __host__ __device__ inline int inv_perm(int dt, int q) {
-    const int q4[16] = {7, 0, 2, 4, 6, 1, 3, 5, 15, 8, 10, 12, 14, 9, 11, 13};
+    const int q4[16] = {0, 2, 4, 6, 1, 3, 5, 7, 8, 10, 12, 14, 9, 11, 13, 15};
     const int q2[16] = {12, 14, 0, 2, 4, 6, 8, 10, 13, 15, 1, 3, 5, 7, 9, 11};
     return dt ? q4[q] : q2[q];
 }
 
 // The kernels feed the tensor cores fp16 values (bias + code) built by OR-ing
-// an exponent pattern over the code bits; the bias depends only on the column.
+// an exponent pattern over code bits that lie inside the 10-bit fp16 mantissa
+// (Q4: every nibble is shifted to bits 4..7, bias 64; Q2: fields at bits 4..9,
+// bias 64/16/4 by position); the bias depends only on the column.
 __host__ __device__ inline float code_bias(int dt, int column) {
-    if (dt) return (column & 1) ? 64.0f : 4.0f;
+    if (dt) return 64.0f;
     const float q2[8] = {64.f, 16.f, 64.f, 16.f, 4.f, 64.f, 16.f, 4.f};
     return q2[column & 7];
 }

@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1) k_matvec_stream(const StreamPa
     const bool has_b = g < nc;
     const bool has_m = t < p.npos;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t cur_rt = (uint32_t)(beg / p.kst);
+    uint32_t cur_rt = (uint32_t)(beg / p.kst), cur_ks = (uint32_t)(beg % p.kst);
 
     auto flush = [&](uint32_t rt) {
         // pieces of this row tile = consecutive warps whose ranges intersect it
@@ -354,13 +354,13 @@ __global__ void __launch_bounds__(kWarps * 32, 1) k_matvec_stream(const StreamPa
         const uint64_t s0 = beg + (uint64_t)c * F::kChunkTiles;
         const uint32_t n = (uint32_t)min((uint64_t)F::kChunkTiles, end - s0);
         for (uint32_t i = 0; i < n; ++i) {
-            const uint64_t s = s0 + i;
-            const uint32_t rt = (uint32_t)(s / p.kst), ks = (uint32_t)(s % p.kst);
-            if (rt != cur_rt) {
+            if (cur_ks == p.kst) {  // crossed into the next row tile
                 flush(cur_rt);
                 acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-                cur_rt = rt;
+                ++cur_rt;
+                cur_ks = 0;
             }
+            const uint32_t ks = cur_ks++;
             const uint32_t tile = my_stage + st * kChunkBytes + i * F::kSuperTileBytes;
             const uint4 sv = lds128(tile + g * 16);
             const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
@@ -383,25 +383,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1) k_matvec_stream(const StreamPa
                 float c4[4] = {mt.x, 0.f, mt.x, 0.f};
                 if (DT == 1) {
                     const uint4 cw = lds128(tile + kScaleBytes + j * 512 + lane * 16);
-                    {
-                        const uint32_t w = cw.x, w8 = cw.z;
-                        const uint32_t r = __funnelshift_r(w, w, 8), r8 = __funnelshift_r(w8, w8, 8);
-                        mma_f16(c4, (w & 0x00f000f0u) | 0x54005400u, (w8 & 0x00f000f0u) | 0x54005400u,
-                                (w & 0x0f000f00u) | 0x44004400u, (w8 & 0x0f000f00u) | 0x44004400u,
-                                bA.x, bA.y);
-                        mma_f16(c4, (r & 0x00f000f0u) | 0x54005400u, (r8 & 0x00f000f0u) | 0x54005400u,
-                                (r & 0x0f000f00u) | 0x44004400u, (r8 & 0x0f000f00u) | 0x44004400u,
-                                bA.z, bA.w);
-                    }
-                    {
-                        const uint32_t w = cw.y, w8 = cw.w;
-                        const uint32_t r = __funnelshift_r(w, w, 8), r8 = __funnelshift_r(w8, w8, 8);
-                        mma_f16(c4, (w & 0x00f000f0u) | 0x54005400u, (w8 & 0x00f000f0u) | 0x54005400u,
-                                (w & 0x0f000f00u) | 0x44004400u, (w8 & 0x0f000f00u) | 0x44004400u,
-                                bB.x, bB.y);
-                        mma_f16(c4, (r & 0x00f000f0u) | 0x54005400u, (r8 & 0x00f000f0u) | 0x54005400u,
-                                (r & 0x0f000f00u) | 0x44004400u, (r8 & 0x0f000f00u) | 0x44004400u,
-                                bB.z, bB.w);
+                    constexpr uint32_t kM = 0x00f000f0u, kE = 0x54005400u;  // (bits & mask) | 64.0h
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t w = h ? cw.y : cw.x, w8 = h ? cw.w : cw.z;
+                        const uint32_t b0 = h ? bB.x : bA.x, b1 = h ? bB.y : bA.y;
+                        const uint32_t b2 = h ? bB.z : bA.z, b3 = h ? bB.w : bA.w;
+                        mma_f16(c4, ((w << 4) & kM) | kE, ((w8 << 4) & kM) | kE, (w & kM) | kE,
+                                (w8 & kM) | kE, b0, b1);
+                        mma_f16(c4, ((w >> 4) & kM) | kE, ((w8 >> 4) & kM) | kE, ((w >> 8) & kM) | kE,
+                                ((w8 >> 8) & kM) | kE, b2, b3);
                     }
                 } else {
                     if ((j & 1) == 0) cw2 = lds128(tile + kScaleBytes + (j >> 1) * 512 + lane * 16);
