@@ -12,8 +12,10 @@
 // The size is unchanged: 16*4*34 = 2176 B (Q4), 16*4*18 = 1152 B (Q2); rows pad
 // to 16 and blocks to 4 with zero-scale blocks.
 //
-// Super-tiles are ordered row-tile major, column super-tile minor, so any
-// contiguous range of the work list is one contiguous byte range.
+// Super-tiles are ordered (row-tile pair, column super-tile, tile of the pair):
+// the two row tiles of a pair share one column range, so a warp that takes a
+// pair loads the activation fragments once for 32 rows, and any contiguous
+// range of the work list (in pair units) is one contiguous byte range.
 #pragma once
 #include <cstdint>
 
@@ -33,35 +35,44 @@ struct Fmt<0> {  // Q2_B64
     static constexpr int kBlockBytes = kQ2BlockBytes;
     static constexpr int kCodeBytes = 16;
     static constexpr int kSuperTileBytes = kScaleBytes + 2 * 512;  // 1152
-    static constexpr int kChunkTiles = 4;                          // super-tiles per bulk copy
+    static constexpr int kChunkPairs = 2;                          // tile pairs per bulk copy
 };
 template <>
 struct Fmt<1> {  // Q4_B64
     static constexpr int kBlockBytes = kQ4BlockBytes;
     static constexpr int kCodeBytes = 32;
     static constexpr int kSuperTileBytes = kScaleBytes + 4 * 512;  // 2176
-    static constexpr int kChunkTiles = 2;
+    static constexpr int kChunkPairs = 1;
 };
 
 // Column order in which a lane's 16 consecutive columns are fed to the four
-// MMAs of a block (two columns per A/B register), and its inverse.
+// MMAs of a block (two columns per A/B register), as the inverse map
+// column -> slot.
 //   Q4: registers are the nibble pairs (0,4)(1,5)(2,6)(3,7) of each 8-code word.
-//   Q2: registers are the field pairs (2,10)(3,11)...(1,9) of the 16-code word.
+//   Q2: registers are the field pairs (0,8)(1,9)...(7,15) of the 16-code word.
 __host__ __device__ inline int inv_perm(int dt, int q) {
     const int q4[16] = {0, 2, 4, 6, 1, 3, 5, 7, 8, 10, 12, 14, 9, 11, 13, 15};
-    const int q2[16] = {12, 14, 0, 2, 4, 6, 8, 10, 13, 15, 1, 3, 5, 7, 9, 11};
+    const int q2[16] = {0, 2, 4, 6, 8, 10, 12, 14, 1, 3, 5, 7, 9, 11, 13, 15};
     return dt ? q4[q] : q2[q];
 }
 
-// The kernels feed the tensor cores fp16 values (bias + code) built by OR-ing
-// an exponent pattern over code bits that lie inside the 10-bit fp16 mantissa
-// (Q4: every nibble is shifted to bits 4..7, bias 64; Q2: fields at bits 4..9,
-// bias 64/16/4 by position); the bias depends only on the column.
-__host__ __device__ inline float code_bias(int dt, int column) {
-    if (dt) return 64.0f;
-    const float q2[8] = {64.f, 16.f, 64.f, 16.f, 4.f, 64.f, 16.f, 4.f};
+// The kernels feed the tensor cores the masked code bits themselves: a code at
+// mantissa bit p of an otherwise zero fp16 is the subnormal  code * 2^(p-24),
+// exact, with no exponent to OR in. Codes at different bit positions carry
+// different powers of two; the activation of that column is pre-multiplied by
+// the inverse power so that every product is  code * x * kCodeScale.
+//   Q4: low nibble p=0 (x16), high nibble p=4 (x1); product scale 2^-20.
+//   Q2: fields at p = 0,2,4,6,8 -> x256,x64,x16,x4,x1; product scale 2^-16.
+__host__ __device__ inline float column_multiplier(int dt, int column) {
+    if (dt) return (column & 1) ? 1.0f : 16.0f;
+    const float q2[8] = {256.f, 64.f, 16.f, 4.f, 1.f, 256.f, 64.f, 16.f};
     return q2[column & 7];
 }
+__host__ __device__ inline float code_scale(int dt) { return dt ? 9.5367431640625e-07f /* 2^-20 */
+                                                               : 1.52587890625e-05f /* 2^-16 */; }
+// Exponent to which a block's largest |activation| is normalised, so that the
+// largest pre-multiplied fp16 stays below 2^15.
+__host__ __device__ inline int norm_exponent(int dt) { return dt ? 10 : 6; }
 // value = unit * (code - offset): Q4 (code-7.5)/7.5, Q2 (2*code-3)/3.
 __host__ __device__ inline float code_offset(int dt) { return dt ? 7.5f : 1.5f; }
 __host__ __device__ inline float code_unit(int dt) { return dt ? (1.0f / 7.5f) : (2.0f / 3.0f); }

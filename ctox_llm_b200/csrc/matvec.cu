@@ -18,12 +18,13 @@
 //    warps of a persistent grid (stream-K); a row tile cut by a split is summed
 //    from per-piece partials in fixed piece order by whichever warp arrives
 //    last, so the result does not depend on timing;
-//  * codes are turned into fp16 operands with one LOP3 per two codes
-//    ((bits & mask) | exponent = bias + code, exact) and the dot products run
-//    on mma.sync.m16n8k16 with fp32 accumulation. The activation is split into
-//    fp16 hi + lo parts (two B columns per position) after a per-block power
-//    of two normalisation, which keeps ~22 bits of each activation; the bias
-//    terms are removed through the accumulator's initial value.
+//  * codes become fp16 operands with one AND per two codes: the masked code
+//    bits, read as an fp16 subnormal, are exactly code * 2^(p-24), and the
+//    dot products run on mma.sync.m16n8k16 with fp32 accumulation. The
+//    activation is split into fp16 hi + lo parts (two B columns per position)
+//    after a per-block power of two normalisation, which keeps ~22 bits of
+//    each activation; the code offset (7.5 / 1.5) enters through the
+//    accumulator's initial value -offset * sum(x).
 #include "common.cuh"
 #include "layout.cuh"
 
@@ -31,13 +32,13 @@
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <vector>
 
 namespace ctox {
 
-constexpr int kWarps = 8;        // consumer warps per CTA (each with a private pipeline)
-constexpr int kStages = 4;       // bulk-copy stages per warp
 constexpr int kMaxPosPerPass = 4;  // positions per pass of the streaming kernel (hi/lo => 8 columns)
+constexpr int kPairRows = 32;      // rows of a tile pair (the unit of work and of the partial sums)
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -67,11 +68,24 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // Bounded wait: gives up after ~0.3 s so that a lost copy can never hang the GPU.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < (1 << 22); ++i) {
-        if (mbar_test(bar, parity)) return true;
-        if (i > 64) __nanosleep(64);
+    if (mbar_test(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (int i = 0; i < (1 << 24); ++i) {
+        if (mbar_try(bar, parity)) return true;  // blocks for a bounded, hardware-defined time
+        if ((i & 255) == 255 && clock64() - t0 > 600000000ll) break;
     }
     return false;
 }
@@ -90,6 +104,15 @@ __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1,
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// d = a * b + (c0, c1, c0, c1): first MMA of a chain, no register copies for the initial value
+__device__ __forceinline__ void mma_f16_init(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1, float c0, float c1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%10,%11,%10,%11};"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -107,13 +130,15 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
 // One warp per super-tile; lane (g, t) gathers its own code bytes.
 template <int DT>
 __global__ void k_repack(const uint8_t *__restrict__ canon, uint8_t *__restrict__ prep,
-                         uint32_t rows, uint32_t blocks, uint32_t row_tiles, uint32_t kst,
+                         uint32_t rows, uint32_t blocks, uint32_t row_tiles_padded, uint32_t kst,
                          int32_t *error_flag) {
     using F = Fmt<DT>;
     const uint64_t s = (uint64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-    if (s >= (uint64_t)row_tiles * kst) return;
+    if (s >= (uint64_t)row_tiles_padded * kst) return;
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t rt = (uint32_t)(s / kst), ks = (uint32_t)(s % kst);
+    // s = ((pair * kst) + ks) * 2 + tile_of_pair
+    const uint32_t rt = (uint32_t)(s / (2ull * kst)) * 2 + (uint32_t)(s & 1);
+    const uint32_t ks = (uint32_t)((s >> 1) % kst);
     uint8_t *out = prep + s * F::kSuperTileBytes;
     const uint64_t row_bytes = (uint64_t)blocks * F::kBlockBytes;
     // scales: lane t == 0 writes the 8 halfs of (row g, row g+8) x 4 blocks
@@ -161,9 +186,10 @@ __global__ void k_repack(const uint8_t *__restrict__ canon, uint8_t *__restrict_
 // ------------------------------------------------------------------ activation preparation
 // Turns positions x columns activations into the B-operand fragments of the
 // streaming kernel: x' = x * s_in, per 64-column block scaled by a power of two
-// so that the block maximum lies in [2^14, 2^15), split as fp16 hi + lo.
+// so that the block maximum lies in [2^E, 2^(E+1)) (E = norm_exponent), split
+// as fp16 hi + lo and pre-multiplied by the column's power of two.
 // Layout per block: [half 0|1][column n = 2*pos + (hi|lo)][lane quarter t][8 fp16].
-// meta[block][pos] = (-(sum over the block of (bias+offset) * x~), unit / scale factor).
+// meta[block][pos] = (-offset * code_scale * sum of the block's x~, unit / (scale factor * code_scale)).
 __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_stride,
                          const float *__restrict__ s_in, int columns, int blocks_padded, int npos,
                          int dt, uint8_t *__restrict__ xfrag, float2 *__restrict__ meta) {
@@ -191,12 +217,13 @@ __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_
     const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
 #pragma unroll
     for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
+    const int ne = norm_exponent(dt);
     int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;
-    if (!(amax > 0.f) || e > 127) e = 14;  // zero block or non-finite input: factor 1
+    if (!(amax > 0.f) || e > 127) e = ne;  // zero block or non-finite input: factor 1
     e = max(e, -100);
-    const float f = __uint_as_float((uint32_t)(14 - e + 127) << 23);
-    const float inv = __uint_as_float((uint32_t)(e - 14 + 127) << 23);
-    float corr = 0.f;
+    const float f = __uint_as_float((uint32_t)(ne - e + 127) << 23);
+    const float inv = __uint_as_float((uint32_t)(e - ne + 127) << 23);
+    float sum = 0.f;
     uint8_t *base = xfrag + (size_t)b * nc * 128;
     const int t = i >> 2;
 #pragma unroll
@@ -205,16 +232,18 @@ __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_
         const float sv = v[j] * f;
         const __half hi = __float2half_rn(sv);
         const __half lo = __float2half_rn(sv - __half2float(hi));
-        const float xt = __half2float(hi) + __half2float(lo);
-        corr += (code_bias(dt, q) + code_offset(dt)) * xt;
+        sum += __half2float(hi) + __half2float(lo);
+        const float mul = column_multiplier(dt, q);  // power of two: exact
         const int pos = inv_perm(dt, q);
         uint8_t *p = base + (pos >> 3) * (nc * 64) + t * 16 + (pos & 7) * 2;
-        *reinterpret_cast<__half *>(p + (2 * m) * 64) = hi;
-        *reinterpret_cast<__half *>(p + (2 * m + 1) * 64) = lo;
+        *reinterpret_cast<__half *>(p + (2 * m) * 64) = __float2half_rn(__half2float(hi) * mul);
+        *reinterpret_cast<__half *>(p + (2 * m + 1) * 64) = __float2half_rn(__half2float(lo) * mul);
     }
 #pragma unroll
-    for (int o = 1; o < 16; o <<= 1) corr += __shfl_xor_sync(gmask, corr, o);
-    if (i == 0) meta[b * npos + m] = make_float2(-corr, inv * code_unit(dt));
+    for (int o = 1; o < 16; o <<= 1) sum += __shfl_xor_sync(gmask, sum, o);
+    if (i == 0)
+        meta[b * npos + m] =
+            make_float2(-code_offset(dt) * code_scale(dt) * sum, inv * code_unit(dt) / code_scale(dt));
 }
 
 // ------------------------------------------------------------------ streaming kernel
@@ -222,219 +251,243 @@ struct StreamParams {
     const uint8_t *wprep;
     const uint8_t *xfrag;   // prepared activations (k_prep_x)
     const float2 *meta;
-    const float *s_out;     // [rows] or null
-    const float *bias;      // [rows] or null
-    float *y;               // [npos][y_stride]
-    float *partial;         // [row_tiles][max_pieces][16][kMaxPosPerPass]
-    unsigned *counters;     // [row_tiles], zero between launches
+    float *partial;         // [pairs][max_pieces][32][kMaxPosPerPass] raw sums
     int32_t *error_flag;
-    long long y_stride;
-    uint32_t rows, row_tiles, kst, npos, activation, max_pieces;
-    uint32_t total_warps;   // warps that take work (<= super-tiles)
+    uint32_t pairs, kst, npos, max_pieces;
+    uint32_t total_warps;   // warps that take work (<= work units)
     uint32_t xfrag_bytes, meta_bytes;
+    uint32_t dbg;
 };
 
-__device__ __forceinline__ float finish_value(float v, uint32_t row, const StreamParams &p) {
-    if (p.bias) v += p.bias[row];
-    if (p.s_out) v *= p.s_out[row];
-    if (p.activation == CTOX_ACT_SILU) v = v / (1.0f + expf(-v));
-    return v;
+// Four MMAs of one 16-row x 64-column block; cw = this lane's code vector(s).
+template <int DT>
+__device__ __forceinline__ void block_mma(float (&c)[4], uint32_t w0, uint32_t w0h, uint32_t w1,
+                                          uint32_t w1h, const uint4 &bA, const uint4 &bB, float c0) {
+    // w0/w1: first/second code word of row g, w0h/w1h: of row g+8 (Q2 uses w0, w0h only)
+    if (DT == 1) {
+        constexpr uint32_t kLo = 0x000f000fu, kHi = 0x00f000f0u;
+        const uint32_t t0 = w0 >> 8, t0h = w0h >> 8, t1 = w1 >> 8, t1h = w1h >> 8;
+        mma_f16_init(c, w0 & kLo, w0h & kLo, w0 & kHi, w0h & kHi, bA.x, bA.y, c0, 0.f);
+        mma_f16(c, t0 & kLo, t0h & kLo, t0 & kHi, t0h & kHi, bA.z, bA.w);
+        mma_f16(c, w1 & kLo, w1h & kLo, w1 & kHi, w1h & kHi, bB.x, bB.y);
+        mma_f16(c, t1 & kLo, t1h & kLo, t1 & kHi, t1h & kHi, bB.z, bB.w);
+    } else {
+        const uint32_t t = w0 >> 10, th = w0h >> 10;
+        mma_f16_init(c, w0 & 0x00030003u, w0h & 0x00030003u, w0 & 0x000c000cu, w0h & 0x000c000cu, bA.x,
+                     bA.y, c0, 0.f);
+        mma_f16(c, w0 & 0x00300030u, w0h & 0x00300030u, w0 & 0x00c000c0u, w0h & 0x00c000c0u, bA.z, bA.w);
+        mma_f16(c, w0 & 0x03000300u, w0h & 0x03000300u, t & 0x00030003u, th & 0x00030003u, bB.x, bB.y);
+        mma_f16(c, t & 0x000c000cu, th & 0x000c000cu, t & 0x00300030u, th & 0x00300030u, bB.z, bB.w);
+    }
 }
 
-template <int DT>
-__global__ void __launch_bounds__(kWarps * 32, 1) k_matvec_stream(const StreamParams p) {
+template <int DT, int WARPS, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamParams p) {
     using F = Fmt<DT>;
-    constexpr uint32_t kChunkBytes = F::kChunkTiles * F::kSuperTileBytes;
+    constexpr uint32_t kST = F::kSuperTileBytes;
+    constexpr uint32_t kUnitBytes = 2 * kST;                      // one tile pair
+    constexpr uint32_t kChunkBytes = F::kChunkPairs * kUnitBytes;  // one bulk copy
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t nc = 2 * p.npos;
 
     uint8_t *stages = smem;
-    uint8_t *xs = smem + kWarps * kStages * kChunkBytes;
+    uint8_t *xs = smem + WARPS * STAGES * kChunkBytes;
     uint8_t *ms = xs + p.xfrag_bytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(ms + ((p.meta_bytes + 15) & ~15u));
-    const uint32_t xbar = smem_u32(&bars[kWarps * kStages]);
-    const uint32_t my_bars = smem_u32(&bars[warp * kStages]);
-    const uint32_t my_stage = smem_u32(stages + warp * kStages * kChunkBytes);
+    uint8_t *zero = ms + ((p.meta_bytes + 15) & ~15u);  // 16 zero bytes for lanes without operands
+    uint64_t *bars = reinterpret_cast<uint64_t *>(zero + 16);
+    const uint32_t xbar = smem_u32(&bars[WARPS * STAGES]);
+    const uint32_t my_bars = smem_u32(&bars[warp * STAGES]);
+    const uint32_t my_stage = smem_u32(stages + warp * STAGES * kChunkBytes);
 
-    // work range of this warp: super-tiles [beg, end)
-    const uint64_t total = (uint64_t)p.row_tiles * p.kst;
-    const uint32_t gw = blockIdx.x * kWarps + warp;
+    // work range of this warp: tile pairs x column super-tiles [beg, end)
+    const uint64_t total = (uint64_t)p.pairs * p.kst;
+    const uint32_t gw = blockIdx.x * WARPS + warp;
     const bool active = gw < p.total_warps;
     uint64_t beg = 0, end = 0;
     if (active) {
         beg = ((uint64_t)gw * total) / p.total_warps;
         end = ((uint64_t)(gw + 1) * total) / p.total_warps;
     }
-    const uint32_t nchunks = (uint32_t)((end - beg + F::kChunkTiles - 1) / F::kChunkTiles);
+    const uint32_t nchunks = (uint32_t)((end - beg + F::kChunkPairs - 1) / F::kChunkPairs);
 
-    if (threadIdx.x == 0) mbar_init(xbar, 1);
+    if (threadIdx.x == 0) {
+        mbar_init(xbar, 1);
+        *reinterpret_cast<uint4 *>(zero) = make_uint4(0, 0, 0, 0);
+    }
     if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) mbar_init(my_bars + 8 * s, 1);
+        for (int s = 0; s < STAGES; ++s) mbar_init(my_bars + 8 * s, 1);
         fence_barrier_init();
         fence_proxy_async();
         // weights do not depend on the activations: start streaming at once
-        for (uint32_t c = 0; c < (uint32_t)kStages && c < nchunks; ++c) {
-            uint64_t s0 = beg + (uint64_t)c * F::kChunkTiles;
-            uint32_t n = (uint32_t)min((uint64_t)F::kChunkTiles, end - s0);
-            mbar_expect_tx(my_bars + 8 * c, n * F::kSuperTileBytes);
-            bulk_g2s(my_stage + c * kChunkBytes, p.wprep + s0 * F::kSuperTileBytes,
-                     n * F::kSuperTileBytes, my_bars + 8 * c);
+        for (uint32_t c = 0; c < (uint32_t)STAGES && c < nchunks; ++c) {
+            const uint64_t u0 = beg + (uint64_t)c * F::kChunkPairs;
+            const uint32_t n = (uint32_t)min((uint64_t)F::kChunkPairs, end - u0);
+            mbar_expect_tx(my_bars + 8 * c, n * kUnitBytes);
+            bulk_g2s(my_stage + c * kChunkBytes, p.wprep + u0 * kUnitBytes, n * kUnitBytes,
+                     my_bars + 8 * c);
         }
     }
-    __syncthreads();  // xbar initialised
+    __syncthreads();  // xbar and the zero bytes are initialised
     if (threadIdx.x == 0) {
         fence_proxy_async();
         mbar_expect_tx(xbar, p.xfrag_bytes + p.meta_bytes);
         uint32_t off = 0;
         while (off < p.xfrag_bytes) {
-            uint32_t n = min(p.xfrag_bytes - off, 32768u);
+            const uint32_t n = min(p.xfrag_bytes - off, 32768u);
             bulk_g2s(smem_u32(xs) + off, p.xfrag + off, n, xbar);
             off += n;
         }
         bulk_g2s(smem_u32(ms), p.meta, p.meta_bytes, xbar);
     }
-    if (!active || nchunks == 0) {
-        // still hold the CTA until the activation copy has landed in our shared memory
-        if (warp == 0 && !mbar_wait(xbar, 0) && lane == 0) atomicExch(p.error_flag, DEV_ERR_WAIT_TIMEOUT);
-        return;
-    }
+    if (!active || nchunks == 0) return;  // warp 0 of every CTA is active and waits for xbar below
     bool ok = mbar_wait(xbar, 0);
 
-    const uint32_t xs_a = smem_u32(xs), ms_a = smem_u32(ms);
-    const bool has_b = g < nc;
-    const bool has_m = t < p.npos;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t cur_rt = (uint32_t)(beg / p.kst), cur_ks = (uint32_t)(beg % p.kst);
+    // lanes whose B column / position does not exist read zeros with stride 0
+    const bool has_b = g < nc, has_m = t < p.npos;
+    const uint32_t b_stride = has_b ? nc * 128 : 0;
+    const uint32_t b_base = has_b ? smem_u32(xs) + lane * 16 : smem_u32(zero);
+    const uint32_t b_half = has_b ? nc * 64 : 0;
+    const uint32_t m_stride = has_m ? p.npos * 8 : 0;
+    const uint32_t m_base = has_m ? smem_u32(ms) + t * 8 : smem_u32(zero);
 
-    auto flush = [&](uint32_t rt) {
-        // pieces of this row tile = consecutive warps whose ranges intersect it
-        const uint64_t s_first = (uint64_t)rt * p.kst, s_last = s_first + p.kst - 1;
-        const uint32_t w_first = (uint32_t)(((s_first + 1) * p.total_warps + total - 1) / total - 1);
-        const uint32_t w_last = (uint32_t)(((s_last + 1) * p.total_warps + total - 1) / total - 1);
-        const uint32_t pieces = w_last - w_first + 1;
-        float v0 = acc[0] + acc[1], v1 = acc[2] + acc[3];  // hi + lo columns of position t
-        const uint32_t r0 = rt * 16 + g, r1 = r0 + 8;
-        if (pieces > 1) {
-            float *slot = p.partial + ((size_t)rt * p.max_pieces + (gw - w_first)) * (16 * kMaxPosPerPass);
-            if (has_m) {
-                __stcg(slot + g * kMaxPosPerPass + t, v0);
-                __stcg(slot + (g + 8) * kMaxPosPerPass + t, v1);
-            }
-            __threadfence();
-            __syncwarp();
-            unsigned old = 0;
-            if (lane == 0) old = atomicAdd(p.counters + rt, 1u);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old != pieces - 1) return;
-            __threadfence();
-            v0 = 0.f;
-            v1 = 0.f;
-            if (has_m) {
-                const float *base = p.partial + (size_t)rt * p.max_pieces * (16 * kMaxPosPerPass);
-                for (uint32_t q = 0; q < pieces; ++q) {  // fixed order: deterministic sum
-                    v0 += __ldcg(base + q * (16 * kMaxPosPerPass) + g * kMaxPosPerPass + t);
-                    v1 += __ldcg(base + q * (16 * kMaxPosPerPass) + (g + 8) * kMaxPosPerPass + t);
-                }
-            }
-            if (lane == 0) p.counters[rt] = 0;  // ready for the next launch
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    uint32_t cur_pair = (uint32_t)(beg / p.kst), cur_ks = (uint32_t)(beg % p.kst);
+
+    const uint32_t rloc[4] = {g, g + 8, 16 + g, 24 + g};  // rows of this lane inside a pair
+    // Raw sums go to the slot (pair, piece): piece = rank of this warp among the consecutive
+    // warps whose ranges intersect the pair. A pair that lies wholly inside this warp's range
+    // has one piece; only the first and the last pair of a range can be cut. k_matvec_finish
+    // adds the pieces in piece order, so the result does not depend on timing and the stream
+    // needs no atomics, counters or fences.
+    auto close_pair = [&](uint32_t pr, bool reached_end_of_pair) {
+        uint32_t piece = 0;
+        if ((uint64_t)pr * p.kst < beg || !reached_end_of_pair) {
+            const uint64_t u_first = (uint64_t)pr * p.kst;
+            const uint32_t w_first = (uint32_t)(((u_first + 1) * p.total_warps + total - 1) / total - 1);
+            piece = gw - w_first;
         }
         if (has_m) {
-            if (r0 < p.rows) p.y[(long long)t * p.y_stride + r0] = finish_value(v0, r0, p);
-            if (r1 < p.rows) p.y[(long long)t * p.y_stride + r1] = finish_value(v1, r1, p);
+            float *slot = p.partial + ((size_t)pr * p.max_pieces + piece) * (kPairRows * kMaxPosPerPass);
+            slot[rloc[0] * kMaxPosPerPass + t] = acc[0] + acc[1];  // hi + lo columns of position t
+            slot[rloc[1] * kMaxPosPerPass + t] = acc[2] + acc[3];
+            slot[rloc[2] * kMaxPosPerPass + t] = acc[4] + acc[5];
+            slot[rloc[3] * kMaxPosPerPass + t] = acc[6] + acc[7];
         }
     };
 
     uint32_t waited = 0;  // chunks whose barrier we have passed (for the drain on failure)
     for (uint32_t c = 0; c < nchunks && ok; ++c) {
-        const uint32_t st = c % kStages, parity = (c / kStages) & 1;
+        const uint32_t st = c % STAGES, parity = (c / STAGES) & 1;
         ok = mbar_wait(my_bars + 8 * st, parity);
         if (!ok) break;
         waited = c + 1;
-        const uint64_t s0 = beg + (uint64_t)c * F::kChunkTiles;
-        const uint32_t n = (uint32_t)min((uint64_t)F::kChunkTiles, end - s0);
+        const uint64_t u0 = beg + (uint64_t)c * F::kChunkPairs;
+        const uint32_t n = (uint32_t)min((uint64_t)F::kChunkPairs, end - u0);
         for (uint32_t i = 0; i < n; ++i) {
-            if (cur_ks == p.kst) {  // crossed into the next row tile
-                flush(cur_rt);
-                acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
-                ++cur_rt;
+            if (p.dbg & 1) continue;
+            if (cur_ks == p.kst) {  // crossed into the next tile pair
+                if (!(p.dbg & 2)) close_pair(cur_pair, true);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+                ++cur_pair;
                 cur_ks = 0;
             }
-            const uint32_t ks = cur_ks++;
-            const uint32_t tile = my_stage + st * kChunkBytes + i * F::kSuperTileBytes;
-            const uint4 sv = lds128(tile + g * 16);
-            const float2 s01 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.x));
-            const float2 s23 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.y));
-            const float2 u01 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.z));
-            const float2 u23 = __half22float2(*reinterpret_cast<const __half2 *>(&sv.w));
-            const float sg[4] = {s01.x, s01.y, s23.x, s23.y};   // row g, blocks 0..3
-            const float sg8[4] = {u01.x, u01.y, u23.x, u23.y};  // row g+8
-            uint4 cw2 = make_uint4(0, 0, 0, 0);
+            const uint32_t b0 = (cur_ks++) * 4;
+            const uint32_t tile0 = my_stage + st * kChunkBytes + i * kUnitBytes, tile1 = tile0 + kST;
+            // scales of both tiles: rows g, g+8 (tile 0) and 16+g, 24+g (tile 1), blocks 0..3
+            const uint4 sv0 = lds128(tile0 + g * 16), sv1 = lds128(tile1 + g * 16);
+            float sc[4][4];
+            {
+                const uint32_t raw[8] = {sv0.x, sv0.y, sv0.z, sv0.w, sv1.x, sv1.y, sv1.z, sv1.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const float2 lo2 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[2 * r]));
+                    const float2 hi2 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[2 * r + 1]));
+                    sc[r][0] = lo2.x;
+                    sc[r][1] = lo2.y;
+                    sc[r][2] = hi2.x;
+                    sc[r][3] = hi2.y;
+                }
+            }
+            uint32_t xb = b_base + b0 * b_stride, mb = m_base + b0 * m_stride;
+            uint4 q0 = make_uint4(0, 0, 0, 0), q1 = make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const uint32_t b = ks * 4 + j;
-                uint4 bA = make_uint4(0, 0, 0, 0), bB = make_uint4(0, 0, 0, 0);
-                if (has_b) {
-                    bA = lds128(xs_a + b * nc * 128 + lane * 16);
-                    bB = lds128(xs_a + b * nc * 128 + nc * 64 + lane * 16);
-                }
-                float2 mt = make_float2(0.f, 0.f);
-                if (has_m) mt = lds64f(ms_a + (b * p.npos + t) * 8);
-                float c4[4] = {mt.x, 0.f, mt.x, 0.f};
+                if ((p.dbg & 4) && j > 0) break;
+                const uint4 bA = lds128(xb), bB = lds128(xb + b_half);
+                const float2 mt = lds64f(mb);
+                xb += b_stride;
+                mb += m_stride;
+                float c0[4], c1[4];
                 if (DT == 1) {
-                    const uint4 cw = lds128(tile + kScaleBytes + j * 512 + lane * 16);
-                    constexpr uint32_t kM = 0x00f000f0u, kE = 0x54005400u;  // (bits & mask) | 64.0h
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t w = h ? cw.y : cw.x, w8 = h ? cw.w : cw.z;
-                        const uint32_t b0 = h ? bB.x : bA.x, b1 = h ? bB.y : bA.y;
-                        const uint32_t b2 = h ? bB.z : bA.z, b3 = h ? bB.w : bA.w;
-                        mma_f16(c4, ((w << 4) & kM) | kE, ((w8 << 4) & kM) | kE, (w & kM) | kE,
-                                (w8 & kM) | kE, b0, b1);
-                        mma_f16(c4, ((w >> 4) & kM) | kE, ((w8 >> 4) & kM) | kE, ((w >> 8) & kM) | kE,
-                                ((w8 >> 8) & kM) | kE, b2, b3);
-                    }
+                    const uint4 a0 = lds128(tile0 + kScaleBytes + j * 512 + lane * 16);
+                    const uint4 a1 = lds128(tile1 + kScaleBytes + j * 512 + lane * 16);
+                    block_mma<1>(c0, a0.x, a0.z, a0.y, a0.w, bA, bB, mt.x);
+                    block_mma<1>(c1, a1.x, a1.z, a1.y, a1.w, bA, bB, mt.x);
                 } else {
-                    if ((j & 1) == 0) cw2 = lds128(tile + kScaleBytes + (j >> 1) * 512 + lane * 16);
-                    const uint32_t w = (j & 1) ? cw2.z : cw2.x, w8 = (j & 1) ? cw2.w : cw2.y;
-                    const uint32_t a = w >> 6, a8 = w8 >> 6, l = w << 4, l8 = w8 << 4;
-                    mma_f16(c4, (w & 0x00300030u) | 0x54005400u, (w8 & 0x00300030u) | 0x54005400u,
-                            (w & 0x00c000c0u) | 0x4c004c00u, (w8 & 0x00c000c0u) | 0x4c004c00u, bA.x, bA.y);
-                    mma_f16(c4, (w & 0x03000300u) | 0x44004400u, (w8 & 0x03000300u) | 0x44004400u,
-                            (a & 0x00300030u) | 0x54005400u, (a8 & 0x00300030u) | 0x54005400u, bA.z, bA.w);
-                    mma_f16(c4, (a & 0x00c000c0u) | 0x4c004c00u, (a8 & 0x00c000c0u) | 0x4c004c00u,
-                            (a & 0x03000300u) | 0x44004400u, (a8 & 0x03000300u) | 0x44004400u, bB.x, bB.y);
-                    mma_f16(c4, (l & 0x00300030u) | 0x54005400u, (l8 & 0x00300030u) | 0x54005400u,
-                            (l & 0x00c000c0u) | 0x4c004c00u, (l8 & 0x00c000c0u) | 0x4c004c00u, bB.z, bB.w);
+                    if ((j & 1) == 0) {
+                        q0 = lds128(tile0 + kScaleBytes + (j >> 1) * 512 + lane * 16);
+                        q1 = lds128(tile1 + kScaleBytes + (j >> 1) * 512 + lane * 16);
+                    }
+                    block_mma<0>(c0, (j & 1) ? q0.z : q0.x, (j & 1) ? q0.w : q0.y, 0, 0, bA, bB, mt.x);
+                    block_mma<0>(c1, (j & 1) ? q1.z : q1.x, (j & 1) ? q1.w : q1.y, 0, 0, bA, bB, mt.x);
                 }
-                const float f0 = sg[j] * mt.y, f1 = sg8[j] * mt.y;
-                acc[0] = fmaf(f0, c4[0], acc[0]);
-                acc[1] = fmaf(f0, c4[1], acc[1]);
-                acc[2] = fmaf(f1, c4[2], acc[2]);
-                acc[3] = fmaf(f1, c4[3], acc[3]);
+                const float f0 = sc[0][j] * mt.y, f1 = sc[1][j] * mt.y;
+                const float f2 = sc[2][j] * mt.y, f3 = sc[3][j] * mt.y;
+                acc[0] = fmaf(f0, c0[0], acc[0]);
+                acc[1] = fmaf(f0, c0[1], acc[1]);
+                acc[2] = fmaf(f1, c0[2], acc[2]);
+                acc[3] = fmaf(f1, c0[3], acc[3]);
+                acc[4] = fmaf(f2, c1[0], acc[4]);
+                acc[5] = fmaf(f2, c1[1], acc[5]);
+                acc[6] = fmaf(f3, c1[2], acc[6]);
+                acc[7] = fmaf(f3, c1[3], acc[7]);
             }
         }
         __syncwarp();
-        if (lane == 0 && c + kStages < nchunks) {
+        if (lane == 0 && c + STAGES < nchunks) {
             // refill the stage we just drained
-            const uint32_t cn = c + kStages;
-            const uint64_t sn = beg + (uint64_t)cn * F::kChunkTiles;
-            const uint32_t nn = (uint32_t)min((uint64_t)F::kChunkTiles, end - sn);
+            const uint32_t cn = c + STAGES;
+            const uint64_t un = beg + (uint64_t)cn * F::kChunkPairs;
+            const uint32_t nn = (uint32_t)min((uint64_t)F::kChunkPairs, end - un);
             fence_proxy_async();
-            mbar_expect_tx(my_bars + 8 * st, nn * F::kSuperTileBytes);
-            bulk_g2s(my_stage + st * kChunkBytes, p.wprep + sn * F::kSuperTileBytes,
-                     nn * F::kSuperTileBytes, my_bars + 8 * st);
+            mbar_expect_tx(my_bars + 8 * st, nn * kUnitBytes);
+            bulk_g2s(my_stage + st * kChunkBytes, p.wprep + un * kUnitBytes, nn * kUnitBytes,
+                     my_bars + 8 * st);
         }
     }
     if (!ok) {
         if (lane == 0) atomicExch(p.error_flag, DEV_ERR_WAIT_TIMEOUT);
         // let copies already issued into our stages land before the CTA can retire
-        const uint32_t issued = min(nchunks, waited + (uint32_t)kStages);
+        const uint32_t issued = min(nchunks, waited + (uint32_t)STAGES);
         for (uint32_t c = waited; c < issued; ++c)
-            mbar_wait(my_bars + 8 * (c % kStages), (c / kStages) & 1);
+            mbar_wait(my_bars + 8 * (c % STAGES), (c / STAGES) & 1);
         return;
     }
-    flush(cur_rt);
+    if (p.dbg & 2) return;
+    close_pair(cur_pair, cur_ks == p.kst);
+}
+
+// y[pos][row] = act((sum of the pair's pieces + bias[row]) * s_out[row]); one thread per (row, pos).
+__global__ void k_matvec_finish(const float *__restrict__ partial, const uint8_t *__restrict__ pieces,
+                                const float *__restrict__ s_out, const float *__restrict__ bias,
+                                float *__restrict__ y, long long y_stride, uint32_t rows, uint32_t npos,
+                                uint32_t max_pieces, uint32_t activation) {
+    const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * npos) return;
+    const uint32_t row = idx / npos, pos = idx % npos;
+    const uint32_t pr = row / kPairRows, rl = row % kPairRows;
+    const float *base = partial + (size_t)pr * max_pieces * (kPairRows * kMaxPosPerPass) + rl * kMaxPosPerPass + pos;
+    const uint32_t n = pieces[pr];
+    float v = 0.f;
+    for (uint32_t q = 0; q < n; ++q) v += base[q * (kPairRows * kMaxPosPerPass)];
+    if (bias) v += bias[row];
+    if (s_out) v *= s_out[row];
+    if (activation == CTOX_ACT_SILU) v = v / (1.0f + expf(-v));
+    y[(long long)pos * y_stride + row] = v;
 }
 
 // ------------------------------------------------------------------ row-per-warp kernel
@@ -541,16 +594,17 @@ using namespace ctox;
 struct MatvecPart {
     int dt = 0;  // 0 Q2, 1 Q4
     uint64_t row_start = 0, rows = 0;
-    uint32_t row_tiles = 0, kst = 0;
+    uint32_t pairs = 0, kst = 0;  // 32-row tile pairs, 256-column super-tiles per row
     uint8_t *prep = nullptr;
     size_t prep_bytes = 0;
     uint8_t *canon = nullptr;
     size_t canon_bytes = 0;
     float *partial = nullptr;
     size_t partial_bytes = 0;
-    unsigned *counters = nullptr;
-    size_t counters_bytes = 0;
-    uint32_t max_pieces = 1, total_warps = 1, grid = 1;
+    uint8_t *pieces = nullptr;  // [pairs] number of partial-sum pieces of each pair
+    size_t pieces_bytes = 0;
+    uint32_t total_warps = 1;   // warps of the streaming kernel that take work
+    uint32_t max_pieces = 1;
 };
 
 struct ctox_matvec {
@@ -675,17 +729,41 @@ ctox_status upload_f32(ctox_ctx *ctx, const float *src, uint64_t n, float **dst,
     return CTOX_OK;
 }
 
-template <int DT>
-size_t stream_smem_bytes(uint32_t blocks_padded, uint32_t npos) {
-    using F = Fmt<DT>;
-    size_t stage = (size_t)kWarps * kStages * F::kChunkTiles * F::kSuperTileBytes;
-    size_t xfrag = (size_t)blocks_padded * 2 * npos * 128;
-    size_t meta = ((size_t)blocks_padded * npos * 8 + 15) & ~(size_t)15;
-    return stage + xfrag + meta + (kWarps * kStages + 1) * 8;
+// Launch shapes of the streaming kernel: warps per CTA x bulk-copy stages per warp.
+struct StreamCfg {
+    int warps, stages;
+};
+
+StreamCfg stream_cfg() {
+    static const StreamCfg cfg = [] {
+        const char *e = getenv("CTOX_MATVEC_CFG");
+        if (e && !strcmp(e, "16x2")) return StreamCfg{16, 2};
+        if (e && !strcmp(e, "12x3")) return StreamCfg{12, 3};
+        if (e && !strcmp(e, "16x3")) return StreamCfg{16, 3};
+        return StreamCfg{8, 4};
+    }();
+    return cfg;
 }
 
-size_t stream_smem_bytes(int dt, uint32_t blocks_padded, uint32_t npos) {
-    return dt ? stream_smem_bytes<1>(blocks_padded, npos) : stream_smem_bytes<0>(blocks_padded, npos);
+size_t stream_smem_bytes(int dt, StreamCfg cfg, uint32_t blocks_padded, uint32_t npos) {
+    const size_t chunk = dt ? (size_t)Fmt<1>::kChunkPairs * 2 * Fmt<1>::kSuperTileBytes
+                            : (size_t)Fmt<0>::kChunkPairs * 2 * Fmt<0>::kSuperTileBytes;
+    const size_t stage = (size_t)cfg.warps * cfg.stages * chunk;
+    const size_t xfrag = (size_t)blocks_padded * 2 * npos * 128;
+    const size_t meta = ((size_t)blocks_padded * npos * 8 + 15) & ~(size_t)15;
+    return stage + xfrag + meta + 16 + ((size_t)cfg.warps * cfg.stages + 1) * 8;
+}
+
+template <int DT>
+void launch_stream(StreamCfg cfg, unsigned grid, size_t smem, cudaStream_t st, const StreamParams &sp) {
+    if (cfg.warps == 16 && cfg.stages == 2)
+        k_matvec_stream<DT, 16, 2><<<grid, 512, smem, st>>>(sp);
+    else if (cfg.warps == 12)
+        k_matvec_stream<DT, 12, 3><<<grid, 384, smem, st>>>(sp);
+    else if (cfg.warps == 16)
+        k_matvec_stream<DT, 16, 3><<<grid, 512, smem, st>>>(sp);
+    else
+        k_matvec_stream<DT, 8, 4><<<grid, 256, smem, st>>>(sp);
 }
 
 void free_matvec(ctox_matvec *mv) {
@@ -694,7 +772,7 @@ void free_matvec(ctox_matvec *mv) {
         dev_free(ctx, p.prep, p.prep_bytes);
         dev_free(ctx, p.canon, p.canon_bytes);
         dev_free(ctx, p.partial, p.partial_bytes);
-        dev_free(ctx, p.counters, p.counters_bytes);
+        dev_free(ctx, p.pieces, p.pieces_bytes);
     }
     dev_free(ctx, mv->s_in, mv->columns * sizeof(float));
     dev_free(ctx, mv->s_out, mv->rows * sizeof(float));
@@ -708,61 +786,77 @@ void free_matvec(ctox_matvec *mv) {
 
 ctox_status prepare_part(ctox_ctx *ctx, ctox_matvec *mv, MatvecPart &part, const uint8_t *host_bytes,
                          size_t nbytes, uint32_t flags) {
-    const int bb = part.dt ? kQ4BlockBytes : kQ2BlockBytes;
     const int stb = part.dt ? Fmt<1>::kSuperTileBytes : Fmt<0>::kSuperTileBytes;
-    part.row_tiles = (uint32_t)((part.rows + kTileRows - 1) / kTileRows);
+    const uint32_t row_tiles = (uint32_t)((part.rows + kTileRows - 1) / kTileRows);
+    part.pairs = (row_tiles + 1) / 2;
     part.kst = mv->blocks_padded / kTileBlocks;
     part.canon_bytes = nbytes;
-    (void)bb;
     ctox_status rc = dev_alloc(ctx, (void **)&part.canon, nbytes);
     if (rc) return rc;
     CTOX_CUDA(ctx, cudaMemcpyAsync(part.canon, host_bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
-    part.prep_bytes = (size_t)part.row_tiles * part.kst * stb;
+    const uint64_t tiles = (uint64_t)part.pairs * 2 * part.kst;
+    part.prep_bytes = (size_t)tiles * stb;
     rc = dev_alloc(ctx, (void **)&part.prep, part.prep_bytes);
     if (rc) return rc;
-    const uint64_t total = (uint64_t)part.row_tiles * part.kst;
-    const uint32_t grid = (uint32_t)((total + 3) / 4);
+    const uint32_t grid = (uint32_t)((tiles + 3) / 4);
     if (part.dt)
         k_repack<1><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
-                                                   part.row_tiles, part.kst, ctx->dev_error);
+                                                   part.pairs * 2, part.kst, ctx->dev_error);
     else
         k_repack<0><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
-                                                   part.row_tiles, part.kst, ctx->dev_error);
+                                                   part.pairs * 2, part.kst, ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());
-    // work split of the streaming kernel
-    uint32_t nw = (uint32_t)ctx->sm_count * kWarps;
-    if ((uint64_t)nw > total) nw = (uint32_t)total;
-    part.total_warps = nw;
-    part.grid = (nw + kWarps - 1) / kWarps;
-    const uint64_t per_warp = total / nw;  // >= 1
-    uint64_t mp = (part.kst + per_warp - 1) / per_warp + 1;
-    if (mp > part.kst) mp = part.kst;
-    if (mp > nw) mp = nw;
-    part.max_pieces = (uint32_t)mp;
-    part.partial_bytes = (size_t)part.row_tiles * part.max_pieces * 16 * kMaxPosPerPass * sizeof(float);
+    // work split of the streaming kernel and the pieces each pair is cut into
+    const StreamCfg cfg = stream_cfg();
+    const uint64_t units = (uint64_t)part.pairs * part.kst;
+    uint64_t nw = (uint64_t)ctx->sm_count * cfg.warps;
+    if (nw > units) nw = units;
+    part.total_warps = (uint32_t)nw;
+    std::vector<uint8_t> pieces(part.pairs);
+    uint32_t mp = 1;
+    for (uint32_t pr = 0; pr < part.pairs; ++pr) {
+        const uint64_t u_first = (uint64_t)pr * part.kst, u_last = u_first + part.kst - 1;
+        const uint64_t w_first = ((u_first + 1) * nw + units - 1) / units - 1;
+        const uint64_t w_last = ((u_last + 1) * nw + units - 1) / units - 1;
+        const uint64_t n = w_last - w_first + 1;
+        if (n > 255) return fail(ctx, CTOX_SHAPE, "row pair split into %llu pieces", (unsigned long long)n);
+        pieces[pr] = (uint8_t)n;
+        if (n > mp) mp = (uint32_t)n;
+    }
+    part.max_pieces = mp;
+    part.partial_bytes = (size_t)part.pairs * part.max_pieces * kPairRows * kMaxPosPerPass * sizeof(float);
     rc = dev_alloc(ctx, (void **)&part.partial, part.partial_bytes);
     if (rc) return rc;
-    part.counters_bytes = (size_t)part.row_tiles * sizeof(unsigned);
-    rc = dev_alloc(ctx, (void **)&part.counters, part.counters_bytes);
+    part.pieces_bytes = part.pairs;
+    rc = dev_alloc(ctx, (void **)&part.pieces, part.pieces_bytes);
     if (rc) return rc;
-    CTOX_CUDA(ctx, cudaMemsetAsync(part.counters, 0, part.counters_bytes, ctx->stream));
+    CTOX_CUDA(ctx, cudaMemcpyAsync(part.pieces, pieces.data(), part.pieces_bytes, cudaMemcpyHostToDevice,
+                                   ctx->stream));
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (!(flags & CTOX_PREPARE_KEEP_CANONICAL)) {
         dev_free(ctx, part.canon, part.canon_bytes);
         part.canon = nullptr;
         part.canon_bytes = 0;
     }
-    mv->device_bytes += part.prep_bytes + part.canon_bytes + part.partial_bytes + part.counters_bytes;
+    mv->device_bytes += part.prep_bytes + part.canon_bytes + part.partial_bytes + part.pieces_bytes;
     return CTOX_OK;
 }
 
 ctox_status set_smem_attr(ctox_ctx *ctx) {
     static thread_local int done_device = -1;
     if (done_device == ctx->device) return CTOX_OK;
-    CTOX_CUDA(ctx, cudaFuncSetAttribute(k_matvec_stream<0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        ctx->max_smem_optin));
-    CTOX_CUDA(ctx, cudaFuncSetAttribute(k_matvec_stream<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        ctx->max_smem_optin));
+#define CTOX_SMEM_ATTR(...)                                                                        \
+    CTOX_CUDA(ctx, cudaFuncSetAttribute(k_matvec_stream<__VA_ARGS__>,                              \
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->max_smem_optin))
+    CTOX_SMEM_ATTR(0, 8, 4);
+    CTOX_SMEM_ATTR(1, 8, 4);
+    CTOX_SMEM_ATTR(0, 16, 2);
+    CTOX_SMEM_ATTR(1, 16, 2);
+    CTOX_SMEM_ATTR(0, 12, 3);
+    CTOX_SMEM_ATTR(1, 12, 3);
+    CTOX_SMEM_ATTR(0, 16, 3);
+    CTOX_SMEM_ATTR(1, 16, 3);
+#undef CTOX_SMEM_ATTR
     done_device = ctx->device;
     return CTOX_OK;
 }
@@ -923,12 +1017,14 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
     if (kernel != CTOX_KERNEL_STREAM) return fail(ctx, CTOX_SHAPE, "dispatch: unknown kernel %u", kernel);
 
     // positions per pass: limited by the hi/lo column count (8) and by shared memory
+    const StreamCfg cfg = stream_cfg();
     uint32_t per_pass = kMaxPosPerPass;
     int worst_dt = 0;
     for (auto &p : mv->parts) worst_dt |= p.dt;
-    while (per_pass > 1 && stream_smem_bytes(worst_dt, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
+    while (per_pass > 1 &&
+           stream_smem_bytes(worst_dt, cfg, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
         --per_pass;
-    if (stream_smem_bytes(worst_dt, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
+    if (stream_smem_bytes(worst_dt, cfg, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
         return fail(ctx, CTOX_MEMORY_BUDGET, "columns %llu exceed the shared-memory budget of the streaming kernel",
                     (unsigned long long)mv->columns);
     const size_t esz = x_dtype == CTOX_BF16 ? 2 : 4;
@@ -936,7 +1032,7 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
         const uint32_t npos = positions - m0 < per_pass ? positions - m0 : per_pass;
         const uint8_t *xp = (const uint8_t *)x_dev + (size_t)m0 * x_stride * esz;
         for (auto &p : mv->parts) {
-            // the activation fragments depend on the code format (bias pattern)
+            // the activation fragments depend on the code format (column multipliers)
             const int groups = (int)(mv->blocks_padded * npos);
             k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, st>>>(xp, x_dtype == CTOX_BF16, (long long)x_stride,
                                                                mv->s_in, (int)mv->columns,
@@ -946,29 +1042,29 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
             sp.wprep = p.prep;
             sp.xfrag = mv->xfrag;
             sp.meta = mv->meta;
-            sp.s_out = mv->s_out ? mv->s_out + p.row_start : nullptr;
-            sp.bias = mv->bias ? mv->bias + p.row_start : nullptr;
-            sp.y = y_dev + (size_t)m0 * y_stride + p.row_start;
             sp.partial = p.partial;
-            sp.counters = p.counters;
             sp.error_flag = ctx->dev_error;
-            sp.y_stride = (long long)y_stride;
-            sp.rows = (uint32_t)p.rows;
-            sp.row_tiles = p.row_tiles;
+            sp.pairs = p.pairs;
             sp.kst = p.kst;
             sp.npos = npos;
-            sp.activation = mv->activation;
             sp.max_pieces = p.max_pieces;
             sp.total_warps = p.total_warps;
             sp.xfrag_bytes = mv->blocks_padded * 2 * npos * 128;
             sp.meta_bytes = mv->blocks_padded * npos * 8;
-            const size_t smem = stream_smem_bytes(p.dt, mv->blocks_padded, npos);
+            sp.dbg = getenv("CTOX_DBG") ? (uint32_t)atoi(getenv("CTOX_DBG")) : 0u;
+            const size_t smem = stream_smem_bytes(p.dt, cfg, mv->blocks_padded, npos);
+            const unsigned grid = (p.total_warps + cfg.warps - 1) / cfg.warps;
             timing_begin(ctx);
             if (p.dt)
-                k_matvec_stream<1><<<p.grid, kWarps * 32, smem, st>>>(sp);
+                launch_stream<1>(cfg, grid, smem, st, sp);
             else
-                k_matvec_stream<0><<<p.grid, kWarps * 32, smem, st>>>(sp);
+                launch_stream<0>(cfg, grid, smem, st, sp);
             timing_end(ctx);
+            const unsigned n_out = (unsigned)(p.rows * npos);
+            k_matvec_finish<<<(n_out + 255) / 256, 256, 0, st>>>(
+                p.partial, p.pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
+                mv->bias ? mv->bias + p.row_start : nullptr, y_dev + (size_t)m0 * y_stride + p.row_start,
+                (long long)y_stride, (uint32_t)p.rows, npos, p.max_pieces, mv->activation);
         }
     }
     CTOX_CUDA(ctx, cudaGetLastError());

@@ -2,7 +2,8 @@
 
 Tolerance: relative L2 <= 1e-3 (fp32 accumulation), the bar the path's north star states; the
 reference's own device-vs-oracle check uses atol 2e-2 + rtol 1e-3 (src/bin/cuda_bench.rs:53-56).
-Measured errors are ~1e-6, so most cases assert a much tighter 2e-5.
+Measured errors are ~1e-6 (Q4) to ~2e-5 (Q2, whose partial sums cancel more and whose tensor-core
+accumulation rounds toward zero), so most cases assert a much tighter 5e-5.
 """
 import os
 
@@ -15,7 +16,7 @@ from gpu_util import rel_l2, to_oracle_op
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-3
-TIGHT = 2e-5
+TIGHT = 5e-5
 f32 = np.float32
 
 
