@@ -48,6 +48,21 @@ class Segment(C.Structure):
     ]
 
 
+MAX_VERIFY_NODES = 16
+
+
+class SpecRecord(C.Structure):
+    """ctox_spec_record (include/ctox_b200.h)."""
+
+    _fields_ = [
+        ("status", C.c_uint32),
+        ("n_emitted", C.c_uint32),
+        ("emitted", C.c_uint32 * (MAX_VERIFY_NODES + 1)),
+        ("path", C.c_int32 * MAX_VERIFY_NODES),
+        ("node_argmax", C.c_uint32 * MAX_VERIFY_NODES),
+    ]
+
+
 class FusedMatVecOp(C.Structure):
     _fields_ = [
         ("dtype", C.c_uint32),
@@ -99,6 +114,15 @@ SIGNATURES = {
                                          C.c_void_p, C.c_uint64, C.c_uint32]),
     "ctox_matvec_dispatch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                               C.c_uint32]),
+    "ctox_gated_delta_scan": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
+    "ctox_gated_delta_prepare": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_uint32] * 2),
+    "ctox_argmax_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
+    "ctox_argmax_f32_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
+                                         C.POINTER(C.c_uint32)]),
+    "ctox_lmhead_verify": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32,
+                                       C.POINTER(C.c_int32), C.POINTER(C.c_uint32), C.c_float,
+                                       C.c_uint64, C.c_uint64, C.c_uint32, C.c_void_p,
+                                       C.POINTER(SpecRecord)]),
     "ctox_matvec_info": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
                                      C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
 }

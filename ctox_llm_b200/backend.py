@@ -162,6 +162,31 @@ class B200Backend:
         self._check(self._lib.ctox_matvec_prepare(self._ctx, C.byref(c), flags, C.byref(handle)))
         return PreparedMatVec(self, handle, int(operation.rows), int(operation.columns))
 
+    # -- gated-delta recurrence (device pointers) -------------------------------------------
+    def gated_delta_scan(self, q: int, k: int, v: int, log_decay: int, beta: int, state_in: int,
+                         state_out: int, out: int, tokens: int, heads: int, qk_heads: int,
+                         key_dim: int = 128, value_dim: int = 128) -> None:
+        """recurrent_gated_delta_sequence (reference.rs:377-415) on raw device addresses."""
+        self._check(self._lib.ctox_gated_delta_scan(
+            self._ctx, *(C.c_void_p(a) for a in (q, k, v, log_decay, beta, state_in, state_out, out)),
+            tokens, heads, qk_heads, key_dim, value_dim))
+
+    def gated_delta_prepare(self, a: int, b: int, a_log: int, dt_bias: int, log_decay: int,
+                            beta: int, tokens: int, heads: int) -> None:
+        self._check(self._lib.ctox_gated_delta_prepare(
+            self._ctx, *(C.c_void_p(x) for x in (a, b, a_log, dt_bias, log_decay, beta)), tokens,
+            heads))
+
+    # -- selection ------------------------------------------------------------------------
+    def argmax(self, logits_ptr: int, n: int, row_ids_ptr: int = 0) -> int:
+        """Greedy token over device logits: last maximal index under f32::total_cmp
+        (sampler.rs:76-82); row_ids maps restricted-vocabulary rows to token ids."""
+        tok = C.c_uint32()
+        self._check(self._lib.ctox_argmax_f32_host(self._ctx, C.c_void_p(logits_ptr), n,
+                                                   C.c_void_p(row_ids_ptr) if row_ids_ptr else None,
+                                                   C.byref(tok)))
+        return tok.value
+
     # -- housekeeping ----------------------------------------------------------------------
     def synchronize(self) -> None:
         self._check(self._lib.ctox_ctx_synchronize(self._ctx))
@@ -225,6 +250,25 @@ class PreparedMatVec:
         self._b._check(self._b._lib.ctox_matvec_dispatch(self._h, C.c_void_p(x_ptr), x_dtype,
                                                          positions, x_stride, C.c_void_p(y_ptr),
                                                          y_stride, kernel))
+
+    def lmhead_verify(self, hidden_ptr: int, hidden_dtype: int, hidden_stride: int, parent, token,
+                      temperature: float, seed: int, step: int, vocab: int = 0,
+                      logits_out_ptr: int = 0) -> dict:
+        """Fused lm_head + softmax statistics + acceptance over a draft tree (this object is the
+        lm_head). Returns the emitted tokens (accepted drafts, then the next token), the accepted
+        node path and the per-node greedy tokens."""
+        n = len(parent)
+        par = (C.c_int32 * n)(*[int(x) for x in parent])
+        tok = (C.c_uint32 * n)(*[int(x) for x in token])
+        rec = N.SpecRecord()
+        self._b._check(self._b._lib.ctox_lmhead_verify(
+            self._h, C.c_void_p(hidden_ptr), hidden_dtype, hidden_stride, n, par, tok,
+            C.c_float(temperature), seed, step, vocab,
+            C.c_void_p(logits_out_ptr) if logits_out_ptr else None, C.byref(rec)))
+        k = rec.n_emitted
+        return {"emitted": [int(x) for x in rec.emitted[:k]],
+                "path": [int(x) for x in rec.path[:max(k - 1, 0)]],
+                "node_argmax": [int(x) for x in rec.node_argmax[:n]]}
 
     def info(self) -> dict:
         r, c, p, d = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_uint64()

@@ -24,6 +24,8 @@ struct ctox_ctx {
     int32_t *host_error = nullptr;  // pinned mirror
     void *pinned = nullptr;         // pinned staging for the host-form calls
     size_t pinned_bytes = 0;
+    void *scratch = nullptr;        // context-owned device scratch of the selection kernels
+    size_t scratch_bytes = 0;
     std::string last_error;
     // optional per-kernel timing of the dominant kernel (benchmark support)
     bool timing = false;
@@ -60,6 +62,8 @@ inline ctox_status fail(ctox_ctx *ctx, ctox_status code, const char *fmt, ...) {
 ctox_status dev_alloc(ctox_ctx *ctx, void **ptr, size_t bytes);
 void dev_free(ctox_ctx *ctx, void *ptr, size_t bytes);
 ctox_status ensure_pinned(ctox_ctx *ctx, size_t bytes);
+// Context-owned device scratch (not counted as a caller-visible allocation); grows on demand.
+ctox_status ensure_scratch(ctox_ctx *ctx, size_t bytes);
 // When timing is enabled, brackets the next launches with a CUDA event pair on
 // the context's stream; both are no-ops otherwise.
 void timing_begin(ctox_ctx *ctx);

@@ -35,6 +35,24 @@ ctox_status ensure_pinned(ctox_ctx *ctx, size_t bytes) {
     ctx->pinned_bytes = want;
     return CTOX_OK;
 }
+ctox_status ensure_scratch(ctox_ctx *ctx, size_t bytes) {
+    if (bytes <= ctx->scratch_bytes) return CTOX_OK;
+    if (ctx->scratch) {
+        CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaFree(ctx->scratch);
+    }
+    ctx->scratch = nullptr;
+    ctx->scratch_bytes = 0;
+    const size_t want = bytes < (1u << 20) ? (1u << 20) : bytes;
+    cudaError_t e = cudaMalloc(&ctx->scratch, want);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, CTOX_MEMORY_BUDGET, "cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+    }
+    ctx->scratch_bytes = want;
+    return CTOX_OK;
+}
+
 void timing_begin(ctox_ctx *ctx) {
     if (!ctx->timing) return;
     cudaEvent_t a = nullptr, b = nullptr;
@@ -117,6 +135,7 @@ ctox_status ctox_ctx_destroy(ctox_ctx *ctx) {
     if (ctx->dev_error) cudaFree(ctx->dev_error);
     if (ctx->host_error) cudaFreeHost(ctx->host_error);
     if (ctx->pinned) cudaFreeHost(ctx->pinned);
+    if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->owns_stream && ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return CTOX_OK;

@@ -1,0 +1,417 @@
+// Selection over the vocabulary: multi-CTA argmax, and the fused
+// lm_head -> softmax statistics -> speculative acceptance path.
+//
+// Reference semantics: greedy = last maximal index under f32::total_cmp
+// (sampler.rs:76-82, engine.rs:906-913; CUDA candidate ctox_argmax_f32_sm86,
+// kernels/cuda/q2q4_fused_matvec_sm86.cu:2568-2620, which scans 248 077 logits
+// with ONE CTA); greedy MTP verification engine.rs:915-963 and the one-thread
+// accept kernel vendor/cuda/tensorrt_llm_mtp/mtp_accept_draft_token_sm86.cu:64-80.
+// The reference has no stochastic acceptance (engine.rs:583-590 fails closed);
+// the rule implemented here is stated in k_spec_accept.
+//
+// The lm_head logits are never written out: the streaming matvec leaves raw
+// per-piece sums, and k_head_stats turns them into per-position (argmax, max,
+// sum of exp, Gumbel-argmax, logits of the candidate tokens) in one sweep.
+#include "common.cuh"
+#include "head.cuh"
+#include "matvec.cuh"
+
+#include <cmath>
+
+namespace ctox {
+
+constexpr int kMaxNodes = 16;     // verify positions (tree nodes incl. the root)
+constexpr int kHeadThreads = 256;
+
+struct NodeStat {
+    unsigned long long argmax;  // pack_key_index(logit, row)
+    unsigned long long gumbel;  // pack_key_index(z + noise, row) over rows that are not children
+    float max;                  // max of z = logit / T
+    float sum;                  // sum of exp(z - max)
+    uint32_t nonfinite;
+    uint32_t pad;
+};
+
+struct TreeDesc {
+    int32_t parent[kMaxNodes];
+    uint32_t token[kMaxNodes];
+    uint32_t n_nodes;
+};
+
+__device__ __forceinline__ void merge_stat(NodeStat &a, const NodeStat &b) {
+    a.argmax = a.argmax > b.argmax ? a.argmax : b.argmax;
+    a.gumbel = a.gumbel > b.gumbel ? a.gumbel : b.gumbel;
+    a.nonfinite |= b.nonfinite;
+    if (b.sum > 0.f) {
+        if (a.sum > 0.f) {
+            const float m = fmaxf(a.max, b.max);
+            a.sum = a.sum * expf(a.max - m) + b.sum * expf(b.max - m);
+            a.max = m;
+        } else {
+            a.max = b.max;
+            a.sum = b.sum;
+        }
+    }
+}
+
+// One sweep over the vocabulary rows for the `npos` positions of the current pass.
+__global__ void __launch_bounds__(kHeadThreads) k_head_stats(
+    const float *__restrict__ partial, const uint8_t *__restrict__ pieces, const float *__restrict__ s_out,
+    const float *__restrict__ bias, uint32_t rows, uint32_t max_pieces, uint32_t node0, uint32_t npos,
+    float inv_temperature, unsigned long long seed, unsigned long long step, TreeDesc tree,
+    NodeStat *__restrict__ cta_stats, float *__restrict__ child_z, float *__restrict__ logits_out,
+    unsigned long long logits_stride) {
+    __shared__ NodeStat sh[kHeadThreads / 32][kMaxPosPerPass];
+    NodeStat st[kMaxPosPerPass];
+#pragma unroll
+    for (int m = 0; m < kMaxPosPerPass; ++m) st[m] = NodeStat{0ull, 0ull, 0.f, 0.f, 0u, 0u};
+    for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += gridDim.x * blockDim.x) {
+        const uint32_t pr = row / kPairRows, rl = row % kPairRows;
+        const float4 *base = reinterpret_cast<const float4 *>(
+            partial + (size_t)pr * max_pieces * (kPairRows * kMaxPosPerPass) + rl * kMaxPosPerPass);
+        const uint32_t n = pieces[pr];
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t q = 0; q < n; ++q) {
+            const float4 v = base[q * (kPairRows * kMaxPosPerPass / 4)];
+            acc.x += v.x;
+            acc.y += v.y;
+            acc.z += v.z;
+            acc.w += v.w;
+        }
+        const float so = s_out ? s_out[row] : 1.0f, bi = bias ? bias[row] : 0.0f;
+        const float lg[4] = {(acc.x + bi) * so, (acc.y + bi) * so, (acc.z + bi) * so, (acc.w + bi) * so};
+#pragma unroll
+        for (int m = 0; m < kMaxPosPerPass; ++m) {
+            if ((uint32_t)m >= npos) break;
+            const uint32_t node = node0 + m;
+            const float logit = lg[m];
+            if (logits_out) logits_out[(size_t)node * logits_stride + row] = logit;
+            if (!isfinite(logit)) {
+                st[m].nonfinite = 1;
+                continue;
+            }
+            const unsigned long long pk = pack_key_index(logit, row);
+            st[m].argmax = pk > st[m].argmax ? pk : st[m].argmax;
+            if (inv_temperature > 0.f) {
+                const float z = logit * inv_temperature;
+                if (st[m].sum > 0.f) {
+                    if (z > st[m].max) {
+                        st[m].sum = st[m].sum * expf(st[m].max - z) + 1.0f;
+                        st[m].max = z;
+                    } else {
+                        st[m].sum += expf(z - st[m].max);
+                    }
+                } else {
+                    st[m].max = z;
+                    st[m].sum = 1.0f;
+                }
+                bool is_child = false;
+                for (uint32_t c = node + 1; c < tree.n_nodes; ++c)
+                    if ((uint32_t)tree.parent[c] == node && tree.token[c] == row) {
+                        is_child = true;
+                        child_z[c] = z;  // one writer: the row is unique
+                    }
+                if (!is_child) {
+                    const unsigned long long gk = pack_key_index(z + gumbel_noise(seed, step, node, row), row);
+                    st[m].gumbel = gk > st[m].gumbel ? gk : st[m].gumbel;
+                }
+            }
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int m = 0; m < kMaxPosPerPass; ++m) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            NodeStat other;
+            other.argmax = __shfl_xor_sync(0xffffffffu, st[m].argmax, o);
+            other.gumbel = __shfl_xor_sync(0xffffffffu, st[m].gumbel, o);
+            other.max = __shfl_xor_sync(0xffffffffu, st[m].max, o);
+            other.sum = __shfl_xor_sync(0xffffffffu, st[m].sum, o);
+            other.nonfinite = __shfl_xor_sync(0xffffffffu, st[m].nonfinite, o);
+            merge_stat(st[m], other);
+        }
+        if (lane == 0) sh[warp][m] = st[m];
+    }
+    __syncthreads();
+    if (threadIdx.x < kMaxPosPerPass) {
+        NodeStat a = sh[0][threadIdx.x];
+        for (int w = 1; w < kHeadThreads / 32; ++w) merge_stat(a, sh[w][threadIdx.x]);
+        cta_stats[(size_t)blockIdx.x * kMaxPosPerPass + threadIdx.x] = a;
+    }
+}
+
+// Merges the per-CTA statistics of one pass into node_stats[node0 .. node0+npos).
+__global__ void k_head_merge(const NodeStat *__restrict__ cta_stats, uint32_t n_ctas, uint32_t node0,
+                             uint32_t npos, NodeStat *__restrict__ node_stats) {
+    const uint32_t m = threadIdx.x;
+    if (m >= npos) return;
+    NodeStat a = cta_stats[m];
+    for (uint32_t c = 1; c < n_ctas; ++c) merge_stat(a, cta_stats[(size_t)c * kMaxPosPerPass + m]);
+    node_stats[node0 + m] = a;
+}
+
+// Walks the draft tree with the statistics of every node. One thread: the walk is
+// a dependent chain of at most kMaxNodes steps.
+//
+// Node 0 is the root (the current position). At node n with children c1..cm in
+// index order: with temperature 0, child c is accepted iff its token equals
+// argmax of n's logits (engine.rs:939-962); otherwise c is accepted with
+// probability p_n(c) / (1 - mass of its rejected elder siblings) on the draw
+// accept_draw(seed, step, c). The drafter is deterministic, so this is speculative
+// sampling with a point-mass proposal and the emitted token is distributed as
+// softmax(logits / T). When no child is accepted the token is the Gumbel-max
+// sample of p_n restricted to non-children (greedy: the argmax).
+__global__ void k_spec_accept(const NodeStat *__restrict__ node_stats, const float *__restrict__ child_z,
+                              TreeDesc tree, float inv_temperature, unsigned long long seed,
+                              unsigned long long step, ctox_spec_record *__restrict__ rec) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint32_t count = 0, node = 0, status = 0;
+    for (uint32_t n = 0; n < tree.n_nodes; ++n) {
+        rec->node_argmax[n] = (uint32_t)(node_stats[n].argmax & 0xffffffffull);
+        if (node_stats[n].nonfinite) status = 1;
+    }
+    for (uint32_t n = tree.n_nodes; n < kMaxNodes; ++n) rec->node_argmax[n] = 0;
+    for (uint32_t i = 0; i < kMaxNodes; ++i) rec->path[i] = -1;
+    if (status == 0) {
+        for (;;) {
+            const NodeStat st = node_stats[node];
+            bool moved = false;
+            if (!(inv_temperature > 0.f)) {
+                const uint32_t target = (uint32_t)(st.argmax & 0xffffffffull);
+                for (uint32_t c = node + 1; c < tree.n_nodes; ++c)
+                    if ((uint32_t)tree.parent[c] == node && tree.token[c] == target) {
+                        rec->path[count] = (int32_t)c;
+                        rec->emitted[count++] = target;
+                        node = c;
+                        moved = true;
+                        break;
+                    }
+                if (!moved) {
+                    rec->emitted[count++] = target;
+                    break;
+                }
+                continue;
+            }
+            float residual = 1.0f;
+            for (uint32_t c = node + 1; c < tree.n_nodes; ++c) {
+                if ((uint32_t)tree.parent[c] != node) continue;
+                const float p = expf(child_z[c] - st.max) / st.sum;
+                const float u = accept_draw(seed, step, c);
+                if (u * residual < p) {
+                    rec->path[count] = (int32_t)c;
+                    rec->emitted[count++] = tree.token[c];
+                    node = c;
+                    moved = true;
+                    break;
+                }
+                residual -= p;
+                if (residual < 0.f) residual = 0.f;
+            }
+            if (moved) continue;
+            rec->emitted[count++] = (uint32_t)(st.gumbel & 0xffffffffull);
+            break;
+        }
+    }
+    for (uint32_t i = count; i < kMaxNodes + 1; ++i) rec->emitted[i] = 0;
+    rec->n_emitted = count;
+    rec->status = status;
+}
+
+// ------------------------------------------------------------------ plain argmax
+struct ArgmaxPartial {
+    unsigned long long best;
+    uint32_t nonfinite;
+    uint32_t pad;
+};
+
+__global__ void __launch_bounds__(kHeadThreads) k_argmax_partial(const float *__restrict__ logits, uint32_t n,
+                                                               ArgmaxPartial *__restrict__ out) {
+    __shared__ ArgmaxPartial sh[kHeadThreads / 32];
+    unsigned long long best = 0ull;
+    uint32_t bad = 0;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = logits[i];
+        if (!isfinite(v)) bad = 1;
+        const unsigned long long pk = pack_key_index(v, i);
+        best = pk > best ? pk : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long ob = __shfl_xor_sync(0xffffffffu, best, o);
+        best = ob > best ? ob : best;
+        bad |= __shfl_xor_sync(0xffffffffu, bad, o);
+    }
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = ArgmaxPartial{best, bad, 0};
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        ArgmaxPartial a = sh[0];
+        for (int w = 1; w < kHeadThreads / 32; ++w) {
+            a.best = sh[w].best > a.best ? sh[w].best : a.best;
+            a.nonfinite |= sh[w].nonfinite;
+        }
+        out[blockIdx.x] = a;
+    }
+}
+
+// result[0] = token (mapped through row_ids when given, engine.rs:203-217), result[1] = status
+// (1 = a logit is not finite, kernels/cuda/q2q4_fused_matvec_sm86.cu:2583-2585).
+__global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t n_parts,
+                               const uint32_t *__restrict__ row_ids, uint32_t *__restrict__ result) {
+    if (threadIdx.x != 0) return;
+    ArgmaxPartial a = parts[0];
+    for (uint32_t i = 1; i < n_parts; ++i) {
+        a.best = parts[i].best > a.best ? parts[i].best : a.best;
+        a.nonfinite |= parts[i].nonfinite;
+    }
+    const uint32_t row = (uint32_t)(a.best & 0xffffffffull);
+    result[0] = row_ids ? row_ids[row] : row;
+    result[1] = a.nonfinite;
+}
+
+}  // namespace ctox
+
+using namespace ctox;
+
+namespace {
+constexpr uint32_t kHeadGridMax = 592;  // 4 CTAs per SM on 148 SMs
+
+struct HeadScratch {
+    NodeStat *cta_stats;   // [grid][kMaxPosPerPass]
+    NodeStat *node_stats;  // [kMaxNodes]
+    float *child_z;        // [kMaxNodes]
+    ctox_spec_record *record;
+    ArgmaxPartial *argmax_parts;  // [grid]
+    uint32_t *argmax_result;      // [2]
+};
+
+ctox_status head_scratch(ctox_ctx *ctx, HeadScratch &hs) {
+    size_t off = 0;
+    auto take = [&](size_t bytes) {
+        const size_t o = off;
+        off += (bytes + 255) & ~(size_t)255;
+        return o;
+    };
+    const size_t o_cta = take(sizeof(NodeStat) * kHeadGridMax * kMaxPosPerPass);
+    const size_t o_node = take(sizeof(NodeStat) * kMaxNodes);
+    const size_t o_child = take(sizeof(float) * kMaxNodes);
+    const size_t o_rec = take(sizeof(ctox_spec_record));
+    const size_t o_ap = take(sizeof(ArgmaxPartial) * kHeadGridMax);
+    const size_t o_ar = take(sizeof(uint32_t) * 2);
+    ctox_status rc = ensure_scratch(ctx, off);
+    if (rc) return rc;
+    uint8_t *b = (uint8_t *)ctx->scratch;
+    hs.cta_stats = (NodeStat *)(b + o_cta);
+    hs.node_stats = (NodeStat *)(b + o_node);
+    hs.child_z = (float *)(b + o_child);
+    hs.record = (ctox_spec_record *)(b + o_rec);
+    hs.argmax_parts = (ArgmaxPartial *)(b + o_ap);
+    hs.argmax_result = (uint32_t *)(b + o_ar);
+    return CTOX_OK;
+}
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_argmax_f32(ctox_ctx *ctx, const float *logits_dev, uint32_t n, const uint32_t *row_ids_dev,
+                            uint32_t *result_dev) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    if (!logits_dev || !result_dev || n == 0) return fail(ctx, CTOX_INVALID_ARTIFACT, "greedy logits are empty");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    uint32_t grid = (n + kHeadThreads * 4 - 1) / (kHeadThreads * 4);
+    if (grid > kHeadGridMax) grid = kHeadGridMax;
+    if (grid == 0) grid = 1;
+    k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
+    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, result_dev);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status ctox_argmax_f32_host(ctox_ctx *ctx, const float *logits_dev, uint32_t n, const uint32_t *row_ids_dev,
+                                 uint32_t *token) {
+    if (!ctx || !token) return CTOX_INVALID_STATE;
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    rc = ctox_argmax_f32(ctx, logits_dev, n, row_ids_dev, hs.argmax_result);
+    if (rc) return rc;
+    rc = ensure_pinned(ctx, 8);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, hs.argmax_result, 8, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const uint32_t *r = (const uint32_t *)ctx->pinned;
+    if (r[1]) return fail(ctx, CTOX_INVALID_STATE, "argmax input contains a non-finite logit");
+    *token = r[0];
+    return CTOX_OK;
+}
+
+ctox_status ctox_lmhead_verify(ctox_matvec *mv, const void *hidden_dev, uint32_t hidden_dtype,
+                               uint64_t hidden_stride, uint32_t n_nodes, const int32_t *parent,
+                               const uint32_t *token, float temperature, uint64_t seed, uint64_t step,
+                               uint32_t vocab, float *logits_out_dev, ctox_spec_record *record) {
+    if (!mv) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = mv->ctx;
+    if (!hidden_dev || !parent || !token || !record) return fail(ctx, CTOX_SHAPE, "lmhead_verify: null pointer");
+    if (n_nodes == 0 || n_nodes > kMaxNodes)
+        return fail(ctx, CTOX_SHAPE, "lmhead_verify: n_nodes must be 1..%d, got %u", kMaxNodes, n_nodes);
+    if (mv->parts.size() != 1)
+        return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "lmhead_verify needs a pure Q2 or Q4 lm_head");
+    if (hidden_dtype != CTOX_F32 && hidden_dtype != CTOX_BF16)
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "lmhead_verify: hidden dtype %u", hidden_dtype);
+    if (hidden_stride < mv->columns) return fail(ctx, CTOX_SHAPE, "lmhead_verify: stride shorter than a row");
+    if (!std::isfinite(temperature) || temperature < 0.f)
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "temperature must be finite and non-negative");
+    const uint32_t rows = vocab ? vocab : (uint32_t)mv->rows;
+    if (rows > mv->rows) return fail(ctx, CTOX_SHAPE, "lmhead_verify: vocab %u exceeds %llu rows", vocab,
+                                     (unsigned long long)mv->rows);
+    TreeDesc tree;
+    memset(&tree, 0, sizeof tree);
+    tree.n_nodes = n_nodes;
+    if (parent[0] != -1) return fail(ctx, CTOX_SHAPE, "lmhead_verify: node 0 must be the root");
+    for (uint32_t i = 0; i < n_nodes; ++i) {
+        if (i && (parent[i] < 0 || (uint32_t)parent[i] >= i))
+            return fail(ctx, CTOX_SHAPE, "lmhead_verify: parent[%u] = %d is not an earlier node", i, parent[i]);
+        if (i && token[i] >= rows) return fail(ctx, CTOX_SHAPE, "lmhead_verify: draft token %u out of range", token[i]);
+        tree.parent[i] = parent[i];
+        tree.token[i] = token[i];
+    }
+    const float inv_t = temperature > 0.f ? 1.0f / temperature : 0.f;
+    if (temperature > 0.f && !std::isfinite(inv_t))
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "inverse temperature must be finite");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    const uint32_t per_pass = matvec_positions_per_pass(mv);
+    if (per_pass == 0) return fail(ctx, CTOX_MEMORY_BUDGET, "lm_head columns exceed the streaming kernel's budget");
+    MatvecPart &p = mv->parts[0];
+    uint32_t grid = (rows + kHeadThreads - 1) / kHeadThreads;
+    if (grid > kHeadGridMax) grid = kHeadGridMax;
+    const size_t esz = hidden_dtype == CTOX_BF16 ? 2 : 4;
+    for (uint32_t n0 = 0; n0 < n_nodes; n0 += per_pass) {
+        const uint32_t npos = n_nodes - n0 < per_pass ? n_nodes - n0 : per_pass;
+        rc = matvec_stream_pass(mv, 0, (const uint8_t *)hidden_dev + (size_t)n0 * hidden_stride * esz,
+                                hidden_dtype, npos, hidden_stride);
+        if (rc) return rc;
+        k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.pieces, mv->s_out, mv->bias, rows,
+                                                            p.max_pieces, n0, npos, inv_t, seed, step, tree,
+                                                            hs.cta_stats, hs.child_z, logits_out_dev,
+                                                            (unsigned long long)mv->rows);
+        k_head_merge<<<1, 32, 0, ctx->stream>>>(hs.cta_stats, grid, n0, npos, hs.node_stats);
+    }
+    k_spec_accept<<<1, 32, 0, ctx->stream>>>(hs.node_stats, hs.child_z, tree, inv_t, seed, step, hs.record);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    rc = ensure_pinned(ctx, sizeof(ctox_spec_record));
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, hs.record, sizeof(ctox_spec_record), cudaMemcpyDeviceToHost,
+                                   ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    memcpy(record, ctx->pinned, sizeof(ctox_spec_record));
+    if (record->status) return fail(ctx, CTOX_INVALID_STATE, "lm_head produced a non-finite logit");
+    return CTOX_OK;
+}
+
+}  // extern "C"

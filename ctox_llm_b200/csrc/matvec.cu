@@ -27,6 +27,7 @@
 //    accumulator's initial value -offset * sum(x).
 #include "common.cuh"
 #include "layout.cuh"
+#include "matvec.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -37,8 +38,6 @@
 
 namespace ctox {
 
-constexpr int kMaxPosPerPass = 4;  // positions per pass of the streaming kernel (hi/lo => 8 columns)
-constexpr int kPairRows = 32;      // rows of a tile pair (the unit of work and of the partial sums)
 
 // ------------------------------------------------------------------ PTX helpers
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -590,40 +589,6 @@ __global__ void k_bf16_to_f32(const __nv_bfloat16 *in, float *out, long long n) 
 
 using namespace ctox;
 
-// ------------------------------------------------------------------ host objects
-struct MatvecPart {
-    int dt = 0;  // 0 Q2, 1 Q4
-    uint64_t row_start = 0, rows = 0;
-    uint32_t pairs = 0, kst = 0;  // 32-row tile pairs, 256-column super-tiles per row
-    uint8_t *prep = nullptr;
-    size_t prep_bytes = 0;
-    uint8_t *canon = nullptr;
-    size_t canon_bytes = 0;
-    float *partial = nullptr;
-    size_t partial_bytes = 0;
-    uint8_t *pieces = nullptr;  // [pairs] number of partial-sum pieces of each pair
-    size_t pieces_bytes = 0;
-    uint32_t total_warps = 1;   // warps of the streaming kernel that take work
-    uint32_t max_pieces = 1;
-};
-
-struct ctox_matvec {
-    ctox_ctx *ctx = nullptr;
-    uint64_t rows = 0, columns = 0, packed_bytes = 0;
-    uint32_t blocks = 0, blocks_padded = 0, activation = 0;
-    std::vector<MatvecPart> parts;
-    float *s_in = nullptr, *s_out = nullptr, *bias = nullptr;
-    uint8_t *xfrag = nullptr;  // [blocks_padded][2*kMaxPosPerPass][128]
-    size_t xfrag_bytes = 0;
-    float2 *meta = nullptr;
-    size_t meta_bytes = 0;
-    float *xtmp = nullptr;  // f32 staging (bf16 input to the row-warp kernel, host form)
-    size_t xtmp_bytes = 0;
-    float *ytmp = nullptr;
-    size_t ytmp_bytes = 0;
-    uint64_t device_bytes = 0;
-};
-
 namespace {
 
 // backend/cpu.rs:41-173
@@ -737,10 +702,11 @@ struct StreamCfg {
 StreamCfg stream_cfg() {
     static const StreamCfg cfg = [] {
         const char *e = getenv("CTOX_MATVEC_CFG");
-        if (e && !strcmp(e, "16x2")) return StreamCfg{16, 2};
+        // 16 warps x 2 stages measured fastest on B200 (more warps hide the unpack/MMA latency)
+        if (e && !strcmp(e, "8x4")) return StreamCfg{8, 4};
         if (e && !strcmp(e, "12x3")) return StreamCfg{12, 3};
         if (e && !strcmp(e, "16x3")) return StreamCfg{16, 3};
-        return StreamCfg{8, 4};
+        return StreamCfg{16, 2};
     }();
     return cfg;
 }
@@ -874,6 +840,65 @@ ctox_status check_device_error(ctox_ctx *ctx, const char *what) {
 }
 
 }  // namespace
+
+namespace ctox {
+
+uint32_t matvec_positions_per_pass(ctox_matvec *mv) {
+    const StreamCfg cfg = stream_cfg();
+    int worst_dt = 0;
+    for (auto &p : mv->parts) worst_dt |= p.dt;
+    uint32_t per_pass = kMaxPosPerPass;
+    while (per_pass > 0 && stream_smem_bytes(worst_dt, cfg, mv->blocks_padded, per_pass) >
+                               (size_t)mv->ctx->max_smem_optin)
+        --per_pass;
+    return per_pass;
+}
+
+ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos) {
+    ctox_ctx *ctx = mv->ctx;
+    const StreamCfg cfg = stream_cfg();
+    MatvecPart &p = mv->parts[part_index];
+    StreamParams sp;
+    sp.wprep = p.prep;
+    sp.xfrag = mv->xfrag;
+    sp.meta = mv->meta;
+    sp.partial = p.partial;
+    sp.error_flag = ctx->dev_error;
+    sp.pairs = p.pairs;
+    sp.kst = p.kst;
+    sp.npos = npos;
+    sp.max_pieces = p.max_pieces;
+    sp.total_warps = p.total_warps;
+    sp.xfrag_bytes = mv->blocks_padded * 2 * npos * 128;
+    sp.meta_bytes = mv->blocks_padded * npos * 8;
+    static const uint32_t dbg = getenv("CTOX_DBG") ? (uint32_t)atoi(getenv("CTOX_DBG")) : 0u;
+    sp.dbg = dbg;
+    const size_t smem = stream_smem_bytes(p.dt, cfg, mv->blocks_padded, npos);
+    if (smem > (size_t)ctx->max_smem_optin)
+        return fail(ctx, CTOX_MEMORY_BUDGET, "streaming kernel needs %zu bytes of shared memory", smem);
+    const unsigned grid = (p.total_warps + cfg.warps - 1) / cfg.warps;
+    timing_begin(ctx);
+    if (p.dt)
+        launch_stream<1>(cfg, grid, smem, ctx->stream, sp);
+    else
+        launch_stream<0>(cfg, grid, smem, ctx->stream, sp);
+    timing_end(ctx);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status matvec_stream_pass(ctox_matvec *mv, size_t part_index, const void *x, uint32_t x_dtype,
+                               uint32_t npos, uint64_t x_stride) {
+    MatvecPart &p = mv->parts[part_index];
+    // the activation fragments depend on the code format (column multipliers)
+    const int groups = (int)(mv->blocks_padded * npos);
+    k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, mv->ctx->stream>>>(
+        x, x_dtype == CTOX_BF16, (long long)x_stride, mv->s_in, (int)mv->columns, (int)mv->blocks_padded,
+        (int)npos, p.dt, mv->xfrag, mv->meta);
+    return matvec_stream_prepared(mv, part_index, npos);
+}
+
+}  // namespace ctox
 
 extern "C" {
 
@@ -1016,50 +1041,18 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
     }
     if (kernel != CTOX_KERNEL_STREAM) return fail(ctx, CTOX_SHAPE, "dispatch: unknown kernel %u", kernel);
 
-    // positions per pass: limited by the hi/lo column count (8) and by shared memory
-    const StreamCfg cfg = stream_cfg();
-    uint32_t per_pass = kMaxPosPerPass;
-    int worst_dt = 0;
-    for (auto &p : mv->parts) worst_dt |= p.dt;
-    while (per_pass > 1 &&
-           stream_smem_bytes(worst_dt, cfg, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
-        --per_pass;
-    if (stream_smem_bytes(worst_dt, cfg, mv->blocks_padded, per_pass) > (size_t)ctx->max_smem_optin)
+    const uint32_t per_pass = matvec_positions_per_pass(mv);
+    if (per_pass == 0)
         return fail(ctx, CTOX_MEMORY_BUDGET, "columns %llu exceed the shared-memory budget of the streaming kernel",
                     (unsigned long long)mv->columns);
     const size_t esz = x_dtype == CTOX_BF16 ? 2 : 4;
     for (uint32_t m0 = 0; m0 < positions; m0 += per_pass) {
         const uint32_t npos = positions - m0 < per_pass ? positions - m0 : per_pass;
         const uint8_t *xp = (const uint8_t *)x_dev + (size_t)m0 * x_stride * esz;
-        for (auto &p : mv->parts) {
-            // the activation fragments depend on the code format (column multipliers)
-            const int groups = (int)(mv->blocks_padded * npos);
-            k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, st>>>(xp, x_dtype == CTOX_BF16, (long long)x_stride,
-                                                               mv->s_in, (int)mv->columns,
-                                                               (int)mv->blocks_padded, (int)npos, p.dt,
-                                                               mv->xfrag, mv->meta);
-            StreamParams sp;
-            sp.wprep = p.prep;
-            sp.xfrag = mv->xfrag;
-            sp.meta = mv->meta;
-            sp.partial = p.partial;
-            sp.error_flag = ctx->dev_error;
-            sp.pairs = p.pairs;
-            sp.kst = p.kst;
-            sp.npos = npos;
-            sp.max_pieces = p.max_pieces;
-            sp.total_warps = p.total_warps;
-            sp.xfrag_bytes = mv->blocks_padded * 2 * npos * 128;
-            sp.meta_bytes = mv->blocks_padded * npos * 8;
-            sp.dbg = getenv("CTOX_DBG") ? (uint32_t)atoi(getenv("CTOX_DBG")) : 0u;
-            const size_t smem = stream_smem_bytes(p.dt, cfg, mv->blocks_padded, npos);
-            const unsigned grid = (p.total_warps + cfg.warps - 1) / cfg.warps;
-            timing_begin(ctx);
-            if (p.dt)
-                launch_stream<1>(cfg, grid, smem, st, sp);
-            else
-                launch_stream<0>(cfg, grid, smem, st, sp);
-            timing_end(ctx);
+        for (size_t pi = 0; pi < mv->parts.size(); ++pi) {
+            ctox_status rc = matvec_stream_pass(mv, pi, xp, x_dtype, npos, x_stride);
+            if (rc) return rc;
+            MatvecPart &p = mv->parts[pi];
             const unsigned n_out = (unsigned)(p.rows * npos);
             k_matvec_finish<<<(n_out + 255) / 256, 256, 0, st>>>(
                 p.partial, p.pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,

@@ -174,6 +174,74 @@ ctox_status ctox_matvec_dispatch_host(ctox_matvec *mv, const float *x_host, uint
 ctox_status ctox_matvec_info(const ctox_matvec *mv, uint64_t *rows, uint64_t *columns,
                              uint64_t *packed_bytes, uint64_t *device_bytes);
 
+/* ---- gated-delta recurrence (reference.rs:230-297,377-415; CUDA candidate
+ * backend/cuda_runtime.rs:3514-3900 prepare_gated_delta_f16 /
+ * dispatch_gated_delta_f16[_scan]_device, kernel ABI backend/cuda.rs:266-387).
+ * All pointers are device memory, fp32. q, k: [tokens][qk_heads][key_dim]; when
+ * qk_heads < heads, head h reads source head h / (heads / qk_heads), which is
+ * repeat_heads (decoder.rs:47-65). v, out: [tokens][heads][value_dim];
+ * log_decay, beta: [tokens][heads]; state: [heads][key_dim][value_dim].
+ * state_out may equal state_in (in place) or be a second buffer, which leaves
+ * state_in untouched for a speculative pass. Enqueued on the context's stream. */
+ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k, const float *v,
+                                  const float *log_decay, const float *beta, const float *state_in,
+                                  float *state_out, float *out, uint32_t tokens, uint32_t heads,
+                                  uint32_t qk_heads, uint32_t key_dim, uint32_t value_dim);
+/* beta = sigmoid(b), log_decay = -exp(A_log) * softplus(a + dt_bias)
+ * (decoder.rs:29-35,881,897-902). a, b, log_decay, beta: [tokens][heads]. */
+ctox_status ctox_gated_delta_prepare(ctox_ctx *ctx, const float *a, const float *b,
+                                     const float *a_log, const float *dt_bias, float *log_decay,
+                                     float *beta, uint32_t tokens, uint32_t heads);
+
+/* ---- selection (sampler.rs:65-144, engine.rs:203-217,906-963; CUDA candidate
+ * backend/cuda_runtime.rs:2376-2917: prepare_argmax_f32 / dispatch_argmax_f32_device,
+ * prepare_mtp_compact_result / enqueue_mtp_accept_from_device_drafts /
+ * verifier_read_mtp_compact_result) ---- */
+
+#define CTOX_MAX_VERIFY_NODES 16
+
+/* Result of one speculative verification, the counterpart of the reference's
+ * CudaMtpCompactResultRecord (backend/cuda_runtime.rs:775-779) and of
+ * ResolvedGreedyMtpVerification (engine.rs:110-116): emitted[0 .. n_emitted-2]
+ * are the accepted draft tokens, emitted[n_emitted-1] is the next token (the
+ * target's correction, or the bonus token when every draft was accepted);
+ * path[i] is the tree node of the i-th accepted draft. */
+typedef struct {
+    uint32_t status; /* 0 = ok, 1 = a logit was not finite */
+    uint32_t n_emitted;
+    uint32_t emitted[CTOX_MAX_VERIFY_NODES + 1];
+    int32_t path[CTOX_MAX_VERIFY_NODES];
+    uint32_t node_argmax[CTOX_MAX_VERIFY_NODES];
+} ctox_spec_record;
+
+/* Greedy selection over device logits: the LAST maximal index under the IEEE
+ * total order. row_ids (device, may be NULL) maps a local row to a token id
+ * (restricted draft vocabulary). result_dev: two uint32 {token, status};
+ * status 1 = non-finite logit. Enqueued on the context's stream. */
+ctox_status ctox_argmax_f32(ctox_ctx *ctx, const float *logits_dev, uint32_t n,
+                            const uint32_t *row_ids_dev, uint32_t *result_dev);
+/* Host form of the same: synchronises and returns the token; a non-finite
+ * logit is CTOX_INVALID_STATE (backend/cuda_runtime.rs:2790-2794). */
+ctox_status ctox_argmax_f32_host(ctox_ctx *ctx, const float *logits_dev, uint32_t n,
+                                 const uint32_t *row_ids_dev, uint32_t *token);
+/* Fused lm_head -> softmax statistics -> acceptance for the n_nodes verify
+ * positions of a draft tree (a chain is the tree parent[i] = i-1). hidden_dev:
+ * n_nodes rows of the lm_head's input (CTOX_F32 or CTOX_BF16), row i being the
+ * final hidden state after node i's token; node 0 is the current position.
+ * parent[0] = -1, parent[i] < i; token[i] is node i's draft token (token[0]
+ * unused). temperature 0 is greedy verification (engine.rs:939-962); otherwise
+ * rejection sampling against softmax(logits/temperature) with Philox4x32-10
+ * draws keyed by (seed, step) - no counterpart in the reference. vocab limits
+ * selection to the first `vocab` rows (0 = all rows). logits_out_dev (may be
+ * NULL): [n_nodes][rows] materialised logits for evidence paths. The weight
+ * matrix is streamed once per four positions. Synchronises; one small
+ * device-to-host read, like backend/cuda_runtime.rs:2707-2726. */
+ctox_status ctox_lmhead_verify(ctox_matvec *lm_head, const void *hidden_dev, uint32_t hidden_dtype,
+                               uint64_t hidden_stride, uint32_t n_nodes, const int32_t *parent,
+                               const uint32_t *token, float temperature, uint64_t seed,
+                               uint64_t step, uint32_t vocab, float *logits_out_dev,
+                               ctox_spec_record *record);
+
 #ifdef __cplusplus
 }
 #endif
