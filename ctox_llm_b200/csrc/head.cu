@@ -57,7 +57,8 @@ __device__ __forceinline__ void merge_stat(NodeStat &a, const NodeStat &b) {
 // One sweep over the vocabulary rows for the `npos` positions of the current pass.
 __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
     const float *__restrict__ partial, const uint8_t *__restrict__ pieces, const float *__restrict__ s_out,
-    const float *__restrict__ bias, uint32_t rows, uint32_t max_pieces, uint32_t node0, uint32_t npos,
+    const float *__restrict__ bias, uint32_t rows, uint32_t slices, uint32_t max_pieces, uint32_t node0,
+    uint32_t npos,
     float inv_temperature, unsigned long long seed, unsigned long long step, TreeDesc tree,
     NodeStat *__restrict__ cta_stats, float *__restrict__ child_z, float *__restrict__ logits_out,
     unsigned long long logits_stride) {
@@ -67,19 +68,32 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
     for (int m = 0; m < kMaxPosPerPass; ++m) st[m] = NodeStat{0ull, 0ull, 0.f, 0.f, 0u, 0u};
     for (uint32_t row = blockIdx.x * blockDim.x + threadIdx.x; row < rows; row += gridDim.x * blockDim.x) {
         const uint32_t pr = row / kPairRows, rl = row % kPairRows;
-        const float4 *base = reinterpret_cast<const float4 *>(
-            partial + (size_t)pr * max_pieces * (kPairRows * kMaxPosPerPass) + rl * kMaxPosPerPass);
-        const uint32_t n = pieces[pr];
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (uint32_t q = 0; q < n; ++q) {
-            const float4 v = base[q * (kPairRows * kMaxPosPerPass / 4)];
-            acc.x += v.x;
-            acc.y += v.y;
-            acc.z += v.z;
-            acc.w += v.w;
+        float lg[kMaxPosPerPass];
+#pragma unroll
+        for (int m = 0; m < kMaxPosPerPass; ++m) lg[m] = 0.f;
+        for (uint32_t sl = 0; sl < slices; ++sl) {
+            const float4 *base = reinterpret_cast<const float4 *>(
+                partial + ((size_t)pr * slices + sl) * max_pieces * (kPairRows * kMaxPosPerPass) +
+                rl * kMaxPosPerPass);
+            const uint32_t n = pieces[pr * slices + sl];
+            for (uint32_t q = 0; q < n; ++q) {
+                const float4 v0 = base[q * (kPairRows * kMaxPosPerPass / 4)];
+                lg[0] += v0.x;
+                lg[1] += v0.y;
+                lg[2] += v0.z;
+                lg[3] += v0.w;
+                if (npos > 4) {
+                    const float4 v1 = base[q * (kPairRows * kMaxPosPerPass / 4) + 1];
+                    lg[4] += v1.x;
+                    lg[5] += v1.y;
+                    lg[6] += v1.z;
+                    lg[7] += v1.w;
+                }
+            }
         }
         const float so = s_out ? s_out[row] : 1.0f, bi = bias ? bias[row] : 0.0f;
-        const float lg[4] = {(acc.x + bi) * so, (acc.y + bi) * so, (acc.z + bi) * so, (acc.w + bi) * so};
+#pragma unroll
+        for (int m = 0; m < kMaxPosPerPass; ++m) lg[m] = (lg[m] + bi) * so;
 #pragma unroll
         for (int m = 0; m < kMaxPosPerPass; ++m) {
             if ((uint32_t)m >= npos) break;
@@ -396,7 +410,8 @@ ctox_status ctox_lmhead_verify(ctox_matvec *mv, const void *hidden_dev, uint32_t
         rc = matvec_stream_pass(mv, 0, (const uint8_t *)hidden_dev + (size_t)n0 * hidden_stride * esz,
                                 hidden_dtype, npos, hidden_stride);
         if (rc) return rc;
-        k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.pieces, mv->s_out, mv->bias, rows,
+        k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.split[npos > 4 ? 1 : 0].pieces,
+                                                            mv->s_out, mv->bias, rows, p.slices,
                                                             p.max_pieces, n0, npos, inv_t, seed, step, tree,
                                                             hs.cta_stats, hs.child_z, logits_out_dev,
                                                             (unsigned long long)mv->rows);

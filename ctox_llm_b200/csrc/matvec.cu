@@ -129,15 +129,18 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
 // One warp per super-tile; lane (g, t) gathers its own code bytes.
 template <int DT>
 __global__ void k_repack(const uint8_t *__restrict__ canon, uint8_t *__restrict__ prep,
-                         uint32_t rows, uint32_t blocks, uint32_t row_tiles_padded, uint32_t kst,
+                         uint32_t rows, uint32_t blocks, uint32_t pairs, uint32_t kst_s, uint32_t slices,
                          int32_t *error_flag) {
     using F = Fmt<DT>;
     const uint64_t s = (uint64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-    if (s >= (uint64_t)row_tiles_padded * kst) return;
+    if (s >= (uint64_t)slices * pairs * kst_s * 2) return;
     const uint32_t lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    // s = ((pair * kst) + ks) * 2 + tile_of_pair
-    const uint32_t rt = (uint32_t)(s / (2ull * kst)) * 2 + (uint32_t)(s & 1);
-    const uint32_t ks = (uint32_t)((s >> 1) % kst);
+    // s = (((slice * pairs + pair) * kst_s) + ks_in_slice) * 2 + tile_of_pair
+    const uint64_t per_slice = (uint64_t)pairs * kst_s * 2;
+    const uint32_t slice = (uint32_t)(s / per_slice);
+    const uint64_t rem = s % per_slice;
+    const uint32_t rt = (uint32_t)(rem / (2ull * kst_s)) * 2 + (uint32_t)(rem & 1);
+    const uint32_t ks = slice * kst_s + (uint32_t)((rem >> 1) % kst_s);
     uint8_t *out = prep + s * F::kSuperTileBytes;
     const uint64_t row_bytes = (uint64_t)blocks * F::kBlockBytes;
     // scales: lane t == 0 writes the 8 halfs of (row g, row g+8) x 4 blocks
@@ -248,13 +251,16 @@ __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_
 // ------------------------------------------------------------------ streaming kernel
 struct StreamParams {
     const uint8_t *wprep;
-    const uint8_t *xfrag;   // prepared activations (k_prep_x)
-    const float2 *meta;
-    float *partial;         // [pairs][max_pieces][32][kMaxPosPerPass] raw sums
+    const uint8_t *xfrag;   // prepared activations (k_prep_x), [block][half][column][quarter][8 fp16]
+    const float2 *meta;     // [block][position]
+    float *partial;         // [pair][slice][piece][32][kMaxPosPerPass] raw sums
     int32_t *error_flag;
-    uint32_t pairs, kst, npos, max_pieces;
-    uint32_t total_warps;   // warps that take work (<= work units)
-    uint32_t xfrag_bytes, meta_bytes;
+    uint32_t pairs;            // 32-row tile pairs
+    uint32_t kst_s;            // 256-column super-tiles per column slice
+    uint32_t slices;           // column slices (each CTA works inside one slice)
+    uint32_t ctas_per_slice;
+    uint32_t warps_per_slice;  // warps that take work (<= units per slice)
+    uint32_t npos, max_pieces;
     uint32_t dbg;
 };
 
@@ -280,7 +286,7 @@ __device__ __forceinline__ void block_mma(float (&c)[4], uint32_t w0, uint32_t w
     }
 }
 
-template <int DT, int WARPS, int STAGES>
+template <int DT, int WARPS, int STAGES, int NT>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamParams p) {
     using F = Fmt<DT>;
     constexpr uint32_t kST = F::kSuperTileBytes;
@@ -289,26 +295,31 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t nc = 2 * p.npos;
+    const uint32_t slice_blocks = p.kst_s * 4;
+    const uint32_t xfrag_bytes = slice_blocks * nc * 128, meta_bytes = slice_blocks * p.npos * 8;
 
     uint8_t *stages = smem;
     uint8_t *xs = smem + WARPS * STAGES * kChunkBytes;
-    uint8_t *ms = xs + p.xfrag_bytes;
-    uint8_t *zero = ms + ((p.meta_bytes + 15) & ~15u);  // 16 zero bytes for lanes without operands
+    uint8_t *ms = xs + xfrag_bytes;
+    uint8_t *zero = ms + ((meta_bytes + 15) & ~15u);  // 16 zero bytes for lanes without operands
     uint64_t *bars = reinterpret_cast<uint64_t *>(zero + 16);
     const uint32_t xbar = smem_u32(&bars[WARPS * STAGES]);
     const uint32_t my_bars = smem_u32(&bars[warp * STAGES]);
     const uint32_t my_stage = smem_u32(stages + warp * STAGES * kChunkBytes);
 
-    // work range of this warp: tile pairs x column super-tiles [beg, end)
-    const uint64_t total = (uint64_t)p.pairs * p.kst;
-    const uint32_t gw = blockIdx.x * WARPS + warp;
-    const bool active = gw < p.total_warps;
+    // This CTA works inside one column slice; its warps split the slice's units
+    // (tile pair x super-tile of the slice, pair-major) evenly: [beg, end).
+    const uint32_t slice = blockIdx.x / p.ctas_per_slice;
+    const uint32_t lw = (blockIdx.x % p.ctas_per_slice) * WARPS + warp;
+    const uint64_t total = (uint64_t)p.pairs * p.kst_s;
+    const bool active = lw < p.warps_per_slice;
     uint64_t beg = 0, end = 0;
     if (active) {
-        beg = ((uint64_t)gw * total) / p.total_warps;
-        end = ((uint64_t)(gw + 1) * total) / p.total_warps;
+        beg = ((uint64_t)lw * total) / p.warps_per_slice;
+        end = ((uint64_t)(lw + 1) * total) / p.warps_per_slice;
     }
     const uint32_t nchunks = (uint32_t)((end - beg + F::kChunkPairs - 1) / F::kChunkPairs);
+    const uint8_t *wsrc = p.wprep + (uint64_t)slice * total * kUnitBytes;
 
     if (threadIdx.x == 0) {
         mbar_init(xbar, 1);
@@ -323,57 +334,71 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
             const uint64_t u0 = beg + (uint64_t)c * F::kChunkPairs;
             const uint32_t n = (uint32_t)min((uint64_t)F::kChunkPairs, end - u0);
             mbar_expect_tx(my_bars + 8 * c, n * kUnitBytes);
-            bulk_g2s(my_stage + c * kChunkBytes, p.wprep + u0 * kUnitBytes, n * kUnitBytes,
-                     my_bars + 8 * c);
+            bulk_g2s(my_stage + c * kChunkBytes, wsrc + u0 * kUnitBytes, n * kUnitBytes, my_bars + 8 * c);
         }
     }
     __syncthreads();  // xbar and the zero bytes are initialised
     if (threadIdx.x == 0) {
         fence_proxy_async();
-        mbar_expect_tx(xbar, p.xfrag_bytes + p.meta_bytes);
+        mbar_expect_tx(xbar, xfrag_bytes + meta_bytes);
+        const uint8_t *xsrc = p.xfrag + (size_t)slice * xfrag_bytes;
         uint32_t off = 0;
-        while (off < p.xfrag_bytes) {
-            const uint32_t n = min(p.xfrag_bytes - off, 32768u);
-            bulk_g2s(smem_u32(xs) + off, p.xfrag + off, n, xbar);
+        while (off < xfrag_bytes) {
+            const uint32_t n = min(xfrag_bytes - off, 32768u);
+            bulk_g2s(smem_u32(xs) + off, xsrc + off, n, xbar);
             off += n;
         }
-        bulk_g2s(smem_u32(ms), p.meta, p.meta_bytes, xbar);
+        bulk_g2s(smem_u32(ms), reinterpret_cast<const uint8_t *>(p.meta) + (size_t)slice * meta_bytes,
+                 meta_bytes, xbar);
     }
     if (!active || nchunks == 0) return;  // warp 0 of every CTA is active and waits for xbar below
     bool ok = mbar_wait(xbar, 0);
 
     // lanes whose B column / position does not exist read zeros with stride 0
-    const bool has_b = g < nc, has_m = t < p.npos;
-    const uint32_t b_stride = has_b ? nc * 128 : 0;
-    const uint32_t b_base = has_b ? smem_u32(xs) + lane * 16 : smem_u32(zero);
-    const uint32_t b_half = has_b ? nc * 64 : 0;
-    const uint32_t m_stride = has_m ? p.npos * 8 : 0;
-    const uint32_t m_base = has_m ? smem_u32(ms) + t * 8 : smem_u32(zero);
-
-    float acc[8];
+    uint32_t b_base[NT], b_stride[NT], b_half[NT], m_base[NT], m_stride[NT];
+    bool has_m[NT];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    uint32_t cur_pair = (uint32_t)(beg / p.kst), cur_ks = (uint32_t)(beg % p.kst);
+    for (int nt = 0; nt < NT; ++nt) {
+        const bool hb = 8 * nt + g < nc;
+        has_m[nt] = 4 * nt + t < p.npos;
+        b_stride[nt] = hb ? nc * 128 : 0;
+        b_base[nt] = hb ? smem_u32(xs) + nt * 512 + lane * 16 : smem_u32(zero);
+        b_half[nt] = hb ? nc * 64 : 0;
+        m_stride[nt] = has_m[nt] ? p.npos * 8 : 0;
+        m_base[nt] = has_m[nt] ? smem_u32(ms) + (4 * nt + t) * 8 : smem_u32(zero);
+    }
+
+    float acc[NT][8];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[nt][i] = 0.f;
+    uint32_t cur_pair = (uint32_t)(beg / p.kst_s), cur_ks = (uint32_t)(beg % p.kst_s);
 
     const uint32_t rloc[4] = {g, g + 8, 16 + g, 24 + g};  // rows of this lane inside a pair
-    // Raw sums go to the slot (pair, piece): piece = rank of this warp among the consecutive
-    // warps whose ranges intersect the pair. A pair that lies wholly inside this warp's range
-    // has one piece; only the first and the last pair of a range can be cut. k_matvec_finish
-    // adds the pieces in piece order, so the result does not depend on timing and the stream
-    // needs no atomics, counters or fences.
+    // Raw sums go to the slot (pair, slice, piece): piece = rank of this warp among the
+    // consecutive warps of the slice whose ranges intersect the pair. A pair that lies wholly
+    // inside this warp's range has one piece; only the first and the last pair of a range can be
+    // cut. The finish kernels add slices and pieces in index order, so the result does not
+    // depend on timing and the stream needs no atomics, counters or fences.
     auto close_pair = [&](uint32_t pr, bool reached_end_of_pair) {
         uint32_t piece = 0;
-        if ((uint64_t)pr * p.kst < beg || !reached_end_of_pair) {
-            const uint64_t u_first = (uint64_t)pr * p.kst;
-            const uint32_t w_first = (uint32_t)(((u_first + 1) * p.total_warps + total - 1) / total - 1);
-            piece = gw - w_first;
+        if ((uint64_t)pr * p.kst_s < beg || !reached_end_of_pair) {
+            const uint64_t u_first = (uint64_t)pr * p.kst_s;
+            const uint32_t w_first =
+                (uint32_t)(((u_first + 1) * p.warps_per_slice + total - 1) / total - 1);
+            piece = lw - w_first;
         }
-        if (has_m) {
-            float *slot = p.partial + ((size_t)pr * p.max_pieces + piece) * (kPairRows * kMaxPosPerPass);
-            slot[rloc[0] * kMaxPosPerPass + t] = acc[0] + acc[1];  // hi + lo columns of position t
-            slot[rloc[1] * kMaxPosPerPass + t] = acc[2] + acc[3];
-            slot[rloc[2] * kMaxPosPerPass + t] = acc[4] + acc[5];
-            slot[rloc[3] * kMaxPosPerPass + t] = acc[6] + acc[7];
+        float *slot = p.partial + (((size_t)pr * p.slices + slice) * p.max_pieces + piece) *
+                                      (kPairRows * kMaxPosPerPass);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            if (has_m[nt]) {  // hi + lo columns of position 4*nt + t
+                slot[rloc[0] * kMaxPosPerPass + 4 * nt + t] = acc[nt][0] + acc[nt][1];
+                slot[rloc[1] * kMaxPosPerPass + 4 * nt + t] = acc[nt][2] + acc[nt][3];
+                slot[rloc[2] * kMaxPosPerPass + 4 * nt + t] = acc[nt][4] + acc[nt][5];
+                slot[rloc[3] * kMaxPosPerPass + 4 * nt + t] = acc[nt][6] + acc[nt][7];
+            }
         }
     };
 
@@ -387,10 +412,12 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         const uint32_t n = (uint32_t)min((uint64_t)F::kChunkPairs, end - u0);
         for (uint32_t i = 0; i < n; ++i) {
             if (p.dbg & 1) continue;
-            if (cur_ks == p.kst) {  // crossed into the next tile pair
+            if (cur_ks == p.kst_s) {  // crossed into the next tile pair
                 if (!(p.dbg & 2)) close_pair(cur_pair, true);
 #pragma unroll
-                for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[nt][k] = 0.f;
                 ++cur_pair;
                 cur_ks = 0;
             }
@@ -411,39 +438,43 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
                     sc[r][3] = hi2.y;
                 }
             }
-            uint32_t xb = b_base + b0 * b_stride, mb = m_base + b0 * m_stride;
             uint4 q0 = make_uint4(0, 0, 0, 0), q1 = make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 if ((p.dbg & 4) && j > 0) break;
-                const uint4 bA = lds128(xb), bB = lds128(xb + b_half);
-                const float2 mt = lds64f(mb);
-                xb += b_stride;
-                mb += m_stride;
-                float c0[4], c1[4];
+                uint32_t w0, w0h, w1, w1h, v0, v0h, v1, v1h;  // tile 0 / tile 1 code words
                 if (DT == 1) {
                     const uint4 a0 = lds128(tile0 + kScaleBytes + j * 512 + lane * 16);
                     const uint4 a1 = lds128(tile1 + kScaleBytes + j * 512 + lane * 16);
-                    block_mma<1>(c0, a0.x, a0.z, a0.y, a0.w, bA, bB, mt.x);
-                    block_mma<1>(c1, a1.x, a1.z, a1.y, a1.w, bA, bB, mt.x);
+                    w0 = a0.x, w0h = a0.z, w1 = a0.y, w1h = a0.w;
+                    v0 = a1.x, v0h = a1.z, v1 = a1.y, v1h = a1.w;
                 } else {
                     if ((j & 1) == 0) {
                         q0 = lds128(tile0 + kScaleBytes + (j >> 1) * 512 + lane * 16);
                         q1 = lds128(tile1 + kScaleBytes + (j >> 1) * 512 + lane * 16);
                     }
-                    block_mma<0>(c0, (j & 1) ? q0.z : q0.x, (j & 1) ? q0.w : q0.y, 0, 0, bA, bB, mt.x);
-                    block_mma<0>(c1, (j & 1) ? q1.z : q1.x, (j & 1) ? q1.w : q1.y, 0, 0, bA, bB, mt.x);
+                    w0 = (j & 1) ? q0.z : q0.x, w0h = (j & 1) ? q0.w : q0.y, w1 = 0, w1h = 0;
+                    v0 = (j & 1) ? q1.z : q1.x, v0h = (j & 1) ? q1.w : q1.y, v1 = 0, v1h = 0;
                 }
-                const float f0 = sc[0][j] * mt.y, f1 = sc[1][j] * mt.y;
-                const float f2 = sc[2][j] * mt.y, f3 = sc[3][j] * mt.y;
-                acc[0] = fmaf(f0, c0[0], acc[0]);
-                acc[1] = fmaf(f0, c0[1], acc[1]);
-                acc[2] = fmaf(f1, c0[2], acc[2]);
-                acc[3] = fmaf(f1, c0[3], acc[3]);
-                acc[4] = fmaf(f2, c1[0], acc[4]);
-                acc[5] = fmaf(f2, c1[1], acc[5]);
-                acc[6] = fmaf(f3, c1[2], acc[6]);
-                acc[7] = fmaf(f3, c1[3], acc[7]);
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const uint32_t xb = b_base[nt] + (b0 + j) * b_stride[nt];
+                    const uint4 bA = lds128(xb), bB = lds128(xb + b_half[nt]);
+                    const float2 mt = lds64f(m_base[nt] + (b0 + j) * m_stride[nt]);
+                    float c0[4], c1[4];
+                    block_mma<DT>(c0, w0, w0h, w1, w1h, bA, bB, mt.x);
+                    block_mma<DT>(c1, v0, v0h, v1, v1h, bA, bB, mt.x);
+                    const float f0 = sc[0][j] * mt.y, f1 = sc[1][j] * mt.y;
+                    const float f2 = sc[2][j] * mt.y, f3 = sc[3][j] * mt.y;
+                    acc[nt][0] = fmaf(f0, c0[0], acc[nt][0]);
+                    acc[nt][1] = fmaf(f0, c0[1], acc[nt][1]);
+                    acc[nt][2] = fmaf(f1, c0[2], acc[nt][2]);
+                    acc[nt][3] = fmaf(f1, c0[3], acc[nt][3]);
+                    acc[nt][4] = fmaf(f2, c1[0], acc[nt][4]);
+                    acc[nt][5] = fmaf(f2, c1[1], acc[nt][5]);
+                    acc[nt][6] = fmaf(f3, c1[2], acc[nt][6]);
+                    acc[nt][7] = fmaf(f3, c1[3], acc[nt][7]);
+                }
             }
         }
         __syncwarp();
@@ -454,8 +485,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
             const uint32_t nn = (uint32_t)min((uint64_t)F::kChunkPairs, end - un);
             fence_proxy_async();
             mbar_expect_tx(my_bars + 8 * st, nn * kUnitBytes);
-            bulk_g2s(my_stage + st * kChunkBytes, p.wprep + un * kUnitBytes, nn * kUnitBytes,
-                     my_bars + 8 * st);
+            bulk_g2s(my_stage + st * kChunkBytes, wsrc + un * kUnitBytes, nn * kUnitBytes, my_bars + 8 * st);
         }
     }
     if (!ok) {
@@ -467,22 +497,26 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         return;
     }
     if (p.dbg & 2) return;
-    close_pair(cur_pair, cur_ks == p.kst);
+    close_pair(cur_pair, cur_ks == p.kst_s);
 }
 
-// y[pos][row] = act((sum of the pair's pieces + bias[row]) * s_out[row]); one thread per (row, pos).
+// y[pos][row] = act((sum over slices and pieces + bias[row]) * s_out[row]); one thread per (row, pos).
+// pieces: [pair][slice] number of pieces.
 __global__ void k_matvec_finish(const float *__restrict__ partial, const uint8_t *__restrict__ pieces,
                                 const float *__restrict__ s_out, const float *__restrict__ bias,
                                 float *__restrict__ y, long long y_stride, uint32_t rows, uint32_t npos,
-                                uint32_t max_pieces, uint32_t activation) {
+                                uint32_t slices, uint32_t max_pieces, uint32_t activation) {
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * npos) return;
     const uint32_t row = idx / npos, pos = idx % npos;
     const uint32_t pr = row / kPairRows, rl = row % kPairRows;
-    const float *base = partial + (size_t)pr * max_pieces * (kPairRows * kMaxPosPerPass) + rl * kMaxPosPerPass + pos;
-    const uint32_t n = pieces[pr];
     float v = 0.f;
-    for (uint32_t q = 0; q < n; ++q) v += base[q * (kPairRows * kMaxPosPerPass)];
+    for (uint32_t sl = 0; sl < slices; ++sl) {
+        const float *base = partial + ((size_t)pr * slices + sl) * max_pieces * (kPairRows * kMaxPosPerPass) +
+                            rl * kMaxPosPerPass + pos;
+        const uint32_t n = pieces[pr * slices + sl];
+        for (uint32_t q = 0; q < n; ++q) v += base[q * (kPairRows * kMaxPosPerPass)];
+    }
     if (bias) v += bias[row];
     if (s_out) v *= s_out[row];
     if (activation == CTOX_ACT_SILU) v = v / (1.0f + expf(-v));
@@ -694,42 +728,52 @@ ctox_status upload_f32(ctox_ctx *ctx, const float *src, uint64_t n, float **dst,
     return CTOX_OK;
 }
 
-// Launch shapes of the streaming kernel: warps per CTA x bulk-copy stages per warp.
+// Launch shapes of the streaming kernel: warps per CTA x bulk-copy stages per warp. More warps
+// hide the unpack/MMA latency better (16x2 measured fastest on B200); fewer leave shared memory
+// for the activation fragments of wide matrices and many positions.
 struct StreamCfg {
     int warps, stages;
 };
 
-StreamCfg stream_cfg() {
-    static const StreamCfg cfg = [] {
-        const char *e = getenv("CTOX_MATVEC_CFG");
-        // 16 warps x 2 stages measured fastest on B200 (more warps hide the unpack/MMA latency)
-        if (e && !strcmp(e, "8x4")) return StreamCfg{8, 4};
-        if (e && !strcmp(e, "12x3")) return StreamCfg{12, 3};
-        if (e && !strcmp(e, "16x3")) return StreamCfg{16, 3};
-        return StreamCfg{16, 2};
-    }();
-    return cfg;
-}
-
-size_t stream_smem_bytes(int dt, StreamCfg cfg, uint32_t blocks_padded, uint32_t npos) {
+size_t stream_smem_bytes(int dt, StreamCfg cfg, uint32_t slice_blocks, uint32_t npos) {
     const size_t chunk = dt ? (size_t)Fmt<1>::kChunkPairs * 2 * Fmt<1>::kSuperTileBytes
                             : (size_t)Fmt<0>::kChunkPairs * 2 * Fmt<0>::kSuperTileBytes;
     const size_t stage = (size_t)cfg.warps * cfg.stages * chunk;
-    const size_t xfrag = (size_t)blocks_padded * 2 * npos * 128;
-    const size_t meta = ((size_t)blocks_padded * npos * 8 + 15) & ~(size_t)15;
+    const size_t xfrag = (size_t)slice_blocks * 2 * npos * 128;
+    const size_t meta = ((size_t)slice_blocks * npos * 8 + 15) & ~(size_t)15;
     return stage + xfrag + meta + 16 + ((size_t)cfg.warps * cfg.stages + 1) * 8;
+}
+
+// The widest launch shape whose shared memory fits; warps == 0 when none does.
+StreamCfg pick_stream_cfg(ctox_ctx *ctx, int dt, uint32_t slice_blocks, uint32_t npos) {
+    static const int forced = [] {
+        const char *e = getenv("CTOX_MATVEC_CFG");
+        if (e && !strcmp(e, "8x4")) return 1;
+        if (e && !strcmp(e, "8x2")) return 2;
+        return 0;
+    }();
+    const StreamCfg order[] = {{16, 2}, {8, 4}, {8, 2}};
+    for (int i = forced; i < 3; ++i)
+        if (stream_smem_bytes(dt, order[i], slice_blocks, npos) <= (size_t)ctx->max_smem_optin) return order[i];
+    return StreamCfg{0, 0};
+}
+
+template <int DT, int NT>
+void launch_stream_nt(StreamCfg cfg, unsigned grid, size_t smem, cudaStream_t st, const StreamParams &sp) {
+    if (cfg.warps == 16)
+        k_matvec_stream<DT, 16, 2, NT><<<grid, 512, smem, st>>>(sp);
+    else if (cfg.stages == 4)
+        k_matvec_stream<DT, 8, 4, NT><<<grid, 256, smem, st>>>(sp);
+    else
+        k_matvec_stream<DT, 8, 2, NT><<<grid, 256, smem, st>>>(sp);
 }
 
 template <int DT>
 void launch_stream(StreamCfg cfg, unsigned grid, size_t smem, cudaStream_t st, const StreamParams &sp) {
-    if (cfg.warps == 16 && cfg.stages == 2)
-        k_matvec_stream<DT, 16, 2><<<grid, 512, smem, st>>>(sp);
-    else if (cfg.warps == 12)
-        k_matvec_stream<DT, 12, 3><<<grid, 384, smem, st>>>(sp);
-    else if (cfg.warps == 16)
-        k_matvec_stream<DT, 16, 3><<<grid, 512, smem, st>>>(sp);
+    if (sp.npos > 4)
+        launch_stream_nt<DT, 2>(cfg, grid, smem, st, sp);
     else
-        k_matvec_stream<DT, 8, 4><<<grid, 256, smem, st>>>(sp);
+        launch_stream_nt<DT, 1>(cfg, grid, smem, st, sp);
 }
 
 void free_matvec(ctox_matvec *mv) {
@@ -738,7 +782,7 @@ void free_matvec(ctox_matvec *mv) {
         dev_free(ctx, p.prep, p.prep_bytes);
         dev_free(ctx, p.canon, p.canon_bytes);
         dev_free(ctx, p.partial, p.partial_bytes);
-        dev_free(ctx, p.pieces, p.pieces_bytes);
+        for (auto &sp : p.split) dev_free(ctx, sp.pieces, sp.pieces_bytes);
     }
     dev_free(ctx, mv->s_in, mv->columns * sizeof(float));
     dev_free(ctx, mv->s_out, mv->rows * sizeof(float));
@@ -750,61 +794,89 @@ void free_matvec(ctox_matvec *mv) {
     delete mv;
 }
 
+// Column slices: the streaming kernel keeps the activation fragments of one slice in shared
+// memory (2 KB per 64-column block at 8 positions), so wide matrices are cut until a slice has
+// at most 72 blocks (4608 columns), which leaves room for the 8-warp bulk-copy ring.
+uint32_t choose_slices(uint32_t kst) {
+    for (uint32_t sl : {1u, 2u, 4u, 8u})
+        if (kst % sl == 0 && kst / sl <= 18) return sl;
+    for (uint32_t sl : {8u, 4u, 2u})
+        if (kst % sl == 0) return sl;
+    return 1;
+}
+
 ctox_status prepare_part(ctox_ctx *ctx, ctox_matvec *mv, MatvecPart &part, const uint8_t *host_bytes,
                          size_t nbytes, uint32_t flags) {
     const int stb = part.dt ? Fmt<1>::kSuperTileBytes : Fmt<0>::kSuperTileBytes;
     const uint32_t row_tiles = (uint32_t)((part.rows + kTileRows - 1) / kTileRows);
+    const uint32_t kst = mv->blocks_padded / kTileBlocks;
     part.pairs = (row_tiles + 1) / 2;
-    part.kst = mv->blocks_padded / kTileBlocks;
+    part.slices = choose_slices(kst);
+    part.kst_s = kst / part.slices;
     part.canon_bytes = nbytes;
     ctox_status rc = dev_alloc(ctx, (void **)&part.canon, nbytes);
     if (rc) return rc;
     CTOX_CUDA(ctx, cudaMemcpyAsync(part.canon, host_bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
-    const uint64_t tiles = (uint64_t)part.pairs * 2 * part.kst;
+    const uint64_t tiles = (uint64_t)part.pairs * 2 * kst;
     part.prep_bytes = (size_t)tiles * stb;
     rc = dev_alloc(ctx, (void **)&part.prep, part.prep_bytes);
     if (rc) return rc;
     const uint32_t grid = (uint32_t)((tiles + 3) / 4);
     if (part.dt)
         k_repack<1><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
-                                                   part.pairs * 2, part.kst, ctx->dev_error);
+                                                   part.pairs, part.kst_s, part.slices, ctx->dev_error);
     else
         k_repack<0><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
-                                                   part.pairs * 2, part.kst, ctx->dev_error);
+                                                   part.pairs, part.kst_s, part.slices, ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());
-    // work split of the streaming kernel and the pieces each pair is cut into
-    const StreamCfg cfg = stream_cfg();
-    const uint64_t units = (uint64_t)part.pairs * part.kst;
-    uint64_t nw = (uint64_t)ctx->sm_count * cfg.warps;
-    if (nw > units) nw = units;
-    part.total_warps = (uint32_t)nw;
-    std::vector<uint8_t> pieces(part.pairs);
-    uint32_t mp = 1;
-    for (uint32_t pr = 0; pr < part.pairs; ++pr) {
-        const uint64_t u_first = (uint64_t)pr * part.kst, u_last = u_first + part.kst - 1;
-        const uint64_t w_first = ((u_first + 1) * nw + units - 1) / units - 1;
-        const uint64_t w_last = ((u_last + 1) * nw + units - 1) / units - 1;
-        const uint64_t n = w_last - w_first + 1;
-        if (n > 255) return fail(ctx, CTOX_SHAPE, "row pair split into %llu pieces", (unsigned long long)n);
-        pieces[pr] = (uint8_t)n;
-        if (n > mp) mp = (uint32_t)n;
+    // work split of the streaming kernel, per launch-shape class, and the pieces each
+    // (pair, slice) is cut into
+    const uint64_t units = (uint64_t)part.pairs * part.kst_s;  // per slice
+    part.max_pieces = 1;
+    for (int cls = 0; cls < 2; ++cls) {
+        MatvecPart::Split &sp = part.split[cls];
+        const StreamCfg cfg = pick_stream_cfg(ctx, part.dt, part.kst_s * 4, cls ? kMaxPosPerPass : 4);
+        sp.warps = cfg.warps;
+        sp.stages = cfg.stages;
+        if (cfg.warps == 0) continue;
+        sp.ctas_per_slice = (uint32_t)ctx->sm_count / part.slices;
+        if (sp.ctas_per_slice == 0) sp.ctas_per_slice = 1;
+        uint64_t nw = (uint64_t)sp.ctas_per_slice * cfg.warps;
+        if (nw > units) nw = units;
+        sp.warps_per_slice = (uint32_t)nw;
+        sp.ctas_per_slice = (uint32_t)((nw + cfg.warps - 1) / cfg.warps);
+        std::vector<uint8_t> pieces((size_t)part.pairs * part.slices);
+        uint32_t mp = 1;
+        for (uint32_t pr = 0; pr < part.pairs; ++pr) {
+            const uint64_t u_first = (uint64_t)pr * part.kst_s, u_last = u_first + part.kst_s - 1;
+            const uint64_t w_first = ((u_first + 1) * nw + units - 1) / units - 1;
+            const uint64_t w_last = ((u_last + 1) * nw + units - 1) / units - 1;
+            const uint64_t n = w_last - w_first + 1;
+            if (n > 255) return fail(ctx, CTOX_SHAPE, "row pair split into %llu pieces", (unsigned long long)n);
+            for (uint32_t sl = 0; sl < part.slices; ++sl) pieces[(size_t)pr * part.slices + sl] = (uint8_t)n;
+            if (n > mp) mp = (uint32_t)n;
+        }
+        sp.max_pieces = mp;
+        if (mp > part.max_pieces) part.max_pieces = mp;
+        sp.pieces_bytes = pieces.size();
+        rc = dev_alloc(ctx, (void **)&sp.pieces, sp.pieces_bytes);
+        if (rc) return rc;
+        CTOX_CUDA(ctx, cudaMemcpyAsync(sp.pieces, pieces.data(), sp.pieces_bytes, cudaMemcpyHostToDevice,
+                                       ctx->stream));
+        CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `pieces` is a temporary
+        mv->device_bytes += sp.pieces_bytes;
     }
-    part.max_pieces = mp;
-    part.partial_bytes = (size_t)part.pairs * part.max_pieces * kPairRows * kMaxPosPerPass * sizeof(float);
+    part.partial_bytes = (size_t)part.pairs * part.slices * part.max_pieces * kPairRows * kMaxPosPerPass *
+                         sizeof(float);
     rc = dev_alloc(ctx, (void **)&part.partial, part.partial_bytes);
     if (rc) return rc;
-    part.pieces_bytes = part.pairs;
-    rc = dev_alloc(ctx, (void **)&part.pieces, part.pieces_bytes);
-    if (rc) return rc;
-    CTOX_CUDA(ctx, cudaMemcpyAsync(part.pieces, pieces.data(), part.pieces_bytes, cudaMemcpyHostToDevice,
-                                   ctx->stream));
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (!(flags & CTOX_PREPARE_KEEP_CANONICAL)) {
         dev_free(ctx, part.canon, part.canon_bytes);
         part.canon = nullptr;
         part.canon_bytes = 0;
     }
-    mv->device_bytes += part.prep_bytes + part.canon_bytes + part.partial_bytes + part.pieces_bytes;
+    mv->device_bytes += part.prep_bytes + part.canon_bytes + part.partial_bytes;
     return CTOX_OK;
 }
 
@@ -814,14 +886,18 @@ ctox_status set_smem_attr(ctox_ctx *ctx) {
 #define CTOX_SMEM_ATTR(...)                                                                        \
     CTOX_CUDA(ctx, cudaFuncSetAttribute(k_matvec_stream<__VA_ARGS__>,                              \
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, ctx->max_smem_optin))
-    CTOX_SMEM_ATTR(0, 8, 4);
-    CTOX_SMEM_ATTR(1, 8, 4);
-    CTOX_SMEM_ATTR(0, 16, 2);
-    CTOX_SMEM_ATTR(1, 16, 2);
-    CTOX_SMEM_ATTR(0, 12, 3);
-    CTOX_SMEM_ATTR(1, 12, 3);
-    CTOX_SMEM_ATTR(0, 16, 3);
-    CTOX_SMEM_ATTR(1, 16, 3);
+    CTOX_SMEM_ATTR(0, 16, 2, 1);
+    CTOX_SMEM_ATTR(1, 16, 2, 1);
+    CTOX_SMEM_ATTR(0, 8, 4, 1);
+    CTOX_SMEM_ATTR(1, 8, 4, 1);
+    CTOX_SMEM_ATTR(0, 8, 2, 1);
+    CTOX_SMEM_ATTR(1, 8, 2, 1);
+    CTOX_SMEM_ATTR(0, 16, 2, 2);
+    CTOX_SMEM_ATTR(1, 16, 2, 2);
+    CTOX_SMEM_ATTR(0, 8, 4, 2);
+    CTOX_SMEM_ATTR(1, 8, 4, 2);
+    CTOX_SMEM_ATTR(0, 8, 2, 2);
+    CTOX_SMEM_ATTR(1, 8, 2, 2);
 #undef CTOX_SMEM_ATTR
     done_device = ctx->device;
     return CTOX_OK;
@@ -844,20 +920,35 @@ ctox_status check_device_error(ctox_ctx *ctx, const char *what) {
 namespace ctox {
 
 uint32_t matvec_positions_per_pass(ctox_matvec *mv) {
-    const StreamCfg cfg = stream_cfg();
-    int worst_dt = 0;
-    for (auto &p : mv->parts) worst_dt |= p.dt;
-    uint32_t per_pass = kMaxPosPerPass;
-    while (per_pass > 0 && stream_smem_bytes(worst_dt, cfg, mv->blocks_padded, per_pass) >
-                               (size_t)mv->ctx->max_smem_optin)
-        --per_pass;
+    // every part must fit: 8 positions if the wide class fits, else up to 4 (shrinking if needed)
+    bool wide = true, narrow = true;
+    for (auto &p : mv->parts) {
+        wide = wide && p.split[1].warps != 0;
+        narrow = narrow && p.split[0].warps != 0;
+    }
+    if (wide) return kMaxPosPerPass;
+    if (narrow) return 4;
+    uint32_t per_pass = 3;
+    for (; per_pass > 0; --per_pass) {
+        bool fits = true;
+        for (auto &p : mv->parts)
+            fits = fits && pick_stream_cfg(mv->ctx, p.dt, p.kst_s * 4, per_pass).warps != 0;
+        if (fits) break;
+    }
     return per_pass;
 }
 
 ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos) {
     ctox_ctx *ctx = mv->ctx;
-    const StreamCfg cfg = stream_cfg();
     MatvecPart &p = mv->parts[part_index];
+    const MatvecPart::Split &split = p.split[npos > 4 ? 1 : 0];
+    StreamCfg cfg{split.warps, split.stages};
+    if (cfg.warps == 0) {
+        // the class shape does not fit; a smaller position count may (same work split as class 0
+        // only if the shape is the same, so recompute nothing: refuse instead)
+        return fail(ctx, CTOX_MEMORY_BUDGET, "streaming kernel: %u positions of %llu columns exceed shared memory",
+                    npos, (unsigned long long)mv->columns);
+    }
     StreamParams sp;
     sp.wprep = p.prep;
     sp.xfrag = mv->xfrag;
@@ -865,18 +956,16 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     sp.partial = p.partial;
     sp.error_flag = ctx->dev_error;
     sp.pairs = p.pairs;
-    sp.kst = p.kst;
+    sp.kst_s = p.kst_s;
+    sp.slices = p.slices;
+    sp.ctas_per_slice = split.ctas_per_slice;
+    sp.warps_per_slice = split.warps_per_slice;
     sp.npos = npos;
     sp.max_pieces = p.max_pieces;
-    sp.total_warps = p.total_warps;
-    sp.xfrag_bytes = mv->blocks_padded * 2 * npos * 128;
-    sp.meta_bytes = mv->blocks_padded * npos * 8;
     static const uint32_t dbg = getenv("CTOX_DBG") ? (uint32_t)atoi(getenv("CTOX_DBG")) : 0u;
     sp.dbg = dbg;
-    const size_t smem = stream_smem_bytes(p.dt, cfg, mv->blocks_padded, npos);
-    if (smem > (size_t)ctx->max_smem_optin)
-        return fail(ctx, CTOX_MEMORY_BUDGET, "streaming kernel needs %zu bytes of shared memory", smem);
-    const unsigned grid = (p.total_warps + cfg.warps - 1) / cfg.warps;
+    const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
+    const unsigned grid = split.ctas_per_slice * p.slices;
     timing_begin(ctx);
     if (p.dt)
         launch_stream<1>(cfg, grid, smem, ctx->stream, sp);
@@ -1055,9 +1144,9 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
             MatvecPart &p = mv->parts[pi];
             const unsigned n_out = (unsigned)(p.rows * npos);
             k_matvec_finish<<<(n_out + 255) / 256, 256, 0, st>>>(
-                p.partial, p.pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
+                p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
                 mv->bias ? mv->bias + p.row_start : nullptr, y_dev + (size_t)m0 * y_stride + p.row_start,
-                (long long)y_stride, (uint32_t)p.rows, npos, p.max_pieces, mv->activation);
+                (long long)y_stride, (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
         }
     }
     CTOX_CUDA(ctx, cudaGetLastError());

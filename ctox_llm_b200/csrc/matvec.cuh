@@ -9,24 +9,31 @@
 #include "common.cuh"
 
 namespace ctox {
-constexpr int kMaxPosPerPass = 4;  // positions per pass of the streaming kernel (hi/lo => 8 columns)
+constexpr int kMaxPosPerPass = 8;  // positions per pass of the streaming kernel (hi/lo => 16 columns)
 constexpr int kPairRows = 32;      // rows of a tile pair (the unit of work and of the partial sums)
 }  // namespace ctox
 
 struct MatvecPart {
     int dt = 0;  // 0 Q2, 1 Q4
     uint64_t row_start = 0, rows = 0;
-    uint32_t pairs = 0, kst = 0;  // 32-row tile pairs, 256-column super-tiles per row
+    uint32_t pairs = 0;   // 32-row tile pairs
+    uint32_t slices = 1;  // column slices; a CTA of the streaming kernel works inside one
+    uint32_t kst_s = 0;   // 256-column super-tiles per slice
     uint8_t *prep = nullptr;
     size_t prep_bytes = 0;
     uint8_t *canon = nullptr;
     size_t canon_bytes = 0;
     float *partial = nullptr;
     size_t partial_bytes = 0;
-    uint8_t *pieces = nullptr;  // [pairs] number of partial-sum pieces of each pair
-    size_t pieces_bytes = 0;
-    uint32_t total_warps = 1;   // warps of the streaming kernel that take work
-    uint32_t max_pieces = 1;
+    // The work split depends on the launch shape, which depends on the number of positions
+    // (shared memory); one table per shape class: [0] 1..4 positions, [1] 5..8 positions.
+    struct Split {
+        int warps = 0, stages = 0;       // launch shape; warps == 0: does not fit
+        uint32_t ctas_per_slice = 0, warps_per_slice = 0, max_pieces = 1;
+        uint8_t *pieces = nullptr;       // [pairs][slices] partial-sum pieces
+        size_t pieces_bytes = 0;
+    } split[2];
+    uint32_t max_pieces = 1;  // slot stride of `partial`: max over both splits
 };
 
 struct ctox_matvec {
