@@ -60,7 +60,41 @@ class SpecRecord(C.Structure):
         ("emitted", C.c_uint32 * (MAX_VERIFY_NODES + 1)),
         ("path", C.c_int32 * MAX_VERIFY_NODES),
         ("node_argmax", C.c_uint32 * MAX_VERIFY_NODES),
+        ("node_token", C.c_uint32 * MAX_VERIFY_NODES),
     ]
+
+
+class ModelConfig(C.Structure):
+    """ctox_model_config (include/ctox_b200.h); Qwen38Config (config.rs:12-58) plus deployment."""
+
+    _fields_ = [(n, C.c_uint32) for n in (
+        "vocab_size", "hidden_size", "intermediate_size", "num_hidden_layers", "num_attention_heads",
+        "num_key_value_heads", "head_dim", "rotary_dim")] + [
+        ("rope_theta", C.c_float), ("rms_norm_epsilon", C.c_float)] + [(n, C.c_uint32) for n in (
+            "full_attention_interval", "linear_num_key_heads", "linear_num_value_heads",
+            "linear_key_head_dim", "linear_value_head_dim", "linear_conv_kernel_dim",
+            "mtp_num_hidden_layers", "max_context_tokens", "kv_page_tokens", "kv_dtype",
+            "max_draft_tokens", "draft_vocab")]
+
+
+class ExecStep(C.Structure):
+    """ctox_exec_step (include/ctox_b200.h)."""
+
+    _fields_ = [
+        ("proposed_drafts", C.c_uint32),
+        ("verified_drafts", C.c_uint32),
+        ("n_accepted", C.c_uint32),
+        ("accepted_draft_tokens", C.c_uint32 * MAX_VERIFY_NODES),
+        ("next_token", C.c_uint32),
+        ("draft_tokens", C.c_uint32 * MAX_VERIFY_NODES),
+        ("target_tokens", C.c_uint32 * (MAX_VERIFY_NODES + 1)),
+    ]
+
+
+(T_EMBED, T_LM_HEAD, T_FINAL_NORM, T_INPUT_NORM, T_POST_NORM, T_ATTN_QKV, T_ATTN_O, T_Q_NORM, T_K_NORM,
+ T_LIN_IN, T_LIN_OUT, T_CONV_W, T_A_LOG, T_DT_BIAS, T_LIN_NORM, T_MLP_GATE_UP, T_MLP_DOWN, T_MTP_FC,
+ T_MTP_NORM_E, T_MTP_NORM_H, T_MTP_NORM, T_DRAFT_IDS) = range(22)
+LAYER_GLOBAL = 0xFFFFFFFF
 
 
 class FusedMatVecOp(C.Structure):
@@ -123,6 +157,22 @@ SIGNATURES = {
                                        C.POINTER(C.c_int32), C.POINTER(C.c_uint32), C.c_float,
                                        C.c_uint64, C.c_uint64, C.c_uint32, C.c_void_p,
                                        C.POINTER(SpecRecord)]),
+    "ctox_exec_create": (C.c_int32, [C.c_void_p, C.POINTER(ModelConfig), C.POINTER(C.c_void_p)]),
+    "ctox_exec_destroy": (C.c_int32, [C.c_void_p]),
+    "ctox_exec_load_matrix": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(FusedMatVecOp)]),
+    "ctox_exec_load_vector": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64]),
+    "ctox_exec_fill_synthetic": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_float, C.c_float]),
+    "ctox_exec_warmup": (C.c_int32, [C.c_void_p]),
+    "ctox_exec_reset_session": (C.c_int32, [C.c_void_p]),
+    "ctox_exec_prefill": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "ctox_exec_prefill_synthetic": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint64]),
+    "ctox_exec_decode": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_int32, C.c_float, C.c_uint64, C.c_int32,
+                                     C.POINTER(ExecStep)]),
+    "ctox_exec_position": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "ctox_exec_last_hidden": (C.c_int32, [C.c_void_p, C.c_void_p]),
+    "ctox_exec_keep_logits": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "ctox_exec_last_logits": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p]),
+    "ctox_exec_allocated_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
     "ctox_matvec_info": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64),
                                      C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
 }

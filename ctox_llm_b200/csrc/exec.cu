@@ -1,0 +1,1000 @@
+// Decode executor: the target model pass, the MTP draft chain, verification and the
+// speculative state transaction, as one sequence of kernels on the context's stream.
+//
+// Reference behaviour: trait ModelExecutor (engine.rs:322-362); CPU oracle executor
+// decoder.rs:1278-1458 (draft, verify, commit by replay); CUDA candidate
+// backend/cuda_executor.rs:797-1073 over backend/cuda_graph.rs (4 chained MTP drafts, one
+// 5-row verify pass, acceptance on the device, one small host read per block,
+// restore + replay on a partial acceptance, cuda_graph.rs:3166-3292,4962-5003).
+//
+// What is different here: a verify pass keeps everything it needs to commit ANY accepted
+// prefix without re-running projections. Attention layers only advance a token count; linear
+// layers write the recurrent state of the whole pass into a second buffer (flip on full
+// acceptance) and keep the pass's conv inputs and (q, k, v, g, beta), so a partial acceptance
+// re-scans the recurrence alone (~6 MB per layer) instead of replaying whole model passes.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <cstdlib>
+#include <vector>
+
+#include "common.cuh"
+#include "layers.cuh"
+#include "matvec.cuh"
+
+namespace ctox {
+constexpr uint32_t kMaxPass = 8;  // positions per pass (verify rows / prefill chunk)
+
+struct LayerW {
+    bool full = false;
+    float *in_ln = nullptr, *post_ln = nullptr;
+    ctox_matvec *in_fan = nullptr, *out = nullptr, *gate_up = nullptr, *down = nullptr;
+    float *conv_w = nullptr, *a_log = nullptr, *dt_bias = nullptr, *lin_norm = nullptr;
+    float *q_norm = nullptr, *k_norm = nullptr;
+};
+
+struct LayerS {
+    float *conv_state = nullptr;                  // [channels][kernel], committed
+    float *delta[2] = {nullptr, nullptr};         // [heads][128][128]; delta[cur] is committed
+    int cur = 0;
+    float *conv_in = nullptr;                     // [kMaxPass][channels] inputs of the last pass
+    float *q = nullptr, *k = nullptr, *v = nullptr, *g = nullptr, *beta = nullptr;  // last pass
+    void *k_cache = nullptr, *v_cache = nullptr;  // [slots][kv_heads][head_dim]
+};
+}  // namespace ctox
+
+using namespace ctox;
+
+struct ctox_exec {
+    ctox_ctx *ctx = nullptr;
+    ctox_model_config cfg{};
+    uint32_t n_layers = 0;  // target layers; index n_layers is the MTP layer when present
+    uint32_t key_width = 0, value_width = 0, channels = 0, q_width = 0, kv_width = 0;
+    std::vector<LayerW> w;
+    std::vector<LayerS> s;
+    ctox_matvec *embed = nullptr, *lm_head = nullptr, *mtp_fc = nullptr, *draft_head = nullptr;
+    float *final_norm = nullptr, *mtp_norm_e = nullptr, *mtp_norm_h = nullptr, *mtp_norm = nullptr;
+    uint32_t *draft_ids = nullptr;  // device, [draft_vocab]
+    bool lm_head_is_embed = false;
+    // session
+    uint64_t position = 0;     // tokens consumed by the target so far
+    bool have_hidden = false;  // hist_hidden[0 .. hist_n) holds the final hidden of the last hist_n positions
+    uint32_t hist_n = 0;       // committed positions of the last block (1..kMaxPass)
+    uint32_t hist_tokens[kMaxPass] = {0};  // tokens at positions position-hist_n+1 .. position-1 (drafts accepted)
+    uint64_t step_counter = 0;
+    bool warmed = false, keep_logits = false;
+    // buffers ([kMaxPass] rows each)
+    float *h = nullptr, *final_hidden = nullptr, *hist_hidden = nullptr, *embed_rows = nullptr;
+    float *mtp_h = nullptr, *mtp_hidden = nullptr, *mtp_prev = nullptr;
+    float *aq = nullptr, *agate = nullptr, *attn_ws = nullptr;
+    float *lz = nullptr, *lcore = nullptr;
+    float *draft_logits = nullptr, *logits = nullptr;
+    uint32_t *tokens_dev = nullptr;  // [kMaxPass + 1]: verify inputs = [token, drafts...]
+    uint32_t *mtp_tokens_dev = nullptr;
+    uint32_t *page_table = nullptr, *mtp_page_table = nullptr;
+    uint32_t attn_splits_max = 64;
+    uint64_t model_bytes = 0, session_bytes = 0;
+    std::vector<std::pair<void *, size_t>> owned;  // tracked raw allocations (vectors, buffers, states)
+};
+
+namespace {
+
+ctox_status xalloc(ctox_exec *e, void **p, size_t bytes, bool session, bool zero = true) {
+    ctox_status rc = dev_alloc(e->ctx, p, bytes);
+    if (rc) return rc;
+    e->owned.emplace_back(*p, bytes);
+    (session ? e->session_bytes : e->model_bytes) += bytes;
+    if (zero) CTOX_CUDA(e->ctx, cudaMemsetAsync(*p, 0, bytes, e->ctx->stream));
+    return CTOX_OK;
+}
+
+bool layer_is_full(const ctox_exec *e, uint32_t l) {
+    if (l >= e->n_layers) return true;  // the MTP layer is a full-attention layer
+    return (l + 1) % e->cfg.full_attention_interval == 0;
+}
+
+size_t kv_elem(const ctox_exec *e) { return e->cfg.kv_dtype == CTOX_BF16 ? 2 : 4; }
+
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c, ctox_exec **out) {
+    if (!ctx || !c || !out) return CTOX_INVALID_STATE;
+    *out = nullptr;
+    if (c->hidden_size == 0 || c->hidden_size % 64 || c->intermediate_size % 64 || c->vocab_size == 0 ||
+        c->num_hidden_layers == 0 || c->full_attention_interval == 0)
+        return fail(ctx, CTOX_SHAPE, "executor: hidden/intermediate sizes must be non-zero multiples of 64");
+    if (c->num_key_value_heads == 0 || c->num_attention_heads % c->num_key_value_heads || c->head_dim % 64 ||
+        c->head_dim > 256 || c->rotary_dim > c->head_dim || c->rotary_dim % 2 ||
+        (c->num_attention_heads * c->head_dim) % 256 ||
+        c->num_attention_heads / c->num_key_value_heads * kMaxPass > 48)
+        return fail(ctx, CTOX_SHAPE, "executor: unsupported attention geometry");
+    if (c->linear_key_head_dim != 128 || c->linear_value_head_dim != 128 || c->linear_num_key_heads == 0 ||
+        c->linear_num_value_heads % c->linear_num_key_heads || (c->linear_num_value_heads * 128) % 256 ||
+        c->linear_conv_kernel_dim == 0 || c->linear_conv_kernel_dim > 8)
+        return fail(ctx, CTOX_SHAPE, "executor: unsupported linear-attention geometry");
+    if (c->kv_dtype != CTOX_F32 && c->kv_dtype != CTOX_BF16)
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "executor: kv dtype %u", c->kv_dtype);
+    if (c->max_draft_tokens + 1 > kMaxPass || c->mtp_num_hidden_layers > 1 || c->kv_page_tokens == 0 ||
+        c->max_context_tokens < 2 * kMaxPass || c->draft_vocab > c->vocab_size)
+        return fail(ctx, CTOX_SHAPE, "executor: unsupported draft, page or context configuration");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    ctox_exec *e = new ctox_exec();
+    e->ctx = ctx;
+    e->cfg = *c;
+    e->n_layers = c->num_hidden_layers;
+    e->key_width = c->linear_num_key_heads * 128;
+    e->value_width = c->linear_num_value_heads * 128;
+    e->channels = 2 * e->key_width + e->value_width;
+    e->q_width = c->num_attention_heads * c->head_dim;
+    e->kv_width = c->num_key_value_heads * c->head_dim;
+    const uint32_t total_layers = e->n_layers + c->mtp_num_hidden_layers;
+    e->w.resize(total_layers);
+    e->s.resize(total_layers);
+    for (uint32_t l = 0; l < total_layers; ++l) e->w[l].full = layer_is_full(e, l);
+    *out = e;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_destroy(ctox_exec *e) {
+    if (!e) return CTOX_OK;
+    cudaSetDevice(e->ctx->device);
+    cudaStreamSynchronize(e->ctx->stream);
+    for (auto &lw : e->w) {
+        ctox_matvec_destroy(lw.in_fan);
+        ctox_matvec_destroy(lw.out);
+        ctox_matvec_destroy(lw.gate_up);
+        ctox_matvec_destroy(lw.down);
+    }
+    if (!e->lm_head_is_embed) ctox_matvec_destroy(e->lm_head);
+    ctox_matvec_destroy(e->embed);
+    ctox_matvec_destroy(e->mtp_fc);
+    ctox_matvec_destroy(e->draft_head);
+    for (auto &o : e->owned) dev_free(e->ctx, o.first, o.second);
+    delete e;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_allocated_bytes(const ctox_exec *e, uint64_t *model, uint64_t *session) {
+    if (!e) return CTOX_INVALID_STATE;
+    uint64_t mats = 0;
+    auto add = [&](ctox_matvec *mv) {
+        if (mv) mats += mv->device_bytes;
+    };
+    for (auto &lw : e->w) {
+        add(lw.in_fan);
+        add(lw.out);
+        add(lw.gate_up);
+        add(lw.down);
+    }
+    add(e->embed);
+    if (!e->lm_head_is_embed) add(e->lm_head);
+    add(e->mtp_fc);
+    add(e->draft_head);
+    if (model) *model = e->model_bytes + mats;
+    if (session) *session = e->session_bytes;
+    return CTOX_OK;
+}
+
+}  // extern "C"
+
+namespace {
+
+struct Shape {
+    uint64_t rows, cols;
+};
+
+bool matrix_slot(ctox_exec *e, uint32_t layer, uint32_t tensor, ctox_matvec ***slot, Shape *shape) {
+    const ctox_model_config &c = e->cfg;
+    const uint64_t H = c.hidden_size, F = c.intermediate_size;
+    if (layer == CTOX_LAYER_GLOBAL) {
+        switch (tensor) {
+            case CTOX_T_EMBED: *slot = &e->embed; *shape = {c.vocab_size, H}; return true;
+            case CTOX_T_LM_HEAD: *slot = &e->lm_head; *shape = {c.vocab_size, H}; return true;
+            case CTOX_T_MTP_FC:
+                if (!c.mtp_num_hidden_layers) return false;
+                *slot = &e->mtp_fc; *shape = {H, 2 * H}; return true;
+            default: return false;
+        }
+    }
+    if (layer >= e->w.size()) return false;
+    LayerW &lw = e->w[layer];
+    switch (tensor) {
+        case CTOX_T_ATTN_QKV:
+            if (!lw.full) return false;
+            *slot = &lw.in_fan; *shape = {2ull * e->q_width + 2ull * e->kv_width, H}; return true;
+        case CTOX_T_ATTN_O:
+            if (!lw.full) return false;
+            *slot = &lw.out; *shape = {H, e->q_width}; return true;
+        case CTOX_T_LIN_IN:
+            if (lw.full) return false;
+            *slot = &lw.in_fan;
+            *shape = {(uint64_t)e->channels + e->value_width + 2ull * c.linear_num_value_heads, H};
+            return true;
+        case CTOX_T_LIN_OUT:
+            if (lw.full) return false;
+            *slot = &lw.out; *shape = {H, e->value_width}; return true;
+        case CTOX_T_MLP_GATE_UP: *slot = &lw.gate_up; *shape = {2 * F, H}; return true;
+        case CTOX_T_MLP_DOWN: *slot = &lw.down; *shape = {H, F}; return true;
+        default: return false;
+    }
+}
+
+bool vector_slot(ctox_exec *e, uint32_t layer, uint32_t tensor, float ***slot, uint64_t *n) {
+    const ctox_model_config &c = e->cfg;
+    if (layer == CTOX_LAYER_GLOBAL) {
+        switch (tensor) {
+            case CTOX_T_FINAL_NORM: *slot = &e->final_norm; *n = c.hidden_size; return true;
+            case CTOX_T_MTP_NORM_E: *slot = &e->mtp_norm_e; *n = c.hidden_size; return true;
+            case CTOX_T_MTP_NORM_H: *slot = &e->mtp_norm_h; *n = c.hidden_size; return true;
+            case CTOX_T_MTP_NORM: *slot = &e->mtp_norm; *n = c.hidden_size; return true;
+            default: return false;
+        }
+    }
+    if (layer >= e->w.size()) return false;
+    LayerW &lw = e->w[layer];
+    switch (tensor) {
+        case CTOX_T_INPUT_NORM: *slot = &lw.in_ln; *n = c.hidden_size; return true;
+        case CTOX_T_POST_NORM: *slot = &lw.post_ln; *n = c.hidden_size; return true;
+        case CTOX_T_Q_NORM: if (!lw.full) return false; *slot = &lw.q_norm; *n = c.head_dim; return true;
+        case CTOX_T_K_NORM: if (!lw.full) return false; *slot = &lw.k_norm; *n = c.head_dim; return true;
+        case CTOX_T_CONV_W:
+            if (lw.full) return false;
+            *slot = &lw.conv_w; *n = (uint64_t)e->channels * c.linear_conv_kernel_dim; return true;
+        case CTOX_T_A_LOG: if (lw.full) return false; *slot = &lw.a_log; *n = c.linear_num_value_heads; return true;
+        case CTOX_T_DT_BIAS: if (lw.full) return false; *slot = &lw.dt_bias; *n = c.linear_num_value_heads; return true;
+        case CTOX_T_LIN_NORM: if (lw.full) return false; *slot = &lw.lin_norm; *n = 128; return true;
+        default: return false;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_exec_load_matrix(ctox_exec *e, uint32_t layer, uint32_t tensor, const ctox_fused_matvec_op *op) {
+    if (!e || !op) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    ctox_matvec **slot = nullptr;
+    Shape shape{};
+    if (!matrix_slot(e, layer, tensor, &slot, &shape))
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "tensor %u is not a matrix of layer %u", tensor, layer);
+    if (op->rows != shape.rows || op->columns != shape.cols)
+        return fail(ctx, CTOX_SHAPE, "tensor %u of layer %u is %llux%llu, expected %llux%llu", tensor, layer,
+                    (unsigned long long)op->rows, (unsigned long long)op->columns,
+                    (unsigned long long)shape.rows, (unsigned long long)shape.cols);
+    if (op->dtype != CTOX_Q2B64 && op->dtype != CTOX_Q4B64)
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "executor matrices must be pure Q2_B64 or Q4_B64");
+    if (op->activation != CTOX_ACT_IDENTITY || op->bias)
+        return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "executor matrices carry no bias or activation");
+    if (*slot) {
+        ctox_matvec_destroy(*slot);
+        *slot = nullptr;
+    }
+    const bool keep = tensor == CTOX_T_EMBED || (tensor == CTOX_T_LM_HEAD && e->cfg.draft_vocab);
+    e->warmed = false;
+    return ctox_matvec_prepare(ctx, op, keep ? CTOX_PREPARE_KEEP_CANONICAL : 0, slot);
+}
+
+ctox_status ctox_exec_load_vector(ctox_exec *e, uint32_t layer, uint32_t tensor, const float *values, uint64_t n) {
+    if (!e || !values) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (layer == CTOX_LAYER_GLOBAL && tensor == CTOX_T_DRAFT_IDS) {
+        if (n != e->cfg.draft_vocab || n == 0)
+            return fail(ctx, CTOX_SHAPE, "draft id table has %llu entries, expected %u", (unsigned long long)n,
+                        e->cfg.draft_vocab);
+        const uint32_t *ids = reinterpret_cast<const uint32_t *>(values);
+        for (uint64_t i = 0; i < n; ++i)
+            if (ids[i] >= e->cfg.vocab_size || (i && ids[i] <= ids[i - 1]))
+                return fail(ctx, CTOX_INVALID_ARTIFACT, "draft token ids must be strictly increasing and in range");
+        if (!e->draft_ids) {
+            ctox_status rc = xalloc(e, (void **)&e->draft_ids, n * 4, false);
+            if (rc) return rc;
+        }
+        CTOX_CUDA(ctx, cudaMemcpyAsync(e->draft_ids, ids, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+        CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        e->warmed = false;
+        return CTOX_OK;
+    }
+    float **slot = nullptr;
+    uint64_t expect = 0;
+    if (!vector_slot(e, layer, tensor, &slot, &expect))
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "tensor %u is not a vector of layer %u", tensor, layer);
+    if (n != expect)
+        return fail(ctx, CTOX_SHAPE, "tensor %u of layer %u has %llu values, expected %llu", tensor, layer,
+                    (unsigned long long)n, (unsigned long long)expect);
+    for (uint64_t i = 0; i < n; ++i)
+        if (!std::isfinite(values[i])) return fail(ctx, CTOX_INVALID_ARTIFACT, "tensor %u has a non-finite value", tensor);
+    if (!*slot) {
+        ctox_status rc = xalloc(e, (void **)slot, n * sizeof(float), false);
+        if (rc) return rc;
+    }
+    CTOX_CUDA(ctx, cudaMemcpyAsync(*slot, values, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    e->warmed = false;
+    return CTOX_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ synthetic tensors, draft head
+namespace ctox {
+
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+
+// Canonical blocks [f16 scale][codes]: codes uniform, scale drawn from a 4096-entry quantile table.
+__global__ void k_fill_canonical(uint8_t *__restrict__ out, uint64_t blocks, uint32_t block_bytes,
+                                 const uint16_t *__restrict__ table, uint64_t seed) {
+    const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= blocks) return;
+    uint8_t *p = out + b * block_bytes;
+    uint64_t r = mix64(seed ^ (b * 0x100000001B3ull));
+    const uint16_t sc = table[r & 4095];
+    p[0] = (uint8_t)(sc & 0xff);
+    p[1] = (uint8_t)(sc >> 8);
+    for (uint32_t i = 2; i < block_bytes; i += 8) {
+        r = mix64(r + i);
+        for (uint32_t j = 0; j < 8 && i + j < block_bytes; ++j) p[i + j] = (uint8_t)(r >> (8 * j));
+    }
+}
+
+__global__ void k_fill_uniform_f16(float *__restrict__ out, uint64_t n, float lo, float hi, uint64_t seed) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float u = (float)(mix64(seed ^ (i * 0x9E3779B1ull)) >> 40) * (1.0f / 16777216.0f);
+    out[i] = __half2float(__float2half_rn(lo + (hi - lo) * u));  // what an f16 payload would hold
+}
+
+template <typename T>
+__global__ void k_fill_normal(T *__restrict__ out, uint64_t n, float mean, float std, uint64_t seed) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t r = mix64(seed ^ (i * 0xD6E8FEB86659FD93ull));
+    const float u1 = ((float)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = (float)((r >> 16) & 0xffffff) * (1.0f / 16777216.0f);
+    const float z = sqrtf(-2.0f * logf(u1)) * cosf(6.28318530718f * u2);
+    const float v = mean + std * z;
+    if (sizeof(T) == 2)
+        reinterpret_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(v);
+    else
+        reinterpret_cast<float *>(out)[i] = v;
+}
+
+__global__ void k_gather_rows(const uint8_t *__restrict__ src, const uint32_t *__restrict__ ids,
+                              uint32_t row_bytes, uint32_t n, uint8_t *__restrict__ dst) {
+    const uint32_t r = blockIdx.x;
+    if (r >= n) return;
+    const uint8_t *s = src + (size_t)ids[r] * row_bytes;
+    uint8_t *d = dst + (size_t)r * row_bytes;
+    for (uint32_t i = threadIdx.x * 2; i < row_bytes; i += blockDim.x * 2)
+        *reinterpret_cast<uint16_t *>(d + i) = *reinterpret_cast<const uint16_t *>(s + i);
+}
+
+__global__ void k_gather_f32(const float *__restrict__ src, const uint32_t *__restrict__ ids, uint32_t n,
+                             float *__restrict__ dst) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[ids[i]];
+}
+
+__global__ void k_iota_u32(uint32_t *out, uint32_t n, uint32_t stride) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = i * stride;
+}
+
+}  // namespace ctox
+
+namespace {
+
+// Inverse normal CDF (Acklam's rational approximation, |error| < 1.2e-9).
+double inv_norm_cdf(double p) {
+    static const double a[] = {-3.969683028665376e+01, 2.209460984245205e+02, -2.759285104469687e+02,
+                               1.383577518672690e+02, -3.066479806614716e+01, 2.506628277459239e+00};
+    static const double b[] = {-5.447609879822406e+01, 1.615858368580409e+02, -1.556989798598866e+02,
+                               6.680131188771972e+01, -1.328068155288572e+01};
+    static const double c[] = {-7.784894002430293e-03, -3.223964580411365e-01, -2.400758277161838e+00,
+                               -2.549732539343734e+00, 4.374664141464968e+00, 2.938163982698783e+00};
+    static const double d[] = {7.784695709041462e-03, 3.224671290700398e-01, 2.445134137142996e+00,
+                               3.754408661907416e+00};
+    if (p < 0.02425) {
+        const double q = std::sqrt(-2 * std::log(p));
+        return (((((c[0] * q + c[1]) * q + c[2]) * q + c[3]) * q + c[4]) * q + c[5]) /
+               ((((d[0] * q + d[1]) * q + d[2]) * q + d[3]) * q + 1);
+    }
+    if (p > 1 - 0.02425) return -inv_norm_cdf(1 - p);
+    const double q = p - 0.5, r = q * q;
+    return (((((a[0] * r + a[1]) * r + a[2]) * r + a[3]) * r + a[4]) * r + a[5]) * q /
+           (((((b[0] * r + b[1]) * r + b[2]) * r + b[3]) * r + b[4]) * r + 1);
+}
+
+uint16_t f32_to_f16_bits(float f) {
+    __half h = __float2half_rn(f);
+    uint16_t u;
+    memcpy(&u, &h, 2);
+    return u;
+}
+
+ctox_status synth_matrix(ctox_exec *e, int dt, uint64_t rows, uint64_t cols, const uint16_t *table_dev,
+                         uint64_t seed, float *shared_s_in, uint32_t flags, ctox_matvec **out) {
+    ctox_ctx *ctx = e->ctx;
+    const uint32_t bb = dt ? 34 : 18;
+    const uint64_t blocks = rows * (cols / 64);
+    uint8_t *canon = nullptr;
+    float *s_in = nullptr, *s_out = nullptr;
+    ctox_status rc = dev_alloc(ctx, (void **)&canon, blocks * bb);
+    if (!rc) rc = dev_alloc(ctx, (void **)&s_in, cols * 4);
+    if (!rc) rc = dev_alloc(ctx, (void **)&s_out, rows * 4);
+    if (rc) return rc;
+    k_fill_canonical<<<(unsigned)((blocks + 255) / 256), 256, 0, ctx->stream>>>(canon, blocks, bb, table_dev, seed);
+    if (shared_s_in)
+        CTOX_CUDA(ctx, cudaMemcpyAsync(s_in, shared_s_in, cols * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    else
+        k_fill_uniform_f16<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(s_in, cols, 0.75f, 1.25f,
+                                                                                 seed ^ 0x5151);
+    k_fill_uniform_f16<<<(unsigned)((rows + 255) / 256), 256, 0, ctx->stream>>>(s_out, rows, 0.75f, 1.25f,
+                                                                             seed ^ 0xA0A0);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return matvec_create_device(ctx, dt, rows, cols, canon, blocks * bb, s_in, s_out, flags, out);
+}
+
+ctox_status synth_vector(ctox_exec *e, float **slot, uint64_t n, float mean, float std, uint64_t seed) {
+    if (!*slot) {
+        ctox_status rc = xalloc(e, (void **)slot, n * 4, false);
+        if (rc) return rc;
+    }
+    k_fill_normal<float><<<(unsigned)((n + 255) / 256), 256, 0, e->ctx->stream>>>(*slot, n, mean, std, seed);
+    return CTOX_OK;
+}
+
+ctox_status build_draft_head(ctox_exec *e) {
+    ctox_ctx *ctx = e->ctx;
+    if (e->draft_head) {
+        ctox_matvec_destroy(e->draft_head);
+        e->draft_head = nullptr;
+    }
+    if (!e->cfg.draft_vocab) return CTOX_OK;
+    if (!e->draft_ids) return fail(ctx, CTOX_INVALID_STATE, "draft vocabulary configured but no id table loaded");
+    MatvecPart &p = e->lm_head->parts[0];
+    if (!p.canon) return fail(ctx, CTOX_INVALID_STATE, "lm_head canonical bytes are not resident");
+    const uint32_t n = e->cfg.draft_vocab;
+    const uint32_t row_bytes = (uint32_t)(e->lm_head->columns / 64) * (p.dt ? 34 : 18);
+    uint8_t *canon = nullptr;
+    float *s_in = nullptr, *s_out = nullptr;
+    ctox_status rc = dev_alloc(ctx, (void **)&canon, (size_t)n * row_bytes);
+    if (!rc) rc = dev_alloc(ctx, (void **)&s_in, e->lm_head->columns * 4);
+    if (!rc) rc = dev_alloc(ctx, (void **)&s_out, (size_t)n * 4);
+    if (rc) return rc;
+    k_gather_rows<<<n, 128, 0, ctx->stream>>>(p.canon, e->draft_ids, row_bytes, n, canon);
+    CTOX_CUDA(ctx, cudaMemcpyAsync(s_in, e->lm_head->s_in, e->lm_head->columns * 4, cudaMemcpyDeviceToDevice,
+                                   ctx->stream));
+    k_gather_f32<<<(n + 255) / 256, 256, 0, ctx->stream>>>(e->lm_head->s_out, e->draft_ids, n, s_out);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return matvec_create_device(ctx, p.dt, n, e->lm_head->columns, canon, (size_t)n * row_bytes, s_in, s_out, 0,
+                                &e->draft_head);
+}
+
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_exec_fill_synthetic(ctox_exec *e, uint64_t seed, float mu, float sigma) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    const ctox_model_config &c = e->cfg;
+    // f16 block-scale quantile table of the log-normal(mu, sigma)
+    std::vector<uint16_t> table(4096);
+    for (int i = 0; i < 4096; ++i)
+        table[i] = f32_to_f16_bits((float)std::exp(mu + sigma * inv_norm_cdf((i + 0.5) / 4096.0)));
+    uint16_t *table_dev = nullptr;
+    ctox_status rc = xalloc(e, (void **)&table_dev, 4096 * 2, false, false);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemcpyAsync(table_dev, table.data(), 4096 * 2, cudaMemcpyHostToDevice, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const uint64_t H = c.hidden_size, F = c.intermediate_size;
+    uint64_t sd = seed * 1000003ull + 17;
+    auto next_seed = [&]() { return sd = sd * 6364136223846793005ull + 1442695040888963407ull; };
+#define SYNTH(expr)    \
+    do {               \
+        rc = (expr);   \
+        if (rc) return rc; \
+    } while (0)
+    auto replace = [&](ctox_matvec **slot) {
+        if (*slot) ctox_matvec_destroy(*slot);
+        *slot = nullptr;
+    };
+    if (e->lm_head && !e->lm_head_is_embed) replace(&e->lm_head);
+    replace(&e->embed);
+    // attention / embedding weights Q4, FFN weights Q2 (the benchmark configuration)
+    SYNTH(synth_matrix(e, 1, c.vocab_size, H, table_dev, next_seed(), nullptr, CTOX_PREPARE_KEEP_CANONICAL,
+                       &e->embed));
+    e->lm_head = e->embed;  // tied: one resident copy serves row gathers and the head
+    e->lm_head_is_embed = true;
+    SYNTH(synth_vector(e, &e->final_norm, H, 0.f, 0.02f, next_seed()));
+    for (uint32_t l = 0; l < e->w.size(); ++l) {
+        LayerW &lw = e->w[l];
+        replace(&lw.in_fan);
+        replace(&lw.out);
+        replace(&lw.gate_up);
+        replace(&lw.down);
+        SYNTH(synth_vector(e, &lw.in_ln, H, 0.f, 0.02f, next_seed()));
+        SYNTH(synth_vector(e, &lw.post_ln, H, 0.f, 0.02f, next_seed()));
+        if (lw.full) {
+            SYNTH(synth_matrix(e, 1, 2ull * e->q_width + 2ull * e->kv_width, H, table_dev, next_seed(), nullptr, 0,
+                               &lw.in_fan));
+            SYNTH(synth_matrix(e, 1, H, e->q_width, table_dev, next_seed(), nullptr, 0, &lw.out));
+            SYNTH(synth_vector(e, &lw.q_norm, c.head_dim, 0.f, 0.02f, next_seed()));
+            SYNTH(synth_vector(e, &lw.k_norm, c.head_dim, 0.f, 0.02f, next_seed()));
+        } else {
+            SYNTH(synth_matrix(e, 1, (uint64_t)e->channels + e->value_width + 2ull * c.linear_num_value_heads, H,
+                               table_dev, next_seed(), nullptr, 0, &lw.in_fan));
+            SYNTH(synth_matrix(e, 1, H, e->value_width, table_dev, next_seed(), nullptr, 0, &lw.out));
+            SYNTH(synth_vector(e, &lw.conv_w, (uint64_t)e->channels * c.linear_conv_kernel_dim, 0.f, 0.3f,
+                               next_seed()));
+            SYNTH(synth_vector(e, &lw.a_log, c.linear_num_value_heads, 0.f, 0.5f, next_seed()));
+            SYNTH(synth_vector(e, &lw.dt_bias, c.linear_num_value_heads, 0.f, 0.5f, next_seed()));
+            SYNTH(synth_vector(e, &lw.lin_norm, 128, 1.f, 0.02f, next_seed()));
+        }
+        SYNTH(synth_matrix(e, 0, 2 * F, H, table_dev, next_seed(), nullptr, 0, &lw.gate_up));
+        SYNTH(synth_matrix(e, 0, H, F, table_dev, next_seed(), nullptr, 0, &lw.down));
+    }
+    if (c.mtp_num_hidden_layers) {
+        replace(&e->mtp_fc);
+        SYNTH(synth_matrix(e, 1, H, 2 * H, table_dev, next_seed(), nullptr, 0, &e->mtp_fc));
+        SYNTH(synth_vector(e, &e->mtp_norm_e, H, 0.f, 0.02f, next_seed()));
+        SYNTH(synth_vector(e, &e->mtp_norm_h, H, 0.f, 0.02f, next_seed()));
+        SYNTH(synth_vector(e, &e->mtp_norm, H, 0.f, 0.02f, next_seed()));
+    }
+    if (c.draft_vocab) {
+        if (!e->draft_ids) SYNTH(xalloc(e, (void **)&e->draft_ids, (size_t)c.draft_vocab * 4, false));
+        k_iota_u32<<<(c.draft_vocab + 255) / 256, 256, 0, ctx->stream>>>(e->draft_ids, c.draft_vocab,
+                                                                        c.vocab_size / c.draft_vocab);
+    }
+#undef SYNTH
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    e->warmed = false;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_warmup(ctox_exec *e) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (!e->embed || !e->lm_head || !e->final_norm)
+        return fail(ctx, CTOX_INVALID_STATE, "warmup: embedding, lm_head or final norm missing");
+    if (!e->embed->parts[0].canon) return fail(ctx, CTOX_INVALID_STATE, "warmup: embedding rows not resident");
+    if (!e->lm_head->s_in || !e->lm_head->s_out || !e->embed->s_in || !e->embed->s_out)
+        return fail(ctx, CTOX_INVALID_STATE, "warmup: embedding and lm_head need recovery scales");
+    for (uint32_t l = 0; l < e->w.size(); ++l) {
+        LayerW &lw = e->w[l];
+        bool ok = lw.in_ln && lw.post_ln && lw.in_fan && lw.out && lw.gate_up && lw.down;
+        ok = ok && (lw.full ? (lw.q_norm && lw.k_norm) : (lw.conv_w && lw.a_log && lw.dt_bias && lw.lin_norm));
+        if (!ok) return fail(ctx, CTOX_INVALID_STATE, "warmup: layer %u has missing tensors", l);
+        for (ctox_matvec *mv : {lw.in_fan, lw.out, lw.gate_up, lw.down})
+            if (mv->parts.size() != 1 || matvec_positions_per_pass(mv) < kMaxPass)
+                return fail(ctx, CTOX_MEMORY_BUDGET, "warmup: layer %u matrix cannot take %u positions per pass", l,
+                            kMaxPass);
+    }
+    if (c.mtp_num_hidden_layers && !(e->mtp_fc && e->mtp_norm_e && e->mtp_norm_h && e->mtp_norm))
+        return fail(ctx, CTOX_INVALID_STATE, "warmup: MTP tensors missing");
+    ctox_status rc = build_draft_head(e);
+    if (rc) return rc;
+    if (e->h) {  // buffers exist from an earlier warmup
+        e->warmed = true;
+        return ctox_exec_reset_session(e);
+    }
+    const uint64_t H = c.hidden_size, P = kMaxPass;
+#define WALLOC(ptr, bytes)                                  \
+    do {                                                    \
+        rc = xalloc(e, (void **)&(ptr), (bytes), true);     \
+        if (rc) return rc;                                  \
+    } while (0)
+    WALLOC(e->h, P * H * 4);
+    WALLOC(e->final_hidden, P * H * 4);
+    WALLOC(e->hist_hidden, P * H * 4);
+    WALLOC(e->embed_rows, P * H * 4);
+    WALLOC(e->mtp_h, P * H * 4);
+    WALLOC(e->mtp_hidden, P * H * 4);
+    WALLOC(e->mtp_prev, P * H * 4);
+    WALLOC(e->aq, P * e->q_width * 4);
+    WALLOC(e->agate, P * e->q_width * 4);
+    AttnGeom g{c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim, c.rope_theta,
+               c.rms_norm_epsilon};
+    WALLOC(e->attn_ws, attn_workspace_bytes(g, kMaxPass, e->attn_splits_max));
+    WALLOC(e->lz, P * e->value_width * 4);
+    WALLOC(e->lcore, P * e->value_width * 4);
+    WALLOC(e->draft_logits, (size_t)(c.draft_vocab ? c.draft_vocab : c.vocab_size) * 4);
+    WALLOC(e->tokens_dev, (P + 1) * 4);
+    WALLOC(e->mtp_tokens_dev, (P + 1) * 4);
+    const uint32_t slots = (c.max_context_tokens + c.kv_page_tokens - 1) / c.kv_page_tokens * c.kv_page_tokens;
+    const uint32_t pages = slots / c.kv_page_tokens;
+    WALLOC(e->page_table, pages * 4);
+    WALLOC(e->mtp_page_table, pages * 4);
+    k_iota_u32<<<(pages + 255) / 256, 256, 0, ctx->stream>>>(e->page_table, pages, 1);
+    k_iota_u32<<<(pages + 255) / 256, 256, 0, ctx->stream>>>(e->mtp_page_table, pages, 1);
+    for (uint32_t l = 0; l < e->w.size(); ++l) {
+        LayerS &ls = e->s[l];
+        if (e->w[l].full) {
+            const size_t kvb = (size_t)slots * e->kv_width * kv_elem(e);
+            WALLOC(ls.k_cache, kvb);
+            WALLOC(ls.v_cache, kvb);
+        } else {
+            WALLOC(ls.conv_state, (size_t)e->channels * c.linear_conv_kernel_dim * 4);
+            WALLOC(ls.delta[0], (size_t)c.linear_num_value_heads * 128 * 128 * 4);
+            WALLOC(ls.delta[1], (size_t)c.linear_num_value_heads * 128 * 128 * 4);
+            WALLOC(ls.conv_in, P * e->channels * 4);
+            WALLOC(ls.q, P * e->key_width * 4);
+            WALLOC(ls.k, P * e->key_width * 4);
+            WALLOC(ls.v, P * e->value_width * 4);
+            WALLOC(ls.g, P * c.linear_num_value_heads * 4);
+            WALLOC(ls.beta, P * c.linear_num_value_heads * 4);
+        }
+    }
+#undef WALLOC
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    e->warmed = true;
+    e->position = 0;
+    e->have_hidden = false;
+    e->hist_n = 0;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_reset_session(ctox_exec *e) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (!e->h) return fail(ctx, CTOX_INVALID_STATE, "reset: executor is not warm");
+    const ctox_model_config &c = e->cfg;
+    for (uint32_t l = 0; l < e->w.size(); ++l) {
+        LayerS &ls = e->s[l];
+        if (e->w[l].full) continue;  // cache slots are rewritten before they are read
+        CTOX_CUDA(ctx, cudaMemsetAsync(ls.conv_state, 0, (size_t)e->channels * c.linear_conv_kernel_dim * 4,
+                                       ctx->stream));
+        CTOX_CUDA(ctx, cudaMemsetAsync(ls.delta[0], 0, (size_t)c.linear_num_value_heads * 128 * 128 * 4,
+                                       ctx->stream));
+        ls.cur = 0;
+    }
+    e->position = 0;
+    e->have_hidden = false;
+    e->hist_n = 0;
+    e->step_counter = 0;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_prefill_synthetic(ctox_exec *e, uint64_t n, uint64_t seed) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "prefill: executor is not warm");
+    const ctox_model_config &c = e->cfg;
+    if (n == 0 || n + 2 * kMaxPass > c.max_context_tokens)
+        return fail(ctx, CTOX_SHAPE, "prefill: %llu tokens do not fit the context", (unsigned long long)n);
+    ctox_status rc = ctox_exec_reset_session(e);
+    if (rc) return rc;
+    uint64_t sd = seed;
+    for (uint32_t l = 0; l < e->w.size(); ++l) {
+        LayerS &ls = e->s[l];
+        if (e->w[l].full) {
+            const uint64_t cnt = n * e->kv_width;
+            for (void *buf : {ls.k_cache, ls.v_cache}) {
+                sd = sd * 6364136223846793005ull + 1442695040888963407ull;
+                if (c.kv_dtype == CTOX_BF16)
+                    k_fill_normal<__nv_bfloat16><<<(unsigned)((cnt + 255) / 256), 256, 0, ctx->stream>>>(
+                        (__nv_bfloat16 *)buf, cnt, 0.f, 1.f, sd);
+                else
+                    k_fill_normal<float><<<(unsigned)((cnt + 255) / 256), 256, 0, ctx->stream>>>((float *)buf, cnt,
+                                                                                              0.f, 1.f, sd);
+            }
+        } else {
+            const uint64_t cnt = (uint64_t)c.linear_num_value_heads * 128 * 128;
+            sd = sd * 6364136223846793005ull + 1442695040888963407ull;
+            k_fill_normal<float><<<(unsigned)((cnt + 255) / 256), 256, 0, ctx->stream>>>(ls.delta[0], cnt, 0.f, 0.02f,
+                                                                                      sd);
+            ls.cur = 0;
+        }
+    }
+    // a plausible previous hidden state so that the first block can draft
+    sd = sd * 6364136223846793005ull + 1442695040888963407ull;
+    k_fill_normal<float><<<(unsigned)((c.hidden_size + 255) / 256), 256, 0, ctx->stream>>>(e->hist_hidden,
+                                                                                        c.hidden_size, 0.f, 1.f, sd);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    e->position = n;
+    e->have_hidden = true;
+    e->hist_n = 1;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_position(const ctox_exec *e, uint64_t *position) {
+    if (!e || !position) return CTOX_INVALID_STATE;
+    *position = e->position;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_keep_logits(ctox_exec *e, int32_t enable) {
+    if (!e) return CTOX_INVALID_STATE;
+    e->keep_logits = enable != 0;
+    if (e->keep_logits && !e->logits)
+        return xalloc(e, (void **)&e->logits, (size_t)kMaxPass * e->cfg.vocab_size * 4, true);
+    return CTOX_OK;
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ passes
+namespace {
+
+#define EX(expr)               \
+    do {                       \
+        ctox_status rc_ = (expr); \
+        if (rc_) return rc_;   \
+    } while (0)
+
+AttnGeom attn_geom(const ctox_exec *e) {
+    const ctox_model_config &c = e->cfg;
+    return AttnGeom{c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim, c.rope_theta,
+                    c.rms_norm_epsilon};
+}
+
+// One decoder layer for m positions. The fragments of the layer's fused input projection are
+// already in place; on return h holds the layer output and the fragments of `next` (if any) hold
+// rmsnorm(h, next_norm); xn_out (if any) receives that normalised vector.
+ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t rope_pos0, uint64_t slot0,
+                       const uint32_t *page_table, const float *next_norm, float *xn_out, ctox_matvec *next) {
+    ctox_ctx *ctx = e->ctx;
+    cudaStream_t st = ctx->stream;
+    const ctox_model_config &c = e->cfg;
+    LayerW &lw = e->w[l];
+    LayerS &ls = e->s[l];
+    EX(matvec_stream_prepared(lw.in_fan, 0, m));
+    const MvOut fan = mv_out(lw.in_fan, m);
+    const MvIn out_in = mv_in(lw.out);
+    if (!lw.full) {
+        launch_linear_mid(st, fan, e->key_width, e->value_width, c.linear_num_value_heads,
+                          c.linear_conv_kernel_dim, ls.conv_state, lw.conv_w, lw.a_log, lw.dt_bias, m, ls.conv_in,
+                          ls.q, ls.k, ls.v, e->lz, ls.g, ls.beta);
+        EX(ctox_gated_delta_scan(ctx, ls.q, ls.k, ls.v, ls.g, ls.beta, ls.delta[ls.cur], ls.delta[ls.cur ^ 1],
+                                 e->lcore, m, c.linear_num_value_heads, c.linear_num_key_heads, 128, 128));
+        launch_gated_norm_prep(st, e->lcore, e->lz, lw.lin_norm, c.rms_norm_epsilon, c.linear_num_value_heads, 128,
+                               m, out_in);
+    } else {
+        const AttnGeom g = attn_geom(e);
+        launch_attn_pre(st, fan, g, lw.q_norm, lw.k_norm, rope_pos0, slot0, m, e->aq, e->agate, ls.k_cache,
+                        ls.v_cache, c.kv_dtype == CTOX_BF16, page_table, c.kv_page_tokens);
+        const uint64_t tiles = (slot0 + m + 31) / 32;
+        const uint32_t splits = (uint32_t)(tiles < e->attn_splits_max ? (tiles ? tiles : 1) : e->attn_splits_max);
+        launch_attention(st, g, e->aq, e->agate, ls.k_cache, ls.v_cache, c.kv_dtype == CTOX_BF16, page_table,
+                         c.kv_page_tokens, slot0, m, splits, e->attn_ws, out_in);
+    }
+    EX(matvec_stream_prepared(lw.out, 0, m));
+    const MvOut o = mv_out(lw.out, m);
+    const MvIn gu_in = mv_in(lw.gate_up);
+    launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in);
+    EX(matvec_stream_prepared(lw.gate_up, 0, m));
+    launch_swiglu_prep(st, mv_out(lw.gate_up, m), c.intermediate_size, m, mv_in(lw.down));
+    EX(matvec_stream_prepared(lw.down, 0, m));
+    const MvOut d = mv_out(lw.down, m);
+    if (next) {
+        const MvIn nin = mv_in(next);
+        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, &nin);
+    } else {
+        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, nullptr);
+    }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+// Target model over the m tokens in tokens_dev at positions pos0 ...: final_hidden[m] and the
+// lm_head fragments on return. Linear layers leave their new state in the spare buffer.
+ctox_status target_pass(ctox_exec *e, uint32_t m, uint64_t pos0) {
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    EX(matvec_embed_rows(e->embed, e->tokens_dev, m, e->h));
+    const MvIn first = mv_in(e->w[0].in_fan);
+    launch_residual_norm_prep(ctx->stream, e->h, nullptr, e->w[0].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
+                              nullptr, &first);
+    for (uint32_t l = 0; l < e->n_layers; ++l) {
+        const bool last = l + 1 == e->n_layers;
+        EX(layer_body(e, l, e->h, m, pos0, pos0, e->page_table, last ? e->final_norm : e->w[l + 1].in_ln,
+                      last ? e->final_hidden : nullptr, last ? e->lm_head : e->w[l + 1].in_fan));
+    }
+    return CTOX_OK;
+}
+
+// Commits the first n of the m positions of the last target pass.
+ctox_status commit_positions(ctox_exec *e, uint32_t m, uint32_t n) {
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    for (uint32_t l = 0; l < e->n_layers; ++l) {
+        if (e->w[l].full) continue;
+        LayerS &ls = e->s[l];
+        if (n < m)  // partial acceptance: re-scan the recurrence alone from the committed state
+            EX(ctox_gated_delta_scan(ctx, ls.q, ls.k, ls.v, ls.g, ls.beta, ls.delta[ls.cur], ls.delta[ls.cur ^ 1],
+                                     e->lcore, n, c.linear_num_value_heads, c.linear_num_key_heads, 128, 128));
+        ls.cur ^= 1;
+        launch_conv_commit(ctx->stream, ls.conv_state, ls.conv_in, e->channels, c.linear_conv_kernel_dim, n);
+    }
+    CTOX_CUDA(ctx, cudaMemcpyAsync(e->hist_hidden, e->final_hidden, (size_t)n * c.hidden_size * 4,
+                                   cudaMemcpyDeviceToDevice, ctx->stream));
+    e->hist_n = n;
+    e->have_hidden = true;
+    e->position += n;
+    return CTOX_OK;
+}
+
+// MTP layer over m (token, previous final hidden) pairs; tokens in mtp_tokens_dev, the pair of
+// absolute position p uses cache slot p - 1 (decoder.rs:1009-1046). With draft_slot >= 0 the greedy
+// draft of the last pair goes to tokens_dev[draft_slot].
+ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const float *hidden_rows, int draft_slot) {
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    const uint32_t L = e->n_layers;
+    EX(matvec_embed_rows(e->embed, e->mtp_tokens_dev, m, e->embed_rows));
+    const MvIn fc_in = mv_in(e->mtp_fc);
+    launch_mtp_pre(ctx->stream, e->embed_rows, hidden_rows, e->mtp_norm_e, e->mtp_norm_h, c.rms_norm_epsilon,
+                   c.hidden_size, m, &fc_in);
+    EX(matvec_stream_prepared(e->mtp_fc, 0, m));
+    CTOX_CUDA(ctx, cudaMemsetAsync(e->mtp_h, 0, (size_t)m * c.hidden_size * 4, ctx->stream));
+    const MvOut fc = mv_out(e->mtp_fc, m);
+    const MvIn lin = mv_in(e->w[L].in_fan);
+    launch_residual_norm_prep(ctx->stream, e->mtp_h, &fc, e->w[L].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
+                              nullptr, &lin);
+    EX(layer_body(e, L, e->mtp_h, m, abs_pos0, abs_pos0 - 1, e->mtp_page_table, e->mtp_norm, e->mtp_hidden,
+                  nullptr));
+    if (draft_slot >= 0) {
+        ctox_matvec *head = e->draft_head ? e->draft_head : e->lm_head;
+        EX(matvec_stream_pass(head, 0, e->mtp_hidden + (size_t)(m - 1) * c.hidden_size, CTOX_F32, 1,
+                              c.hidden_size));
+        matvec_finish_enqueue(head, 1, e->draft_logits, head->rows);
+        EX(argmax_enqueue(ctx, e->draft_logits, (uint32_t)head->rows, e->draft_head ? e->draft_ids : nullptr,
+                          e->tokens_dev + draft_slot, nullptr));
+    }
+    return CTOX_OK;
+}
+
+ctox_status upload_u32(ctox_exec *e, uint32_t *dst, const uint32_t *src, uint32_t n) {
+    ctox_ctx *ctx = e->ctx;
+    // pageable source: the copy is staged by the runtime before the call returns
+    CTOX_CUDA(ctx, cudaMemcpyAsync(dst, src, n * 4, cudaMemcpyHostToDevice, ctx->stream));
+    return CTOX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_exec_prefill(ctox_exec *e, const uint32_t *tokens, uint64_t n) {
+    if (!e || !tokens) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "prefill: executor is not warm");
+    if (n == 0 || n + 2 * kMaxPass > e->cfg.max_context_tokens)
+        return fail(ctx, CTOX_SHAPE, "prefill: %llu tokens do not fit the context", (unsigned long long)n);
+    for (uint64_t i = 0; i < n; ++i)
+        if (tokens[i] >= e->cfg.vocab_size) return fail(ctx, CTOX_SHAPE, "prefill: token %u out of range", tokens[i]);
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    EX(ctox_exec_reset_session(e));
+    const uint64_t consume = n - 1;  // the last token is the input of the first decode
+    for (uint64_t a = 0; a < consume; a += kMaxPass) {
+        const uint32_t m = (uint32_t)(consume - a < kMaxPass ? consume - a : kMaxPass);
+        EX(upload_u32(e, e->tokens_dev, tokens + a, m));
+        EX(target_pass(e, m, a));
+        EX(commit_positions(e, m, m));
+        for (uint32_t j = 0; j + 1 < m; ++j) e->hist_tokens[j] = tokens[a + 1 + j];
+        const bool last_chunk = a + m >= consume;
+        if (e->cfg.mtp_num_hidden_layers && !last_chunk) {
+            // keep the MTP cache exact: pairs (token p+1, final hidden p) of this chunk
+            EX(upload_u32(e, e->mtp_tokens_dev, tokens + a + 1, m));
+            EX(mtp_pass(e, m, a + 1, e->hist_hidden, -1));
+        }
+        CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `tokens` may be pageable host memory
+    }
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float temperature, uint64_t seed,
+                             int32_t force_accept, ctox_exec_step *step) {
+    if (!e || !step) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "decode: executor is not warm");
+    if (token >= c.vocab_size) return fail(ctx, CTOX_SHAPE, "decode: token %u out of range", token);
+    if (!std::isfinite(temperature) || temperature < 0.f)
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "temperature must be finite and non-negative");
+    if (e->position + 2 * kMaxPass >= c.max_context_tokens)
+        return fail(ctx, CTOX_SHAPE, "decode: context capacity exhausted at position %llu",
+                    (unsigned long long)e->position);
+    if (mtp_enabled && !c.mtp_num_hidden_layers)
+        return fail(ctx, CTOX_INVALID_STATE, "decode enabled MTP but the model has no MTP layer");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    memset(step, 0, sizeof *step);
+    const uint32_t k = (mtp_enabled && e->have_hidden && e->position > 0) ? c.max_draft_tokens : 0;
+    const uint64_t P = e->position;
+    uint32_t host_tokens[kMaxPass + 1] = {0};
+    host_tokens[0] = token;
+    EX(upload_u32(e, e->tokens_dev, host_tokens, 1));
+    if (k > 0) {
+        // catch-up over the pairs of the last block (true target hiddens), then the chained drafts
+        const uint32_t n = e->hist_n;
+        uint32_t mt[kMaxPass];
+        for (uint32_t j = 0; j + 1 < n; ++j) mt[j] = e->hist_tokens[j];
+        mt[n - 1] = token;
+        EX(upload_u32(e, e->mtp_tokens_dev, mt, n));
+        EX(mtp_pass(e, n, P - n + 1, e->hist_hidden, 1));
+        for (uint32_t i = 1; i < k; ++i) {
+            CTOX_CUDA(ctx, cudaMemcpyAsync(e->mtp_tokens_dev, e->tokens_dev + i, 4, cudaMemcpyDeviceToDevice,
+                                           ctx->stream));
+            const uint32_t prev_rows = i == 1 ? n : 1;
+            CTOX_CUDA(ctx, cudaMemcpyAsync(e->mtp_prev, e->mtp_hidden + (size_t)(prev_rows - 1) * c.hidden_size,
+                                           (size_t)c.hidden_size * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+            EX(mtp_pass(e, 1, P + i, e->mtp_prev, (int)(1 + i)));
+        }
+    }
+    const uint32_t m = k + 1;
+    EX(target_pass(e, m, P));
+    EX(matvec_stream_prepared(e->lm_head, 0, m));
+    int32_t parent[kMaxPass];
+    for (uint32_t i = 0; i < m; ++i) parent[i] = (int32_t)i - 1;
+    const float inv_t = temperature > 0.f ? 1.0f / temperature : 0.f;
+    const uint64_t step_id = e->step_counter++;
+    EX(head_verify_enqueue(e->lm_head, 0, m, m, parent, e->tokens_dev, inv_t, seed, step_id, c.vocab_size,
+                           e->keep_logits ? e->logits : nullptr));
+    ctox_spec_record *rec_dev = nullptr;
+    EX(head_accept_enqueue(ctx, m, parent, e->tokens_dev, inv_t, seed, step_id,
+                           force_accept < 0 ? -1 : (force_accept > (int32_t)k ? (int32_t)k : force_accept),
+                           &rec_dev));
+    EX(ensure_pinned(ctx, sizeof(ctox_spec_record) + 16));
+    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, rec_dev, sizeof(ctox_spec_record), cudaMemcpyDeviceToHost,
+                                   ctx->stream));
+    CTOX_CUDA(ctx, cudaMemcpyAsync((uint8_t *)ctx->pinned + sizeof(ctox_spec_record), ctx->dev_error, 4,
+                                   cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the one host read of the block
+    ctox_spec_record rec;
+    memcpy(&rec, ctx->pinned, sizeof rec);
+    int32_t dev_err;
+    memcpy(&dev_err, (uint8_t *)ctx->pinned + sizeof(ctox_spec_record), 4);
+    if (dev_err) {
+        cudaMemsetAsync(ctx->dev_error, 0, 4, ctx->stream);
+        return fail(ctx, CTOX_INVALID_STATE, "decode: device error %d", dev_err);
+    }
+    if (rec.status) return fail(ctx, CTOX_INVALID_STATE, "decode: the target produced a non-finite logit");
+    if (rec.n_emitted == 0 || rec.n_emitted > m)
+        return fail(ctx, CTOX_INVALID_STATE, "decode: malformed acceptance record");
+    const uint32_t n_acc = rec.n_emitted - 1;
+    EX(commit_positions(e, m, n_acc + 1));
+    for (uint32_t j = 0; j < n_acc; ++j) e->hist_tokens[j] = rec.emitted[j];
+    step->proposed_drafts = k;
+    step->n_accepted = n_acc;
+    step->verified_drafts = k == 0 ? 0 : (n_acc == k ? k : n_acc + 1);  // engine.rs:118-136
+    for (uint32_t j = 0; j < n_acc; ++j) step->accepted_draft_tokens[j] = rec.emitted[j];
+    step->next_token = rec.emitted[n_acc];
+    for (uint32_t j = 0; j < k; ++j) step->draft_tokens[j] = rec.node_token[1 + j];
+    for (uint32_t j = 0; j < m; ++j) step->target_tokens[j] = rec.node_argmax[j];
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_last_hidden(ctox_exec *e, float *out) {
+    if (!e || !out) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (!e->have_hidden || e->hist_n == 0) return fail(ctx, CTOX_INVALID_STATE, "no committed hidden state");
+    CTOX_CUDA(ctx, cudaMemcpyAsync(out, e->hist_hidden + (size_t)(e->hist_n - 1) * e->cfg.hidden_size,
+                                   (size_t)e->cfg.hidden_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_last_logits(ctox_exec *e, uint32_t position, float *out) {
+    if (!e || !out) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (!e->keep_logits || !e->logits || position >= kMaxPass)
+        return fail(ctx, CTOX_INVALID_STATE, "logits are not kept (ctox_exec_keep_logits) or position out of range");
+    CTOX_CUDA(ctx, cudaMemcpyAsync(out, e->logits + (size_t)position * e->cfg.vocab_size,
+                                   (size_t)e->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return CTOX_OK;
+}
+
+}  // extern "C"

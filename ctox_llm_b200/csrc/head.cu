@@ -32,9 +32,11 @@ struct NodeStat {
     uint32_t pad;
 };
 
+// parent[] travels by value; the node tokens stay in device memory because the drafts
+// of a speculative block are produced on the device and never visit the host.
 struct TreeDesc {
     int32_t parent[kMaxNodes];
-    uint32_t token[kMaxNodes];
+    const uint32_t *token;  // device, [n_nodes]
     uint32_t n_nodes;
 };
 
@@ -178,16 +180,25 @@ __global__ void k_head_merge(const NodeStat *__restrict__ cta_stats, uint32_t n_
 // sample of p_n restricted to non-children (greedy: the argmax).
 __global__ void k_spec_accept(const NodeStat *__restrict__ node_stats, const float *__restrict__ child_z,
                               TreeDesc tree, float inv_temperature, unsigned long long seed,
-                              unsigned long long step, ctox_spec_record *__restrict__ rec) {
+                              unsigned long long step, int force_accept, ctox_spec_record *__restrict__ rec) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     uint32_t count = 0, node = 0, status = 0;
+    for (uint32_t n = 0; n < tree.n_nodes; ++n) rec->node_token[n] = tree.token[n];
     for (uint32_t n = 0; n < tree.n_nodes; ++n) {
         rec->node_argmax[n] = (uint32_t)(node_stats[n].argmax & 0xffffffffull);
         if (node_stats[n].nonfinite) status = 1;
     }
     for (uint32_t n = tree.n_nodes; n < kMaxNodes; ++n) rec->node_argmax[n] = 0;
     for (uint32_t i = 0; i < kMaxNodes; ++i) rec->path[i] = -1;
-    if (status == 0) {
+    if (status == 0 && force_accept >= 0) {
+        // throughput buckets: accept exactly force_accept drafts of the chain, then the target's token
+        while (count < (uint32_t)force_accept && node + 1 < tree.n_nodes) {
+            rec->path[count] = (int32_t)(node + 1);
+            rec->emitted[count++] = tree.token[node + 1];
+            ++node;
+        }
+        rec->emitted[count++] = (uint32_t)(node_stats[node].argmax & 0xffffffffull);
+    } else if (status == 0) {
         for (;;) {
             const NodeStat st = node_stats[node];
             bool moved = false;
@@ -271,7 +282,8 @@ __global__ void __launch_bounds__(kHeadThreads) k_argmax_partial(const float *__
 // result[0] = token (mapped through row_ids when given, engine.rs:203-217), result[1] = status
 // (1 = a logit is not finite, kernels/cuda/q2q4_fused_matvec_sm86.cu:2583-2585).
 __global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t n_parts,
-                               const uint32_t *__restrict__ row_ids, uint32_t *__restrict__ result) {
+                               const uint32_t *__restrict__ row_ids, uint32_t *__restrict__ token_out,
+                               uint32_t *__restrict__ status_out) {
     if (threadIdx.x != 0) return;
     ArgmaxPartial a = parts[0];
     for (uint32_t i = 1; i < n_parts; ++i) {
@@ -279,8 +291,8 @@ __global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t
         a.nonfinite |= parts[i].nonfinite;
     }
     const uint32_t row = (uint32_t)(a.best & 0xffffffffull);
-    result[0] = row_ids ? row_ids[row] : row;
-    result[1] = a.nonfinite;
+    *token_out = row_ids ? row_ids[row] : row;
+    if (status_out) *status_out = a.nonfinite;
 }
 
 }  // namespace ctox
@@ -297,6 +309,7 @@ struct HeadScratch {
     ctox_spec_record *record;
     ArgmaxPartial *argmax_parts;  // [grid]
     uint32_t *argmax_result;      // [2]
+    uint32_t *tokens;             // [kMaxNodes] node tokens of the host-form verify call
 };
 
 ctox_status head_scratch(ctox_ctx *ctx, HeadScratch &hs) {
@@ -312,6 +325,7 @@ ctox_status head_scratch(ctox_ctx *ctx, HeadScratch &hs) {
     const size_t o_rec = take(sizeof(ctox_spec_record));
     const size_t o_ap = take(sizeof(ArgmaxPartial) * kHeadGridMax);
     const size_t o_ar = take(sizeof(uint32_t) * 2);
+    const size_t o_tok = take(sizeof(uint32_t) * kMaxNodes);
     ctox_status rc = ensure_scratch(ctx, off);
     if (rc) return rc;
     uint8_t *b = (uint8_t *)ctx->scratch;
@@ -321,6 +335,7 @@ ctox_status head_scratch(ctox_ctx *ctx, HeadScratch &hs) {
     hs.record = (ctox_spec_record *)(b + o_rec);
     hs.argmax_parts = (ArgmaxPartial *)(b + o_ap);
     hs.argmax_result = (uint32_t *)(b + o_ar);
+    hs.tokens = (uint32_t *)(b + o_tok);
     return CTOX_OK;
 }
 }  // namespace
@@ -339,7 +354,7 @@ ctox_status ctox_argmax_f32(ctox_ctx *ctx, const float *logits_dev, uint32_t n, 
     if (grid > kHeadGridMax) grid = kHeadGridMax;
     if (grid == 0) grid = 1;
     k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
-    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, result_dev);
+    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, result_dev, result_dev + 1);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
@@ -362,6 +377,70 @@ ctox_status ctox_argmax_f32_host(ctox_ctx *ctx, const float *logits_dev, uint32_
     return CTOX_OK;
 }
 
+}  // extern "C"
+
+namespace ctox {
+
+ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, uint32_t n_nodes,
+                                const int32_t *parent, const uint32_t *tokens_dev, float inv_t, uint64_t seed,
+                                uint64_t step, uint32_t rows, float *logits_out_dev) {
+    ctox_ctx *ctx = mv->ctx;
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    TreeDesc tree;
+    memset(&tree, 0, sizeof tree);
+    tree.n_nodes = n_nodes;
+    tree.token = tokens_dev;
+    for (uint32_t i = 0; i < n_nodes; ++i) tree.parent[i] = parent[i];
+    MatvecPart &p = mv->parts[0];
+    uint32_t grid = (rows + kHeadThreads - 1) / kHeadThreads;
+    if (grid > kHeadGridMax) grid = kHeadGridMax;
+    k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out,
+                                                        mv->bias, rows, p.slices, p.max_pieces, node0, npos,
+                                                        inv_t, seed, step, tree, hs.cta_stats, hs.child_z,
+                                                        logits_out_dev, (unsigned long long)mv->rows);
+    k_head_merge<<<1, 32, 0, ctx->stream>>>(hs.cta_stats, grid, node0, npos, hs.node_stats);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status head_accept_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *parent,
+                                const uint32_t *tokens_dev, float inv_t, uint64_t seed, uint64_t step,
+                                int force_accept, ctox_spec_record **record_dev) {
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    TreeDesc tree;
+    memset(&tree, 0, sizeof tree);
+    tree.n_nodes = n_nodes;
+    tree.token = tokens_dev;
+    for (uint32_t i = 0; i < n_nodes; ++i) tree.parent[i] = parent[i];
+    k_spec_accept<<<1, 32, 0, ctx->stream>>>(hs.node_stats, hs.child_z, tree, inv_t, seed, step, force_accept,
+                                            hs.record);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    *record_dev = hs.record;
+    return CTOX_OK;
+}
+
+ctox_status argmax_enqueue(ctox_ctx *ctx, const float *logits_dev, uint32_t n, const uint32_t *row_ids_dev,
+                           uint32_t *token_dev, uint32_t *status_dev) {
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    uint32_t grid = (n + kHeadThreads * 4 - 1) / (kHeadThreads * 4);
+    if (grid > kHeadGridMax) grid = kHeadGridMax;
+    if (grid == 0) grid = 1;
+    k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
+    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, token_dev, status_dev);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+}  // namespace ctox
+
+extern "C" {
+
 ctox_status ctox_lmhead_verify(ctox_matvec *mv, const void *hidden_dev, uint32_t hidden_dtype,
                                uint64_t hidden_stride, uint32_t n_nodes, const int32_t *parent,
                                const uint32_t *token, float temperature, uint64_t seed, uint64_t step,
@@ -381,16 +460,11 @@ ctox_status ctox_lmhead_verify(ctox_matvec *mv, const void *hidden_dev, uint32_t
     const uint32_t rows = vocab ? vocab : (uint32_t)mv->rows;
     if (rows > mv->rows) return fail(ctx, CTOX_SHAPE, "lmhead_verify: vocab %u exceeds %llu rows", vocab,
                                      (unsigned long long)mv->rows);
-    TreeDesc tree;
-    memset(&tree, 0, sizeof tree);
-    tree.n_nodes = n_nodes;
     if (parent[0] != -1) return fail(ctx, CTOX_SHAPE, "lmhead_verify: node 0 must be the root");
-    for (uint32_t i = 0; i < n_nodes; ++i) {
-        if (i && (parent[i] < 0 || (uint32_t)parent[i] >= i))
+    for (uint32_t i = 1; i < n_nodes; ++i) {
+        if (parent[i] < 0 || (uint32_t)parent[i] >= i)
             return fail(ctx, CTOX_SHAPE, "lmhead_verify: parent[%u] = %d is not an earlier node", i, parent[i]);
-        if (i && token[i] >= rows) return fail(ctx, CTOX_SHAPE, "lmhead_verify: draft token %u out of range", token[i]);
-        tree.parent[i] = parent[i];
-        tree.token[i] = token[i];
+        if (token[i] >= rows) return fail(ctx, CTOX_SHAPE, "lmhead_verify: draft token %u out of range", token[i]);
     }
     const float inv_t = temperature > 0.f ? 1.0f / temperature : 0.f;
     if (temperature > 0.f && !std::isfinite(inv_t))
@@ -399,29 +473,28 @@ ctox_status ctox_lmhead_verify(ctox_matvec *mv, const void *hidden_dev, uint32_t
     HeadScratch hs;
     ctox_status rc = head_scratch(ctx, hs);
     if (rc) return rc;
+    rc = ensure_pinned(ctx, sizeof(ctox_spec_record) + kMaxNodes * sizeof(uint32_t));
+    if (rc) return rc;
+    uint32_t *tok_pinned = (uint32_t *)((uint8_t *)ctx->pinned + sizeof(ctox_spec_record));
+    memcpy(tok_pinned, token, n_nodes * sizeof(uint32_t));
+    CTOX_CUDA(ctx, cudaMemcpyAsync(hs.tokens, tok_pinned, n_nodes * sizeof(uint32_t), cudaMemcpyHostToDevice,
+                                   ctx->stream));
     const uint32_t per_pass = matvec_positions_per_pass(mv);
     if (per_pass == 0) return fail(ctx, CTOX_MEMORY_BUDGET, "lm_head columns exceed the streaming kernel's budget");
-    MatvecPart &p = mv->parts[0];
-    uint32_t grid = (rows + kHeadThreads - 1) / kHeadThreads;
-    if (grid > kHeadGridMax) grid = kHeadGridMax;
     const size_t esz = hidden_dtype == CTOX_BF16 ? 2 : 4;
     for (uint32_t n0 = 0; n0 < n_nodes; n0 += per_pass) {
         const uint32_t npos = n_nodes - n0 < per_pass ? n_nodes - n0 : per_pass;
         rc = matvec_stream_pass(mv, 0, (const uint8_t *)hidden_dev + (size_t)n0 * hidden_stride * esz,
                                 hidden_dtype, npos, hidden_stride);
         if (rc) return rc;
-        k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.split[npos > 4 ? 1 : 0].pieces,
-                                                            mv->s_out, mv->bias, rows, p.slices,
-                                                            p.max_pieces, n0, npos, inv_t, seed, step, tree,
-                                                            hs.cta_stats, hs.child_z, logits_out_dev,
-                                                            (unsigned long long)mv->rows);
-        k_head_merge<<<1, 32, 0, ctx->stream>>>(hs.cta_stats, grid, n0, npos, hs.node_stats);
+        rc = head_verify_enqueue(mv, n0, npos, n_nodes, parent, hs.tokens, inv_t, seed, step, rows,
+                                 logits_out_dev);
+        if (rc) return rc;
     }
-    k_spec_accept<<<1, 32, 0, ctx->stream>>>(hs.node_stats, hs.child_z, tree, inv_t, seed, step, hs.record);
-    CTOX_CUDA(ctx, cudaGetLastError());
-    rc = ensure_pinned(ctx, sizeof(ctox_spec_record));
+    ctox_spec_record *rec_dev = nullptr;
+    rc = head_accept_enqueue(ctx, n_nodes, parent, hs.tokens, inv_t, seed, step, -1, &rec_dev);
     if (rc) return rc;
-    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, hs.record, sizeof(ctox_spec_record), cudaMemcpyDeviceToHost,
+    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, rec_dev, sizeof(ctox_spec_record), cudaMemcpyDeviceToHost,
                                    ctx->stream));
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     memcpy(record, ctx->pinned, sizeof(ctox_spec_record));

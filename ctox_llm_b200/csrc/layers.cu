@@ -1,0 +1,569 @@
+// Element-wise and attention kernels of the decode executor.
+//
+// Reference semantics: the scalar operators of reference.rs composed in the order of
+// decoder.rs (ArtifactDecoder::{decoder_mlp_residual :636-670, full_attention_residual_at
+// :687-800, linear_attention_residual :806-938, mtp_final_hidden :1009-1046}). Each kernel
+// consumes the raw partial sums of the preceding streamed matvec and emits the activation
+// fragments of the next one, so a matvec output never makes a round trip as a plain vector
+// unless a later step needs it.
+#include "layers.cuh"
+
+#include <cuda_bf16.h>
+
+#include "prep.cuh"
+
+namespace ctox {
+
+MvOut mv_out(ctox_matvec *mv, uint32_t npos) {
+    MatvecPart &p = mv->parts[0];
+    return MvOut{p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, p.slices, p.max_pieces};
+}
+MvIn mv_in(ctox_matvec *mv) {
+    return MvIn{mv->xfrag, mv->meta, mv->s_in, (uint32_t)mv->columns, mv->blocks_padded, mv->parts[0].dt};
+}
+
+__device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t pos) {
+    return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
+}
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+    for (unsigned w = 0; w < blockDim.x / 32; ++w) s += red[w];  // fixed order
+    return s;
+}
+
+// Writes the fragments of `vals` (one position, already normalised, not yet times s_in) for
+// all blocks of the next matvec; 16-lane groups take blocks round-robin. vals lives in shared
+// memory; columns beyond `n` (padding blocks) are zero.
+__device__ __forceinline__ void prep_from_smem(const float *vals, uint32_t n, uint32_t col0, int m, int npos,
+                                               const MvIn &next) {
+    const int i = threadIdx.x & 15;
+    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    const uint32_t b_first = col0 / 64, b_end = (col0 + n + 63) / 64;
+    for (uint32_t b = b_first + (threadIdx.x >> 4); b < b_end; b += blockDim.x >> 4) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t c = b * 64 + i * 4 + j;
+            v[j] = (c >= col0 && c - col0 < n) ? vals[c - col0] * (next.s_in ? next.s_in[c] : 1.0f) : 0.f;
+        }
+        prep_block(v, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+    }
+}
+
+// One CTA per position.
+__global__ void __launch_bounds__(512) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
+                                                          const float *__restrict__ w, float eps,
+                                                          uint32_t hidden, int npos, float *__restrict__ xn_out,
+                                                          MvIn next, int has_next) {
+    extern __shared__ float sh[];  // [hidden] + 32
+    float *vals = sh, *red = sh + hidden;
+    const int m = blockIdx.x;
+    float *hm = h + (size_t)m * hidden;
+    float sq = 0.f;
+    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = hm[c];
+        if (has_add) {
+            v += out_of(add, c, m);
+            hm[c] = v;
+        }
+        vals[c] = v;
+        sq += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(sq, red) / (float)hidden + eps);
+    __syncthreads();
+    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float xn = vals[c] * inv * (1.0f + w[c]);
+        vals[c] = xn;
+        if (xn_out) xn_out[(size_t)m * hidden + c] = xn;
+    }
+    __syncthreads();
+    if (has_next) {
+        prep_from_smem(vals, hidden, 0, m, npos, next);
+        // zero padding blocks beyond the matrix columns
+        const int i = threadIdx.x & 15;
+        const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+        for (uint32_t b = (hidden + 63) / 64 + (threadIdx.x >> 4); b < next.blocks_padded; b += blockDim.x >> 4) {
+            const float z[4] = {0.f, 0.f, 0.f, 0.f};
+            prep_block(z, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+        }
+    }
+}
+
+void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
+                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next) {
+    const size_t smem = (hidden + 32) * sizeof(float);
+    MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0};
+    MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
+    k_residual_norm_prep<<<m, 512, smem, st>>>(h, a, add != nullptr, w, eps, hidden, (int)m, xn_out, n,
+                                              next != nullptr);
+}
+
+// One CTA per position: [rmsnorm(embed) | rmsnorm(prev_hidden)] -> fragments (2 * hidden columns).
+__global__ void __launch_bounds__(512) k_mtp_pre(const float *__restrict__ embed_rows,
+                                               const float *__restrict__ prev_hidden,
+                                               const float *__restrict__ w_embed,
+                                               const float *__restrict__ w_hidden, float eps, uint32_t hidden,
+                                               int npos, MvIn next) {
+    extern __shared__ float sh[];  // [2 * hidden] + 32
+    float *vals = sh, *red = sh + 2 * hidden;
+    const int m = blockIdx.x;
+    for (int part = 0; part < 2; ++part) {
+        const float *src = (part ? prev_hidden : embed_rows) + (size_t)m * hidden;
+        const float *w = part ? w_hidden : w_embed;
+        float sq = 0.f;
+        for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+            const float v = src[c];
+            vals[part * hidden + c] = v;
+            sq += v * v;
+        }
+        const float inv = 1.0f / sqrtf(block_sum(sq, red) / (float)hidden + eps);
+        __syncthreads();
+        for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x)
+            vals[part * hidden + c] = vals[part * hidden + c] * inv * (1.0f + w[c]);
+        __syncthreads();
+    }
+    prep_from_smem(vals, 2 * hidden, 0, m, npos, next);
+    const int i = threadIdx.x & 15;
+    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    for (uint32_t b = (2 * hidden + 63) / 64 + (threadIdx.x >> 4); b < next.blocks_padded; b += blockDim.x >> 4) {
+        const float z[4] = {0.f, 0.f, 0.f, 0.f};
+        prep_block(z, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+    }
+}
+
+void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
+                    const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next) {
+    const size_t smem = (2 * hidden + 32) * sizeof(float);
+    k_mtp_pre<<<m, 512, smem, st>>>(embed_rows, prev_hidden, w_embed, w_hidden, eps, hidden, (int)m, *next);
+}
+
+// One 16-lane group per (position, 64-column block of the intermediate width).
+__global__ void k_swiglu_prep(MvOut gu, uint32_t inter, int npos, MvIn next) {
+    const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int i = threadIdx.x & 15;
+    const uint32_t nb = next.blocks_padded;
+    if (gid >= nb * (uint32_t)npos) return;
+    const uint32_t b = gid / npos;
+    const int m = gid % npos;
+    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t c = b * 64 + i * 4 + j;
+        v[j] = 0.f;
+        if (c < inter) {
+            const float gate = out_of(gu, c, m), up = out_of(gu, inter + c, m);
+            v[j] = silu_f(gate) * up * (next.s_in ? next.s_in[c] : 1.0f);
+        }
+    }
+    prep_block(v, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+}
+
+void launch_swiglu_prep(cudaStream_t st, const MvOut &gate_up, uint32_t inter, uint32_t m, const MvIn &next) {
+    const uint32_t groups = next.blocks_padded * m;
+    k_swiglu_prep<<<(groups * 16 + 255) / 256, 256, 0, st>>>(gate_up, inter, (int)m, next);
+}
+
+// ------------------------------------------------------------------ linear attention
+// Rows of the fused projection: [q | k | v] (conv channels), z, a, b (decoder.rs:832-867).
+// One thread per output row; the conv state of a channel is walked over the m positions
+// (causal_conv_silu_update, reference.rs:159-187: shift left, append, dot, SiLU). The
+// committed conv state is only read; the inputs are kept so that a commit of any prefix can
+// rebuild it.
+__global__ void k_linear_mid(MvOut fan, uint32_t key_width, uint32_t value_width, uint32_t value_heads,
+                             uint32_t conv_kernel, const float *__restrict__ conv_state,
+                             const float *__restrict__ conv_w, const float *__restrict__ a_log,
+                             const float *__restrict__ dt_bias, int npos, float *__restrict__ conv_in,
+                             float *__restrict__ q, float *__restrict__ k, float *__restrict__ v,
+                             float *__restrict__ z, float *__restrict__ log_decay, float *__restrict__ beta) {
+    const uint32_t channels = 2 * key_width + value_width;
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < channels) {
+        float st[8];
+        for (uint32_t j = 0; j < conv_kernel; ++j) st[j] = conv_state[(size_t)r * conv_kernel + j];
+        for (int m = 0; m < npos; ++m) {
+            const float x = out_of(fan, r, m);
+            conv_in[(size_t)m * channels + r] = x;
+            for (uint32_t j = 0; j + 1 < conv_kernel; ++j) st[j] = st[j + 1];
+            st[conv_kernel - 1] = x;
+            float sum = 0.f;
+            for (uint32_t j = 0; j < conv_kernel; ++j) sum += st[j] * conv_w[(size_t)r * conv_kernel + j];
+            const float y = silu_f(sum);
+            if (r < key_width)
+                q[(size_t)m * key_width + r] = y;
+            else if (r < 2 * key_width)
+                k[(size_t)m * key_width + (r - key_width)] = y;
+            else
+                v[(size_t)m * value_width + (r - 2 * key_width)] = y;
+        }
+    } else if (r < channels + value_width) {
+        const uint32_t c = r - channels;
+        for (int m = 0; m < npos; ++m) z[(size_t)m * value_width + c] = out_of(fan, r, m);
+    } else if (r < channels + value_width + value_heads) {
+        const uint32_t hh = r - channels - value_width;
+        for (int m = 0; m < npos; ++m) {
+            const float x = out_of(fan, r, m) + dt_bias[hh];
+            const float sp = x > 20.0f ? x : log1pf(expf(x));  // decoder.rs:29-35
+            log_decay[(size_t)m * value_heads + hh] = -expf(a_log[hh]) * sp;
+        }
+    } else if (r < channels + value_width + 2 * value_heads) {
+        const uint32_t hh = r - channels - value_width - value_heads;
+        for (int m = 0; m < npos; ++m)
+            beta[(size_t)m * value_heads + hh] = 1.0f / (1.0f + expf(-out_of(fan, r, m)));
+    }
+}
+
+void launch_linear_mid(cudaStream_t st, const MvOut &fan, uint32_t key_width, uint32_t value_width,
+                       uint32_t value_heads, uint32_t conv_kernel, const float *conv_state,
+                       const float *conv_w, const float *a_log, const float *dt_bias, uint32_t m,
+                       float *conv_in, float *q, float *k, float *v, float *z, float *log_decay, float *beta) {
+    const uint32_t rows = 2 * key_width + 2 * value_width + 2 * value_heads;
+    k_linear_mid<<<(rows + 127) / 128, 128, 0, st>>>(fan, key_width, value_width, value_heads, conv_kernel,
+                                                    conv_state, conv_w, a_log, dt_bias, (int)m, conv_in, q, k,
+                                                    v, z, log_decay, beta);
+}
+
+__global__ void k_conv_commit(float *__restrict__ conv_state, const float *__restrict__ conv_in,
+                              uint32_t channels, uint32_t conv_kernel, uint32_t n) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= channels) return;
+    float st[8];
+    for (uint32_t j = 0; j < conv_kernel; ++j) st[j] = conv_state[(size_t)r * conv_kernel + j];
+    for (uint32_t m = 0; m < n; ++m) {
+        for (uint32_t j = 0; j + 1 < conv_kernel; ++j) st[j] = st[j + 1];
+        st[conv_kernel - 1] = conv_in[(size_t)m * channels + r];
+    }
+    for (uint32_t j = 0; j < conv_kernel; ++j) conv_state[(size_t)r * conv_kernel + j] = st[j];
+}
+
+void launch_conv_commit(cudaStream_t st, float *conv_state, const float *conv_in, uint32_t channels,
+                        uint32_t conv_kernel, uint32_t n) {
+    k_conv_commit<<<(channels + 127) / 128, 128, 0, st>>>(conv_state, conv_in, channels, conv_kernel, n);
+}
+
+// rms_norm_gated (reference.rs:66-93) per (position, value head) of 128 values: one warp,
+// four values per lane, two 64-column blocks of the out_proj input.
+__global__ void k_gated_norm_prep(const float *__restrict__ core, const float *__restrict__ z,
+                                  const float *__restrict__ w, float eps, uint32_t value_heads, int npos,
+                                  MvIn next) {
+    const uint32_t wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (wid >= value_heads * (uint32_t)npos) return;
+    const uint32_t head = wid / npos;
+    const int m = wid % npos;
+    const size_t off = ((size_t)m * value_heads + head) * 128 + lane * 4;
+    const float4 c = *reinterpret_cast<const float4 *>(core + off);
+    const float4 g = *reinterpret_cast<const float4 *>(z + off);
+    float sq = c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float inv = 1.0f / sqrtf(sq / 128.0f + eps);
+    const uint32_t col = head * 128 + lane * 4;
+    const float cs[4] = {c.x, c.y, c.z, c.w}, gs[4] = {g.x, g.y, g.z, g.w};
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        v[j] = cs[j] * inv * w[lane * 4 + j] * silu_f(gs[j]) * (next.s_in ? next.s_in[col + j] : 1.0f);
+    const unsigned gmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+    prep_block(v, lane & 15, gmask, (int)(head * 2 + (lane >> 4)), m, npos, next.dt, next.xfrag, next.meta);
+}
+
+void launch_gated_norm_prep(cudaStream_t st, const float *core, const float *z, const float *w, float eps,
+                            uint32_t value_heads, uint32_t value_dim, uint32_t m, const MvIn &next) {
+    (void)value_dim;  // 128: checked by the executor
+    const uint32_t warps = value_heads * m;
+    k_gated_norm_prep<<<(warps * 32 + 255) / 256, 256, 0, st>>>(core, z, w, eps, value_heads, (int)m, next);
+}
+
+// ------------------------------------------------------------------ full attention
+template <typename T>
+__device__ __forceinline__ float kv_load(const T *p);
+template <>
+__device__ __forceinline__ float kv_load<float>(const float *p) { return *p; }
+template <>
+__device__ __forceinline__ float kv_load<__nv_bfloat16>(const __nv_bfloat16 *p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void kv_store(T *p, float v);
+template <>
+__device__ __forceinline__ void kv_store<float>(float *p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void kv_store<__nv_bfloat16>(__nv_bfloat16 *p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ size_t kv_slot(const uint32_t *page_table, uint32_t page_tokens, uint64_t t) {
+    return (size_t)page_table[t / page_tokens] * page_tokens + (size_t)(t % page_tokens);
+}
+
+// One warp per (position, head) over the fused [q+gate | k | v] projection (decoder.rs:717-772):
+// q rows are [query(hd), gate(hd)] per head; q and k get the (1+w) RMS norm per head and the
+// non-interleaved partial RoPE (reference.rs:115-155); k and v go to the cache slot of the position.
+template <typename T>
+__global__ void k_attn_pre(MvOut fan, AttnGeom g, const float *__restrict__ q_norm,
+                           const float *__restrict__ k_norm, uint64_t rope_position, uint64_t cache_slot,
+                           int npos, float *__restrict__ q, float *__restrict__ gate, T *__restrict__ k_cache,
+                           T *__restrict__ v_cache, const uint32_t *__restrict__ page_table,
+                           uint32_t page_tokens) {
+    extern __shared__ float sh[];  // [warps][head_dim]
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t wid = blockIdx.x * (blockDim.x >> 5) + warp;
+    const uint32_t heads_total = g.q_heads + 2 * g.kv_heads;
+    if (wid >= heads_total * (uint32_t)npos) return;
+    const uint32_t hi = wid % heads_total;
+    const int m = wid / heads_total;
+    const uint32_t hd = g.head_dim;
+    float *buf = sh + warp * hd;
+    const uint32_t k_row0 = g.q_heads * 2 * hd, v_row0 = k_row0 + g.kv_heads * hd;
+    const size_t slot = kv_slot(page_table, page_tokens, cache_slot + m);
+    if (hi >= g.q_heads + g.kv_heads) {  // value head: plain copy into the cache
+        const uint32_t kh = hi - g.q_heads - g.kv_heads;
+        for (uint32_t d = lane; d < hd; d += 32)
+            kv_store(v_cache + (slot * g.kv_heads + kh) * hd + d, out_of(fan, v_row0 + kh * hd + d, m));
+        return;
+    }
+    const bool is_q = hi < g.q_heads;
+    const uint32_t head = is_q ? hi : hi - g.q_heads;
+    const uint32_t row0 = is_q ? head * 2 * hd : k_row0 + head * hd;
+    const float *w = is_q ? q_norm : k_norm;
+    float sq = 0.f;
+    for (uint32_t d = lane; d < hd; d += 32) {
+        const float v = out_of(fan, row0 + d, m);
+        buf[d] = v;
+        sq += v * v;
+        if (is_q) gate[((size_t)m * g.q_heads + head) * hd + d] = out_of(fan, row0 + hd + d, m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float inv = 1.0f / sqrtf(sq / (float)hd + g.eps);
+    __syncwarp();
+    for (uint32_t d = lane; d < hd; d += 32) buf[d] = buf[d] * inv * (1.0f + w[d]);
+    __syncwarp();
+    const uint32_t half = g.rotary_dim / 2;
+    const float pos = (float)(rope_position + (uint64_t)m);
+    for (uint32_t d = lane; d < hd; d += 32) {
+        float out = buf[d];
+        if (d < g.rotary_dim) {
+            const uint32_t i = d < half ? d : d - half;
+            const float inv_freq = powf(g.theta, -((float)(2 * i)) / (float)g.rotary_dim);
+            const float ang = pos * inv_freq, cs = cosf(ang), sn = sinf(ang);
+            out = d < half ? buf[d] * cs - buf[d + half] * sn : buf[d] * cs + buf[d - half] * sn;
+        }
+        if (is_q)
+            q[((size_t)m * g.q_heads + head) * hd + d] = out;
+        else
+            kv_store(k_cache + (slot * g.kv_heads + head) * hd + d, out);
+    }
+}
+
+void launch_attn_pre(cudaStream_t st, const MvOut &fan, const AttnGeom &g, const float *q_norm,
+                     const float *k_norm, uint64_t rope_position, uint64_t cache_slot, uint32_t m, float *q,
+                     float *gate, void *k_cache, void *v_cache, int kv_bf16, const uint32_t *page_table,
+                     uint32_t page_tokens) {
+    const uint32_t warps = (g.q_heads + 2 * g.kv_heads) * m;
+    const uint32_t wpb = 4;
+    const size_t smem = wpb * g.head_dim * sizeof(float);
+    const uint32_t grid = (warps + wpb - 1) / wpb;
+    if (kv_bf16)
+        k_attn_pre<__nv_bfloat16><<<grid, wpb * 32, smem, st>>>(fan, g, q_norm, k_norm, rope_position, cache_slot,
+                                                                (int)m, q, gate, (__nv_bfloat16 *)k_cache,
+                                                                (__nv_bfloat16 *)v_cache, page_table, page_tokens);
+    else
+        k_attn_pre<float><<<grid, wpb * 32, smem, st>>>(fan, g, q_norm, k_norm, rope_position, cache_slot, (int)m, q,
+                                                        gate, (float *)k_cache, (float *)v_cache, page_table,
+                                                        page_tokens);
+}
+
+constexpr int kAttnTile = 32;      // tokens per tile
+constexpr int kAttnThreads = 256;
+
+// grouped_query_attention (reference.rs:420-499) for the m query positions of one KV head over
+// one split of the context, flash-decoding style: per tile of 32 tokens the K rows are staged in
+// shared memory, every warp scores its queries against the 32 tokens (lane = token), keeps the
+// running max / sum per query, and each thread then owns one output dimension of all queries.
+// Partial (max, sum, unnormalised output) go to the workspace; k_attn_combine_prep merges them.
+template <typename T, int NQMAX>
+__global__ void __launch_bounds__(kAttnThreads) k_attention(
+    AttnGeom g, const float *__restrict__ q, const T *__restrict__ k_cache, const T *__restrict__ v_cache,
+    const uint32_t *__restrict__ page_table, uint32_t page_tokens, uint64_t cache_slot, int npos,
+    uint32_t splits, float *__restrict__ ws) {
+    extern __shared__ __align__(16) uint8_t smraw[];
+    const uint32_t hd = g.head_dim, G = g.q_heads / g.kv_heads, NQ = G * npos;
+    const uint32_t kh = blockIdx.x / splits, sp = blockIdx.x % splits;
+    const uint32_t kstride = hd + 16 / sizeof(T);  // padded row: conflict-free 16-byte reads
+    float *q_s = reinterpret_cast<float *>(smraw);                       // [NQ][hd]
+    float *p_s = q_s + NQMAX * hd;                                        // [NQ][tile]
+    float *m_run = p_s + NQMAX * kAttnTile, *l_run = m_run + NQMAX, *alpha = l_run + NQMAX;
+    T *k_s = reinterpret_cast<T *>(alpha + NQMAX);                        // [tile][kstride]
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t total = cache_slot + (uint64_t)npos;  // tokens visible to the last query
+    const uint64_t tiles = (total + kAttnTile - 1) / kAttnTile;
+    const uint64_t tile_beg = tiles * sp / splits, tile_end = tiles * (sp + 1) / splits;
+    for (uint32_t i = tid; i < NQ * hd; i += kAttnThreads) {
+        const uint32_t qi = i / hd, d = i % hd, mi = qi / G, gq = qi % G;
+        q_s[i] = q[((size_t)mi * g.q_heads + kh * G + gq) * hd + d];
+    }
+    if (tid < NQMAX) {
+        m_run[tid] = -INFINITY;
+        l_run[tid] = 0.f;
+    }
+    float o[NQMAX];
+#pragma unroll
+    for (int i = 0; i < NQMAX; ++i) o[i] = 0.f;
+    const float scale = 1.0f / sqrtf((float)hd);
+    __syncthreads();
+    for (uint64_t tile = tile_beg; tile < tile_end; ++tile) {
+        const uint64_t t0 = tile * kAttnTile;
+        // stage K rows (16-byte chunks, coalesced)
+        const uint32_t chunks_per_row = hd * sizeof(T) / 16;
+        for (uint32_t c = tid; c < kAttnTile * chunks_per_row; c += kAttnThreads) {
+            const uint32_t r = c / chunks_per_row, cc = c % chunks_per_row;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (t0 + r < total) {
+                const size_t slot = kv_slot(page_table, page_tokens, t0 + r);
+                v = *reinterpret_cast<const uint4 *>(reinterpret_cast<const uint8_t *>(
+                        k_cache + (slot * g.kv_heads + kh) * hd) + cc * 16);
+            }
+            *reinterpret_cast<uint4 *>(reinterpret_cast<uint8_t *>(k_s + r * kstride) + cc * 16) = v;
+        }
+        __syncthreads();
+        // scores + running softmax: warp w takes queries w, w+8, ...; lane = token of the tile
+        const uint64_t t = t0 + lane;
+        for (uint32_t qi = warp; qi < NQ; qi += kAttnThreads / 32) {
+            const uint32_t mi = qi / G;
+            float s = 0.f;
+            const T *kr = k_s + lane * kstride;
+            const float *qr = q_s + qi * hd;
+            for (uint32_t d = 0; d < hd; ++d) s += qr[d] * kv_load(kr + d);
+            s *= scale;
+            const bool valid = t < total && t <= cache_slot + mi;  // causal inside the pass
+            if (!valid) s = -INFINITY;
+            float tmax = s;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, of));
+            const float m_old = m_run[qi], m_new = fmaxf(m_old, tmax);
+            const float p = (valid && m_new > -INFINITY) ? expf(s - m_new) : 0.f;
+            float psum = p;
+#pragma unroll
+            for (int of = 16; of > 0; of >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, of);
+            p_s[qi * kAttnTile + lane] = p;
+            if (lane == 0) {
+                const float a = m_old > -INFINITY ? expf(m_old - m_new) : 0.f;
+                alpha[qi] = a;
+                l_run[qi] = l_run[qi] * a + psum;
+                m_run[qi] = m_new;
+            }
+        }
+        __syncthreads();
+        // output: thread d owns dimension d of every query
+        if (tid < hd) {
+#pragma unroll
+            for (int qi = 0; qi < NQMAX; ++qi)
+                if ((uint32_t)qi < NQ) o[qi] *= alpha[qi];
+            for (uint32_t r = 0; r < (uint32_t)kAttnTile && t0 + r < total; ++r) {
+                const size_t slot = kv_slot(page_table, page_tokens, t0 + r);
+                const float vv = kv_load(v_cache + (slot * g.kv_heads + kh) * hd + tid);
+#pragma unroll
+                for (int qi = 0; qi < NQMAX; ++qi)
+                    if ((uint32_t)qi < NQ) o[qi] += p_s[qi * kAttnTile + r] * vv;
+            }
+        }
+        __syncthreads();
+    }
+    // workspace: [kv head][split][query][hd + 2]
+    float *out = ws + ((size_t)(kh * splits + sp) * NQ) * (hd + 2);
+    if (tid < hd) {
+#pragma unroll
+        for (int qi = 0; qi < NQMAX; ++qi)
+            if ((uint32_t)qi < NQ) out[(size_t)qi * (hd + 2) + tid] = o[qi];
+    }
+    if (tid < NQ) {
+        out[(size_t)tid * (hd + 2) + hd] = m_run[tid];
+        out[(size_t)tid * (hd + 2) + hd + 1] = l_run[tid];
+    }
+}
+
+// Merge of the splits, sigmoid gate (reference.rs:502-515) and fragments for o_proj: one
+// 16-lane group per (position, query head, 64-dimension block).
+__global__ void k_attn_combine_prep(AttnGeom g, const float *__restrict__ ws, const float *__restrict__ gate,
+                                    int npos, uint32_t splits, MvIn next) {
+    const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int i = threadIdx.x & 15;
+    const uint32_t hd = g.head_dim, bph = hd / 64, G = g.q_heads / g.kv_heads, NQ = G * npos;
+    if (gid >= (uint32_t)npos * g.q_heads * bph) return;
+    const uint32_t blk = gid % bph, hq = (gid / bph) % g.q_heads;
+    const int m = gid / (bph * g.q_heads);
+    const uint32_t kh = hq / G, qi = m * G + hq % G;
+    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    float mx = -INFINITY;
+    for (uint32_t sp = 0; sp < splits; ++sp)
+        mx = fmaxf(mx, ws[((size_t)(kh * splits + sp) * NQ + qi) * (hd + 2) + hd]);
+    float den = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (uint32_t sp = 0; sp < splits; ++sp) {
+        const float *r = ws + ((size_t)(kh * splits + sp) * NQ + qi) * (hd + 2);
+        const float ms = r[hd];
+        if (!(ms > -INFINITY)) continue;
+        const float wgt = expf(ms - mx);
+        den += r[hd + 1] * wgt;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[j] += r[blk * 64 + i * 4 + j] * wgt;
+    }
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t d = blk * 64 + i * 4 + j, col = hq * hd + d;
+        const float gt = gate[((size_t)m * g.q_heads + hq) * hd + d];
+        v[j] = acc[j] / den * (1.0f / (1.0f + expf(-gt))) * (next.s_in ? next.s_in[col] : 1.0f);
+    }
+    prep_block(v, i, gmask, (int)(hq * bph + blk), m, npos, next.dt, next.xfrag, next.meta);
+}
+
+size_t attn_workspace_bytes(const AttnGeom &g, uint32_t m, uint32_t max_splits) {
+    return (size_t)g.q_heads * m * max_splits * (g.head_dim + 2) * sizeof(float);
+}
+
+template <typename T, int NQMAX>
+static void launch_attention_t(cudaStream_t st, const AttnGeom &g, const float *q, const void *k_cache,
+                               const void *v_cache, const uint32_t *page_table, uint32_t page_tokens,
+                               uint64_t cache_slot, uint32_t m, uint32_t splits, float *ws) {
+    const size_t smem = (size_t)NQMAX * g.head_dim * 4 + (size_t)NQMAX * kAttnTile * 4 + 3 * NQMAX * 4 +
+                        (size_t)kAttnTile * (g.head_dim + 16 / sizeof(T)) * sizeof(T) + 16;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaFuncSetAttribute(k_attention<T, NQMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
+    }
+    k_attention<T, NQMAX><<<g.kv_heads * splits, kAttnThreads, smem, st>>>(
+        g, q, (const T *)k_cache, (const T *)v_cache, page_table, page_tokens, cache_slot, (int)m, splits, ws);
+}
+
+void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const float *gate,
+                      const void *k_cache, const void *v_cache, int kv_bf16, const uint32_t *page_table,
+                      uint32_t page_tokens, uint64_t cache_slot, uint32_t m, uint32_t splits, float *workspace,
+                      const MvIn &next) {
+    const uint32_t nq = g.q_heads / g.kv_heads * m;
+#define CTOX_ATTN(T)                                                                                        \
+    do {                                                                                                    \
+        if (nq <= 8)                                                                                        \
+            launch_attention_t<T, 8>(st, g, q, k_cache, v_cache, page_table, page_tokens, cache_slot, m,    \
+                                     splits, workspace);                                                    \
+        else if (nq <= 24)                                                                                  \
+            launch_attention_t<T, 24>(st, g, q, k_cache, v_cache, page_table, page_tokens, cache_slot, m,   \
+                                      splits, workspace);                                                   \
+        else                                                                                                \
+            launch_attention_t<T, 48>(st, g, q, k_cache, v_cache, page_table, page_tokens, cache_slot, m,   \
+                                      splits, workspace);                                                   \
+    } while (0)
+    if (kv_bf16)
+        CTOX_ATTN(__nv_bfloat16);
+    else
+        CTOX_ATTN(float);
+#undef CTOX_ATTN
+    const uint32_t groups = m * g.q_heads * (g.head_dim / 64);
+    k_attn_combine_prep<<<(groups * 16 + 255) / 256, 256, 0, st>>>(g, workspace, gate, (int)m, splits, next);
+}
+
+}  // namespace ctox

@@ -1,0 +1,68 @@
+// Element-wise and attention kernels of the decode executor (layers.cu), as host launchers.
+// Every tensor is device memory; `m` counts the positions of the current pass (1..8).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "matvec.cuh"
+
+namespace ctox {
+
+// Output of a streamed matvec, still as partial sums (consumers add them up themselves).
+struct MvOut {
+    const float *partial;
+    const uint8_t *pieces;
+    const float *s_out;
+    uint32_t slices, max_pieces;
+};
+// Input of the next matvec: where to write the activation fragments.
+struct MvIn {
+    uint8_t *xfrag;
+    float2 *meta;
+    const float *s_in;
+    uint32_t columns, blocks_padded;
+    int dt;
+};
+
+MvOut mv_out(ctox_matvec *mv, uint32_t npos);
+MvIn mv_in(ctox_matvec *mv);
+
+struct AttnGeom {
+    uint32_t q_heads, kv_heads, head_dim, rotary_dim;
+    float theta, eps;
+};
+
+// h[m] (+= matvec output) ; xn = rmsnorm_1p(h[m], w) ; optional copy of xn ; fragments of xn * s_in.
+void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
+                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next);
+// MTP input: fragments of concat(rmsnorm_1p(embed(tok[m])), rmsnorm_1p(prev_hidden[m])) * s_in.
+void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
+                    const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next);
+// silu(gate) * up of a fused [gate; up] projection -> fragments for the down projection.
+void launch_swiglu_prep(cudaStream_t st, const MvOut &gate_up, uint32_t inter, uint32_t m, const MvIn &next);
+// Linear-attention middle: conv + SiLU over [q|k|v], z, decay and beta from a, b.
+void launch_linear_mid(cudaStream_t st, const MvOut &fan, uint32_t key_width, uint32_t value_width,
+                       uint32_t value_heads, uint32_t conv_kernel, const float *conv_state,
+                       const float *conv_w, const float *a_log, const float *dt_bias, uint32_t m,
+                       float *conv_in, float *q, float *k, float *v, float *z, float *log_decay, float *beta);
+// conv_state <- conv_state shifted by the first n inputs of the pass (commit of n positions).
+void launch_conv_commit(cudaStream_t st, float *conv_state, const float *conv_in, uint32_t channels,
+                        uint32_t conv_kernel, uint32_t n);
+// rms_norm_gated(core, z) per value head -> fragments for out_proj.
+void launch_gated_norm_prep(cudaStream_t st, const float *core, const float *z, const float *w, float eps,
+                            uint32_t value_heads, uint32_t value_dim, uint32_t m, const MvIn &next);
+// Full attention, before the cache: split q/gate, per-head norms, partial RoPE, K/V append.
+void launch_attn_pre(cudaStream_t st, const MvOut &fan, const AttnGeom &g, const float *q_norm,
+                     const float *k_norm, uint64_t rope_position, uint64_t cache_slot, uint32_t m, float *q,
+                     float *gate, void *k_cache, void *v_cache, int kv_bf16, const uint32_t *page_table,
+                     uint32_t page_tokens);
+// Causal GQA over the paged cache for m query positions, split over the context; then the
+// sigmoid gate and the fragments for o_proj.
+size_t attn_workspace_bytes(const AttnGeom &g, uint32_t m, uint32_t max_splits);
+void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const float *gate,
+                      const void *k_cache, const void *v_cache, int kv_bf16, const uint32_t *page_table,
+                      uint32_t page_tokens, uint64_t cache_slot, uint32_t m, uint32_t splits, float *workspace,
+                      const MvIn &next);
+
+}  // namespace ctox

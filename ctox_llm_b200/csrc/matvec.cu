@@ -28,6 +28,7 @@
 #include "common.cuh"
 #include "layout.cuh"
 #include "matvec.cuh"
+#include "prep.cuh"
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -199,7 +200,6 @@ __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_
     const int i = threadIdx.x & 15;
     if (gid >= blocks_padded * npos) return;  // whole 16-lane groups leave together
     const int b = gid / npos, m = gid % npos;
-    const int nc = 2 * npos;
     float v[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -214,38 +214,9 @@ __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_
         }
         v[j] = xv;
     }
-    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
     // the 16 lanes of a group are lanes 0-15 or 16-31 of a warp
     const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, o));
-    const int ne = norm_exponent(dt);
-    int e = (int)((__float_as_uint(amax) >> 23) & 0xff) - 127;
-    if (!(amax > 0.f) || e > 127) e = ne;  // zero block or non-finite input: factor 1
-    e = max(e, -100);
-    const float f = __uint_as_float((uint32_t)(ne - e + 127) << 23);
-    const float inv = __uint_as_float((uint32_t)(e - ne + 127) << 23);
-    float sum = 0.f;
-    uint8_t *base = xfrag + (size_t)b * nc * 128;
-    const int t = i >> 2;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int q = (i & 3) * 4 + j;
-        const float sv = v[j] * f;
-        const __half hi = __float2half_rn(sv);
-        const __half lo = __float2half_rn(sv - __half2float(hi));
-        sum += __half2float(hi) + __half2float(lo);
-        const float mul = column_multiplier(dt, q);  // power of two: exact
-        const int pos = inv_perm(dt, q);
-        uint8_t *p = base + (pos >> 3) * (nc * 64) + t * 16 + (pos & 7) * 2;
-        *reinterpret_cast<__half *>(p + (2 * m) * 64) = __float2half_rn(__half2float(hi) * mul);
-        *reinterpret_cast<__half *>(p + (2 * m + 1) * 64) = __float2half_rn(__half2float(lo) * mul);
-    }
-#pragma unroll
-    for (int o = 1; o < 16; o <<= 1) sum += __shfl_xor_sync(gmask, sum, o);
-    if (i == 0)
-        meta[b * npos + m] =
-            make_float2(-code_offset(dt) * code_scale(dt) * sum, inv * code_unit(dt) / code_scale(dt));
+    prep_block(v, i, gmask, b, m, npos, dt, xfrag, meta);
 }
 
 // ------------------------------------------------------------------ streaming kernel
@@ -805,6 +776,8 @@ uint32_t choose_slices(uint32_t kst) {
     return 1;
 }
 
+// host_bytes != NULL: the canonical bytes are uploaded; otherwise part.canon already holds them
+// on the device (tracked allocation of nbytes, ownership taken).
 ctox_status prepare_part(ctox_ctx *ctx, ctox_matvec *mv, MatvecPart &part, const uint8_t *host_bytes,
                          size_t nbytes, uint32_t flags) {
     const int stb = part.dt ? Fmt<1>::kSuperTileBytes : Fmt<0>::kSuperTileBytes;
@@ -814,9 +787,12 @@ ctox_status prepare_part(ctox_ctx *ctx, ctox_matvec *mv, MatvecPart &part, const
     part.slices = choose_slices(kst);
     part.kst_s = kst / part.slices;
     part.canon_bytes = nbytes;
-    ctox_status rc = dev_alloc(ctx, (void **)&part.canon, nbytes);
-    if (rc) return rc;
-    CTOX_CUDA(ctx, cudaMemcpyAsync(part.canon, host_bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    ctox_status rc = CTOX_OK;
+    if (host_bytes) {
+        rc = dev_alloc(ctx, (void **)&part.canon, nbytes);
+        if (rc) return rc;
+        CTOX_CUDA(ctx, cudaMemcpyAsync(part.canon, host_bytes, nbytes, cudaMemcpyHostToDevice, ctx->stream));
+    }
     const uint64_t tiles = (uint64_t)part.pairs * 2 * kst;
     part.prep_bytes = (size_t)tiles * stb;
     rc = dev_alloc(ctx, (void **)&part.prep, part.prep_bytes);
@@ -985,6 +961,75 @@ ctox_status matvec_stream_pass(ctox_matvec *mv, size_t part_index, const void *x
         x, x_dtype == CTOX_BF16, (long long)x_stride, mv->s_in, (int)mv->columns, (int)mv->blocks_padded,
         (int)npos, p.dt, mv->xfrag, mv->meta);
     return matvec_stream_prepared(mv, part_index, npos);
+}
+
+ctox_status matvec_create_device(ctox_ctx *ctx, int dt, uint64_t rows, uint64_t columns, uint8_t *canon,
+                                 size_t canon_bytes, float *s_in, float *s_out, uint32_t flags,
+                                 ctox_matvec **out) {
+    *out = nullptr;
+    ctox_status rc = set_smem_attr(ctx);
+    if (rc) return rc;
+    ctox_matvec *mv = new ctox_matvec();
+    mv->ctx = ctx;
+    mv->rows = rows;
+    mv->columns = columns;
+    mv->packed_bytes = canon_bytes;
+    mv->blocks = (uint32_t)(columns / kBlockLen);
+    mv->blocks_padded = (mv->blocks + kTileBlocks - 1) / kTileBlocks * kTileBlocks;
+    mv->activation = CTOX_ACT_IDENTITY;
+    mv->s_in = s_in;
+    mv->s_out = s_out;
+    mv->device_bytes += (s_in ? columns * 4 : 0) + (s_out ? rows * 4 : 0);
+    MatvecPart part;
+    part.dt = dt;
+    part.rows = rows;
+    part.canon = canon;
+    mv->parts.push_back(part);
+    rc = prepare_part(ctx, mv, mv->parts.back(), nullptr, canon_bytes, flags);
+    if (!rc) {
+        mv->xfrag_bytes = (size_t)mv->blocks_padded * 2 * kMaxPosPerPass * 128;
+        rc = dev_alloc(ctx, (void **)&mv->xfrag, mv->xfrag_bytes);
+    }
+    if (!rc) {
+        mv->meta_bytes = (size_t)mv->blocks_padded * kMaxPosPerPass * sizeof(float2);
+        rc = dev_alloc(ctx, (void **)&mv->meta, mv->meta_bytes);
+    }
+    if (!rc) {
+        mv->device_bytes += mv->xfrag_bytes + mv->meta_bytes;
+        rc = check_device_error(ctx, "prepare");
+    }
+    if (rc) {
+        free_matvec(mv);
+        return rc;
+    }
+    *out = mv;
+    return CTOX_OK;
+}
+
+ctox_status matvec_embed_rows(ctox_matvec *mv, const uint32_t *row_ids_dev, uint32_t n, float *out) {
+    ctox_ctx *ctx = mv->ctx;
+    MatvecPart &p = mv->parts[0];
+    if (!p.canon)
+        return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "row gather needs CTOX_PREPARE_KEEP_CANONICAL at prepare");
+    dim3 grid((unsigned)((mv->columns / 2 + 127) / 128), n);
+    if (p.dt)
+        k_recovered_rows<1><<<grid, 128, 0, ctx->stream>>>(p.canon, row_ids_dev, mv->s_in, mv->s_out, 1.0f, out,
+                                                           (uint32_t)mv->columns, n, (uint32_t)mv->rows,
+                                                           ctx->dev_error);
+    else
+        k_recovered_rows<0><<<grid, 128, 0, ctx->stream>>>(p.canon, row_ids_dev, mv->s_in, mv->s_out, 1.0f, out,
+                                                           (uint32_t)mv->columns, n, (uint32_t)mv->rows,
+                                                           ctx->dev_error);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+void matvec_finish_enqueue(ctox_matvec *mv, uint32_t npos, float *y, uint64_t y_stride) {
+    MatvecPart &p = mv->parts[0];
+    const unsigned n_out = (unsigned)(p.rows * npos);
+    k_matvec_finish<<<(n_out + 255) / 256, 256, 0, mv->ctx->stream>>>(
+        p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, mv->bias, y, (long long)y_stride,
+        (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
 }
 
 }  // namespace ctox

@@ -62,4 +62,22 @@ ctox_status matvec_stream_pass(ctox_matvec *mv, size_t part_index, const void *x
                                uint32_t npos, uint64_t x_stride);
 // Same, for activations that are already in fragment form in mv->xfrag / mv->meta.
 ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos);
+// Takes ownership of tracked device buffers: canonical bytes, widened s_in [columns], s_out [rows].
+ctox_status matvec_create_device(ctox_ctx *ctx, int dt, uint64_t rows, uint64_t columns, uint8_t *canon,
+                                 size_t canon_bytes, float *s_in, float *s_out, uint32_t flags,
+                                 ctox_matvec **out);
+// out[i][c] = W[row_ids[i]][c] * s_in[c] * s_out[row] (embedding rows, backend/cpu.rs:312-370).
+ctox_status matvec_embed_rows(ctox_matvec *mv, const uint32_t *row_ids_dev, uint32_t n, float *out);
+// y[pos][row] from the partial sums of the last streamed pass.
+void matvec_finish_enqueue(ctox_matvec *mv, uint32_t npos, float *y, uint64_t y_stride);
+// Selection over the partial sums of an lm_head pass (head.cu). Statistics of verify nodes
+// node0 .. node0+npos; then the acceptance walk over all nodes, whose record stays on the device.
+ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, uint32_t n_nodes,
+                                const int32_t *parent, const uint32_t *tokens_dev, float inv_t, uint64_t seed,
+                                uint64_t step, uint32_t rows, float *logits_out_dev);
+ctox_status head_accept_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *parent,
+                                const uint32_t *tokens_dev, float inv_t, uint64_t seed, uint64_t step,
+                                int force_accept, ctox_spec_record **record_dev);
+ctox_status argmax_enqueue(ctox_ctx *ctx, const float *logits_dev, uint32_t n, const uint32_t *row_ids_dev,
+                           uint32_t *token_dev, uint32_t *status_dev);
 }  // namespace ctox

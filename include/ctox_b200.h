@@ -211,7 +211,8 @@ typedef struct {
     uint32_t n_emitted;
     uint32_t emitted[CTOX_MAX_VERIFY_NODES + 1];
     int32_t path[CTOX_MAX_VERIFY_NODES];
-    uint32_t node_argmax[CTOX_MAX_VERIFY_NODES];
+    uint32_t node_argmax[CTOX_MAX_VERIFY_NODES]; /* greedy token of every node's distribution */
+    uint32_t node_token[CTOX_MAX_VERIFY_NODES];  /* the draft token of every node, as verified */
 } ctox_spec_record;
 
 /* Greedy selection over device logits: the LAST maximal index under the IEEE
@@ -241,6 +242,105 @@ ctox_status ctox_lmhead_verify(ctox_matvec *lm_head, const void *hidden_dev, uin
                                const uint32_t *token, float temperature, uint64_t seed,
                                uint64_t step, uint32_t vocab, float *logits_out_dev,
                                ctox_spec_record *record);
+
+/* ---- executor (engine.rs:322-362 trait ModelExecutor; CPU oracle executor
+ * decoder.rs:1278-1458; CUDA candidate backend/cuda_executor.rs:797-1073 and the
+ * graph backend/cuda_graph.rs:3166-3292,3763-5003) ---- */
+
+typedef struct ctox_exec ctox_exec;
+
+/* Qwen38Config (config.rs:12-58) plus deployment choices. */
+typedef struct {
+    uint32_t vocab_size, hidden_size, intermediate_size, num_hidden_layers;
+    uint32_t num_attention_heads, num_key_value_heads, head_dim, rotary_dim;
+    float rope_theta, rms_norm_epsilon;
+    uint32_t full_attention_interval; /* layer l is full attention iff (l+1) % interval == 0 */
+    uint32_t linear_num_key_heads, linear_num_value_heads, linear_key_head_dim, linear_value_head_dim;
+    uint32_t linear_conv_kernel_dim;
+    uint32_t mtp_num_hidden_layers; /* 0 or 1 */
+    uint32_t max_context_tokens;
+    uint32_t kv_page_tokens;    /* tokens per KV page */
+    uint32_t kv_dtype;          /* CTOX_F32 or CTOX_BF16 */
+    uint32_t max_draft_tokens;  /* k: drafts per speculative block, 0..7 */
+    uint32_t draft_vocab;       /* rows of the restricted draft head, 0 = full vocabulary */
+} ctox_model_config;
+
+/* Tensors of the model. Fan-out groups are single matrices whose rows are the
+ * members' rows in the listed order; they share one s_in (fanout.rs:31-70). */
+enum {
+    CTOX_T_EMBED = 0,          /* global, matrix vocab x hidden (tensor_contract.rs:70-249) */
+    CTOX_T_LM_HEAD = 1,        /* global, matrix vocab x hidden */
+    CTOX_T_FINAL_NORM = 2,     /* global, vector hidden */
+    CTOX_T_INPUT_NORM = 3,     /* layer, vector hidden */
+    CTOX_T_POST_NORM = 4,      /* layer, vector hidden */
+    CTOX_T_ATTN_QKV = 5,       /* full layer, matrix [q+gate interleaved per head | k | v] x hidden */
+    CTOX_T_ATTN_O = 6,         /* full layer, matrix hidden x (heads*head_dim) */
+    CTOX_T_Q_NORM = 7,         /* full layer, vector head_dim */
+    CTOX_T_K_NORM = 8,         /* full layer, vector head_dim */
+    CTOX_T_LIN_IN = 9,         /* linear layer, matrix [in_proj_qkv | in_proj_z | in_proj_a | in_proj_b] x hidden */
+    CTOX_T_LIN_OUT = 10,       /* linear layer, matrix hidden x (value_heads*value_dim) */
+    CTOX_T_CONV_W = 11,        /* linear layer, vector channels*kernel */
+    CTOX_T_A_LOG = 12,         /* linear layer, vector value_heads */
+    CTOX_T_DT_BIAS = 13,       /* linear layer, vector value_heads */
+    CTOX_T_LIN_NORM = 14,      /* linear layer, vector value_dim */
+    CTOX_T_MLP_GATE_UP = 15,   /* layer, matrix [gate | up] x hidden */
+    CTOX_T_MLP_DOWN = 16,      /* layer, matrix hidden x intermediate */
+    CTOX_T_MTP_FC = 17,        /* global, matrix hidden x 2*hidden */
+    CTOX_T_MTP_NORM_E = 18,    /* global, vector hidden (pre_fc_norm_embedding) */
+    CTOX_T_MTP_NORM_H = 19,    /* global, vector hidden (pre_fc_norm_hidden) */
+    CTOX_T_MTP_NORM = 20,      /* global, vector hidden (mtp.norm) */
+    CTOX_T_DRAFT_IDS = 21      /* global, draft_vocab strictly increasing token ids (as uint32) */
+};
+#define CTOX_LAYER_GLOBAL 0xffffffffu
+/* layer index of the MTP decoder layer = num_hidden_layers */
+
+/* One speculative block (engine.rs:110-116 ResolvedGreedyMtpVerification). */
+typedef struct {
+    uint32_t proposed_drafts;
+    uint32_t verified_drafts;
+    uint32_t n_accepted;
+    uint32_t accepted_draft_tokens[CTOX_MAX_VERIFY_NODES];
+    uint32_t next_token;
+    uint32_t draft_tokens[CTOX_MAX_VERIFY_NODES];
+    uint32_t target_tokens[CTOX_MAX_VERIFY_NODES + 1]; /* greedy token after each verify position */
+} ctox_exec_step;
+
+ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *config, ctox_exec **out);
+ctox_status ctox_exec_destroy(ctox_exec *exec); /* unload: frees every allocation */
+/* load(): one tensor at a time, host memory. Matrices are FusedMatVec descriptions
+ * without input (weights, s_in, s_out, optional bias). */
+ctox_status ctox_exec_load_matrix(ctox_exec *exec, uint32_t layer, uint32_t tensor,
+                                  const ctox_fused_matvec_op *op);
+ctox_status ctox_exec_load_vector(ctox_exec *exec, uint32_t layer, uint32_t tensor, const float *values,
+                                  uint64_t n);
+/* Random-init weights of the configured shapes, generated on the device: codes
+ * uniform, f16 block scales log-normal(mu, sigma) from a quantile table, recovery
+ * scales U(0.75, 1.25), norm weights ~ N(0, 0.02). */
+ctox_status ctox_exec_fill_synthetic(ctox_exec *exec, uint64_t seed, float scale_mu, float scale_sigma);
+/* warmup(): checks that every tensor is present and builds launch plans. */
+ctox_status ctox_exec_warmup(ctox_exec *exec);
+ctox_status ctox_exec_reset_session(ctox_exec *exec);
+/* prefill(): runs the tokens through the target (and the MTP cache) in chunks;
+ * the last token is NOT consumed: it is the input of the first decode. */
+ctox_status ctox_exec_prefill(ctox_exec *exec, const uint32_t *tokens, uint64_t n);
+/* Benchmark prefill: fills `n` cache positions with random K/V ~ N(0,1) and random
+ * recurrent state instead of running the model, and sets the position. */
+ctox_status ctox_exec_prefill_synthetic(ctox_exec *exec, uint64_t n, uint64_t seed);
+/* decode(): consumes `token` at the current position. With mtp_enabled, drafts
+ * max_draft_tokens tokens, verifies them in one target pass and resolves the
+ * acceptance on the device (temperature 0: engine.rs:939-962). The state is
+ * committed for the accepted prefix before returning. force_accept >= 0 accepts
+ * exactly that many drafts regardless of the target (throughput buckets). */
+ctox_status ctox_exec_decode(ctox_exec *exec, uint32_t token, int32_t mtp_enabled, float temperature,
+                             uint64_t seed, int32_t force_accept, ctox_exec_step *step);
+ctox_status ctox_exec_position(const ctox_exec *exec, uint64_t *position);
+/* Final hidden state of the last committed position (device -> host), for parity tests. */
+ctox_status ctox_exec_last_hidden(ctox_exec *exec, float *out);
+/* Logits of the verify positions of the last decode: [positions][vocab] (evidence path;
+ * enabled with ctox_exec_keep_logits). */
+ctox_status ctox_exec_keep_logits(ctox_exec *exec, int32_t enable);
+ctox_status ctox_exec_last_logits(ctox_exec *exec, uint32_t position, float *out);
+ctox_status ctox_exec_allocated_bytes(const ctox_exec *exec, uint64_t *model, uint64_t *session);
 
 #ifdef __cplusplus
 }

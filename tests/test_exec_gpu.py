@@ -1,0 +1,118 @@
+"""GPU parity of the decode executor against the CPU oracle composed as the reference's scalar
+executor composes it (decoder.rs): logits within rel-L2 1e-3 and, for greedy decoding, the emitted
+token sequence identical with MTP on and off (engine.rs:939-962: verification guards every draft,
+so the emitted sequence does not depend on the drafter)."""
+import numpy as np
+import pytest
+
+import ctox_llm_b200 as ctox
+from gpu_util import rel_l2
+from oracle_model import OracleModel, tiny_config
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def setup(orc):
+    be = ctox.B200Backend(0)
+    cfg = tiny_config()
+    model = OracleModel(orc, cfg, seed=3)
+    ex = ctox.B200Executor(be, cfg)
+    model.load_into(ex)
+    ex.warmup()
+    yield be, ex, model
+    ex.unload()
+    assert be.allocated_bytes() == 0
+    be.close()
+
+
+PROMPT = [5, 17, 900, 3, 3, 41, 512, 77, 1001, 64, 9]
+
+
+def test_plain_greedy_decode_matches_oracle(setup):
+    be, ex, model = setup
+    n_new = 12
+    exp_tokens, exp_logits, _ = model.greedy(PROMPT, n_new)
+    ex.keep_logits(True)
+    ex.prefill(PROMPT)
+    assert ex.position() == len(PROMPT) - 1
+    tok, got = PROMPT[-1], []
+    for i in range(n_new):
+        blk = ex.decode(tok, mtp_enabled=False)
+        ex.commit_speculative(0)
+        assert blk.draft_tokens_proposed == 0 and blk.accepted_draft_tokens == []
+        err = rel_l2(ex.last_logits(0), exp_logits[i])
+        assert err <= 1e-3, (i, err)
+        tok = blk.token_id
+        got.append(tok)
+    assert got == exp_tokens
+    assert ex.position() == len(PROMPT) - 1 + n_new
+
+
+def test_mtp_greedy_emits_the_same_sequence(setup):
+    be, ex, model = setup
+    n_new = 24
+    exp_tokens, _, exp_hidden = model.greedy(PROMPT, n_new)
+    ex.prefill(PROMPT)
+    tok, got, proposed, accepted = PROMPT[-1], [], 0, 0
+    while len(got) < n_new:
+        blk = ex.decode(tok, mtp_enabled=True)
+        ex.commit_speculative(len(blk.accepted_draft_tokens))
+        assert blk.draft_tokens_proposed == 4
+        # engine.rs:118-136
+        k, a = blk.draft_tokens_proposed, len(blk.accepted_draft_tokens)
+        assert blk.draft_tokens_verified == (k if a == k else a + 1)
+        assert blk.accepted_draft_tokens == blk.draft_tokens[:a]
+        got += blk.emitted
+        tok = blk.token_id
+        proposed += k
+        accepted += a
+    assert got[:n_new] == exp_tokens
+    assert ex.position() == len(PROMPT) - 1 + len(got)
+
+
+def test_forced_acceptance_commits_the_prefix_state(setup):
+    """Accepting n drafts must leave exactly the state of having decoded those tokens one by one."""
+    be, ex, model = setup
+    for n_force in (0, 1, 2, 3, 4):
+        ex.prefill(PROMPT)
+        blk = ex.decode(PROMPT[-1], mtp_enabled=True, force_accept=n_force)
+        assert len(blk.accepted_draft_tokens) == n_force
+        seq = PROMPT + blk.accepted_draft_tokens
+        model.reset()
+        for t in seq[:-1]:
+            model.decode_target_step(int(t))
+        fh, logits = model.decode_target_step(int(seq[-1]))
+        assert rel_l2(ex.last_hidden(), fh) <= 1e-3
+        assert blk.token_id == model.orc.greedy_token(logits)
+        # and decoding continues correctly from the committed state
+        nxt = ex.decode(blk.token_id, mtp_enabled=False)
+        _, logits2 = model.decode_target_step(blk.token_id)
+        assert nxt.token_id == model.orc.greedy_token(logits2)
+
+
+def test_sampled_decode_runs_and_is_reproducible(setup):
+    be, ex, model = setup
+    runs = []
+    for _ in range(2):
+        ex.prefill(PROMPT)
+        tok, got = PROMPT[-1], []
+        for _ in range(6):
+            blk = ex.decode(tok, mtp_enabled=True, temperature=0.7, seed=11)
+            got += blk.emitted
+            tok = blk.token_id
+        runs.append(got)
+    assert runs[0] == runs[1]
+    assert all(0 <= t < 1024 for t in runs[0])
+
+
+def test_lifecycle_errors(setup):
+    be, ex, model = setup
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.decode(5000)
+    assert e.value.kind == "Shape"
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.prefill([])
+    assert e.value.kind == "Shape"
+    alloc = ex.allocations()
+    assert alloc["model_bytes"] > 0 and alloc["session_bytes"] > 0
