@@ -176,7 +176,6 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
         return fail(ctx, CTOX_SHAPE, "gated delta: tokens %u heads %u qk_heads %u key_dim %u value_dim %u",
                     tokens, heads, qk_heads, key_dim, value_dim);
     CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
-    timing_begin(ctx);
     if (key_dim == kDeltaDim && value_dim == kDeltaDim) {
         k_gated_delta_scan128<<<heads * 4, 128, 0, ctx->stream>>>(q, k, v, log_decay, beta, state_in, state_out,
                                                                  out, (int)tokens, (int)heads, (int)qk_heads);
@@ -186,7 +185,6 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
             q, k, v, log_decay, beta, state_in, state_out, out, (int)tokens, (int)heads, (int)qk_heads,
             (int)key_dim, (int)value_dim);
     }
-    timing_end(ctx);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }

@@ -68,7 +68,7 @@ struct ctox_exec {
     float *h = nullptr, *final_hidden = nullptr, *hist_hidden = nullptr, *embed_rows = nullptr;
     float *mtp_h = nullptr, *mtp_hidden = nullptr, *mtp_prev = nullptr;
     float *aq = nullptr, *agate = nullptr, *attn_ws = nullptr;
-    float *lz = nullptr, *lcore = nullptr;
+    float *lz = nullptr, *lcore = nullptr, *norm_scratch = nullptr;
     float *draft_logits = nullptr, *logits = nullptr;
     uint32_t *tokens_dev = nullptr;  // [kMaxPass + 1]: verify inputs = [token, drafts...]
     uint32_t *mtp_tokens_dev = nullptr;
@@ -130,6 +130,10 @@ ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c, ctox_exe
     e->channels = 2 * e->key_width + e->value_width;
     e->q_width = c->num_attention_heads * c->head_dim;
     e->kv_width = c->num_key_value_heads * c->head_dim;
+    // one CTA per (KV head, context split): fill the SMs once
+    e->attn_splits_max = (uint32_t)ctx->sm_count / c->num_key_value_heads;
+    if (e->attn_splits_max < 1) e->attn_splits_max = 1;
+    if (e->attn_splits_max > 64) e->attn_splits_max = 64;
     const uint32_t total_layers = e->n_layers + c->mtp_num_hidden_layers;
     e->w.resize(total_layers);
     e->s.resize(total_layers);
@@ -610,6 +614,7 @@ ctox_status ctox_exec_warmup(ctox_exec *e) {
     WALLOC(e->attn_ws, attn_workspace_bytes(g, kMaxPass, e->attn_splits_max));
     WALLOC(e->lz, P * e->value_width * 4);
     WALLOC(e->lcore, P * e->value_width * 4);
+    WALLOC(e->norm_scratch, P * ((H + 255) / 256) * 4);
     WALLOC(e->draft_logits, (size_t)(c.draft_vocab ? c.draft_vocab : c.vocab_size) * 4);
     WALLOC(e->tokens_dev, (P + 1) * 4);
     WALLOC(e->mtp_tokens_dev, (P + 1) * 4);
@@ -765,7 +770,7 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
         const AttnGeom g = attn_geom(e);
         launch_attn_pre(st, fan, g, lw.q_norm, lw.k_norm, rope_pos0, slot0, m, e->aq, e->agate, ls.k_cache,
                         ls.v_cache, c.kv_dtype == CTOX_BF16, page_table, c.kv_page_tokens);
-        const uint64_t tiles = (slot0 + m + 31) / 32;
+        const uint64_t tiles = (slot0 + m + 63) / 64;
         const uint32_t splits = (uint32_t)(tiles < e->attn_splits_max ? (tiles ? tiles : 1) : e->attn_splits_max);
         launch_attention(st, g, e->aq, e->agate, ls.k_cache, ls.v_cache, c.kv_dtype == CTOX_BF16, page_table,
                          c.kv_page_tokens, slot0, m, splits, e->attn_ws, out_in);
@@ -773,16 +778,16 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
     EX(matvec_stream_prepared(lw.out, 0, m));
     const MvOut o = mv_out(lw.out, m);
     const MvIn gu_in = mv_in(lw.gate_up);
-    launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in);
+    launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in, e->norm_scratch);
     EX(matvec_stream_prepared(lw.gate_up, 0, m));
     launch_swiglu_prep(st, mv_out(lw.gate_up, m), c.intermediate_size, m, mv_in(lw.down));
     EX(matvec_stream_prepared(lw.down, 0, m));
     const MvOut d = mv_out(lw.down, m);
     if (next) {
         const MvIn nin = mv_in(next);
-        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, &nin);
+        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, &nin, e->norm_scratch);
     } else {
-        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, nullptr);
+        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, nullptr, e->norm_scratch);
     }
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
@@ -796,7 +801,7 @@ ctox_status target_pass(ctox_exec *e, uint32_t m, uint64_t pos0) {
     EX(matvec_embed_rows(e->embed, e->tokens_dev, m, e->h));
     const MvIn first = mv_in(e->w[0].in_fan);
     launch_residual_norm_prep(ctx->stream, e->h, nullptr, e->w[0].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
-                              nullptr, &first);
+                              nullptr, &first, e->norm_scratch);
     for (uint32_t l = 0; l < e->n_layers; ++l) {
         const bool last = l + 1 == e->n_layers;
         EX(layer_body(e, l, e->h, m, pos0, pos0, e->page_table, last ? e->final_norm : e->w[l + 1].in_ln,
@@ -842,7 +847,7 @@ ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const float *h
     const MvOut fc = mv_out(e->mtp_fc, m);
     const MvIn lin = mv_in(e->w[L].in_fan);
     launch_residual_norm_prep(ctx->stream, e->mtp_h, &fc, e->w[L].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
-                              nullptr, &lin);
+                              nullptr, &lin, e->norm_scratch);
     EX(layer_body(e, L, e->mtp_h, m, abs_pos0, abs_pos0 - 1, e->mtp_page_table, e->mtp_norm, e->mtp_hidden,
                   nullptr));
     if (draft_slot >= 0) {

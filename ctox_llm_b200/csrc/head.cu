@@ -157,14 +157,26 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
     }
 }
 
-// Merges the per-CTA statistics of one pass into node_stats[node0 .. node0+npos).
+// Merges the per-CTA statistics of one pass into node_stats[node0 .. node0+npos): one warp per
+// position, lanes stride over the CTAs, then a butterfly (max/sum merges are order-insensitive up
+// to rounding; the lane order is fixed, so the result is reproducible).
 __global__ void k_head_merge(const NodeStat *__restrict__ cta_stats, uint32_t n_ctas, uint32_t node0,
                              uint32_t npos, NodeStat *__restrict__ node_stats) {
-    const uint32_t m = threadIdx.x;
+    const uint32_t m = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (m >= npos) return;
-    NodeStat a = cta_stats[m];
-    for (uint32_t c = 1; c < n_ctas; ++c) merge_stat(a, cta_stats[(size_t)c * kMaxPosPerPass + m]);
-    node_stats[node0 + m] = a;
+    NodeStat a{0ull, 0ull, 0.f, 0.f, 0u, 0u};
+    for (uint32_t c = lane; c < n_ctas; c += 32) merge_stat(a, cta_stats[(size_t)c * kMaxPosPerPass + m]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        NodeStat other;
+        other.argmax = __shfl_xor_sync(0xffffffffu, a.argmax, o);
+        other.gumbel = __shfl_xor_sync(0xffffffffu, a.gumbel, o);
+        other.max = __shfl_xor_sync(0xffffffffu, a.max, o);
+        other.sum = __shfl_xor_sync(0xffffffffu, a.sum, o);
+        other.nonfinite = __shfl_xor_sync(0xffffffffu, a.nonfinite, o);
+        merge_stat(a, other);
+    }
+    if (lane == 0) node_stats[node0 + m] = a;
 }
 
 // Walks the draft tree with the statistics of every node. One thread: the walk is
@@ -400,7 +412,7 @@ ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, 
                                                         mv->bias, rows, p.slices, p.max_pieces, node0, npos,
                                                         inv_t, seed, step, tree, hs.cta_stats, hs.child_z,
                                                         logits_out_dev, (unsigned long long)mv->rows);
-    k_head_merge<<<1, 32, 0, ctx->stream>>>(hs.cta_stats, grid, node0, npos, hs.node_stats);
+    k_head_merge<<<1, 32 * kMaxPosPerPass, 0, ctx->stream>>>(hs.cta_stats, grid, node0, npos, hs.node_stats);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }

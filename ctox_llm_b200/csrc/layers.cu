@@ -57,52 +57,64 @@ __device__ __forceinline__ void prep_from_smem(const float *vals, uint32_t n, ui
     }
 }
 
-// One CTA per position.
-__global__ void __launch_bounds__(512) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
-                                                          const float *__restrict__ w, float eps,
-                                                          uint32_t hidden, int npos, float *__restrict__ xn_out,
-                                                          MvIn next, int has_next) {
-    extern __shared__ float sh[];  // [hidden] + 32
-    float *vals = sh, *red = sh + hidden;
-    const int m = blockIdx.x;
-    float *hm = h + (size_t)m * hidden;
-    float sq = 0.f;
-    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = hm[c];
+// h[m][c] (+= matvec output); per-CTA partial sums of squares go to sumsq[m][blockIdx.x].
+__global__ void __launch_bounds__(256) k_residual_add(float *__restrict__ h, MvOut add, int has_add,
+                                                    uint32_t hidden, float *__restrict__ sumsq) {
+    __shared__ float red[8];
+    const int m = blockIdx.y;
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    float v = 0.f;
+    if (c < hidden) {
+        v = h[(size_t)m * hidden + c];
         if (has_add) {
             v += out_of(add, c, m);
-            hm[c] = v;
+            h[(size_t)m * hidden + c] = v;
         }
-        vals[c] = v;
-        sq += v * v;
     }
-    const float inv = 1.0f / sqrtf(block_sum(sq, red) / (float)hidden + eps);
-    __syncthreads();
-    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
-        const float xn = vals[c] * inv * (1.0f + w[c]);
-        vals[c] = xn;
-        if (xn_out) xn_out[(size_t)m * hidden + c] = xn;
+    const float s = block_sum(v * v, red);
+    if (threadIdx.x == 0) sumsq[m * gridDim.x + blockIdx.x] = s;
+}
+
+// xn = h * rsqrt(mean(h^2) + eps) * (1 + w); optional copy; fragments of xn * s_in. One 16-lane
+// group per (position, 64-column block); every group adds the partial sums in the same order.
+__global__ void k_norm_prep(const float *__restrict__ h, const float *__restrict__ sumsq, uint32_t nparts,
+                            const float *__restrict__ w, float eps, uint32_t hidden, int npos,
+                            float *__restrict__ xn_out, MvIn next, int has_next, uint32_t nblocks) {
+    const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int i = threadIdx.x & 15;
+    if (gid >= nblocks * (uint32_t)npos) return;
+    const uint32_t b = gid / npos;
+    const int m = gid % npos;
+    float sq = 0.f;
+    for (uint32_t q = 0; q < nparts; ++q) sq += sumsq[m * nparts + q];
+    const float inv = 1.0f / sqrtf(sq / (float)hidden + eps);
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t c = b * 64 + i * 4 + j;
+        v[j] = 0.f;
+        if (c < hidden) {
+            const float xn = h[(size_t)m * hidden + c] * inv * (1.0f + w[c]);
+            if (xn_out) xn_out[(size_t)m * hidden + c] = xn;
+            v[j] = has_next ? xn * (next.s_in ? next.s_in[c] : 1.0f) : 0.f;
+        }
     }
-    __syncthreads();
     if (has_next) {
-        prep_from_smem(vals, hidden, 0, m, npos, next);
-        // zero padding blocks beyond the matrix columns
-        const int i = threadIdx.x & 15;
         const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-        for (uint32_t b = (hidden + 63) / 64 + (threadIdx.x >> 4); b < next.blocks_padded; b += blockDim.x >> 4) {
-            const float z[4] = {0.f, 0.f, 0.f, 0.f};
-            prep_block(z, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
-        }
+        prep_block(v, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
     }
 }
 
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
-                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next) {
-    const size_t smem = (hidden + 32) * sizeof(float);
+                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch) {
     MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0};
     MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
-    k_residual_norm_prep<<<m, 512, smem, st>>>(h, a, add != nullptr, w, eps, hidden, (int)m, xn_out, n,
-                                              next != nullptr);
+    const uint32_t nparts = (hidden + 255) / 256;
+    k_residual_add<<<dim3(nparts, m), 256, 0, st>>>(h, a, add != nullptr, hidden, scratch);
+    const uint32_t nblocks = next ? next->blocks_padded : (hidden + 63) / 64;
+    const uint32_t groups = nblocks * m;
+    k_norm_prep<<<(groups * 16 + 127) / 128, 128, 0, st>>>(h, scratch, nparts, w, eps, hidden, (int)m, xn_out, n,
+                                                          next != nullptr, nblocks);
 }
 
 // One CTA per position: [rmsnorm(embed) | rmsnorm(prev_hidden)] -> fragments (2 * hidden columns).
@@ -144,31 +156,33 @@ void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_
     k_mtp_pre<<<m, 512, smem, st>>>(embed_rows, prev_hidden, w_embed, w_hidden, eps, hidden, (int)m, *next);
 }
 
-// One 16-lane group per (position, 64-column block of the intermediate width).
-__global__ void k_swiglu_prep(MvOut gu, uint32_t inter, int npos, MvIn next) {
-    const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
-    const int i = threadIdx.x & 15;
-    const uint32_t nb = next.blocks_padded;
-    if (gid >= nb * (uint32_t)npos) return;
-    const uint32_t b = gid / npos;
-    const int m = gid % npos;
-    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t c = b * 64 + i * 4 + j;
-        v[j] = 0.f;
-        if (c < inter) {
-            const float gate = out_of(gu, c, m), up = out_of(gu, inter + c, m);
-            v[j] = silu_f(gate) * up * (next.s_in ? next.s_in[c] : 1.0f);
+// One CTA per (position, 256 columns of the intermediate width): every thread finishes one
+// column (two matvec outputs), then four 16-lane groups write the four 64-column blocks.
+__global__ void __launch_bounds__(256) k_swiglu_prep(MvOut gu, uint32_t inter, int npos, MvIn next) {
+    __shared__ float vals[256];
+    const int m = blockIdx.y;
+    const uint32_t c = blockIdx.x * 256 + threadIdx.x;
+    float v = 0.f;
+    if (c < inter) {
+        const float gate = out_of(gu, c, m), up = out_of(gu, inter + c, m);
+        v = silu_f(gate) * up * (next.s_in ? next.s_in[c] : 1.0f);
+    }
+    vals[threadIdx.x] = v;
+    __syncthreads();
+    if (threadIdx.x < 64) {
+        const int i = threadIdx.x & 15, grp = threadIdx.x >> 4;
+        const uint32_t b = blockIdx.x * 4 + grp;
+        if (b < next.blocks_padded) {
+            const float x[4] = {vals[grp * 64 + i * 4], vals[grp * 64 + i * 4 + 1], vals[grp * 64 + i * 4 + 2],
+                                vals[grp * 64 + i * 4 + 3]};
+            const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+            prep_block(x, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
         }
     }
-    prep_block(v, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
 }
 
 void launch_swiglu_prep(cudaStream_t st, const MvOut &gate_up, uint32_t inter, uint32_t m, const MvIn &next) {
-    const uint32_t groups = next.blocks_padded * m;
-    k_swiglu_prep<<<(groups * 16 + 255) / 256, 256, 0, st>>>(gate_up, inter, (int)m, next);
+    k_swiglu_prep<<<dim3((next.blocks_padded + 3) / 4, m), 256, 0, st>>>(gate_up, inter, (int)m, next);
 }
 
 // ------------------------------------------------------------------ linear attention
@@ -390,7 +404,7 @@ __global__ void __launch_bounds__(kAttnThreads) k_attention(
     AttnGeom g, const float *__restrict__ q, const T *__restrict__ k_cache, const T *__restrict__ v_cache,
     const uint32_t *__restrict__ page_table, uint32_t page_tokens, uint64_t cache_slot, int npos,
     uint32_t splits, float *__restrict__ ws) {
-    extern __shared__ __align__(16) uint8_t smraw[];
+    extern __shared__ __align__(128) uint8_t smraw[];
     const uint32_t hd = g.head_dim, G = g.q_heads / g.kv_heads, NQ = G * npos;
     const uint32_t kh = blockIdx.x / splits, sp = blockIdx.x % splits;
     const uint32_t kstride = hd + 16 / sizeof(T);  // padded row: conflict-free 16-byte reads
@@ -486,6 +500,217 @@ __global__ void __launch_bounds__(kAttnThreads) k_attention(
     }
 }
 
+// ------------------------------------------------------------------ tensor-core attention (bf16 cache)
+// Same contract as k_attention for a bf16 cache and head_dim 256, built for HBM speed:
+//  * 64-token K and V tiles are staged in shared memory with 16-byte cp.async, double buffered;
+//  * each warp owns 16 tokens of a tile and 16 queries (warps 0-3: queries 0-15, warps 4-7:
+//    queries 16-31) and runs flash-attention on mma.sync.m16n8k16 (bf16 in, fp32 accumulate):
+//    S = Q K^T with Q split as bf16 hi + lo (16 significant bits, K exact), online softmax in the
+//    accumulator layout, O += P V with P split the same way and V read through ldmatrix.trans;
+//  * no barrier between the four warps of a group inside a tile: each keeps its own running
+//    max / sum / O and the four are merged once at the end, like the context splits.
+constexpr int kFaTile = 64, kFaHd = 256, kFaStride = kFaHd + 8;  // padded rows: conflict-free ldmatrix
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&v);
+}
+// hi and lo parts of two floats as packed bf16 pairs
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+    hi = pack_bf16(__bfloat162float(xh), __bfloat162float(yh));
+    lo = pack_bf16(x - __bfloat162float(xh), y - __bfloat162float(yh));
+}
+
+template <int GROUPS>  // 1: up to 16 queries (4 warps), 2: up to 32 queries (8 warps)
+__global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
+    AttnGeom g, const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
+    const __nv_bfloat16 *__restrict__ v_cache, const uint32_t *__restrict__ page_table, uint32_t page_tokens,
+    uint64_t cache_slot, int npos, uint32_t splits, float *__restrict__ ws) {
+    extern __shared__ __align__(128) uint8_t smraw[];
+    constexpr int NT = GROUPS * 128;
+    const uint32_t G = g.q_heads / g.kv_heads, NQ = G * npos;
+    const uint32_t kh = blockIdx.x / splits, sp = blockIdx.x % splits;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+    const uint32_t grp = warp >> 2, wg = warp & 3;  // query group, warp inside the group
+    // shared memory: Q [2 terms][32 queries][stride], then 2 buffers of (K tile, V tile)
+    __nv_bfloat16 *q_s = reinterpret_cast<__nv_bfloat16 *>(smraw);
+    constexpr uint32_t kQBytes = 2 * 32 * kFaStride * 2, kTileBytes = kFaTile * kFaStride * 2;
+    const uint32_t q_a = (uint32_t)__cvta_generic_to_shared(q_s);
+    const uint32_t buf_a = q_a + kQBytes;  // buffer b: K at buf_a + b*2*kTileBytes, V right after
+    const uint64_t total = cache_slot + (uint64_t)npos;
+    const uint64_t tiles = (total + kFaTile - 1) / kFaTile;
+    const uint64_t tile_beg = tiles * sp / splits, tile_end = tiles * (sp + 1) / splits;
+    const float scale = 1.0f / sqrtf((float)kFaHd);
+    for (uint32_t i = tid; i < 32 * kFaHd; i += NT) {
+        const uint32_t qi = i / kFaHd, d = i % kFaHd;
+        float v = 0.f;
+        if (qi < NQ) v = q[((size_t)(qi / G) * g.q_heads + kh * G + qi % G) * kFaHd + d] * scale;
+        const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+        q_s[qi * kFaStride + d] = hi;
+        q_s[(32 + qi) * kFaStride + d] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    }
+    auto load_tile = [&](uint64_t tile, uint32_t b) {
+        const uint64_t t0 = tile * kFaTile;
+        // 64 rows x 32 chunks of 16 B for K and for V
+        for (uint32_t c = tid; c < 2 * kFaTile * 32; c += NT) {
+            const uint32_t which = c / (kFaTile * 32), r = (c / 32) % kFaTile, cc = c % 32;
+            const uint32_t dst = buf_a + b * 2 * kTileBytes + which * kTileBytes + r * kFaStride * 2 + cc * 16;
+            if (t0 + r < total) {
+                const size_t slot = kv_slot(page_table, page_tokens, t0 + r);
+                const __nv_bfloat16 *src = (which ? v_cache : k_cache) + (slot * g.kv_heads + kh) * kFaHd + cc * 8;
+                cp_async16(dst, src);
+            } else {
+                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    float oacc[32][4];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const uint32_t qrow[2] = {grp * 16 + gq, grp * 16 + gq + 8};
+    uint64_t limit[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) limit[r] = cache_slot + (qrow[r] < NQ ? qrow[r] / G : 0);
+    if (tile_beg < tile_end) load_tile(tile_beg, 0);
+    for (uint64_t tile = tile_beg; tile < tile_end; ++tile) {
+        const uint32_t b = (uint32_t)(tile - tile_beg) & 1;
+        if (tile + 1 < tile_end) {
+            load_tile(tile + 1, b ^ 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        const uint32_t k_a = buf_a + b * 2 * kTileBytes, v_a = k_a + kTileBytes;
+        const uint32_t tok0 = wg * 16;
+        // ---- S = Q K^T for this warp's 16 queries x 16 tokens
+        float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll 4
+        for (int ks = 0; ks < kFaHd / 16; ++ks) {
+            uint32_t bk[4], aq[4];
+            // K matrices: (tokens 0-7, k 0-7), (tokens 0-7, k 8-15), (tokens 8-15, k 0-7), (tokens 8-15, k 8-15)
+            ldsm_x4(bk, k_a + (tok0 + (lane & 7) + 8 * (lane >> 4)) * kFaStride * 2 +
+                            (ks * 16 + 8 * ((lane >> 3) & 1)) * 2);
+#pragma unroll
+            for (int term = 0; term < 2; ++term) {
+                // Q matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
+                ldsm_x4(aq, q_a + ((term * 32 + grp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kFaStride +
+                                   ks * 16 + 8 * (lane >> 4)) * 2);
+                mma_bf16(sacc[0], aq, bk[0], bk[1]);
+                mma_bf16(sacc[1], aq, bk[2], bk[3]);
+            }
+        }
+        // ---- online softmax; this lane holds rows gq, gq+8 and tokens tok0 + {2tq, 2tq+1, 8+2tq, 9+2tq}
+        const uint64_t tbase = tile * kFaTile + tok0;
+        uint32_t p_hi[4], p_lo[4];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float sv[4] = {sacc[0][2 * r], sacc[0][2 * r + 1], sacc[1][2 * r], sacc[1][2 * r + 1]};
+            const uint32_t toff[4] = {2 * tq, 2 * tq + 1, 8 + 2 * tq, 9 + 2 * tq};
+            float tmax = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (tbase + toff[j] > limit[r] || tbase + toff[j] >= total) sv[j] = -INFINITY;
+                tmax = fmaxf(tmax, sv[j]);
+            }
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 1));
+            tmax = fmaxf(tmax, __shfl_xor_sync(0xffffffffu, tmax, 2));
+            const float m_new = fmaxf(m_run[r], tmax);
+            const float alpha = m_run[r] > -INFINITY ? expf(m_run[r] - m_new) : 0.f;
+            float ps[4], sum = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                ps[j] = sv[j] > -INFINITY ? expf(sv[j] - m_new) : 0.f;
+                sum += ps[j];
+            }
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            l_run[r] = l_run[r] * alpha + sum;
+            m_run[r] = m_new;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                oacc[i][2 * r] *= alpha;
+                oacc[i][2 * r + 1] *= alpha;
+            }
+            // A fragment of P: a0 (row g, k 2t..) / a1 (row g+8) from n-tile 0, a2 / a3 from n-tile 1
+            split_bf16(ps[0], ps[1], p_hi[r], p_lo[r]);
+            split_bf16(ps[2], ps[3], p_hi[2 + r], p_lo[2 + r]);
+        }
+        // ---- O += P V: V matrices (trans): (tokens 0-7, dims n0..), (tokens 8-15, dims n0..),
+        //      (tokens 0-7, dims n0+8..), (tokens 8-15, dims n0+8..)
+#pragma unroll
+        for (int dn = 0; dn < kFaHd / 16; ++dn) {
+            uint32_t bv[4];
+            ldsm_x4_trans(bv, v_a + (tok0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kFaStride * 2 +
+                                  (dn * 16 + 8 * (lane >> 4)) * 2);
+            mma_bf16(oacc[2 * dn], p_hi, bv[0], bv[1]);
+            mma_bf16(oacc[2 * dn], p_lo, bv[0], bv[1]);
+            mma_bf16(oacc[2 * dn + 1], p_hi, bv[2], bv[3]);
+            mma_bf16(oacc[2 * dn + 1], p_lo, bv[2], bv[3]);
+        }
+        __syncthreads();  // everyone is done with buffer b before it is refilled
+    }
+    // ---- merge the four warps of each group through shared memory (reusing the tile buffers)
+    float *mo = reinterpret_cast<float *>(smraw + kQBytes);  // [warp][16 rows][hd + 2]
+    float *mine = mo + (size_t)warp * 16 * (kFaHd + 2);
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float *row = mine + (gq + 8 * r) * (kFaHd + 2);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            row[i * 8 + 2 * tq] = oacc[i][2 * r];
+            row[i * 8 + 2 * tq + 1] = oacc[i][2 * r + 1];
+        }
+        if (tq == 0) {
+            row[kFaHd] = m_run[r];
+            row[kFaHd + 1] = l_run[r];
+        }
+    }
+    __syncthreads();
+    float *out = ws + ((size_t)(kh * splits + sp) * NQ) * (kFaHd + 2);
+    for (uint32_t i = tid; i < 16 * GROUPS * kFaHd; i += NT) {
+        const uint32_t qi = i / kFaHd, d = i % kFaHd;
+        if (qi >= NQ) continue;
+        const uint32_t gg = qi / 16, rr = qi % 16;
+        float mx = -INFINITY;
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mo[((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2) + kFaHd]);
+        float acc = 0.f, den = 0.f;
+        for (int w = 0; w < 4; ++w) {
+            const float *row = mo + ((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2);
+            if (!(row[kFaHd] > -INFINITY)) continue;
+            const float wgt = expf(row[kFaHd] - mx);
+            acc += row[d] * wgt;
+            den += row[kFaHd + 1] * wgt;
+        }
+        out[(size_t)qi * (kFaHd + 2) + d] = acc;
+        if (d == 0) {
+            out[(size_t)qi * (kFaHd + 2) + kFaHd] = mx;
+            out[(size_t)qi * (kFaHd + 2) + kFaHd + 1] = den;
+        }
+    }
+}
+
 // Merge of the splits, sigmoid gate (reference.rs:502-515) and fragments for o_proj: one
 // 16-lane group per (position, query head, 64-dimension block).
 __global__ void k_attn_combine_prep(AttnGeom g, const float *__restrict__ ws, const float *__restrict__ gate,
@@ -545,6 +770,26 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
                       uint32_t page_tokens, uint64_t cache_slot, uint32_t m, uint32_t splits, float *workspace,
                       const MvIn &next) {
     const uint32_t nq = g.q_heads / g.kv_heads * m;
+    if (kv_bf16 && g.head_dim == kFaHd && nq <= 32) {
+        const size_t smem = 2 * 32 * kFaStride * 2 + 4 * (size_t)kFaTile * kFaStride * 2;
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaFuncSetAttribute(k_attention_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(k_attention_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr_done = true;
+        }
+        if (nq <= 16)
+            k_attention_mma<1><<<g.kv_heads * splits, 128, smem, st>>>(
+                g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
+                cache_slot, (int)m, splits, workspace);
+        else
+            k_attention_mma<2><<<g.kv_heads * splits, 256, smem, st>>>(
+                g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
+                cache_slot, (int)m, splits, workspace);
+        const uint32_t groups = m * g.q_heads * (g.head_dim / 64);
+        k_attn_combine_prep<<<(groups * 16 + 255) / 256, 256, 0, st>>>(g, workspace, gate, (int)m, splits, next);
+        return;
+    }
 #define CTOX_ATTN(T)                                                                                        \
     do {                                                                                                    \
         if (nq <= 8)                                                                                        \

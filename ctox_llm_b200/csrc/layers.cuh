@@ -34,8 +34,9 @@ struct AttnGeom {
 };
 
 // h[m] (+= matvec output) ; xn = rmsnorm_1p(h[m], w) ; optional copy of xn ; fragments of xn * s_in.
+// scratch: m * ceil(hidden / 256) floats.
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
-                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next);
+                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch);
 // MTP input: fragments of concat(rmsnorm_1p(embed(tok[m])), rmsnorm_1p(prev_hidden[m])) * s_in.
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next);

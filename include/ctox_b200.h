@@ -125,9 +125,9 @@ ctox_status ctox_ctx_allocated_bytes(const ctox_ctx *ctx, uint64_t *bytes);
  * instead of trapping, e.g. when a bounded wait ran out. */
 ctox_status ctox_ctx_device_error(ctox_ctx *ctx, int32_t *code);
 /* Benchmark support (the reference's verify/bench binaries time dispatches the
- * same way, src/bin/cuda_bench.rs): when enabled, every launch of a dominant
- * kernel (the streaming matvec, the recurrence, the fused head) is bracketed by
- * a CUDA event pair on the context's stream. _read synchronises, returns the
+ * same way, src/bin/cuda_bench.rs): when enabled, every launch of the dominant
+ * kernel (the streaming / row-warp matvec) is bracketed by a CUDA event pair on
+ * the context's stream. _read synchronises, returns the
  * summed duration and the number of launches since the last read, and clears. */
 ctox_status ctox_ctx_kernel_timing(ctox_ctx *ctx, int32_t enable);
 ctox_status ctox_ctx_kernel_timing_read(ctox_ctx *ctx, double *total_ms, uint64_t *launches);

@@ -20,6 +20,13 @@ def tiny_config(**kw):
     return cfg
 
 
+def bf16_round(x):
+    """float32 -> bfloat16 (round to nearest even) -> float32."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    b = ((b + 0x7FFF + ((b >> 16) & 1)) >> 16) << 16
+    return b.astype(np.uint32).view(np.float32)
+
+
 class Matrix:
     def __init__(self, orc, rng, dtype, rows, cols, s_in=None, scale=1.0):
         self.dtype, self.rows, self.cols = dtype, rows, cols
@@ -44,6 +51,7 @@ def concat(mats):
 class OracleModel:
     def __init__(self, orc, cfg, seed=0):
         self.orc, self.cfg = orc, cfg
+        self.kv_bf16 = cfg.kv_dtype == N.BF16  # the cache stores K and V rounded to bfloat16
         rng = np.random.default_rng(seed)
         c = cfg
         H, F = c.hidden_size, c.intermediate_size
@@ -157,6 +165,8 @@ class OracleModel:
         key = orc.rms_norm_1p_weight(key, c.num_key_value_heads, c.head_dim, L["k_norm"], c.rms_norm_epsilon)
         query, key = orc.apply_partial_rope(query, key, c.num_attention_heads, c.num_key_value_heads, c.head_dim,
                                             c.rotary_dim, rope_pos, c.rope_theta)
+        if self.kv_bf16:
+            key, value = bf16_round(key), bf16_round(value)
         st["k"].append(key)
         st["v"].append(value)
         T = len(st["k"])

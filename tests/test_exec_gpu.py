@@ -116,3 +116,37 @@ def test_lifecycle_errors(setup):
     assert e.value.kind == "Shape"
     alloc = ex.allocations()
     assert alloc["model_bytes"] > 0 and alloc["session_bytes"] > 0
+
+
+def test_bf16_cache_tensor_core_attention_matches_oracle(orc):
+    """head_dim 256 with a bfloat16 KV cache runs the tensor-core attention kernel; the oracle
+    stores the same bf16-rounded K and V, so the logits still agree within rel-L2 1e-3."""
+    be = ctox.B200Backend(0)
+    cfg = tiny_config(num_attention_heads=4, num_key_value_heads=1, head_dim=256, rotary_dim=64,
+                      kv_dtype=ctox.BF16, max_context_tokens=512, full_attention_interval=2)
+    model = OracleModel(orc, cfg, seed=5)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex)
+        ex.warmup()
+        ex.keep_logits(True)
+        rng = np.random.default_rng(7)
+        prompt = [int(t) for t in rng.integers(0, 1024, 150)]  # > 2 tiles of 64 tokens
+        n_new = 6
+        exp_tokens, exp_logits, _ = model.greedy(prompt, n_new)
+        ex.prefill(prompt)
+        tok, got = prompt[-1], []
+        for i in range(n_new):
+            blk = ex.decode(tok, mtp_enabled=False)
+            assert rel_l2(ex.last_logits(0), exp_logits[i]) <= 1e-3
+            tok = blk.token_id
+            got.append(tok)
+        assert got == exp_tokens
+        # verify rows (5 queries per head group) through the same kernel
+        ex.prefill(prompt)
+        blk = ex.decode(prompt[-1], mtp_enabled=True)
+        assert blk.emitted[0] == exp_tokens[0] or blk.accepted_draft_tokens[:1] == exp_tokens[:1]
+        assert (blk.accepted_draft_tokens + [blk.token_id]) == exp_tokens[:len(blk.emitted)]
+    finally:
+        ex.unload()
+        be.close()
