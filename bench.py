@@ -111,12 +111,13 @@ def cpu_baseline(threads: int, avx2: bool, repeats: int):
 
 
 def run_reference(args):
+    """The reference's CPU path (C restatement of backend/cpu.rs, AVX2 arm, rows split over all host
+    threads). Each step is one bounded sample: a 17408x5120 Q4 fused matvec. For the decode workload
+    the sample's bandwidth is scaled to the bytes of one target pass of the same configuration."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = os.cpu_count() or 1
-    # each step is one full matvec on the host; warm-up inside cpu_baseline
-    times = []
     import oracle
     from ctox_llm_b200 import synthetic
     w = synthetic.packed_weights(oracle.Q4B64, Q4_ROWS, Q4_COLS, 0)
@@ -129,19 +130,184 @@ def run_reference(args):
     for _ in range(steps):
         oracle.fused_matvec(op, threads=cores, avx2=True)
     dt = time.perf_counter() - t0
-    value = ALGO_BYTES * steps / dt / 1e9
+    gbs = ALGO_BYTES * steps / dt / 1e9
+    if args.workload == "decode":
+        import ctox_llm_b200 as ctox
+        cfg = ctox.qwen38_27b_config(max_context_tokens=args.context + 4096)
+        weights, kv, state = decode_config_bytes(cfg, args.context)
+        value = 1.0 / ((weights + kv + state) / (gbs * 1e9))
+        metric, unit = "decode_tokens_per_s_mtp", "tokens/s"
+        workload = (f"qwen3.8-27b-shaped decode, 64 layers, batch 1, context {args.context}, MTP k=4 "
+                    "(BASELINE config 4)")
+        sample = (f"one 17408x5120 Q4 fused matvec per step at {gbs:.2f} GB/s, scaled to the "
+                  f"{(weights + kv + state) / 1e9:.1f} GB of one target pass (one token per pass)")
+    else:
+        value, metric, unit = gbs, "q4_matvec_hbm_gbs", "GB/s"
+        workload = "q4_matvec 17408x5120 Q4_B64, f32 activations (BASELINE config 0)"
+        sample = "whole 17408x5120 matvec per step"
     line = {
-        "impl": "reference", "metric": "q4_matvec_hbm_gbs", "value": value, "unit": "GB/s",
+        "impl": "reference", "metric": metric, "value": value, "unit": unit,
         "n_gpus": args.gpus, "steps": steps, "warmup": max(args.warmup, 1),
         "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "q4_matvec 17408x5120 Q4_B64, f32 activations (BASELINE config 0)"},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": "whole 17408x5120 matvec per step, AVX2 arm of backend/cpu.rs "
-                                   "restated in C, rows split over all host threads"},
-        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "config": {"workload": workload},
+        "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port",
+                         "sample": sample + "; AVX2 arm of backend/cpu.rs restated in C, rows split over "
+                                            "all host threads"},
+        "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def decode_config_bytes(cfg, positions):
+    """Algorithmic bytes of one target pass (weights once, bf16 KV of the context, state r/w)."""
+    H, F, V = cfg.hidden_size, cfg.intermediate_size, cfg.vocab_size
+    qw, kvw = cfg.num_attention_heads * cfg.head_dim, cfg.num_key_value_heads * cfg.head_dim
+    vw = cfg.linear_num_value_heads * 128
+    ch = 2 * cfg.linear_num_key_heads * 128 + vw
+    q4 = lambda r, c: r * (c // 64) * 34
+    q2 = lambda r, c: r * (c // 64) * 18
+    n_full = cfg.num_hidden_layers // cfg.full_attention_interval
+    n_lin = cfg.num_hidden_layers - n_full
+    mlp = q2(2 * F, H) + q2(H, F)
+    full = q4(2 * qw + 2 * kvw, H) + q4(H, qw) + mlp
+    lin = q4(ch + vw + 2 * cfg.linear_num_value_heads, H) + q4(H, vw) + mlp
+    weights = n_full * full + n_lin * lin + q4(V, H)
+    kv = n_full * positions * kvw * 2 * 2
+    state = n_lin * cfg.linear_num_value_heads * 128 * 128 * 4 * 2
+    return weights, kv, state
+
+
+def launches_per_block(cfg):
+    """Kernels of this library launched by one speculative block (counted from the executor's
+    structure: 12 per decoder layer, 3 to start a pass, 5 for the head, 1-2 per linear layer to
+    commit; an MTP pass is one layer plus 4 around the fc and 5 for the draft head)."""
+    n_lin = cfg.num_hidden_layers - cfg.num_hidden_layers // cfg.full_attention_interval
+    target = 3 + 12 * cfg.num_hidden_layers + 5 + 2 * n_lin
+    mtp = cfg.max_draft_tokens * (4 + 12 + 5)
+    return target + mtp
+
+
+def run_decode(args):
+    """BASELINE config 4: random-init Qwen3.8-27B-shaped hybrid decode, Q4 attention/embedding and
+    Q2 FFN weights, bf16 paged KV (16-token pages) prefilled to 32768 tokens with random K/V,
+    batch 1, MTP speculation (4 chained drafts, restricted 40000-row draft head)."""
+    import torch
+    import torch.distributed as dist
+    import ctox_llm_b200 as ctox
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    stream = torch.cuda.Stream(device=local)
+    be = ctox.B200Backend(local, stream=stream.cuda_stream)
+    context = args.context
+    cfg = ctox.qwen38_27b_config(max_context_tokens=context + 4096)
+    ex = ctox.B200Executor(be, cfg)
+    ex.fill_synthetic(seed=0)
+    ex.warmup()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def run_blocks(n_blocks, mtp, force, timed):
+        """Returns (device ms, wall s, tokens emitted, drafts accepted) for n_blocks decode calls."""
+        ex.prefill_synthetic(context, seed=1)
+        tok = 1
+        for _ in range(args.warmup):
+            tok = ex.decode(tok, mtp_enabled=mtp, force_accept=force).token_id
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        emitted = accepted = 0
+        ev0.record(stream)
+        t0 = time.perf_counter()
+        for _ in range(n_blocks):
+            blk = ex.decode(tok, mtp_enabled=mtp, force_accept=force)
+            tok = blk.token_id
+            emitted += len(blk.emitted)
+            accepted += len(blk.accepted_draft_tokens)
+        wall = time.perf_counter() - t0
+        ev1.record(stream)
+        barrier()
+        return ev0.elapsed_time(ev1), wall, emitted, accepted
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms, wall, emitted, accepted = run_blocks(args.steps, True, -1, True)
+    clocks = sampler.stop() if rank == 0 else None
+    buckets = {}
+    for force in (0, 2, 4):
+        bms, _, bem, _ = run_blocks(max(args.steps // 8, 8), True, force, False)
+        buckets[f"accept_{force}"] = bem / (bms * 1e-3)
+    pms, _, pem, _ = run_blocks(max(args.steps // 8, 8), False, -1, False)
+    plain = pem / (pms * 1e-3)
+    # dominant kernel (the streaming matvec) alone, event pairs around every launch
+    be.kernel_timing(True)
+    _, _, _, _ = run_blocks(4, True, -1, False)
+    kernel_ms, launches = be.kernel_timing_read()
+    be.kernel_timing(False)
+    blocks_timed = 4 + args.warmup
+
+    t = torch.tensor([ms, wall], dtype=torch.float64, device=f"cuda:{local}")
+    cnt = torch.tensor([emitted, accepted], dtype=torch.float64, device=f"cuda:{local}")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(cnt, op=dist.ReduceOp.SUM)
+    ms, wall = float(t[0]), float(t[1])
+    emitted, accepted = float(cnt[0]), float(cnt[1])
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        weights, kv, state = decode_config_bytes(cfg, context)
+        # bytes streamed by the matvec kernel per block: target pass + k MTP passes + draft heads
+        mtp_layer = (weights - (cfg.vocab_size * (cfg.hidden_size // 64) * 34)) // cfg.num_hidden_layers
+        stream_bytes = weights + cfg.max_draft_tokens * (
+            mtp_layer + cfg.hidden_size * (2 * cfg.hidden_size // 64) * 34 +
+            cfg.draft_vocab * (cfg.hidden_size // 64) * 34)
+        achieved = stream_bytes * blocks_timed / (kernel_ms * 1e-3) / 1e9
+        cpu_val, cpu_s = cpu_baseline(threads=1, avx2=False, repeats=3)
+        cpu_tok_s = 1.0 / ((weights + kv + state) / (cpu_val * 1e9))
+        line = {
+            "metric": "decode_tokens_per_s_mtp", "value": emitted / (ms * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": f"qwen3.8-27b-shaped decode, 64 layers, batch 1, context {context}, MTP k=4 "
+                                   "(BASELINE config 4)",
+                       "weights": "Q4_B64 attention/embedding, Q2_B64 FFN, random init",
+                       "kv": "bf16, 16-token pages", "l2": "11.8 GB streamed per pass (>> 126 MB L2)",
+                       "parallelism": "replicas" if world > 1 else "single",
+                       "acceptance": "as measured on random-init weights"},
+            "mean_accepted_drafts_per_block": accepted / (args.steps * world),
+            "tokens_per_s_without_mtp": plain,
+            "tokens_per_s_forced_acceptance": buckets,
+            "host_reads_per_block": 1,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "frac_of_8000_nominal": achieved / 8000.0,
+                         "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (all launches of a block)",
+                         "bytes_per_block": stream_bytes, "launches_per_block": launches / blocks_timed,
+                         "traffic": None},
+            "pass_bytes": {"weights": weights, "kv": kv, "state": state},
+            "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": 1, "kind": "port",
+                             "sample": f"scalar-verifier matvec on one 17408x5120 Q4 matrix ({cpu_val:.3f} GB/s, "
+                                       f"{cpu_s * 1e3:.0f} ms), scaled to the {(weights + kv + state) / 1e9:.1f} GB "
+                                       "of one target pass"},
+            "e2e": {"value": emitted / world / wall * world, "unit": "tokens/s",
+                    "h2d_bytes_per_step": 4 * (1 + 5), "d2h_bytes_per_step": 292,
+                    "note": "decode() takes a host token and returns a host record; same calls, wall clock"},
+            "gpu_launches": launches_per_block(cfg) * args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    ex.unload()
+    be.close()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_b200(args):
@@ -258,12 +424,20 @@ def run_b200(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "q4_matvec"])
+    ap.add_argument("--context", type=int, default=32768)
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 256 if args.workload == "decode" else 2000
+    if args.warmup is None:
+        args.warmup = 4 if args.workload == "decode" else 50
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_b200(args)
 
