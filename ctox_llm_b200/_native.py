@@ -146,6 +146,8 @@ SIGNATURES = {
     "ctox_matvec_destroy": (C.c_int32, [C.c_void_p]),
     "ctox_matvec_dispatch": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64,
                                          C.c_void_p, C.c_uint64, C.c_uint32]),
+    "ctox_matvec_dispatch_static": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32,
+                                                C.c_uint64, C.c_void_p, C.c_uint64]),
     "ctox_matvec_dispatch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                               C.c_uint32]),
     "ctox_gated_delta_scan": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),

@@ -270,6 +270,14 @@ class PreparedMatVec:
                 "path": [int(x) for x in rec.path[:max(k - 1, 0)]],
                 "node_argmax": [int(x) for x in rec.node_argmax[:n]]}
 
+    def dispatch_static(self, x_ptr: int, x_dtype: int, positions: int, x_stride: int, y_ptr: int,
+                        y_stride: int) -> None:
+        """Same as dispatch_device, but the kernel's scratch is the fixed 8 MiB array inside the
+        library, so nothing is allocated: for callers that must not touch the device allocator
+        (see ctox_matvec_dispatch_static in include/ctox_b200.h for the limits)."""
+        self._b._check(self._b._lib.ctox_matvec_dispatch_static(
+            self._h, C.c_void_p(x_ptr), x_dtype, positions, x_stride, C.c_void_p(y_ptr), y_stride))
+
     def info(self) -> dict:
         r, c, p, d = C.c_uint64(), C.c_uint64(), C.c_uint64(), C.c_uint64()
         self._b._check(self._b._lib.ctox_matvec_info(self._h, C.byref(r), C.byref(c), C.byref(p),

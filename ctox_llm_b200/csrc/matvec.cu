@@ -1368,3 +1368,119 @@ ctox_status ctox_recovered_row_matvec(ctox_ctx *ctx, uint32_t dtype, const uint8
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------ dispatch without allocation
+// Some callers must not allocate device memory around a dispatch: a real-time serving loop that
+// has handed every free byte to its KV cache, a plug-in running inside another framework's
+// memory pool, or code between two points where cudaMalloc's implicit device synchronisation
+// would stall other streams. For them the scratch of the streaming kernel (activation fragments,
+// per-block metadata and the partial sums) lives in one fixed array inside the library image
+// instead of buffers owned by the handle. Every GPU that loads the library carries the array
+// until the process exits.
+namespace {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;  // 8 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// The array's name is only a host-side stand-in; kernels need its device address, which is looked
+// up once per device with that device current.
+ctox_status static_scratch_address(ctox_ctx *ctx, unsigned char **out) {
+    constexpr int kMaxDevices = 64;
+    static unsigned char *cached[kMaxDevices] = {nullptr};
+    if (ctx->device < 0 || ctx->device >= kMaxDevices)
+        return fail(ctx, CTOX_SHAPE, "device index %d has no static scratch slot", ctx->device);
+    if (!cached[ctx->device]) {
+        CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(ctx, CTOX_INVALID_STATE, "cudaGetSymbolAddress(static scratch) failed: %s",
+                        cudaGetErrorString(e));
+        cached[ctx->device] = static_cast<unsigned char *>(ptr);
+    }
+    *out = cached[ctx->device];
+    return CTOX_OK;
+}
+
+size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+}  // namespace
+
+extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *x_dev, uint32_t x_dtype,
+                                                   uint32_t positions, uint64_t x_stride, float *y_dev,
+                                                   uint64_t y_stride) {
+    if (!mv) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = mv->ctx;
+    if (!x_dev || !y_dev) return fail(ctx, CTOX_SHAPE, "dispatch_static: null device pointer");
+    if (positions == 0 || positions > 16)
+        return fail(ctx, CTOX_SHAPE, "dispatch_static: positions must be 1..16, got %u", positions);
+    if (x_dtype != CTOX_F32 && x_dtype != CTOX_BF16)
+        return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "dispatch_static: activation dtype %u", x_dtype);
+    if (x_stride < mv->columns || y_stride < mv->rows)
+        return fail(ctx, CTOX_SHAPE, "dispatch_static: stride shorter than a row");
+    const uint32_t per_pass = matvec_positions_per_pass(mv);
+    if (per_pass == 0)
+        return fail(ctx, CTOX_MEMORY_BUDGET, "dispatch_static: columns %llu exceed the streaming kernel's budget",
+                    (unsigned long long)mv->columns);
+    // scratch layout: [fragments][metadata][partial sums of the largest part]
+    const uint32_t pass_max = positions < per_pass ? positions : per_pass;
+    const size_t frag_bytes = align256((size_t)mv->blocks_padded * 2 * pass_max * 128);
+    const size_t meta_bytes = align256((size_t)mv->blocks_padded * pass_max * sizeof(float2));
+    size_t partial_bytes = 0;
+    for (auto &p : mv->parts) partial_bytes = partial_bytes > p.partial_bytes ? partial_bytes : p.partial_bytes;
+    const size_t need = frag_bytes + meta_bytes + align256(partial_bytes);
+    if (need > kStaticScratchBytes)
+        return fail(ctx, CTOX_MEMORY_BUDGET,
+                    "dispatch_static: this %llux%llu operation needs %zu bytes of scratch, the built-in array "
+                    "holds %zu; use ctox_matvec_dispatch",
+                    (unsigned long long)mv->rows, (unsigned long long)mv->columns, need, kStaticScratchBytes);
+    unsigned char *base = nullptr;
+    ctox_status rc = static_scratch_address(ctx, &base);
+    if (rc) return rc;
+    uint8_t *xfrag = base;
+    float2 *meta = reinterpret_cast<float2 *>(base + frag_bytes);
+    float *partial = reinterpret_cast<float *>(base + frag_bytes + meta_bytes);
+    cudaStream_t st = ctx->stream;
+    const size_t esz = x_dtype == CTOX_BF16 ? 2 : 4;
+    for (uint32_t m0 = 0; m0 < positions; m0 += per_pass) {
+        const uint32_t npos = positions - m0 < per_pass ? positions - m0 : per_pass;
+        const uint8_t *xp = (const uint8_t *)x_dev + (size_t)m0 * x_stride * esz;
+        for (auto &p : mv->parts) {
+            const MatvecPart::Split &split = p.split[npos > 4 ? 1 : 0];
+            if (split.warps == 0)
+                return fail(ctx, CTOX_MEMORY_BUDGET, "dispatch_static: %u positions do not fit shared memory", npos);
+            const int groups = (int)(mv->blocks_padded * npos);
+            k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, st>>>(xp, x_dtype == CTOX_BF16, (long long)x_stride,
+                                                               mv->s_in, (int)mv->columns,
+                                                               (int)mv->blocks_padded, (int)npos, p.dt, xfrag, meta);
+            StreamParams sp;
+            sp.wprep = p.prep;
+            sp.xfrag = xfrag;
+            sp.meta = meta;
+            sp.partial = partial;
+            sp.error_flag = ctx->dev_error;
+            sp.pairs = p.pairs;
+            sp.kst_s = p.kst_s;
+            sp.slices = p.slices;
+            sp.ctas_per_slice = split.ctas_per_slice;
+            sp.warps_per_slice = split.warps_per_slice;
+            sp.npos = npos;
+            sp.max_pieces = p.max_pieces;
+            sp.dbg = 0;
+            const StreamCfg cfg{split.warps, split.stages};
+            const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
+            const unsigned grid = split.ctas_per_slice * p.slices;
+            if (p.dt)
+                launch_stream<1>(cfg, grid, smem, st, sp);
+            else
+                launch_stream<0>(cfg, grid, smem, st, sp);
+            const unsigned n_out = (unsigned)(p.rows * npos);
+            k_matvec_finish<<<(n_out + 255) / 256, 256, 0, st>>>(
+                partial, split.pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
+                mv->bias ? mv->bias + p.row_start : nullptr, y_dev + (size_t)m0 * y_stride + p.row_start,
+                (long long)y_stride, (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
+        }
+    }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}

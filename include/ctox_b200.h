@@ -170,6 +170,23 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
 /* Same, with host x and y (pinned staging inside the library); synchronises. */
 ctox_status ctox_matvec_dispatch_host(ctox_matvec *mv, const float *x_host, uint32_t positions,
                                       float *y_host, uint32_t kernel);
+/* No counterpart in the reference. Same result as ctox_matvec_dispatch (kernel
+ * AUTO) for callers that may not allocate device memory around a dispatch - a
+ * serving loop that has given every free byte to its cache, a plug-in inside a
+ * foreign memory pool, code where an allocation's implicit synchronisation is
+ * not acceptable. The kernel's scratch (activation fragments, block metadata,
+ * partial sums) is an 8 MiB array built into the library image; every GPU that
+ * loads the library keeps it until exit. Operations that need more scratch than
+ * that (for example a 248320-row head) fail with CTOX_MEMORY_BUDGET. The call
+ * makes no cudaMalloc/cudaFree and calls no allocating routine. The first call
+ * on a device looks the array's address up (cudaGetSymbolAddress) and should
+ * therefore come before any stream capture. All calls on a device share the one
+ * array and nothing in it has to start at zero, but two calls whose kernels
+ * overlap on the GPU (different streams or contexts) race on it: keep them on
+ * one stream or order them yourself. */
+ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *x_dev, uint32_t x_dtype,
+                                        uint32_t positions, uint64_t x_stride, float *y_dev,
+                                        uint64_t y_stride);
 /* Geometry of the prepared operation. */
 ctox_status ctox_matvec_info(const ctox_matvec *mv, uint64_t *rows, uint64_t *columns,
                              uint64_t *packed_bytes, uint64_t *device_bytes);
