@@ -241,18 +241,20 @@ def run_decode(args):
         sampler.start()
     ms, wall, emitted, accepted = run_blocks(args.steps, True, -1, True)
     clocks = sampler.stop() if rank == 0 else None
-    buckets = {}
-    for force in (0, 2, 4):
-        bms, _, bem, _ = run_blocks(max(args.steps // 8, 8), True, force, False)
-        buckets[f"accept_{force}"] = bem / (bms * 1e-3)
-    pms, _, pem, _ = run_blocks(max(args.steps // 8, 8), False, -1, False)
-    plain = pem / (pms * 1e-3)
+    buckets, plain = {}, None
+    if not args.quick:
+        for force in (0, 2, 4):
+            bms, _, bem, _ = run_blocks(max(args.steps // 8, 8), True, force, False)
+            buckets[f"accept_{force}"] = bem / (bms * 1e-3)
+        pms, _, pem, _ = run_blocks(max(args.steps // 8, 8), False, -1, False)
+        plain = pem / (pms * 1e-3)
     # dominant kernel (the streaming matvec) alone, event pairs around every launch
+    timing_blocks = 1 if args.quick else 4
     be.kernel_timing(True)
-    _, _, _, _ = run_blocks(4, True, -1, False)
+    _, _, _, _ = run_blocks(timing_blocks, True, -1, False)
     kernel_ms, launches = be.kernel_timing_read()
     be.kernel_timing(False)
-    blocks_timed = 4 + args.warmup
+    blocks_timed = timing_blocks + args.warmup
 
     t = torch.tensor([ms, wall], dtype=torch.float64, device=f"cuda:{local}")
     cnt = torch.tensor([emitted, accepted], dtype=torch.float64, device=f"cuda:{local}")
@@ -429,6 +431,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "q4_matvec"])
     ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--quick", action="store_true",
+                    help="decode: only the timed region and one kernel-timing block (for launch lists)")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 256 if args.workload == "decode" else 2000

@@ -27,6 +27,9 @@ struct ctox_ctx {
     void *scratch = nullptr;        // context-owned device scratch of the selection kernels
     size_t scratch_bytes = 0;
     std::string last_error;
+    // tensor parallelism: NCCL communicator over the GPUs of one box (tp.cu); world 1 = none
+    int tp_rank = 0, tp_world = 1;
+    void *nccl_comm = nullptr;
     // optional per-kernel timing of the dominant kernel (benchmark support)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timing_events;
@@ -64,6 +67,9 @@ void dev_free(ctox_ctx *ctx, void *ptr, size_t bytes);
 ctox_status ensure_pinned(ctox_ctx *ctx, size_t bytes);
 // Context-owned device scratch (not counted as a caller-visible allocation); grows on demand.
 ctox_status ensure_scratch(ctox_ctx *ctx, size_t bytes);
+// Collectives over the tensor-parallel group, enqueued on the context's stream (tp.cu).
+ctox_status tp_all_reduce_sum_f32(ctox_ctx *ctx, float *buf, size_t n);
+ctox_status tp_all_gather(ctox_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
 // When timing is enabled, brackets the next launches with a CUDA event pair on
 // the context's stream; both are no-ops otherwise.
 void timing_begin(ctox_ctx *ctx);
