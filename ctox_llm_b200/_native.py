@@ -128,6 +128,10 @@ SIGNATURES = {
     "ctox_ctx_create": (C.c_int32, [C.c_int32, C.c_void_p, C.POINTER(C.c_void_p)]),
     "ctox_ctx_destroy": (C.c_int32, [C.c_void_p]),
     "ctox_ctx_synchronize": (C.c_int32, [C.c_void_p]),
+    "ctox_tp_unique_id": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_void_p]),
+    "ctox_tp_init": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_int32, C.c_void_p]),
+    "ctox_tp_destroy": (C.c_int32, [C.c_void_p]),
+    "ctox_tp_all_reduce_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64]),
     "ctox_ctx_allocated_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "ctox_ctx_device_error": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32)]),
     "ctox_ctx_kernel_timing": (C.c_int32, [C.c_void_p, C.c_int32]),

@@ -10,6 +10,7 @@ on device pointers or host arrays.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -209,6 +210,44 @@ class B200Backend:
         ms, n = C.c_double(), C.c_uint64()
         self._check(self._lib.ctox_ctx_kernel_timing_read(self._ctx, C.byref(ms), C.byref(n)))
         return ms.value, n.value
+
+    # -- tensor-parallel group (one process per GPU; no counterpart in the reference) --------
+    tp_rank, tp_world = 0, 1
+
+    @staticmethod
+    def nccl_library() -> str:
+        """The NCCL that torch itself uses, so that one copy of the library serves both."""
+        try:
+            import nvidia.nccl as pkg
+            path = os.path.join(list(pkg.__path__)[0], "lib", "libnccl.so.2")
+            if os.path.exists(path):
+                return path
+        except ImportError:
+            pass
+        return "libnccl.so.2"
+
+    def tp_unique_id(self) -> bytes:
+        buf = (C.c_uint8 * 128)()
+        self._check(self._lib.ctox_tp_unique_id(self._ctx, self.nccl_library().encode(), buf))
+        return bytes(buf)
+
+    def tp_init(self, rank: int, world: int, unique_id: bytes) -> None:
+        if len(unique_id) != 128:
+            raise ValueError("a group id is 128 bytes")
+        buf = (C.c_uint8 * 128).from_buffer_copy(unique_id)
+        self._check(self._lib.ctox_tp_init(self._ctx, self.nccl_library().encode(), rank, world, buf))
+        self.tp_rank, self.tp_world = rank, world
+
+    def tp_init_from_torch(self) -> None:
+        """Joins a group that mirrors the default torch.distributed group (rank 0 draws the id)."""
+        import torch.distributed as dist
+        rank, world = dist.get_rank(), dist.get_world_size()
+        box = [self.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        self.tp_init(rank, world, box[0])
+
+    def tp_all_reduce(self, buf_ptr: int, n: int) -> None:
+        self._check(self._lib.ctox_tp_all_reduce_f32(self._ctx, C.c_void_p(buf_ptr), n))
 
     def close(self) -> None:
         if getattr(self, "_ctx", None):

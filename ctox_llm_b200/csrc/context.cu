@@ -128,6 +128,7 @@ ctox_status ctox_ctx_destroy(ctox_ctx *ctx) {
     if (!ctx) return CTOX_OK;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    ctox_tp_destroy(ctx);
     for (auto &ev : ctx->timing_events) {
         cudaEventDestroy(ev.first);
         cudaEventDestroy(ev.second);

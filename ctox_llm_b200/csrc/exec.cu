@@ -12,9 +12,17 @@
 // layers write the recurrent state of the whole pass into a second buffer (flip on full
 // acceptance) and keep the pass's conv inputs and (q, k, v, g, beta), so a partial acceptance
 // re-scans the recurrence alone (~6 MB per layer) instead of replaying whole model passes.
+//
+// Tensor parallelism (no counterpart in the reference): when the context belongs to a group of W
+// GPUs, every rank holds 1/W of the heads, of the FFN width and of the vocabulary. Fan-out
+// matrices are split by rows, the projections back to the hidden width by columns; their partial
+// results are summed over the group (2 all-reduces of m x hidden floats per layer). The residual
+// stream, the norms, the embedding and the small MTP input projection are replicated. The head
+// exchanges per-rank statistics (one all-gather per block), never logits.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdlib>
 #include <vector>
@@ -48,7 +56,12 @@ using namespace ctox;
 
 struct ctox_exec {
     ctox_ctx *ctx = nullptr;
-    ctox_model_config cfg{};
+    ctox_model_config cfg{};  // this rank's shard: heads and FFN width divided by the group size
+    uint32_t tp_world = 1, tp_rank = 0;
+    uint32_t vocab_l = 0, vocab_off = 0;      // rows of lm_head on this rank
+    uint32_t draft_lo = 0, draft_n = 0;       // this rank's range of the draft id table
+    std::vector<uint32_t> draft_ids_host;
+    float *tp_buf = nullptr;                  // [kMaxPass][hidden] vector being summed over the group
     uint32_t n_layers = 0;  // target layers; index n_layers is the MTP layer when present
     uint32_t key_width = 0, value_width = 0, channels = 0, q_width = 0, kv_width = 0;
     std::vector<LayerW> w;
@@ -100,9 +113,25 @@ size_t kv_elem(const ctox_exec *e) { return e->cfg.kv_dtype == CTOX_BF16 ? 2 : 4
 
 extern "C" {
 
-ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c, ctox_exec **out) {
-    if (!ctx || !c || !out) return CTOX_INVALID_STATE;
+ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c_global, ctox_exec **out) {
+    if (!ctx || !c_global || !out) return CTOX_INVALID_STATE;
     *out = nullptr;
+    const uint32_t W = (uint32_t)ctx->tp_world, R = (uint32_t)ctx->tp_rank;
+    ctox_model_config local = *c_global;
+    if (W > 1) {
+        const ctox_model_config &g = *c_global;
+        if (g.num_attention_heads % W || g.linear_num_key_heads % W || g.linear_num_value_heads % W ||
+            g.intermediate_size % (64 * W) || g.vocab_size % W || g.num_key_value_heads == 0 ||
+            (g.num_key_value_heads % W && W % g.num_key_value_heads))
+            return fail(ctx, CTOX_SHAPE, "executor: the model does not split over %u GPUs", W);
+        local.num_attention_heads /= W;
+        // fewer KV heads than ranks: neighbouring ranks hold a copy of the same KV head
+        local.num_key_value_heads = g.num_key_value_heads >= W ? g.num_key_value_heads / W : 1;
+        local.linear_num_key_heads /= W;
+        local.linear_num_value_heads /= W;
+        local.intermediate_size /= W;
+    }
+    const ctox_model_config *c = &local;
     if (c->hidden_size == 0 || c->hidden_size % 64 || c->intermediate_size % 64 || c->vocab_size == 0 ||
         c->num_hidden_layers == 0 || c->full_attention_interval == 0)
         return fail(ctx, CTOX_SHAPE, "executor: hidden/intermediate sizes must be non-zero multiples of 64");
@@ -125,6 +154,10 @@ ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c, ctox_exe
     e->ctx = ctx;
     e->cfg = *c;
     e->n_layers = c->num_hidden_layers;
+    e->tp_world = W;
+    e->tp_rank = R;
+    e->vocab_l = c->vocab_size / W;
+    e->vocab_off = R * e->vocab_l;
     e->key_width = c->linear_num_key_heads * 128;
     e->value_width = c->linear_num_value_heads * 128;
     e->channels = 2 * e->key_width + e->value_width;
@@ -196,7 +229,7 @@ bool matrix_slot(ctox_exec *e, uint32_t layer, uint32_t tensor, ctox_matvec ***s
     if (layer == CTOX_LAYER_GLOBAL) {
         switch (tensor) {
             case CTOX_T_EMBED: *slot = &e->embed; *shape = {c.vocab_size, H}; return true;
-            case CTOX_T_LM_HEAD: *slot = &e->lm_head; *shape = {c.vocab_size, H}; return true;
+            case CTOX_T_LM_HEAD: *slot = &e->lm_head; *shape = {e->vocab_l, H}; return true;
             case CTOX_T_MTP_FC:
                 if (!c.mtp_num_hidden_layers) return false;
                 *slot = &e->mtp_fc; *shape = {H, 2 * H}; return true;
@@ -299,6 +332,7 @@ ctox_status ctox_exec_load_vector(ctox_exec *e, uint32_t layer, uint32_t tensor,
         }
         CTOX_CUDA(ctx, cudaMemcpyAsync(e->draft_ids, ids, n * 4, cudaMemcpyHostToDevice, ctx->stream));
         CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        e->draft_ids_host.assign(ids, ids + n);
         e->warmed = false;
         return CTOX_OK;
     }
@@ -372,19 +406,19 @@ __global__ void k_fill_normal(T *__restrict__ out, uint64_t n, float mean, float
 }
 
 __global__ void k_gather_rows(const uint8_t *__restrict__ src, const uint32_t *__restrict__ ids,
-                              uint32_t row_bytes, uint32_t n, uint8_t *__restrict__ dst) {
+                              uint32_t id_offset, uint32_t row_bytes, uint32_t n, uint8_t *__restrict__ dst) {
     const uint32_t r = blockIdx.x;
     if (r >= n) return;
-    const uint8_t *s = src + (size_t)ids[r] * row_bytes;
+    const uint8_t *s = src + (size_t)(ids[r] - id_offset) * row_bytes;
     uint8_t *d = dst + (size_t)r * row_bytes;
     for (uint32_t i = threadIdx.x * 2; i < row_bytes; i += blockDim.x * 2)
         *reinterpret_cast<uint16_t *>(d + i) = *reinterpret_cast<const uint16_t *>(s + i);
 }
 
-__global__ void k_gather_f32(const float *__restrict__ src, const uint32_t *__restrict__ ids, uint32_t n,
-                             float *__restrict__ dst) {
+__global__ void k_gather_f32(const float *__restrict__ src, const uint32_t *__restrict__ ids,
+                             uint32_t id_offset, uint32_t n, float *__restrict__ dst) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dst[i] = src[ids[i]];
+    if (i < n) dst[i] = src[ids[i] - id_offset];
 }
 
 __global__ void k_iota_u32(uint32_t *out, uint32_t n, uint32_t stride) {
@@ -424,8 +458,10 @@ uint16_t f32_to_f16_bits(float f) {
     return u;
 }
 
+// `sharded`: this rank's slice of a matrix that is split over the group; its codes differ per rank,
+// the recovery scales follow the rank-independent seed.
 ctox_status synth_matrix(ctox_exec *e, int dt, uint64_t rows, uint64_t cols, const uint16_t *table_dev,
-                         uint64_t seed, float *shared_s_in, uint32_t flags, ctox_matvec **out) {
+                         uint64_t seed, bool sharded, uint32_t flags, ctox_matvec **out) {
     ctox_ctx *ctx = e->ctx;
     const uint32_t bb = dt ? 34 : 18;
     const uint64_t blocks = rows * (cols / 64);
@@ -435,12 +471,11 @@ ctox_status synth_matrix(ctox_exec *e, int dt, uint64_t rows, uint64_t cols, con
     if (!rc) rc = dev_alloc(ctx, (void **)&s_in, cols * 4);
     if (!rc) rc = dev_alloc(ctx, (void **)&s_out, rows * 4);
     if (rc) return rc;
-    k_fill_canonical<<<(unsigned)((blocks + 255) / 256), 256, 0, ctx->stream>>>(canon, blocks, bb, table_dev, seed);
-    if (shared_s_in)
-        CTOX_CUDA(ctx, cudaMemcpyAsync(s_in, shared_s_in, cols * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    else
-        k_fill_uniform_f16<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(s_in, cols, 0.75f, 1.25f,
-                                                                                 seed ^ 0x5151);
+    const uint64_t code_seed = sharded ? seed ^ (0xC2B2AE3D27D4EB4Full * (e->tp_rank + 1)) : seed;
+    k_fill_canonical<<<(unsigned)((blocks + 255) / 256), 256, 0, ctx->stream>>>(canon, blocks, bb, table_dev,
+                                                                               code_seed);
+    k_fill_uniform_f16<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(s_in, cols, 0.75f, 1.25f,
+                                                                             seed ^ 0x5151);
     k_fill_uniform_f16<<<(unsigned)((rows + 255) / 256), 256, 0, ctx->stream>>>(s_out, rows, 0.75f, 1.25f,
                                                                              seed ^ 0xA0A0);
     CTOX_CUDA(ctx, cudaGetLastError());
@@ -466,7 +501,15 @@ ctox_status build_draft_head(ctox_exec *e) {
     if (!e->draft_ids) return fail(ctx, CTOX_INVALID_STATE, "draft vocabulary configured but no id table loaded");
     MatvecPart &p = e->lm_head->parts[0];
     if (!p.canon) return fail(ctx, CTOX_INVALID_STATE, "lm_head canonical bytes are not resident");
-    const uint32_t n = e->cfg.draft_vocab;
+    // this rank's rows: the draft ids that fall into its vocabulary shard (ids ascend)
+    const auto &ids = e->draft_ids_host;
+    if (ids.size() != e->cfg.draft_vocab) return fail(ctx, CTOX_INVALID_STATE, "draft id table is incomplete");
+    const uint32_t lo = (uint32_t)(std::lower_bound(ids.begin(), ids.end(), e->vocab_off) - ids.begin());
+    const uint32_t hi = (uint32_t)(std::lower_bound(ids.begin(), ids.end(), e->vocab_off + e->vocab_l) - ids.begin());
+    e->draft_lo = lo;
+    e->draft_n = hi - lo;
+    const uint32_t n = e->draft_n;
+    if (n == 0) return CTOX_OK;  // no draft token in this shard: the rank only takes part in the merge
     const uint32_t row_bytes = (uint32_t)(e->lm_head->columns / 64) * (p.dt ? 34 : 18);
     uint8_t *canon = nullptr;
     float *s_in = nullptr, *s_out = nullptr;
@@ -474,10 +517,11 @@ ctox_status build_draft_head(ctox_exec *e) {
     if (!rc) rc = dev_alloc(ctx, (void **)&s_in, e->lm_head->columns * 4);
     if (!rc) rc = dev_alloc(ctx, (void **)&s_out, (size_t)n * 4);
     if (rc) return rc;
-    k_gather_rows<<<n, 128, 0, ctx->stream>>>(p.canon, e->draft_ids, row_bytes, n, canon);
+    k_gather_rows<<<n, 128, 0, ctx->stream>>>(p.canon, e->draft_ids + lo, e->vocab_off, row_bytes, n, canon);
     CTOX_CUDA(ctx, cudaMemcpyAsync(s_in, e->lm_head->s_in, e->lm_head->columns * 4, cudaMemcpyDeviceToDevice,
                                    ctx->stream));
-    k_gather_f32<<<(n + 255) / 256, 256, 0, ctx->stream>>>(e->lm_head->s_out, e->draft_ids, n, s_out);
+    k_gather_f32<<<(n + 255) / 256, 256, 0, ctx->stream>>>(e->lm_head->s_out, e->draft_ids + lo, e->vocab_off, n,
+                                                           s_out);
     CTOX_CUDA(ctx, cudaGetLastError());
     return matvec_create_device(ctx, p.dt, n, e->lm_head->columns, canon, (size_t)n * row_bytes, s_in, s_out, 0,
                                 &e->draft_head);
@@ -516,10 +560,17 @@ ctox_status ctox_exec_fill_synthetic(ctox_exec *e, uint64_t seed, float mu, floa
     if (e->lm_head && !e->lm_head_is_embed) replace(&e->lm_head);
     replace(&e->embed);
     // attention / embedding weights Q4, FFN weights Q2 (the benchmark configuration)
-    SYNTH(synth_matrix(e, 1, c.vocab_size, H, table_dev, next_seed(), nullptr, CTOX_PREPARE_KEEP_CANONICAL,
+    SYNTH(synth_matrix(e, 1, c.vocab_size, H, table_dev, next_seed(), false, CTOX_PREPARE_KEEP_CANONICAL,
                        &e->embed));
-    e->lm_head = e->embed;  // tied: one resident copy serves row gathers and the head
-    e->lm_head_is_embed = true;
+    if (e->tp_world == 1) {
+        e->lm_head = e->embed;  // tied: one resident copy serves row gathers and the head
+        e->lm_head_is_embed = true;
+    } else {  // the embedding is replicated, the head holds this rank's vocabulary rows
+        e->lm_head = nullptr;
+        e->lm_head_is_embed = false;
+        SYNTH(synth_matrix(e, 1, e->vocab_l, H, table_dev, next_seed(), true, CTOX_PREPARE_KEEP_CANONICAL,
+                           &e->lm_head));
+    }
     SYNTH(synth_vector(e, &e->final_norm, H, 0.f, 0.02f, next_seed()));
     for (uint32_t l = 0; l < e->w.size(); ++l) {
         LayerW &lw = e->w[l];
@@ -530,35 +581,37 @@ ctox_status ctox_exec_fill_synthetic(ctox_exec *e, uint64_t seed, float mu, floa
         SYNTH(synth_vector(e, &lw.in_ln, H, 0.f, 0.02f, next_seed()));
         SYNTH(synth_vector(e, &lw.post_ln, H, 0.f, 0.02f, next_seed()));
         if (lw.full) {
-            SYNTH(synth_matrix(e, 1, 2ull * e->q_width + 2ull * e->kv_width, H, table_dev, next_seed(), nullptr, 0,
+            SYNTH(synth_matrix(e, 1, 2ull * e->q_width + 2ull * e->kv_width, H, table_dev, next_seed(), true, 0,
                                &lw.in_fan));
-            SYNTH(synth_matrix(e, 1, H, e->q_width, table_dev, next_seed(), nullptr, 0, &lw.out));
+            SYNTH(synth_matrix(e, 1, H, e->q_width, table_dev, next_seed(), true, 0, &lw.out));
             SYNTH(synth_vector(e, &lw.q_norm, c.head_dim, 0.f, 0.02f, next_seed()));
             SYNTH(synth_vector(e, &lw.k_norm, c.head_dim, 0.f, 0.02f, next_seed()));
         } else {
             SYNTH(synth_matrix(e, 1, (uint64_t)e->channels + e->value_width + 2ull * c.linear_num_value_heads, H,
-                               table_dev, next_seed(), nullptr, 0, &lw.in_fan));
-            SYNTH(synth_matrix(e, 1, H, e->value_width, table_dev, next_seed(), nullptr, 0, &lw.out));
+                               table_dev, next_seed(), true, 0, &lw.in_fan));
+            SYNTH(synth_matrix(e, 1, H, e->value_width, table_dev, next_seed(), true, 0, &lw.out));
             SYNTH(synth_vector(e, &lw.conv_w, (uint64_t)e->channels * c.linear_conv_kernel_dim, 0.f, 0.3f,
                                next_seed()));
             SYNTH(synth_vector(e, &lw.a_log, c.linear_num_value_heads, 0.f, 0.5f, next_seed()));
             SYNTH(synth_vector(e, &lw.dt_bias, c.linear_num_value_heads, 0.f, 0.5f, next_seed()));
             SYNTH(synth_vector(e, &lw.lin_norm, 128, 1.f, 0.02f, next_seed()));
         }
-        SYNTH(synth_matrix(e, 0, 2 * F, H, table_dev, next_seed(), nullptr, 0, &lw.gate_up));
-        SYNTH(synth_matrix(e, 0, H, F, table_dev, next_seed(), nullptr, 0, &lw.down));
+        SYNTH(synth_matrix(e, 0, 2 * F, H, table_dev, next_seed(), true, 0, &lw.gate_up));
+        SYNTH(synth_matrix(e, 0, H, F, table_dev, next_seed(), true, 0, &lw.down));
     }
     if (c.mtp_num_hidden_layers) {
         replace(&e->mtp_fc);
-        SYNTH(synth_matrix(e, 1, H, 2 * H, table_dev, next_seed(), nullptr, 0, &e->mtp_fc));
+        SYNTH(synth_matrix(e, 1, H, 2 * H, table_dev, next_seed(), false, 0, &e->mtp_fc));
         SYNTH(synth_vector(e, &e->mtp_norm_e, H, 0.f, 0.02f, next_seed()));
         SYNTH(synth_vector(e, &e->mtp_norm_h, H, 0.f, 0.02f, next_seed()));
         SYNTH(synth_vector(e, &e->mtp_norm, H, 0.f, 0.02f, next_seed()));
     }
     if (c.draft_vocab) {
         if (!e->draft_ids) SYNTH(xalloc(e, (void **)&e->draft_ids, (size_t)c.draft_vocab * 4, false));
-        k_iota_u32<<<(c.draft_vocab + 255) / 256, 256, 0, ctx->stream>>>(e->draft_ids, c.draft_vocab,
-                                                                        c.vocab_size / c.draft_vocab);
+        const uint32_t stride = c.vocab_size / c.draft_vocab;
+        k_iota_u32<<<(c.draft_vocab + 255) / 256, 256, 0, ctx->stream>>>(e->draft_ids, c.draft_vocab, stride);
+        e->draft_ids_host.resize(c.draft_vocab);
+        for (uint32_t i = 0; i < c.draft_vocab; ++i) e->draft_ids_host[i] = i * stride;
     }
 #undef SYNTH
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -615,7 +668,8 @@ ctox_status ctox_exec_warmup(ctox_exec *e) {
     WALLOC(e->lz, P * e->value_width * 4);
     WALLOC(e->lcore, P * e->value_width * 4);
     WALLOC(e->norm_scratch, P * ((H + 255) / 256) * 4);
-    WALLOC(e->draft_logits, (size_t)(c.draft_vocab ? c.draft_vocab : c.vocab_size) * 4);
+    WALLOC(e->draft_logits, (size_t)(c.draft_vocab ? (e->draft_n ? e->draft_n : 1) : e->vocab_l) * 4);
+    if (e->tp_world > 1) WALLOC(e->tp_buf, P * H * 4);
     WALLOC(e->tokens_dev, (P + 1) * 4);
     WALLOC(e->mtp_tokens_dev, (P + 1) * 4);
     const uint32_t slots = (c.max_context_tokens + c.kv_page_tokens - 1) / c.kv_page_tokens * c.kv_page_tokens;
@@ -724,7 +778,7 @@ ctox_status ctox_exec_keep_logits(ctox_exec *e, int32_t enable) {
     if (!e) return CTOX_INVALID_STATE;
     e->keep_logits = enable != 0;
     if (e->keep_logits && !e->logits)
-        return xalloc(e, (void **)&e->logits, (size_t)kMaxPass * e->cfg.vocab_size * 4, true);
+        return xalloc(e, (void **)&e->logits, (size_t)kMaxPass * e->vocab_l * 4, true);
     return CTOX_OK;
 }
 
@@ -743,6 +797,18 @@ AttnGeom attn_geom(const ctox_exec *e) {
     const ctox_model_config &c = e->cfg;
     return AttnGeom{c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim, c.rope_theta,
                     c.rms_norm_epsilon};
+}
+
+// Column-split projection in a tensor-parallel group: finish this rank's partial result, sum it
+// over the group and hand the sum on as a plain vector. A single GPU passes the raw sums through.
+ctox_status group_sum(ctox_exec *e, ctox_matvec *mv, uint32_t m, MvOut *o) {
+    if (e->tp_world <= 1) return CTOX_OK;
+    const uint32_t H = e->cfg.hidden_size;
+    matvec_finish_enqueue(mv, m, e->tp_buf, H);
+    EX(tp_all_reduce_sum_f32(e->ctx, e->tp_buf, (size_t)m * H));
+    o->plain = e->tp_buf;
+    o->plain_stride = H;
+    return CTOX_OK;
 }
 
 // One decoder layer for m positions. The fragments of the layer's fused input projection are
@@ -776,13 +842,15 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
                          c.kv_page_tokens, slot0, m, splits, e->attn_ws, out_in);
     }
     EX(matvec_stream_prepared(lw.out, 0, m));
-    const MvOut o = mv_out(lw.out, m);
+    MvOut o = mv_out(lw.out, m);
+    EX(group_sum(e, lw.out, m, &o));
     const MvIn gu_in = mv_in(lw.gate_up);
     launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in, e->norm_scratch);
     EX(matvec_stream_prepared(lw.gate_up, 0, m));
     launch_swiglu_prep(st, mv_out(lw.gate_up, m), c.intermediate_size, m, mv_in(lw.down));
     EX(matvec_stream_prepared(lw.down, 0, m));
-    const MvOut d = mv_out(lw.down, m);
+    MvOut d = mv_out(lw.down, m);
+    EX(group_sum(e, lw.down, m, &d));
     if (next) {
         const MvIn nin = mv_in(next);
         launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, &nin, e->norm_scratch);
@@ -851,11 +919,15 @@ ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const float *h
     EX(layer_body(e, L, e->mtp_h, m, abs_pos0, abs_pos0 - 1, e->mtp_page_table, e->mtp_norm, e->mtp_hidden,
                   nullptr));
     if (draft_slot >= 0) {
-        ctox_matvec *head = e->draft_head ? e->draft_head : e->lm_head;
-        EX(matvec_stream_pass(head, 0, e->mtp_hidden + (size_t)(m - 1) * c.hidden_size, CTOX_F32, 1,
-                              c.hidden_size));
-        matvec_finish_enqueue(head, 1, e->draft_logits, head->rows);
-        EX(argmax_enqueue(ctx, e->draft_logits, (uint32_t)head->rows, e->draft_head ? e->draft_ids : nullptr,
+        const bool restricted = c.draft_vocab != 0;
+        ctox_matvec *head = restricted ? e->draft_head : e->lm_head;  // null: no draft row on this rank
+        if (head) {
+            EX(matvec_stream_pass(head, 0, e->mtp_hidden + (size_t)(m - 1) * c.hidden_size, CTOX_F32, 1,
+                                  c.hidden_size));
+            matvec_finish_enqueue(head, 1, e->draft_logits, head->rows);
+        }
+        EX(argmax_enqueue(ctx, e->draft_logits, head ? (uint32_t)head->rows : 0,
+                          restricted ? e->draft_ids + e->draft_lo : nullptr, e->vocab_off,
                           e->tokens_dev + draft_slot, nullptr));
     }
     return CTOX_OK;
@@ -945,8 +1017,9 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
     for (uint32_t i = 0; i < m; ++i) parent[i] = (int32_t)i - 1;
     const float inv_t = temperature > 0.f ? 1.0f / temperature : 0.f;
     const uint64_t step_id = e->step_counter++;
-    EX(head_verify_enqueue(e->lm_head, 0, m, m, parent, e->tokens_dev, inv_t, seed, step_id, c.vocab_size,
-                           e->keep_logits ? e->logits : nullptr));
+    EX(head_verify_enqueue(e->lm_head, 0, m, m, parent, e->tokens_dev, inv_t, seed, step_id, e->vocab_l,
+                           e->keep_logits ? e->logits : nullptr, e->vocab_off));
+    EX(head_tp_merge_enqueue(ctx, m, parent, e->tokens_dev, e->vocab_l));
     ctox_spec_record *rec_dev = nullptr;
     EX(head_accept_enqueue(ctx, m, parent, e->tokens_dev, inv_t, seed, step_id,
                            force_accept < 0 ? -1 : (force_accept > (int32_t)k ? (int32_t)k : force_accept),
@@ -996,8 +1069,8 @@ ctox_status ctox_exec_last_logits(ctox_exec *e, uint32_t position, float *out) {
     ctox_ctx *ctx = e->ctx;
     if (!e->keep_logits || !e->logits || position >= kMaxPass)
         return fail(ctx, CTOX_INVALID_STATE, "logits are not kept (ctox_exec_keep_logits) or position out of range");
-    CTOX_CUDA(ctx, cudaMemcpyAsync(out, e->logits + (size_t)position * e->cfg.vocab_size,
-                                   (size_t)e->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaMemcpyAsync(out, e->logits + (size_t)position * e->vocab_l, (size_t)e->vocab_l * 4,
+                                   cudaMemcpyDeviceToHost, ctx->stream));
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return CTOX_OK;
 }

@@ -17,6 +17,7 @@
 #include "matvec.cuh"
 
 #include <cmath>
+#include <cstddef>
 
 namespace ctox {
 
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
     uint32_t npos,
     float inv_temperature, unsigned long long seed, unsigned long long step, TreeDesc tree,
     NodeStat *__restrict__ cta_stats, float *__restrict__ child_z, float *__restrict__ logits_out,
-    unsigned long long logits_stride) {
+    unsigned long long logits_stride, uint32_t row_offset) {
     __shared__ NodeStat sh[kHeadThreads / 32][kMaxPosPerPass];
     NodeStat st[kMaxPosPerPass];
 #pragma unroll
@@ -106,7 +107,8 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
                 st[m].nonfinite = 1;
                 continue;
             }
-            const unsigned long long pk = pack_key_index(logit, row);
+            const uint32_t token = row + row_offset;  // rows of a vocabulary shard start at row_offset
+            const unsigned long long pk = pack_key_index(logit, token);
             st[m].argmax = pk > st[m].argmax ? pk : st[m].argmax;
             if (inv_temperature > 0.f) {
                 const float z = logit * inv_temperature;
@@ -123,12 +125,12 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
                 }
                 bool is_child = false;
                 for (uint32_t c = node + 1; c < tree.n_nodes; ++c)
-                    if ((uint32_t)tree.parent[c] == node && tree.token[c] == row) {
+                    if ((uint32_t)tree.parent[c] == node && tree.token[c] == token) {
                         is_child = true;
                         child_z[c] = z;  // one writer: the row is unique
                     }
                 if (!is_child) {
-                    const unsigned long long gk = pack_key_index(z + gumbel_noise(seed, step, node, row), row);
+                    const unsigned long long gk = pack_key_index(z + gumbel_noise(seed, step, node, token), token);
                     st[m].gumbel = gk > st[m].gumbel ? gk : st[m].gumbel;
                 }
             }
@@ -177,6 +179,25 @@ __global__ void k_head_merge(const NodeStat *__restrict__ cta_stats, uint32_t n_
         merge_stat(a, other);
     }
     if (lane == 0) node_stats[node0 + m] = a;
+}
+
+// Tensor-parallel vocabulary: every rank holds the statistics of its shard and the logit of the
+// children whose token lies in its shard. gathered = [world][kMaxNodes stats | kMaxNodes child_z];
+// the merge runs in rank order on every rank, so all ranks resolve the same record.
+struct RankStats {
+    NodeStat node[kMaxNodes];
+    float child_z[kMaxNodes];
+};
+__global__ void k_head_merge_ranks(const RankStats *__restrict__ gathered, uint32_t world, uint32_t shard_rows,
+                                   TreeDesc tree, RankStats *__restrict__ out) {
+    const uint32_t n = threadIdx.x;
+    if (n >= tree.n_nodes) return;
+    NodeStat a = gathered[0].node[n];
+    for (uint32_t r = 1; r < world; ++r) merge_stat(a, gathered[r].node[n]);
+    out->node[n] = a;
+    uint32_t owner = tree.token[n] / shard_rows;
+    if (owner >= world) owner = world - 1;
+    out->child_z[n] = gathered[owner].child_z[n];
 }
 
 // Walks the draft tree with the statistics of every node. One thread: the walk is
@@ -293,9 +314,11 @@ __global__ void __launch_bounds__(kHeadThreads) k_argmax_partial(const float *__
 
 // result[0] = token (mapped through row_ids when given, engine.rs:203-217), result[1] = status
 // (1 = a logit is not finite, kernels/cuda/q2q4_fused_matvec_sm86.cu:2583-2585).
+// With packed_out the (key, token) pair is stored as well, for the merge over a tensor-parallel group.
 __global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t n_parts,
-                               const uint32_t *__restrict__ row_ids, uint32_t *__restrict__ token_out,
-                               uint32_t *__restrict__ status_out) {
+                               const uint32_t *__restrict__ row_ids, uint32_t row_offset,
+                               uint32_t *__restrict__ token_out, uint32_t *__restrict__ status_out,
+                               ArgmaxPartial *__restrict__ packed_out) {
     if (threadIdx.x != 0) return;
     ArgmaxPartial a = parts[0];
     for (uint32_t i = 1; i < n_parts; ++i) {
@@ -303,7 +326,22 @@ __global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t
         a.nonfinite |= parts[i].nonfinite;
     }
     const uint32_t row = (uint32_t)(a.best & 0xffffffffull);
-    *token_out = row_ids ? row_ids[row] : row;
+    const uint32_t token = row_ids ? row_ids[row] : row + row_offset;
+    if (token_out) *token_out = token;
+    if (status_out) *status_out = a.nonfinite;
+    if (packed_out) *packed_out = ArgmaxPartial{(a.best & 0xffffffff00000000ull) | token, a.nonfinite, 0};
+}
+
+// Greatest (key, token) over the ranks' local results; an empty shard contributes best == 0.
+__global__ void k_argmax_ranks(const ArgmaxPartial *__restrict__ gathered, uint32_t world,
+                               uint32_t *__restrict__ token_out, uint32_t *__restrict__ status_out) {
+    if (threadIdx.x != 0) return;
+    ArgmaxPartial a = gathered[0];
+    for (uint32_t r = 1; r < world; ++r) {
+        a.best = gathered[r].best > a.best ? gathered[r].best : a.best;
+        a.nonfinite |= gathered[r].nonfinite;
+    }
+    *token_out = (uint32_t)(a.best & 0xffffffffull);
     if (status_out) *status_out = a.nonfinite;
 }
 
@@ -314,10 +352,14 @@ using namespace ctox;
 namespace {
 constexpr uint32_t kHeadGridMax = 592;  // 4 CTAs per SM on 148 SMs
 
+constexpr uint32_t kMaxTpWorld = 8;
+
 struct HeadScratch {
     NodeStat *cta_stats;   // [grid][kMaxPosPerPass]
-    NodeStat *node_stats;  // [kMaxNodes]
-    float *child_z;        // [kMaxNodes]
+    NodeStat *node_stats;  // [kMaxNodes]   } one RankStats: what a rank contributes to the
+    float *child_z;        // [kMaxNodes]   } tensor-parallel merge
+    RankStats *gathered;   // [kMaxTpWorld]
+    ArgmaxPartial *argmax_send, *argmax_gathered;  // [1], [kMaxTpWorld]
     ctox_spec_record *record;
     ArgmaxPartial *argmax_parts;  // [grid]
     uint32_t *argmax_result;      // [2]
@@ -332,8 +374,11 @@ ctox_status head_scratch(ctox_ctx *ctx, HeadScratch &hs) {
         return o;
     };
     const size_t o_cta = take(sizeof(NodeStat) * kHeadGridMax * kMaxPosPerPass);
-    const size_t o_node = take(sizeof(NodeStat) * kMaxNodes);
-    const size_t o_child = take(sizeof(float) * kMaxNodes);
+    const size_t o_node = take(sizeof(RankStats));
+    const size_t o_child = o_node + offsetof(RankStats, child_z);
+    const size_t o_gath = take(sizeof(RankStats) * kMaxTpWorld);
+    const size_t o_as = take(sizeof(ArgmaxPartial));
+    const size_t o_ag = take(sizeof(ArgmaxPartial) * kMaxTpWorld);
     const size_t o_rec = take(sizeof(ctox_spec_record));
     const size_t o_ap = take(sizeof(ArgmaxPartial) * kHeadGridMax);
     const size_t o_ar = take(sizeof(uint32_t) * 2);
@@ -344,6 +389,9 @@ ctox_status head_scratch(ctox_ctx *ctx, HeadScratch &hs) {
     hs.cta_stats = (NodeStat *)(b + o_cta);
     hs.node_stats = (NodeStat *)(b + o_node);
     hs.child_z = (float *)(b + o_child);
+    hs.gathered = (RankStats *)(b + o_gath);
+    hs.argmax_send = (ArgmaxPartial *)(b + o_as);
+    hs.argmax_gathered = (ArgmaxPartial *)(b + o_ag);
     hs.record = (ctox_spec_record *)(b + o_rec);
     hs.argmax_parts = (ArgmaxPartial *)(b + o_ap);
     hs.argmax_result = (uint32_t *)(b + o_ar);
@@ -366,7 +414,8 @@ ctox_status ctox_argmax_f32(ctox_ctx *ctx, const float *logits_dev, uint32_t n, 
     if (grid > kHeadGridMax) grid = kHeadGridMax;
     if (grid == 0) grid = 1;
     k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
-    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, result_dev, result_dev + 1);
+    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, 0, result_dev, result_dev + 1,
+                                              nullptr);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
@@ -395,7 +444,7 @@ namespace ctox {
 
 ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, uint32_t n_nodes,
                                 const int32_t *parent, const uint32_t *tokens_dev, float inv_t, uint64_t seed,
-                                uint64_t step, uint32_t rows, float *logits_out_dev) {
+                                uint64_t step, uint32_t rows, float *logits_out_dev, uint32_t row_offset) {
     ctox_ctx *ctx = mv->ctx;
     HeadScratch hs;
     ctox_status rc = head_scratch(ctx, hs);
@@ -411,7 +460,7 @@ ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, 
     k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out,
                                                         mv->bias, rows, p.slices, p.max_pieces, node0, npos,
                                                         inv_t, seed, step, tree, hs.cta_stats, hs.child_z,
-                                                        logits_out_dev, (unsigned long long)mv->rows);
+                                                        logits_out_dev, (unsigned long long)mv->rows, row_offset);
     k_head_merge<<<1, 32 * kMaxPosPerPass, 0, ctx->stream>>>(hs.cta_stats, grid, node0, npos, hs.node_stats);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
@@ -436,15 +485,50 @@ ctox_status head_accept_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *
 }
 
 ctox_status argmax_enqueue(ctox_ctx *ctx, const float *logits_dev, uint32_t n, const uint32_t *row_ids_dev,
-                           uint32_t *token_dev, uint32_t *status_dev) {
+                           uint32_t row_offset, uint32_t *token_dev, uint32_t *status_dev) {
     HeadScratch hs;
     ctox_status rc = head_scratch(ctx, hs);
     if (rc) return rc;
-    uint32_t grid = (n + kHeadThreads * 4 - 1) / (kHeadThreads * 4);
-    if (grid > kHeadGridMax) grid = kHeadGridMax;
-    if (grid == 0) grid = 1;
-    k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
-    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, token_dev, status_dev);
+    const bool tp = ctx->tp_world > 1;
+    if (n == 0) {  // an empty shard of a tensor-parallel draft head
+        if (!tp) return fail(ctx, CTOX_INVALID_ARTIFACT, "greedy logits are empty");
+        CTOX_CUDA(ctx, cudaMemsetAsync(hs.argmax_send, 0, sizeof(ArgmaxPartial), ctx->stream));
+    } else {
+        uint32_t grid = (n + kHeadThreads * 4 - 1) / (kHeadThreads * 4);
+        if (grid > kHeadGridMax) grid = kHeadGridMax;
+        if (grid == 0) grid = 1;
+        k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
+        k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, row_offset,
+                                                  tp ? nullptr : token_dev, tp ? nullptr : status_dev,
+                                                  tp ? hs.argmax_send : nullptr);
+    }
+    if (tp) {
+        rc = tp_all_gather(ctx, hs.argmax_send, hs.argmax_gathered, sizeof(ArgmaxPartial));
+        if (rc) return rc;
+        k_argmax_ranks<<<1, 32, 0, ctx->stream>>>(hs.argmax_gathered, (uint32_t)ctx->tp_world, token_dev, status_dev);
+    }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+// Tensor-parallel vocabulary: exchanges the per-rank statistics and leaves the merged ones where
+// head_accept_enqueue reads them. shard_rows = vocabulary rows per rank.
+ctox_status head_tp_merge_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *parent,
+                                  const uint32_t *tokens_dev, uint32_t shard_rows) {
+    if (ctx->tp_world <= 1) return CTOX_OK;
+    if ((uint32_t)ctx->tp_world > kMaxTpWorld) return fail(ctx, CTOX_SHAPE, "tensor-parallel group larger than %u", kMaxTpWorld);
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    rc = tp_all_gather(ctx, hs.node_stats, hs.gathered, sizeof(RankStats));
+    if (rc) return rc;
+    TreeDesc tree;
+    memset(&tree, 0, sizeof tree);
+    tree.n_nodes = n_nodes;
+    tree.token = tokens_dev;
+    for (uint32_t i = 0; i < n_nodes; ++i) tree.parent[i] = parent[i];
+    k_head_merge_ranks<<<1, 32, 0, ctx->stream>>>(hs.gathered, (uint32_t)ctx->tp_world, shard_rows, tree,
+                                                  (RankStats *)hs.node_stats);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
@@ -500,7 +584,7 @@ ctox_status ctox_lmhead_verify(ctox_matvec *mv, const void *hidden_dev, uint32_t
                                 hidden_dtype, npos, hidden_stride);
         if (rc) return rc;
         rc = head_verify_enqueue(mv, n0, npos, n_nodes, parent, hs.tokens, inv_t, seed, step, rows,
-                                 logits_out_dev);
+                                 logits_out_dev, 0);
         if (rc) return rc;
     }
     ctox_spec_record *rec_dev = nullptr;

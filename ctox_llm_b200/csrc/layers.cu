@@ -16,13 +16,14 @@ namespace ctox {
 
 MvOut mv_out(ctox_matvec *mv, uint32_t npos) {
     MatvecPart &p = mv->parts[0];
-    return MvOut{p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, p.slices, p.max_pieces};
+    return MvOut{p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, p.slices, p.max_pieces, nullptr, 0};
 }
 MvIn mv_in(ctox_matvec *mv) {
     return MvIn{mv->xfrag, mv->meta, mv->s_in, (uint32_t)mv->columns, mv->blocks_padded, mv->parts[0].dt};
 }
 
 __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t pos) {
+    if (o.plain) return o.plain[(size_t)pos * o.plain_stride + row];
     return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
 }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
@@ -107,7 +108,7 @@ __global__ void k_norm_prep(const float *__restrict__ h, const float *__restrict
 
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
                                uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch) {
-    MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0};
+    MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0, nullptr, 0};
     MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
     const uint32_t nparts = (hidden + 255) / 256;
     k_residual_add<<<dim3(nparts, m), 256, 0, st>>>(h, a, add != nullptr, hidden, scratch);

@@ -15,6 +15,10 @@ struct MvOut {
     const uint8_t *pieces;
     const float *s_out;
     uint32_t slices, max_pieces;
+    // When set, the output is this finished vector instead ([position][plain_stride]): the form a
+    // column-split matvec has after its partial results were summed over the tensor-parallel group.
+    const float *plain;
+    uint32_t plain_stride;
 };
 // Input of the next matvec: where to write the activation fragments.
 struct MvIn {

@@ -74,10 +74,15 @@ void matvec_finish_enqueue(ctox_matvec *mv, uint32_t npos, float *y, uint64_t y_
 // node0 .. node0+npos; then the acceptance walk over all nodes, whose record stays on the device.
 ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, uint32_t n_nodes,
                                 const int32_t *parent, const uint32_t *tokens_dev, float inv_t, uint64_t seed,
-                                uint64_t step, uint32_t rows, float *logits_out_dev);
+                                uint64_t step, uint32_t rows, float *logits_out_dev, uint32_t row_offset);
+// Tensor-parallel vocabulary: merges the ranks' statistics (all-gather) before the acceptance walk.
+ctox_status head_tp_merge_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *parent,
+                                  const uint32_t *tokens_dev, uint32_t shard_rows);
 ctox_status head_accept_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *parent,
                                 const uint32_t *tokens_dev, float inv_t, uint64_t seed, uint64_t step,
                                 int force_accept, ctox_spec_record **record_dev);
+// Greedy token of a logit vector; token = row_ids[row] or row + row_offset. In a tensor-parallel
+// group every rank passes its shard and all ranks receive the group's token.
 ctox_status argmax_enqueue(ctox_ctx *ctx, const float *logits_dev, uint32_t n, const uint32_t *row_ids_dev,
-                           uint32_t *token_dev, uint32_t *status_dev);
+                           uint32_t row_offset, uint32_t *token_dev, uint32_t *status_dev);
 }  // namespace ctox

@@ -129,7 +129,8 @@ class B200Executor:
         self._b._check(self._lib.ctox_exec_keep_logits(self._h, int(enable)))
 
     def last_logits(self, position: int = 0) -> np.ndarray:
-        out = np.zeros(self.config.vocab_size, dtype=np.float32)
+        # in a tensor-parallel group: this rank's vocabulary rows [rank * n, (rank + 1) * n)
+        out = np.zeros(self.config.vocab_size // self._b.tp_world, dtype=np.float32)
         self._b._check(self._lib.ctox_exec_last_logits(self._h, position,
                                                        out.ctypes.data_as(C.c_void_p)))
         return out

@@ -115,6 +115,20 @@ typedef struct {
 ctox_status ctox_ctx_create(int32_t device, void *stream, ctox_ctx **out);
 ctox_status ctox_ctx_destroy(ctox_ctx *ctx);
 ctox_status ctox_ctx_synchronize(ctox_ctx *ctx);
+
+/* ---- tensor-parallel group (no counterpart in the reference, which runs on one GPU) ----
+ * One process per GPU of an NVSwitch box. Rank 0 draws an id, the caller carries its 128 bytes
+ * to the other ranks (any rendezvous, e.g. torch.distributed), then every rank joins. NCCL is
+ * loaded at run time from nccl_path (NULL or "" = "libnccl.so.2" on the loader's search path).
+ * An executor created on a context that has joined a group holds this rank's shard of the model
+ * (include/ctox_b200.h: ctox_exec_create). Collectives are enqueued on the context's stream;
+ * every rank must make the same executor calls in the same order. */
+ctox_status ctox_tp_unique_id(ctox_ctx *ctx, const char *nccl_path, uint8_t *id128);
+ctox_status ctox_tp_init(ctox_ctx *ctx, const char *nccl_path, int32_t rank, int32_t world,
+                         const uint8_t *id128);
+ctox_status ctox_tp_destroy(ctox_ctx *ctx);
+/* Sum of an fp32 device buffer over the group, in place (the collective the executor uses). */
+ctox_status ctox_tp_all_reduce_f32(ctox_ctx *ctx, float *buf_dev, uint64_t n);
 /* Never NULL; empty when no call has failed. ctx may be NULL (creation errors). */
 const char *ctox_last_error_message(const ctox_ctx *ctx);
 /* Bytes of device memory currently owned through this context

@@ -40,6 +40,32 @@ class Matrix:
                                s_out=self.s_out)
 
 
+class Shard:
+    """Rows or columns of a Matrix, as the tensor-parallel executor of one rank loads them."""
+
+    def __init__(self, dtype, packed, rows, cols, s_in, s_out):
+        self.dtype, self.packed, self.rows, self.cols, self.s_in, self.s_out = dtype, packed, rows, cols, s_in, s_out
+
+
+def row_shard(m, ranges):
+    sel = np.concatenate([np.arange(a, b) for a, b in ranges])
+    packed = np.ascontiguousarray(m.packed.reshape(m.rows, -1)[sel]).reshape(-1)
+    s_out = np.ascontiguousarray(m.s_out.reshape(-1, 2)[sel]).reshape(-1)
+    return Shard(m.dtype, packed, sel.size, m.cols, m.s_in, s_out)
+
+
+def col_shard(m, c0, c1):
+    blocks = m.cols // 64
+    packed = np.ascontiguousarray(m.packed.reshape(m.rows, blocks, -1)[:, c0 // 64:c1 // 64]).reshape(-1)
+    s_in = np.ascontiguousarray(m.s_in.reshape(-1, 2)[c0:c1]).reshape(-1)
+    return Shard(m.dtype, packed, m.rows, c1 - c0, s_in, m.s_out)
+
+
+def span(rank, world, total):
+    n = total // world
+    return rank * n, (rank + 1) * n
+
+
 def concat(mats):
     """Rows of a fan-out group as one matrix (shared s_in)."""
     m0 = mats[0]
@@ -95,30 +121,52 @@ class OracleModel:
         self.reset()
 
     # ---- loading into the device executor
-    def load_into(self, ex):
+    def load_into(self, ex, rank=0, world=1):
+        """Loads the model, or with world > 1 this rank's shard of it: heads, FFN width and
+        vocabulary rows [rank/world, (rank+1)/world); norms, embedding and mtp.fc whole."""
         c, G = self.cfg, N.LAYER_GLOBAL
+        hd = c.head_dim
         emb = ctox.FusedMatVec(self.embed.dtype, self.embed.packed, self.embed.rows, self.embed.cols, None,
                                s_in=self.embed.s_in, s_out=self.embed.s_out)
         ex.load_matrix(G, N.T_EMBED, emb)
-        ex.load_matrix(G, N.T_LM_HEAD, concat([self.lm_head]))
+        ex.load_matrix(G, N.T_LM_HEAD, concat([row_shard(self.lm_head, [span(rank, world, c.vocab_size)])]))
         ex.load_vector(G, N.T_FINAL_NORM, self.final_norm)
+        q0, q1 = span(rank, world, c.num_attention_heads)
+        if c.num_key_value_heads >= world:
+            kv0, kv1 = span(rank, world, c.num_key_value_heads)
+        else:  # fewer KV heads than ranks: neighbours share one
+            kv0 = rank * c.num_key_value_heads // world
+            kv1 = kv0 + 1
+        lk0, lk1 = span(rank, world, c.linear_num_key_heads)
+        lv0, lv1 = span(rank, world, c.linear_num_value_heads)
+        f0, f1 = span(rank, world, c.intermediate_size)
+        lin_rows = [(lk0 * 128, lk1 * 128), (self.kw + lk0 * 128, self.kw + lk1 * 128),
+                    (2 * self.kw + lv0 * 128, 2 * self.kw + lv1 * 128)]
         for l, L in enumerate(self.layers):
             ex.load_vector(l, N.T_INPUT_NORM, L["in_ln"])
             ex.load_vector(l, N.T_POST_NORM, L["post_ln"])
             if L["full"]:
-                ex.load_matrix(l, N.T_ATTN_QKV, concat([L["q"], L["k"], L["v"]]))
-                ex.load_matrix(l, N.T_ATTN_O, concat([L["o"]]))
+                ex.load_matrix(l, N.T_ATTN_QKV, concat([row_shard(L["q"], [(q0 * 2 * hd, q1 * 2 * hd)]),
+                                                        row_shard(L["k"], [(kv0 * hd, kv1 * hd)]),
+                                                        row_shard(L["v"], [(kv0 * hd, kv1 * hd)])]))
+                ex.load_matrix(l, N.T_ATTN_O, concat([col_shard(L["o"], q0 * hd, q1 * hd)]))
                 ex.load_vector(l, N.T_Q_NORM, L["q_norm"])
                 ex.load_vector(l, N.T_K_NORM, L["k_norm"])
             else:
-                ex.load_matrix(l, N.T_LIN_IN, concat([L["qkv"], L["z"], L["a"], L["b"]]))
-                ex.load_matrix(l, N.T_LIN_OUT, concat([L["out"]]))
-                ex.load_vector(l, N.T_CONV_W, L["conv_w"])
-                ex.load_vector(l, N.T_A_LOG, L["a_log"])
-                ex.load_vector(l, N.T_DT_BIAS, L["dt_bias"])
+                ex.load_matrix(l, N.T_LIN_IN, concat([row_shard(L["qkv"], lin_rows),
+                                                      row_shard(L["z"], [(lv0 * 128, lv1 * 128)]),
+                                                      row_shard(L["a"], [(lv0, lv1)]),
+                                                      row_shard(L["b"], [(lv0, lv1)])]))
+                ex.load_matrix(l, N.T_LIN_OUT, concat([col_shard(L["out"], lv0 * 128, lv1 * 128)]))
+                kd = c.linear_conv_kernel_dim
+                conv = L["conv_w"].reshape(self.channels, kd)
+                ex.load_vector(l, N.T_CONV_W, np.concatenate([conv[a:b] for a, b in lin_rows]).reshape(-1))
+                ex.load_vector(l, N.T_A_LOG, L["a_log"][lv0:lv1])
+                ex.load_vector(l, N.T_DT_BIAS, L["dt_bias"][lv0:lv1])
                 ex.load_vector(l, N.T_LIN_NORM, L["lin_norm"])
-            ex.load_matrix(l, N.T_MLP_GATE_UP, concat([L["gate"], L["up"]]))
-            ex.load_matrix(l, N.T_MLP_DOWN, concat([L["down"]]))
+            ex.load_matrix(l, N.T_MLP_GATE_UP, concat([row_shard(L["gate"], [(f0, f1)]),
+                                                       row_shard(L["up"], [(f0, f1)])]))
+            ex.load_matrix(l, N.T_MLP_DOWN, concat([col_shard(L["down"], f0, f1)]))
         if c.mtp_num_hidden_layers:
             ex.load_matrix(G, N.T_MTP_FC, concat([self.mtp_fc]))
             ex.load_vector(G, N.T_MTP_NORM_E, self.mtp_norm_e)
