@@ -33,6 +33,11 @@ ALGO_BYTES = Q4_ROWS * (Q4_COLS // 64) * 34 + Q4_COLS * 4 + Q4_ROWS * 4  # 47 43
 REPLICAS = 8
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_stream launch over its algorithmic
+# bytes, from the ncu capture summarised in profiles/ (47.3907 MB for 47.3498 MB).
+NCU_TRAFFIC_RATIO = 47.3907 / 47.3498
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -298,7 +303,9 @@ def run_decode(args):
                          "frac": achieved / peak, "frac_of_8000_nominal": achieved / 8000.0,
                          "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (all launches of a block, per GPU)",
                          "bytes_per_block": stream_bytes, "launches_per_block": launches / blocks_timed,
-                         "traffic": None},
+                         "traffic": stream_bytes * NCU_TRAFFIC_RATIO,
+                         "traffic_note": "per block; dram bytes of the ncu capture of one 47.35 MB launch "
+                                         "(47.39 MB read, 0 written) scaled by the bytes streamed"},
             "pass_bytes": {"weights": weights, "kv": kv, "state": state},
             "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": 1, "kind": "port",
                              "sample": f"scalar-verifier matvec on one 17408x5120 Q4 matrix ({cpu_val:.3f} GB/s, "
@@ -410,7 +417,8 @@ def run_b200(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_8000_nominal": achieved / 8000.0,
                          "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream<Q4>",
-                         "kernel_us": kernel_ms / max(launches, 1) * 1e3, "traffic": None},
+                         "kernel_us": kernel_ms / max(launches, 1) * 1e3,
+                         "traffic": ALGO_BYTES * NCU_TRAFFIC_RATIO},
             "cpu_baseline": {"value": cpu_val, "unit": "GB/s", "cores": 1, "kind": "port",
                              "sample": f"whole 17408x5120 matvec, scalar-verifier arm, median of 5 "
                                        f"({cpu_s * 1e3:.1f} ms each)"},

@@ -75,6 +75,36 @@ ctox_status tp_all_gather(ctox_ctx *ctx, const void *send, void *recv, size_t by
 void timing_begin(ctox_ctx *ctx);
 void timing_end(ctox_ctx *ctx);
 
+// Programmatic dependent launch. A kernel launched through launch_pdl may begin while the kernel
+// before it in the stream is still running; it must execute pdl_wait() before it touches memory
+// that earlier work writes or reads (the wait returns once everything earlier in the stream has
+// completed and is visible), and EVERY kernel launched this way must execute it, so that
+// completion stays transitive along the stream. What a kernel does before the wait (staging its
+// own constant weights into shared memory) overlaps the tail of its predecessors.
+// pdl_launch() lets the next kernel in the stream be scheduled. CTOX_PDL=0 in the environment
+// turns the early start off (every launch then serialises as usual).
+bool pdl_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Device error codes written by kernels into ctx->dev_error.
 enum : int32_t {
     DEV_ERR_NONE = 0,

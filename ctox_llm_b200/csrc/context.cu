@@ -69,6 +69,16 @@ void timing_end(ctox_ctx *ctx) {
 
 using namespace ctox;
 
+namespace ctox {
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *v = getenv("CTOX_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return on;
+}
+}  // namespace ctox
+
 extern "C" {
 
 uint32_t ctox_abi_version(void) { return 1; }

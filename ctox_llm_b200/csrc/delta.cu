@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(128) k_gated_delta_scan128(
     const float *__restrict__ log_decay, const float *__restrict__ beta,
     const float *__restrict__ state_in, float *__restrict__ state_out, float *__restrict__ out,
     int tokens, int heads, int qk_heads) {
+    pdl_launch();
+    pdl_wait();
     const int head = blockIdx.x >> 2, slice = blockIdx.x & 3;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = slice * kDeltaSlice + lane;
@@ -107,6 +109,8 @@ __global__ void k_gated_delta_scan_generic(const float *__restrict__ q, const fl
                                            const float *__restrict__ beta, const float *__restrict__ state_in,
                                            float *__restrict__ state_out, float *__restrict__ out, int tokens,
                                            int heads, int qk_heads, int key_dim, int value_dim) {
+    pdl_launch();
+    pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= heads * value_dim) return;
     const int head = idx / value_dim, col = idx % value_dim;
@@ -150,6 +154,8 @@ __global__ void k_gated_delta_prepare(const float *__restrict__ a, const float *
                                       const float *__restrict__ a_log, const float *__restrict__ dt_bias,
                                       float *__restrict__ log_decay, float *__restrict__ beta, int tokens,
                                       int heads) {
+    pdl_launch();
+    pdl_wait();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= tokens * heads) return;
     const int h = idx % heads;
@@ -177,11 +183,11 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
                     tokens, heads, qk_heads, key_dim, value_dim);
     CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
     if (key_dim == kDeltaDim && value_dim == kDeltaDim) {
-        k_gated_delta_scan128<<<heads * 4, 128, 0, ctx->stream>>>(q, k, v, log_decay, beta, state_in, state_out,
+        launch_pdl(k_gated_delta_scan128, dim3(heads * 4), dim3(128), 0, ctx->stream, q, k, v, log_decay, beta, state_in, state_out,
                                                                  out, (int)tokens, (int)heads, (int)qk_heads);
     } else {
         const unsigned n = heads * value_dim;
-        k_gated_delta_scan_generic<<<(n + 127) / 128, 128, 0, ctx->stream>>>(
+        launch_pdl(k_gated_delta_scan_generic, dim3((n + 127) / 128), dim3(128), 0, ctx->stream, 
             q, k, v, log_decay, beta, state_in, state_out, out, (int)tokens, (int)heads, (int)qk_heads,
             (int)key_dim, (int)value_dim);
     }
@@ -197,7 +203,7 @@ ctox_status ctox_gated_delta_prepare(ctox_ctx *ctx, const float *a, const float 
         return fail(ctx, CTOX_SHAPE, "gated delta prepare: bad arguments");
     CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
     const unsigned n = tokens * heads;
-    k_gated_delta_prepare<<<(n + 127) / 128, 128, 0, ctx->stream>>>(a, b, a_log, dt_bias, log_decay, beta,
+    launch_pdl(k_gated_delta_prepare, dim3((n + 127) / 128), dim3(128), 0, ctx->stream, a, b, a_log, dt_bias, log_decay, beta,
                                                                    (int)tokens, (int)heads);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;

@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
     float inv_temperature, unsigned long long seed, unsigned long long step, TreeDesc tree,
     NodeStat *__restrict__ cta_stats, float *__restrict__ child_z, float *__restrict__ logits_out,
     unsigned long long logits_stride, uint32_t row_offset) {
+    pdl_launch();
+    pdl_wait();
     __shared__ NodeStat sh[kHeadThreads / 32][kMaxPosPerPass];
     NodeStat st[kMaxPosPerPass];
 #pragma unroll
@@ -164,6 +166,8 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
 // to rounding; the lane order is fixed, so the result is reproducible).
 __global__ void k_head_merge(const NodeStat *__restrict__ cta_stats, uint32_t n_ctas, uint32_t node0,
                              uint32_t npos, NodeStat *__restrict__ node_stats) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t m = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (m >= npos) return;
     NodeStat a{0ull, 0ull, 0.f, 0.f, 0u, 0u};
@@ -190,6 +194,8 @@ struct RankStats {
 };
 __global__ void k_head_merge_ranks(const RankStats *__restrict__ gathered, uint32_t world, uint32_t shard_rows,
                                    TreeDesc tree, RankStats *__restrict__ out) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t n = threadIdx.x;
     if (n >= tree.n_nodes) return;
     NodeStat a = gathered[0].node[n];
@@ -214,6 +220,8 @@ __global__ void k_head_merge_ranks(const RankStats *__restrict__ gathered, uint3
 __global__ void k_spec_accept(const NodeStat *__restrict__ node_stats, const float *__restrict__ child_z,
                               TreeDesc tree, float inv_temperature, unsigned long long seed,
                               unsigned long long step, int force_accept, ctox_spec_record *__restrict__ rec) {
+    pdl_launch();
+    pdl_wait();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     uint32_t count = 0, node = 0, status = 0;
     for (uint32_t n = 0; n < tree.n_nodes; ++n) rec->node_token[n] = tree.token[n];
@@ -285,6 +293,8 @@ struct ArgmaxPartial {
 
 __global__ void __launch_bounds__(kHeadThreads) k_argmax_partial(const float *__restrict__ logits, uint32_t n,
                                                                ArgmaxPartial *__restrict__ out) {
+    pdl_launch();
+    pdl_wait();
     __shared__ ArgmaxPartial sh[kHeadThreads / 32];
     unsigned long long best = 0ull;
     uint32_t bad = 0;
@@ -319,6 +329,8 @@ __global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t
                                const uint32_t *__restrict__ row_ids, uint32_t row_offset,
                                uint32_t *__restrict__ token_out, uint32_t *__restrict__ status_out,
                                ArgmaxPartial *__restrict__ packed_out) {
+    pdl_launch();
+    pdl_wait();
     if (threadIdx.x != 0) return;
     ArgmaxPartial a = parts[0];
     for (uint32_t i = 1; i < n_parts; ++i) {
@@ -335,6 +347,8 @@ __global__ void k_argmax_final(const ArgmaxPartial *__restrict__ parts, uint32_t
 // Greatest (key, token) over the ranks' local results; an empty shard contributes best == 0.
 __global__ void k_argmax_ranks(const ArgmaxPartial *__restrict__ gathered, uint32_t world,
                                uint32_t *__restrict__ token_out, uint32_t *__restrict__ status_out) {
+    pdl_launch();
+    pdl_wait();
     if (threadIdx.x != 0) return;
     ArgmaxPartial a = gathered[0];
     for (uint32_t r = 1; r < world; ++r) {
@@ -413,8 +427,8 @@ ctox_status ctox_argmax_f32(ctox_ctx *ctx, const float *logits_dev, uint32_t n, 
     uint32_t grid = (n + kHeadThreads * 4 - 1) / (kHeadThreads * 4);
     if (grid > kHeadGridMax) grid = kHeadGridMax;
     if (grid == 0) grid = 1;
-    k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
-    k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, 0, result_dev, result_dev + 1,
+    launch_pdl(k_argmax_partial, dim3(grid), dim3(kHeadThreads), 0, ctx->stream, logits_dev, n, hs.argmax_parts);
+    launch_pdl(k_argmax_final, dim3(1), dim3(32), 0, ctx->stream, hs.argmax_parts, grid, row_ids_dev, 0, result_dev, result_dev + 1,
                                               nullptr);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
@@ -457,11 +471,11 @@ ctox_status head_verify_enqueue(ctox_matvec *mv, uint32_t node0, uint32_t npos, 
     MatvecPart &p = mv->parts[0];
     uint32_t grid = (rows + kHeadThreads - 1) / kHeadThreads;
     if (grid > kHeadGridMax) grid = kHeadGridMax;
-    k_head_stats<<<grid, kHeadThreads, 0, ctx->stream>>>(p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out,
+    launch_pdl(k_head_stats, dim3(grid), dim3(kHeadThreads), 0, ctx->stream, p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out,
                                                         mv->bias, rows, p.slices, p.max_pieces, node0, npos,
                                                         inv_t, seed, step, tree, hs.cta_stats, hs.child_z,
                                                         logits_out_dev, (unsigned long long)mv->rows, row_offset);
-    k_head_merge<<<1, 32 * kMaxPosPerPass, 0, ctx->stream>>>(hs.cta_stats, grid, node0, npos, hs.node_stats);
+    launch_pdl(k_head_merge, dim3(1), dim3(32 * kMaxPosPerPass), 0, ctx->stream, hs.cta_stats, grid, node0, npos, hs.node_stats);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
@@ -477,7 +491,7 @@ ctox_status head_accept_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t *
     tree.n_nodes = n_nodes;
     tree.token = tokens_dev;
     for (uint32_t i = 0; i < n_nodes; ++i) tree.parent[i] = parent[i];
-    k_spec_accept<<<1, 32, 0, ctx->stream>>>(hs.node_stats, hs.child_z, tree, inv_t, seed, step, force_accept,
+    launch_pdl(k_spec_accept, dim3(1), dim3(32), 0, ctx->stream, hs.node_stats, hs.child_z, tree, inv_t, seed, step, force_accept,
                                             hs.record);
     CTOX_CUDA(ctx, cudaGetLastError());
     *record_dev = hs.record;
@@ -497,15 +511,15 @@ ctox_status argmax_enqueue(ctox_ctx *ctx, const float *logits_dev, uint32_t n, c
         uint32_t grid = (n + kHeadThreads * 4 - 1) / (kHeadThreads * 4);
         if (grid > kHeadGridMax) grid = kHeadGridMax;
         if (grid == 0) grid = 1;
-        k_argmax_partial<<<grid, kHeadThreads, 0, ctx->stream>>>(logits_dev, n, hs.argmax_parts);
-        k_argmax_final<<<1, 32, 0, ctx->stream>>>(hs.argmax_parts, grid, row_ids_dev, row_offset,
+        launch_pdl(k_argmax_partial, dim3(grid), dim3(kHeadThreads), 0, ctx->stream, logits_dev, n, hs.argmax_parts);
+        launch_pdl(k_argmax_final, dim3(1), dim3(32), 0, ctx->stream, hs.argmax_parts, grid, row_ids_dev, row_offset,
                                                   tp ? nullptr : token_dev, tp ? nullptr : status_dev,
                                                   tp ? hs.argmax_send : nullptr);
     }
     if (tp) {
         rc = tp_all_gather(ctx, hs.argmax_send, hs.argmax_gathered, sizeof(ArgmaxPartial));
         if (rc) return rc;
-        k_argmax_ranks<<<1, 32, 0, ctx->stream>>>(hs.argmax_gathered, (uint32_t)ctx->tp_world, token_dev, status_dev);
+        launch_pdl(k_argmax_ranks, dim3(1), dim3(32), 0, ctx->stream, hs.argmax_gathered, (uint32_t)ctx->tp_world, token_dev, status_dev);
     }
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
@@ -527,7 +541,7 @@ ctox_status head_tp_merge_enqueue(ctox_ctx *ctx, uint32_t n_nodes, const int32_t
     tree.n_nodes = n_nodes;
     tree.token = tokens_dev;
     for (uint32_t i = 0; i < n_nodes; ++i) tree.parent[i] = parent[i];
-    k_head_merge_ranks<<<1, 32, 0, ctx->stream>>>(hs.gathered, (uint32_t)ctx->tp_world, shard_rows, tree,
+    launch_pdl(k_head_merge_ranks, dim3(1), dim3(32), 0, ctx->stream, hs.gathered, (uint32_t)ctx->tp_world, shard_rows, tree,
                                                   (RankStats *)hs.node_stats);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;

@@ -61,6 +61,8 @@ __device__ __forceinline__ void prep_from_smem(const float *vals, uint32_t n, ui
 // h[m][c] (+= matvec output); per-CTA partial sums of squares go to sumsq[m][blockIdx.x].
 __global__ void __launch_bounds__(256) k_residual_add(float *__restrict__ h, MvOut add, int has_add,
                                                     uint32_t hidden, float *__restrict__ sumsq) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float red[8];
     const int m = blockIdx.y;
     const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(256) k_residual_add(float *__restrict__ h, MvO
 __global__ void k_norm_prep(const float *__restrict__ h, const float *__restrict__ sumsq, uint32_t nparts,
                             const float *__restrict__ w, float eps, uint32_t hidden, int npos,
                             float *__restrict__ xn_out, MvIn next, int has_next, uint32_t nblocks) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
     const int i = threadIdx.x & 15;
     if (gid >= nblocks * (uint32_t)npos) return;
@@ -111,10 +115,10 @@ void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, cons
     MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0, nullptr, 0};
     MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
     const uint32_t nparts = (hidden + 255) / 256;
-    k_residual_add<<<dim3(nparts, m), 256, 0, st>>>(h, a, add != nullptr, hidden, scratch);
+    launch_pdl(k_residual_add, dim3(nparts, m), dim3(256), 0, st, h, a, add != nullptr, hidden, scratch);
     const uint32_t nblocks = next ? next->blocks_padded : (hidden + 63) / 64;
     const uint32_t groups = nblocks * m;
-    k_norm_prep<<<(groups * 16 + 127) / 128, 128, 0, st>>>(h, scratch, nparts, w, eps, hidden, (int)m, xn_out, n,
+    launch_pdl(k_norm_prep, dim3((groups * 16 + 127) / 128), dim3(128), 0, st, h, scratch, nparts, w, eps, hidden, (int)m, xn_out, n,
                                                           next != nullptr, nblocks);
 }
 
@@ -124,6 +128,8 @@ __global__ void __launch_bounds__(512) k_mtp_pre(const float *__restrict__ embed
                                                const float *__restrict__ w_embed,
                                                const float *__restrict__ w_hidden, float eps, uint32_t hidden,
                                                int npos, MvIn next) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ float sh[];  // [2 * hidden] + 32
     float *vals = sh, *red = sh + 2 * hidden;
     const int m = blockIdx.x;
@@ -154,12 +160,14 @@ __global__ void __launch_bounds__(512) k_mtp_pre(const float *__restrict__ embed
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next) {
     const size_t smem = (2 * hidden + 32) * sizeof(float);
-    k_mtp_pre<<<m, 512, smem, st>>>(embed_rows, prev_hidden, w_embed, w_hidden, eps, hidden, (int)m, *next);
+    launch_pdl(k_mtp_pre, dim3(m), dim3(512), smem, st, embed_rows, prev_hidden, w_embed, w_hidden, eps, hidden, (int)m, *next);
 }
 
 // One CTA per (position, 256 columns of the intermediate width): every thread finishes one
 // column (two matvec outputs), then four 16-lane groups write the four 64-column blocks.
 __global__ void __launch_bounds__(256) k_swiglu_prep(MvOut gu, uint32_t inter, int npos, MvIn next) {
+    pdl_launch();
+    pdl_wait();
     __shared__ float vals[256];
     const int m = blockIdx.y;
     const uint32_t c = blockIdx.x * 256 + threadIdx.x;
@@ -183,7 +191,7 @@ __global__ void __launch_bounds__(256) k_swiglu_prep(MvOut gu, uint32_t inter, i
 }
 
 void launch_swiglu_prep(cudaStream_t st, const MvOut &gate_up, uint32_t inter, uint32_t m, const MvIn &next) {
-    k_swiglu_prep<<<dim3((next.blocks_padded + 3) / 4, m), 256, 0, st>>>(gate_up, inter, (int)m, next);
+    launch_pdl(k_swiglu_prep, dim3((next.blocks_padded + 3) / 4, m), dim3(256), 0, st, gate_up, inter, (int)m, next);
 }
 
 // ------------------------------------------------------------------ linear attention
@@ -198,6 +206,8 @@ __global__ void k_linear_mid(MvOut fan, uint32_t key_width, uint32_t value_width
                              const float *__restrict__ dt_bias, int npos, float *__restrict__ conv_in,
                              float *__restrict__ q, float *__restrict__ k, float *__restrict__ v,
                              float *__restrict__ z, float *__restrict__ log_decay, float *__restrict__ beta) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t channels = 2 * key_width + value_width;
     const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r < channels) {
@@ -240,13 +250,15 @@ void launch_linear_mid(cudaStream_t st, const MvOut &fan, uint32_t key_width, ui
                        const float *conv_w, const float *a_log, const float *dt_bias, uint32_t m,
                        float *conv_in, float *q, float *k, float *v, float *z, float *log_decay, float *beta) {
     const uint32_t rows = 2 * key_width + 2 * value_width + 2 * value_heads;
-    k_linear_mid<<<(rows + 127) / 128, 128, 0, st>>>(fan, key_width, value_width, value_heads, conv_kernel,
+    launch_pdl(k_linear_mid, dim3((rows + 127) / 128), dim3(128), 0, st, fan, key_width, value_width, value_heads, conv_kernel,
                                                     conv_state, conv_w, a_log, dt_bias, (int)m, conv_in, q, k,
                                                     v, z, log_decay, beta);
 }
 
 __global__ void k_conv_commit(float *__restrict__ conv_state, const float *__restrict__ conv_in,
                               uint32_t channels, uint32_t conv_kernel, uint32_t n) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= channels) return;
     float st[8];
@@ -260,7 +272,7 @@ __global__ void k_conv_commit(float *__restrict__ conv_state, const float *__res
 
 void launch_conv_commit(cudaStream_t st, float *conv_state, const float *conv_in, uint32_t channels,
                         uint32_t conv_kernel, uint32_t n) {
-    k_conv_commit<<<(channels + 127) / 128, 128, 0, st>>>(conv_state, conv_in, channels, conv_kernel, n);
+    launch_pdl(k_conv_commit, dim3((channels + 127) / 128), dim3(128), 0, st, conv_state, conv_in, channels, conv_kernel, n);
 }
 
 // rms_norm_gated (reference.rs:66-93) per (position, value head) of 128 values: one warp,
@@ -268,6 +280,8 @@ void launch_conv_commit(cudaStream_t st, float *conv_state, const float *conv_in
 __global__ void k_gated_norm_prep(const float *__restrict__ core, const float *__restrict__ z,
                                   const float *__restrict__ w, float eps, uint32_t value_heads, int npos,
                                   MvIn next) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (wid >= value_heads * (uint32_t)npos) return;
     const uint32_t head = wid / npos;
@@ -293,7 +307,7 @@ void launch_gated_norm_prep(cudaStream_t st, const float *core, const float *z, 
                             uint32_t value_heads, uint32_t value_dim, uint32_t m, const MvIn &next) {
     (void)value_dim;  // 128: checked by the executor
     const uint32_t warps = value_heads * m;
-    k_gated_norm_prep<<<(warps * 32 + 255) / 256, 256, 0, st>>>(core, z, w, eps, value_heads, (int)m, next);
+    launch_pdl(k_gated_norm_prep, dim3((warps * 32 + 255) / 256), dim3(256), 0, st, core, z, w, eps, value_heads, (int)m, next);
 }
 
 // ------------------------------------------------------------------ full attention
@@ -323,6 +337,8 @@ __global__ void k_attn_pre(MvOut fan, AttnGeom g, const float *__restrict__ q_no
                            int npos, float *__restrict__ q, float *__restrict__ gate, T *__restrict__ k_cache,
                            T *__restrict__ v_cache, const uint32_t *__restrict__ page_table,
                            uint32_t page_tokens) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ float sh[];  // [warps][head_dim]
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t wid = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -383,11 +399,11 @@ void launch_attn_pre(cudaStream_t st, const MvOut &fan, const AttnGeom &g, const
     const size_t smem = wpb * g.head_dim * sizeof(float);
     const uint32_t grid = (warps + wpb - 1) / wpb;
     if (kv_bf16)
-        k_attn_pre<__nv_bfloat16><<<grid, wpb * 32, smem, st>>>(fan, g, q_norm, k_norm, rope_position, cache_slot,
+        launch_pdl(k_attn_pre<__nv_bfloat16>, dim3(grid), dim3(wpb * 32), smem, st, fan, g, q_norm, k_norm, rope_position, cache_slot,
                                                                 (int)m, q, gate, (__nv_bfloat16 *)k_cache,
                                                                 (__nv_bfloat16 *)v_cache, page_table, page_tokens);
     else
-        k_attn_pre<float><<<grid, wpb * 32, smem, st>>>(fan, g, q_norm, k_norm, rope_position, cache_slot, (int)m, q,
+        launch_pdl(k_attn_pre<float>, dim3(grid), dim3(wpb * 32), smem, st, fan, g, q_norm, k_norm, rope_position, cache_slot, (int)m, q,
                                                         gate, (float *)k_cache, (float *)v_cache, page_table,
                                                         page_tokens);
 }
@@ -405,6 +421,8 @@ __global__ void __launch_bounds__(kAttnThreads) k_attention(
     AttnGeom g, const float *__restrict__ q, const T *__restrict__ k_cache, const T *__restrict__ v_cache,
     const uint32_t *__restrict__ page_table, uint32_t page_tokens, uint64_t cache_slot, int npos,
     uint32_t splits, float *__restrict__ ws) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smraw[];
     const uint32_t hd = g.head_dim, G = g.q_heads / g.kv_heads, NQ = G * npos;
     const uint32_t kh = blockIdx.x / splits, sp = blockIdx.x % splits;
@@ -546,6 +564,8 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     AttnGeom g, const float *__restrict__ q, const __nv_bfloat16 *__restrict__ k_cache,
     const __nv_bfloat16 *__restrict__ v_cache, const uint32_t *__restrict__ page_table, uint32_t page_tokens,
     uint64_t cache_slot, int npos, uint32_t splits, float *__restrict__ ws) {
+    pdl_launch();
+    pdl_wait();
     extern __shared__ __align__(128) uint8_t smraw[];
     constexpr int NT = GROUPS * 128;
     const uint32_t G = g.q_heads / g.kv_heads, NQ = G * npos;
@@ -716,6 +736,8 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
 // 16-lane group per (position, query head, 64-dimension block).
 __global__ void k_attn_combine_prep(AttnGeom g, const float *__restrict__ ws, const float *__restrict__ gate,
                                     int npos, uint32_t splits, MvIn next) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
     const int i = threadIdx.x & 15;
     const uint32_t hd = g.head_dim, bph = hd / 64, G = g.q_heads / g.kv_heads, NQ = G * npos;
@@ -762,7 +784,7 @@ static void launch_attention_t(cudaStream_t st, const AttnGeom &g, const float *
         cudaFuncSetAttribute(k_attention<T, NQMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_done = true;
     }
-    k_attention<T, NQMAX><<<g.kv_heads * splits, kAttnThreads, smem, st>>>(
+    launch_pdl(k_attention<T, NQMAX>, dim3(g.kv_heads * splits), dim3(kAttnThreads), smem, st, 
         g, q, (const T *)k_cache, (const T *)v_cache, page_table, page_tokens, cache_slot, (int)m, splits, ws);
 }
 
@@ -780,15 +802,15 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
             attr_done = true;
         }
         if (nq <= 16)
-            k_attention_mma<1><<<g.kv_heads * splits, 128, smem, st>>>(
+            launch_pdl(k_attention_mma<1>, dim3(g.kv_heads * splits), dim3(128), smem, st, 
                 g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
                 cache_slot, (int)m, splits, workspace);
         else
-            k_attention_mma<2><<<g.kv_heads * splits, 256, smem, st>>>(
+            launch_pdl(k_attention_mma<2>, dim3(g.kv_heads * splits), dim3(256), smem, st, 
                 g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
                 cache_slot, (int)m, splits, workspace);
         const uint32_t groups = m * g.q_heads * (g.head_dim / 64);
-        k_attn_combine_prep<<<(groups * 16 + 255) / 256, 256, 0, st>>>(g, workspace, gate, (int)m, splits, next);
+        launch_pdl(k_attn_combine_prep, dim3((groups * 16 + 255) / 256), dim3(256), 0, st, g, workspace, gate, (int)m, splits, next);
         return;
     }
 #define CTOX_ATTN(T)                                                                                        \
@@ -809,7 +831,7 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
         CTOX_ATTN(float);
 #undef CTOX_ATTN
     const uint32_t groups = m * g.q_heads * (g.head_dim / 64);
-    k_attn_combine_prep<<<(groups * 16 + 255) / 256, 256, 0, st>>>(g, workspace, gate, (int)m, splits, next);
+    launch_pdl(k_attn_combine_prep, dim3((groups * 16 + 255) / 256), dim3(256), 0, st, g, workspace, gate, (int)m, splits, next);
 }
 
 }  // namespace ctox

@@ -132,6 +132,8 @@ template <int DT>
 __global__ void k_repack(const uint8_t *__restrict__ canon, uint8_t *__restrict__ prep,
                          uint32_t rows, uint32_t blocks, uint32_t pairs, uint32_t kst_s, uint32_t slices,
                          int32_t *error_flag) {
+    pdl_launch();
+    pdl_wait();
     using F = Fmt<DT>;
     const uint64_t s = (uint64_t)blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
     if (s >= (uint64_t)slices * pairs * kst_s * 2) return;
@@ -196,6 +198,8 @@ __global__ void k_repack(const uint8_t *__restrict__ canon, uint8_t *__restrict_
 __global__ void k_prep_x(const void *__restrict__ x, int x_is_bf16, long long x_stride,
                          const float *__restrict__ s_in, int columns, int blocks_padded, int npos,
                          int dt, uint8_t *__restrict__ xfrag, float2 *__restrict__ meta) {
+    pdl_launch();
+    pdl_wait();
     const int gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
     const int i = threadIdx.x & 15;
     if (gid >= blocks_padded * npos) return;  // whole 16-lane groups leave together
@@ -232,7 +236,6 @@ struct StreamParams {
     uint32_t ctas_per_slice;
     uint32_t warps_per_slice;  // warps that take work (<= units per slice)
     uint32_t npos, max_pieces;
-    uint32_t dbg;
 };
 
 // Four MMAs of one 16-row x 64-column block; cw = this lane's code vector(s).
@@ -259,6 +262,7 @@ __device__ __forceinline__ void block_mma(float (&c)[4], uint32_t w0, uint32_t w
 
 template <int DT, int WARPS, int STAGES, int NT>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamParams p) {
+    pdl_launch();
     using F = Fmt<DT>;
     constexpr uint32_t kST = F::kSuperTileBytes;
     constexpr uint32_t kUnitBytes = 2 * kST;                      // one tile pair
@@ -309,6 +313,10 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         }
     }
     __syncthreads();  // xbar and the zero bytes are initialised
+    // Everything above touched only this matrix's weights, which nothing in the stream writes.
+    // The activations come from the kernels before this one: wait for them here, with the first
+    // STAGES chunks of every warp already on their way.
+    pdl_wait();
     if (threadIdx.x == 0) {
         fence_proxy_async();
         mbar_expect_tx(xbar, xfrag_bytes + meta_bytes);
@@ -382,9 +390,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         const uint64_t u0 = beg + (uint64_t)c * F::kChunkPairs;
         const uint32_t n = (uint32_t)min((uint64_t)F::kChunkPairs, end - u0);
         for (uint32_t i = 0; i < n; ++i) {
-            if (p.dbg & 1) continue;
             if (cur_ks == p.kst_s) {  // crossed into the next tile pair
-                if (!(p.dbg & 2)) close_pair(cur_pair, true);
+                close_pair(cur_pair, true);
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -412,7 +419,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
             uint4 q0 = make_uint4(0, 0, 0, 0), q1 = make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                if ((p.dbg & 4) && j > 0) break;
                 uint32_t w0, w0h, w1, w1h, v0, v0h, v1, v1h;  // tile 0 / tile 1 code words
                 if (DT == 1) {
                     const uint4 a0 = lds128(tile0 + kScaleBytes + j * 512 + lane * 16);
@@ -467,7 +473,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
             mbar_wait(my_bars + 8 * (c % STAGES), (c / STAGES) & 1);
         return;
     }
-    if (p.dbg & 2) return;
     close_pair(cur_pair, cur_ks == p.kst_s);
 }
 
@@ -477,6 +482,8 @@ __global__ void k_matvec_finish(const float *__restrict__ partial, const uint8_t
                                 const float *__restrict__ s_out, const float *__restrict__ bias,
                                 float *__restrict__ y, long long y_stride, uint32_t rows, uint32_t npos,
                                 uint32_t slices, uint32_t max_pieces, uint32_t activation) {
+    pdl_launch();
+    pdl_wait();
     const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * npos) return;
     const uint32_t row = idx / npos, pos = idx % npos;
@@ -504,6 +511,8 @@ __global__ void k_matvec_rowwarp(const uint8_t *__restrict__ canon, const float 
                                  const float *__restrict__ s_in, const float *__restrict__ s_out,
                                  const float *__restrict__ bias, float *__restrict__ y,
                                  uint32_t rows, uint32_t blocks, uint32_t activation) {
+    pdl_launch();
+    pdl_wait();
     using F = Fmt<DT>;
     const uint32_t row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const uint32_t lane = threadIdx.x & 31;
@@ -555,6 +564,8 @@ __global__ void k_recovered_rows(const uint8_t *__restrict__ canon, const uint32
                                  const float *__restrict__ s_in, const float *__restrict__ s_out,
                                  float s_out_scalar, float *__restrict__ out, uint32_t columns,
                                  uint32_t n_rows, uint32_t matrix_rows, int32_t *error_flag) {
+    pdl_launch();
+    pdl_wait();
     using F = Fmt<DT>;
     const uint32_t i = blockIdx.y;
     const uint32_t c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
@@ -586,6 +597,8 @@ __global__ void k_recovered_rows(const uint8_t *__restrict__ canon, const uint32
 }
 
 __global__ void k_bf16_to_f32(const __nv_bfloat16 *in, float *out, long long n) {
+    pdl_launch();
+    pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __bfloat162float(in[i]);
 }
@@ -732,11 +745,11 @@ StreamCfg pick_stream_cfg(ctox_ctx *ctx, int dt, uint32_t slice_blocks, uint32_t
 template <int DT, int NT>
 void launch_stream_nt(StreamCfg cfg, unsigned grid, size_t smem, cudaStream_t st, const StreamParams &sp) {
     if (cfg.warps == 16)
-        k_matvec_stream<DT, 16, 2, NT><<<grid, 512, smem, st>>>(sp);
+        launch_pdl(k_matvec_stream<DT, 16, 2, NT>, dim3(grid), dim3(512), smem, st, sp);
     else if (cfg.stages == 4)
-        k_matvec_stream<DT, 8, 4, NT><<<grid, 256, smem, st>>>(sp);
+        launch_pdl(k_matvec_stream<DT, 8, 4, NT>, dim3(grid), dim3(256), smem, st, sp);
     else
-        k_matvec_stream<DT, 8, 2, NT><<<grid, 256, smem, st>>>(sp);
+        launch_pdl(k_matvec_stream<DT, 8, 2, NT>, dim3(grid), dim3(256), smem, st, sp);
 }
 
 template <int DT>
@@ -799,10 +812,10 @@ ctox_status prepare_part(ctox_ctx *ctx, ctox_matvec *mv, MatvecPart &part, const
     if (rc) return rc;
     const uint32_t grid = (uint32_t)((tiles + 3) / 4);
     if (part.dt)
-        k_repack<1><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
+        launch_pdl(k_repack<1>, dim3(grid), dim3(128), 0, ctx->stream, part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
                                                    part.pairs, part.kst_s, part.slices, ctx->dev_error);
     else
-        k_repack<0><<<grid, 128, 0, ctx->stream>>>(part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
+        launch_pdl(k_repack<0>, dim3(grid), dim3(128), 0, ctx->stream, part.canon, part.prep, (uint32_t)part.rows, mv->blocks,
                                                    part.pairs, part.kst_s, part.slices, ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());
     // work split of the streaming kernel, per launch-shape class, and the pieces each
@@ -938,8 +951,6 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     sp.warps_per_slice = split.warps_per_slice;
     sp.npos = npos;
     sp.max_pieces = p.max_pieces;
-    static const uint32_t dbg = getenv("CTOX_DBG") ? (uint32_t)atoi(getenv("CTOX_DBG")) : 0u;
-    sp.dbg = dbg;
     const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
     const unsigned grid = split.ctas_per_slice * p.slices;
     timing_begin(ctx);
@@ -957,7 +968,7 @@ ctox_status matvec_stream_pass(ctox_matvec *mv, size_t part_index, const void *x
     MatvecPart &p = mv->parts[part_index];
     // the activation fragments depend on the code format (column multipliers)
     const int groups = (int)(mv->blocks_padded * npos);
-    k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, mv->ctx->stream>>>(
+    launch_pdl(k_prep_x, dim3((groups * 16 + 255) / 256), dim3(256), 0, mv->ctx->stream, 
         x, x_dtype == CTOX_BF16, (long long)x_stride, mv->s_in, (int)mv->columns, (int)mv->blocks_padded,
         (int)npos, p.dt, mv->xfrag, mv->meta);
     return matvec_stream_prepared(mv, part_index, npos);
@@ -1013,11 +1024,11 @@ ctox_status matvec_embed_rows(ctox_matvec *mv, const uint32_t *row_ids_dev, uint
         return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "row gather needs CTOX_PREPARE_KEEP_CANONICAL at prepare");
     dim3 grid((unsigned)((mv->columns / 2 + 127) / 128), n);
     if (p.dt)
-        k_recovered_rows<1><<<grid, 128, 0, ctx->stream>>>(p.canon, row_ids_dev, mv->s_in, mv->s_out, 1.0f, out,
+        launch_pdl(k_recovered_rows<1>, dim3(grid), dim3(128), 0, ctx->stream, p.canon, row_ids_dev, mv->s_in, mv->s_out, 1.0f, out,
                                                            (uint32_t)mv->columns, n, (uint32_t)mv->rows,
                                                            ctx->dev_error);
     else
-        k_recovered_rows<0><<<grid, 128, 0, ctx->stream>>>(p.canon, row_ids_dev, mv->s_in, mv->s_out, 1.0f, out,
+        launch_pdl(k_recovered_rows<0>, dim3(grid), dim3(128), 0, ctx->stream, p.canon, row_ids_dev, mv->s_in, mv->s_out, 1.0f, out,
                                                            (uint32_t)mv->columns, n, (uint32_t)mv->rows,
                                                            ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());
@@ -1027,7 +1038,7 @@ ctox_status matvec_embed_rows(ctox_matvec *mv, const uint32_t *row_ids_dev, uint
 void matvec_finish_enqueue(ctox_matvec *mv, uint32_t npos, float *y, uint64_t y_stride) {
     MatvecPart &p = mv->parts[0];
     const unsigned n_out = (unsigned)(p.rows * npos);
-    k_matvec_finish<<<(n_out + 255) / 256, 256, 0, mv->ctx->stream>>>(
+    launch_pdl(k_matvec_finish, dim3((n_out + 255) / 256), dim3(256), 0, mv->ctx->stream, 
         p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, mv->bias, y, (long long)y_stride,
         (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
 }
@@ -1147,7 +1158,7 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
                 mv->xtmp_bytes = need;
             }
             long long n = (long long)positions * x_stride;
-            k_bf16_to_f32<<<(unsigned)((n + 255) / 256), 256, 0, st>>>((const __nv_bfloat16 *)x_dev,
+            launch_pdl(k_bf16_to_f32, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, (const __nv_bfloat16 *)x_dev,
                                                                        mv->xtmp, n);
             xf = mv->xtmp;
         }
@@ -1162,10 +1173,10 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
                 float *yy = y_dev + m * y_stride + p.row_start;
                 timing_begin(ctx);
                 if (p.dt)
-                    k_matvec_rowwarp<1><<<grid, 128, 0, st>>>(p.canon, xf + m * x_stride, mv->s_in, so, bi,
+                    launch_pdl(k_matvec_rowwarp<1>, dim3(grid), dim3(128), 0, st, p.canon, xf + m * x_stride, mv->s_in, so, bi,
                                                               yy, (uint32_t)p.rows, mv->blocks, mv->activation);
                 else
-                    k_matvec_rowwarp<0><<<grid, 128, 0, st>>>(p.canon, xf + m * x_stride, mv->s_in, so, bi,
+                    launch_pdl(k_matvec_rowwarp<0>, dim3(grid), dim3(128), 0, st, p.canon, xf + m * x_stride, mv->s_in, so, bi,
                                                               yy, (uint32_t)p.rows, mv->blocks, mv->activation);
                 timing_end(ctx);
             }
@@ -1188,7 +1199,7 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
             if (rc) return rc;
             MatvecPart &p = mv->parts[pi];
             const unsigned n_out = (unsigned)(p.rows * npos);
-            k_matvec_finish<<<(n_out + 255) / 256, 256, 0, st>>>(
+            launch_pdl(k_matvec_finish, dim3((n_out + 255) / 256), dim3(256), 0, st, 
                 p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
                 mv->bias ? mv->bias + p.row_start : nullptr, y_dev + (size_t)m0 * y_stride + p.row_start,
                 (long long)y_stride, (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
@@ -1323,10 +1334,10 @@ ctox_status ctox_recovered_row(ctox_ctx *ctx, uint32_t dtype, const uint8_t *wei
         if (e == cudaSuccess) {
             dim3 grid((unsigned)((columns / 2 + 127) / 128), 1);
             if (dtype == CTOX_Q4B64)
-                k_recovered_rows<1><<<grid, 128, 0, ctx->stream>>>(dw, nullptr, dsi, nullptr, s_out, dout,
+                launch_pdl(k_recovered_rows<1>, dim3(grid), dim3(128), 0, ctx->stream, dw, nullptr, dsi, nullptr, s_out, dout,
                                                                    (uint32_t)columns, 1, 1, ctx->dev_error);
             else
-                k_recovered_rows<0><<<grid, 128, 0, ctx->stream>>>(dw, nullptr, dsi, nullptr, s_out, dout,
+                launch_pdl(k_recovered_rows<0>, dim3(grid), dim3(128), 0, ctx->stream, dw, nullptr, dsi, nullptr, s_out, dout,
                                                                    (uint32_t)columns, 1, 1, ctx->dev_error);
             e = cudaGetLastError();
         }
@@ -1450,7 +1461,7 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             if (split.warps == 0)
                 return fail(ctx, CTOX_MEMORY_BUDGET, "dispatch_static: %u positions do not fit shared memory", npos);
             const int groups = (int)(mv->blocks_padded * npos);
-            k_prep_x<<<(groups * 16 + 255) / 256, 256, 0, st>>>(xp, x_dtype == CTOX_BF16, (long long)x_stride,
+            launch_pdl(k_prep_x, dim3((groups * 16 + 255) / 256), dim3(256), 0, st, xp, x_dtype == CTOX_BF16, (long long)x_stride,
                                                                mv->s_in, (int)mv->columns,
                                                                (int)mv->blocks_padded, (int)npos, p.dt, xfrag, meta);
             StreamParams sp;
@@ -1466,7 +1477,6 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             sp.warps_per_slice = split.warps_per_slice;
             sp.npos = npos;
             sp.max_pieces = p.max_pieces;
-            sp.dbg = 0;
             const StreamCfg cfg{split.warps, split.stages};
             const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
             const unsigned grid = split.ctas_per_slice * p.slices;
@@ -1475,7 +1485,7 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             else
                 launch_stream<0>(cfg, grid, smem, st, sp);
             const unsigned n_out = (unsigned)(p.rows * npos);
-            k_matvec_finish<<<(n_out + 255) / 256, 256, 0, st>>>(
+            launch_pdl(k_matvec_finish, dim3((n_out + 255) / 256), dim3(256), 0, st, 
                 partial, split.pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
                 mv->bias ? mv->bias + p.row_start : nullptr, y_dev + (size_t)m0 * y_stride + p.row_start,
                 (long long)y_stride, (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
