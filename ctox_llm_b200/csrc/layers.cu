@@ -39,25 +39,6 @@ __device__ __forceinline__ float block_sum(float v, float *red) {
     return s;
 }
 
-// Writes the fragments of `vals` (one position, already normalised, not yet times s_in) for
-// all blocks of the next matvec; 16-lane groups take blocks round-robin. vals lives in shared
-// memory; columns beyond `n` (padding blocks) are zero.
-__device__ __forceinline__ void prep_from_smem(const float *vals, uint32_t n, uint32_t col0, int m, int npos,
-                                               const MvIn &next) {
-    const int i = threadIdx.x & 15;
-    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-    const uint32_t b_first = col0 / 64, b_end = (col0 + n + 63) / 64;
-    for (uint32_t b = b_first + (threadIdx.x >> 4); b < b_end; b += blockDim.x >> 4) {
-        float v[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const uint32_t c = b * 64 + i * 4 + j;
-            v[j] = (c >= col0 && c - col0 < n) ? vals[c - col0] * (next.s_in ? next.s_in[c] : 1.0f) : 0.f;
-        }
-        prep_block(v, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
-    }
-}
-
 // h[m][c] (+= matvec output); per-CTA partial sums of squares go to sumsq[m][blockIdx.x].
 __global__ void __launch_bounds__(256) k_residual_add(float *__restrict__ h, MvOut add, int has_add,
                                                     uint32_t hidden, float *__restrict__ sumsq) {
@@ -122,45 +103,50 @@ void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, cons
                                                           next != nullptr, nblocks);
 }
 
-// One CTA per position: [rmsnorm(embed) | rmsnorm(prev_hidden)] -> fragments (2 * hidden columns).
-__global__ void __launch_bounds__(512) k_mtp_pre(const float *__restrict__ embed_rows,
+// [rmsnorm(embed) | rmsnorm(prev_hidden)] -> fragments (2 * hidden columns). One CTA per
+// (16 blocks of 64 columns, position); every CTA adds up both sums of squares itself (40 KB from L2),
+// then each 16-lane group writes one block.
+__global__ void __launch_bounds__(256) k_mtp_pre(const float *__restrict__ embed_rows,
                                                const float *__restrict__ prev_hidden,
                                                const float *__restrict__ w_embed,
                                                const float *__restrict__ w_hidden, float eps, uint32_t hidden,
                                                int npos, MvIn next) {
     pdl_launch();
     pdl_wait();
-    extern __shared__ float sh[];  // [2 * hidden] + 32
-    float *vals = sh, *red = sh + 2 * hidden;
-    const int m = blockIdx.x;
-    for (int part = 0; part < 2; ++part) {
-        const float *src = (part ? prev_hidden : embed_rows) + (size_t)m * hidden;
-        const float *w = part ? w_hidden : w_embed;
-        float sq = 0.f;
-        for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
-            const float v = src[c];
-            vals[part * hidden + c] = v;
-            sq += v * v;
-        }
-        const float inv = 1.0f / sqrtf(block_sum(sq, red) / (float)hidden + eps);
-        __syncthreads();
-        for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x)
-            vals[part * hidden + c] = vals[part * hidden + c] * inv * (1.0f + w[c]);
-        __syncthreads();
+    __shared__ float red[8];
+    const int m = blockIdx.y;
+    const float *e = embed_rows + (size_t)m * hidden, *h = prev_hidden + (size_t)m * hidden;
+    float sq_e = 0.f, sq_h = 0.f;
+    for (uint32_t c = threadIdx.x; c < hidden; c += blockDim.x) {
+        const float a = e[c], b = h[c];
+        sq_e += a * a;
+        sq_h += b * b;
     }
-    prep_from_smem(vals, 2 * hidden, 0, m, npos, next);
+    const float inv_e = 1.0f / sqrtf(block_sum(sq_e, red) / (float)hidden + eps);
+    const float inv_h = 1.0f / sqrtf(block_sum(sq_h, red) / (float)hidden + eps);
+    const uint32_t b = blockIdx.x * 16 + (threadIdx.x >> 4);
+    if (b >= next.blocks_padded) return;
     const int i = threadIdx.x & 15;
-    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-    for (uint32_t b = (2 * hidden + 63) / 64 + (threadIdx.x >> 4); b < next.blocks_padded; b += blockDim.x >> 4) {
-        const float z[4] = {0.f, 0.f, 0.f, 0.f};
-        prep_block(z, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t c = b * 64 + i * 4 + j;
+        v[j] = 0.f;
+        if (c < 2 * hidden) {
+            const bool second = c >= hidden;
+            const uint32_t cc = second ? c - hidden : c;
+            const float xn = second ? h[cc] * inv_h * (1.0f + w_hidden[cc]) : e[cc] * inv_e * (1.0f + w_embed[cc]);
+            v[j] = xn * (next.s_in ? next.s_in[c] : 1.0f);
+        }
     }
+    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+    prep_block(v, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
 }
 
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next) {
-    const size_t smem = (2 * hidden + 32) * sizeof(float);
-    launch_pdl(k_mtp_pre, dim3(m), dim3(512), smem, st, embed_rows, prev_hidden, w_embed, w_hidden, eps, hidden, (int)m, *next);
+    launch_pdl(k_mtp_pre, dim3((next->blocks_padded + 15) / 16, m), dim3(256), 0, st, embed_rows, prev_hidden,
+               w_embed, w_hidden, eps, hidden, (int)m, *next);
 }
 
 // One CTA per (position, 256 columns of the intermediate width): every thread finishes one
@@ -328,84 +314,70 @@ __device__ __forceinline__ size_t kv_slot(const uint32_t *page_table, uint32_t p
     return (size_t)page_table[t / page_tokens] * page_tokens + (size_t)(t % page_tokens);
 }
 
-// One warp per (position, head) over the fused [q+gate | k | v] projection (decoder.rs:717-772):
-// q rows are [query(hd), gate(hd)] per head; q and k get the (1+w) RMS norm per head and the
-// non-interleaved partial RoPE (reference.rs:115-155); k and v go to the cache slot of the position.
+// One CTA per (position, head) and one thread per head dimension over the fused [q+gate | k | v]
+// projection (decoder.rs:717-772): q rows are [query(hd), gate(hd)] per head; q and k get the
+// (1+w) RMS norm per head and the non-interleaved partial RoPE (reference.rs:115-155); k and v go
+// to the cache slot of the position. One element per thread keeps the chain of dependent loads
+// (piece count, then the partial sums) one deep.
 template <typename T>
-__global__ void k_attn_pre(MvOut fan, AttnGeom g, const float *__restrict__ q_norm,
-                           const float *__restrict__ k_norm, uint64_t rope_position, uint64_t cache_slot,
-                           int npos, float *__restrict__ q, float *__restrict__ gate, T *__restrict__ k_cache,
-                           T *__restrict__ v_cache, const uint32_t *__restrict__ page_table,
-                           uint32_t page_tokens) {
+__global__ void __launch_bounds__(256) k_attn_pre(MvOut fan, AttnGeom g, const float *__restrict__ q_norm,
+                                                  const float *__restrict__ k_norm, uint64_t rope_position,
+                                                  uint64_t cache_slot, int npos, float *__restrict__ q,
+                                                  float *__restrict__ gate, T *__restrict__ k_cache,
+                                                  T *__restrict__ v_cache, const uint32_t *__restrict__ page_table,
+                                                  uint32_t page_tokens) {
     pdl_launch();
     pdl_wait();
-    extern __shared__ float sh[];  // [warps][head_dim]
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t wid = blockIdx.x * (blockDim.x >> 5) + warp;
+    __shared__ float buf[256];
+    __shared__ float red[8];
     const uint32_t heads_total = g.q_heads + 2 * g.kv_heads;
-    if (wid >= heads_total * (uint32_t)npos) return;
-    const uint32_t hi = wid % heads_total;
-    const int m = wid / heads_total;
-    const uint32_t hd = g.head_dim;
-    float *buf = sh + warp * hd;
+    const uint32_t hi = blockIdx.x % heads_total;
+    const int m = blockIdx.x / heads_total;
+    const uint32_t hd = g.head_dim, d = threadIdx.x;  // blockDim.x == head_dim
     const uint32_t k_row0 = g.q_heads * 2 * hd, v_row0 = k_row0 + g.kv_heads * hd;
     const size_t slot = kv_slot(page_table, page_tokens, cache_slot + m);
     if (hi >= g.q_heads + g.kv_heads) {  // value head: plain copy into the cache
         const uint32_t kh = hi - g.q_heads - g.kv_heads;
-        for (uint32_t d = lane; d < hd; d += 32)
-            kv_store(v_cache + (slot * g.kv_heads + kh) * hd + d, out_of(fan, v_row0 + kh * hd + d, m));
+        kv_store(v_cache + (slot * g.kv_heads + kh) * hd + d, out_of(fan, v_row0 + kh * hd + d, m));
         return;
     }
     const bool is_q = hi < g.q_heads;
     const uint32_t head = is_q ? hi : hi - g.q_heads;
     const uint32_t row0 = is_q ? head * 2 * hd : k_row0 + head * hd;
-    const float *w = is_q ? q_norm : k_norm;
-    float sq = 0.f;
-    for (uint32_t d = lane; d < hd; d += 32) {
-        const float v = out_of(fan, row0 + d, m);
-        buf[d] = v;
-        sq += v * v;
-        if (is_q) gate[((size_t)m * g.q_heads + head) * hd + d] = out_of(fan, row0 + hd + d, m);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    const float v = out_of(fan, row0 + d, m);
+    if (is_q) gate[((size_t)m * g.q_heads + head) * hd + d] = out_of(fan, row0 + hd + d, m);
+    const float sq = block_sum(v * v, red);
     const float inv = 1.0f / sqrtf(sq / (float)hd + g.eps);
-    __syncwarp();
-    for (uint32_t d = lane; d < hd; d += 32) buf[d] = buf[d] * inv * (1.0f + w[d]);
-    __syncwarp();
-    const uint32_t half = g.rotary_dim / 2;
-    const float pos = (float)(rope_position + (uint64_t)m);
-    for (uint32_t d = lane; d < hd; d += 32) {
-        float out = buf[d];
-        if (d < g.rotary_dim) {
-            const uint32_t i = d < half ? d : d - half;
-            const float inv_freq = powf(g.theta, -((float)(2 * i)) / (float)g.rotary_dim);
-            const float ang = pos * inv_freq, cs = cosf(ang), sn = sinf(ang);
-            out = d < half ? buf[d] * cs - buf[d + half] * sn : buf[d] * cs + buf[d - half] * sn;
-        }
-        if (is_q)
-            q[((size_t)m * g.q_heads + head) * hd + d] = out;
-        else
-            kv_store(k_cache + (slot * g.kv_heads + head) * hd + d, out);
+    const float xn = v * inv * (1.0f + (is_q ? q_norm : k_norm)[d]);
+    buf[d] = xn;
+    __syncthreads();
+    float out = xn;
+    if (d < g.rotary_dim) {
+        const uint32_t half = g.rotary_dim / 2;
+        const uint32_t i = d < half ? d : d - half;
+        const float pos = (float)(rope_position + (uint64_t)m);
+        const float inv_freq = powf(g.theta, -((float)(2 * i)) / (float)g.rotary_dim);
+        const float ang = pos * inv_freq, cs = cosf(ang), sn = sinf(ang);
+        out = d < half ? xn * cs - buf[d + half] * sn : xn * cs + buf[d - half] * sn;
     }
+    if (is_q)
+        q[((size_t)m * g.q_heads + head) * hd + d] = out;
+    else
+        kv_store(k_cache + (slot * g.kv_heads + head) * hd + d, out);
 }
 
 void launch_attn_pre(cudaStream_t st, const MvOut &fan, const AttnGeom &g, const float *q_norm,
                      const float *k_norm, uint64_t rope_position, uint64_t cache_slot, uint32_t m, float *q,
                      float *gate, void *k_cache, void *v_cache, int kv_bf16, const uint32_t *page_table,
                      uint32_t page_tokens) {
-    const uint32_t warps = (g.q_heads + 2 * g.kv_heads) * m;
-    const uint32_t wpb = 4;
-    const size_t smem = wpb * g.head_dim * sizeof(float);
-    const uint32_t grid = (warps + wpb - 1) / wpb;
+    const uint32_t grid = (g.q_heads + 2 * g.kv_heads) * m;
     if (kv_bf16)
-        launch_pdl(k_attn_pre<__nv_bfloat16>, dim3(grid), dim3(wpb * 32), smem, st, fan, g, q_norm, k_norm, rope_position, cache_slot,
-                                                                (int)m, q, gate, (__nv_bfloat16 *)k_cache,
-                                                                (__nv_bfloat16 *)v_cache, page_table, page_tokens);
+        launch_pdl(k_attn_pre<__nv_bfloat16>, dim3(grid), dim3(g.head_dim), 0, st, fan, g, q_norm, k_norm,
+                   rope_position, cache_slot, (int)m, q, gate, (__nv_bfloat16 *)k_cache, (__nv_bfloat16 *)v_cache,
+                   page_table, page_tokens);
     else
-        launch_pdl(k_attn_pre<float>, dim3(grid), dim3(wpb * 32), smem, st, fan, g, q_norm, k_norm, rope_position, cache_slot, (int)m, q,
-                                                        gate, (float *)k_cache, (float *)v_cache, page_table,
-                                                        page_tokens);
+        launch_pdl(k_attn_pre<float>, dim3(grid), dim3(g.head_dim), 0, st, fan, g, q_norm, k_norm, rope_position,
+                   cache_slot, (int)m, q, gate, (float *)k_cache, (float *)v_cache, page_table, page_tokens);
 }
 
 constexpr int kAttnTile = 32;      // tokens per tile
@@ -589,18 +561,32 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
         q_s[qi * kFaStride + d] = hi;
         q_s[(32 + qi) * kFaStride + d] = __float2bfloat16_rn(v - __bfloat162float(hi));
     }
-    auto load_tile = [&](uint64_t tile, uint32_t b) {
-        const uint64_t t0 = tile * kFaTile;
-        // 64 rows x 32 chunks of 16 B for K and for V
-        for (uint32_t c = tid; c < 2 * kFaTile * 32; c += NT) {
-            const uint32_t which = c / (kFaTile * 32), r = (c / 32) % kFaTile, cc = c % 32;
-            const uint32_t dst = buf_a + b * 2 * kTileBytes + which * kTileBytes + r * kFaStride * 2 + cc * 16;
-            if (t0 + r < total) {
-                const size_t slot = kv_slot(page_table, page_tokens, t0 + r);
-                const __nv_bfloat16 *src = (which ? v_cache : k_cache) + (slot * g.kv_heads + kh) * kFaHd + cc * 8;
-                cp_async16(dst, src);
+    // Tile loads. Thread (warp, lane) copies the 16-byte chunk `lane` of rows warp, warp + NT/32, ...
+    // of the K and of the V tile. The cache slots of a tile (page-table lookups) are fetched one
+    // tile ahead of the copies that use them, so the lookups never sit between two copies.
+    constexpr int kRowStep = NT / 32, kRowsPerThread = kFaTile / kRowStep;
+    constexpr uint32_t kNoSlot = 0xffffffffu;
+    uint32_t slots[kRowsPerThread];
+    auto fetch_slots = [&](uint64_t tile) {
+#pragma unroll
+        for (int j = 0; j < kRowsPerThread; ++j) {
+            const uint64_t t = tile * kFaTile + warp + j * kRowStep;
+            const uint32_t t32 = (uint32_t)t;
+            slots[j] = t < total ? page_table[t32 / page_tokens] * page_tokens + t32 % page_tokens : kNoSlot;
+        }
+    };
+    auto issue_tile = [&](uint32_t b) {
+#pragma unroll
+        for (int j = 0; j < kRowsPerThread; ++j) {
+            const uint32_t r = warp + j * kRowStep;
+            const uint32_t dst = buf_a + b * 2 * kTileBytes + r * kFaStride * 2 + lane * 16;
+            if (slots[j] != kNoSlot) {
+                const size_t off = ((size_t)slots[j] * g.kv_heads + kh) * kFaHd + lane * 8;
+                cp_async16(dst, k_cache + off);
+                cp_async16(dst + kTileBytes, v_cache + off);
             } else {
                 asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst), "r"(0u) : "memory");
+                asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};" ::"r"(dst + kTileBytes), "r"(0u) : "memory");
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -613,11 +599,16 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     uint64_t limit[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) limit[r] = cache_slot + (qrow[r] < NQ ? qrow[r] / G : 0);
-    if (tile_beg < tile_end) load_tile(tile_beg, 0);
+    if (tile_beg < tile_end) {
+        fetch_slots(tile_beg);
+        issue_tile(0);
+        if (tile_beg + 1 < tile_end) fetch_slots(tile_beg + 1);
+    }
     for (uint64_t tile = tile_beg; tile < tile_end; ++tile) {
         const uint32_t b = (uint32_t)(tile - tile_beg) & 1;
         if (tile + 1 < tile_end) {
-            load_tile(tile + 1, b ^ 1);
+            issue_tile(b ^ 1);
+            if (tile + 2 < tile_end) fetch_slots(tile + 2);
             asm volatile("cp.async.wait_group 1;" ::: "memory");
         } else {
             asm volatile("cp.async.wait_group 0;" ::: "memory");
