@@ -553,21 +553,54 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     const uint64_t tiles = (total + kFaTile - 1) / kFaTile;
     const uint64_t tile_beg = tiles * sp / splits, tile_end = tiles * (sp + 1) / splits;
     const float scale = 1.0f / sqrtf((float)kFaHd);
-    for (uint32_t i = tid; i < 32 * kFaHd; i += NT) {
-        const uint32_t qi = i / kFaHd, d = i % kFaHd;
-        float v = 0.f;
-        if (qi < NQ) v = q[((size_t)(qi / G) * g.q_heads + kh * G + qi % G) * kFaHd + d] * scale;
-        const __nv_bfloat16 hi = __float2bfloat16_rn(v);
-        q_s[qi * kFaStride + d] = hi;
-        q_s[(32 + qi) * kFaStride + d] = __float2bfloat16_rn(v - __bfloat162float(hi));
+    {   // Q as bf16 hi + lo: 8 float4 per thread, all loads issued before the first conversion
+        constexpr int kQRows = 16 * GROUPS, kVec = kQRows * kFaHd / 4 / NT;
+        float4 qv[kVec];
+#pragma unroll
+        for (int it = 0; it < kVec; ++it) {
+            const uint32_t i = (tid + it * NT) * 4, qi = i / kFaHd, d = i % kFaHd;
+            qv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (qi < NQ)
+                qv[it] = *reinterpret_cast<const float4 *>(
+                    q + ((size_t)(qi / G) * g.q_heads + kh * G + qi % G) * kFaHd + d);
+        }
+#pragma unroll
+        for (int it = 0; it < kVec; ++it) {
+            const uint32_t i = (tid + it * NT) * 4, qi = i / kFaHd, d = i % kFaHd;
+            const float v[4] = {qv[it].x * scale, qv[it].y * scale, qv[it].z * scale, qv[it].w * scale};
+            uint32_t hi[2], lo[2];
+            split_bf16(v[0], v[1], hi[0], lo[0]);
+            split_bf16(v[2], v[3], hi[1], lo[1]);
+            *reinterpret_cast<uint2 *>(q_s + qi * kFaStride + d) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2 *>(q_s + (32 + qi) * kFaStride + d) = make_uint2(lo[0], lo[1]);
+        }
     }
     // Tile loads. Thread (warp, lane) copies the 16-byte chunk `lane` of rows warp, warp + NT/32, ...
     // of the K and of the V tile. The cache slots of a tile (page-table lookups) are fetched one
     // tile ahead of the copies that use them, so the lookups never sit between two copies.
     constexpr int kRowStep = NT / 32, kRowsPerThread = kFaTile / kRowStep;
     constexpr uint32_t kNoSlot = 0xffffffffu;
+    const int page_shift = (page_tokens & (page_tokens - 1)) == 0 ? 31 - __clz(page_tokens) : -1;
     uint32_t slots[kRowsPerThread];
+    // a tile is 2..32 whole pages: one lookup per lane
+    const bool tile_pages = page_shift >= 1 && page_tokens <= (uint32_t)kFaTile;
     auto fetch_slots = [&](uint64_t tile) {
+        if (tile_pages) {
+            // lane l reads the l-th page of the tile; the rows pick theirs with a shuffle
+            const uint32_t first_page = (uint32_t)(tile * kFaTile) >> page_shift;
+            const uint32_t pages_per_tile = (uint32_t)kFaTile >> page_shift;
+            const uint32_t last_page = (uint32_t)(total - 1) >> page_shift;
+            uint32_t mine = 0;
+            if (lane < pages_per_tile && first_page + lane <= last_page) mine = page_table[first_page + lane];
+#pragma unroll
+            for (int j = 0; j < kRowsPerThread; ++j) {
+                const uint32_t r = warp + j * kRowStep;
+                const uint32_t pg = __shfl_sync(0xffffffffu, mine, r >> page_shift);
+                const uint64_t t = tile * kFaTile + r;
+                slots[j] = t < total ? (pg << page_shift) + (r & (page_tokens - 1)) : kNoSlot;
+            }
+            return;
+        }
 #pragma unroll
         for (int j = 0; j < kRowsPerThread; ++j) {
             const uint64_t t = tile * kFaTile + warp + j * kRowStep;
@@ -618,6 +651,7 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
         const uint32_t tok0 = wg * 16;
         // ---- S = Q K^T for this warp's 16 queries x 16 tokens
         float sacc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float slo[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};  // the lo term's own chains
 #pragma unroll 4
         for (int ks = 0; ks < kFaHd / 16; ++ks) {
             uint32_t bk[4], aq[4];
@@ -629,9 +663,14 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
                 // Q matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
                 ldsm_x4(aq, q_a + ((term * 32 + grp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kFaStride +
                                    ks * 16 + 8 * (lane >> 4)) * 2);
-                mma_bf16(sacc[0], aq, bk[0], bk[1]);
-                mma_bf16(sacc[1], aq, bk[2], bk[3]);
+                mma_bf16(term ? slo[0] : sacc[0], aq, bk[0], bk[1]);
+                mma_bf16(term ? slo[1] : sacc[1], aq, bk[2], bk[3]);
             }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            sacc[0][i] += slo[0][i];
+            sacc[1][i] += slo[1][i];
         }
         // ---- online softmax; this lane holds rows gq, gq+8 and tokens tok0 + {2tq, 2tq+1, 8+2tq, 9+2tq}
         const uint64_t tbase = tile * kFaTile + tok0;
@@ -660,10 +699,12 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
             l_run[r] = l_run[r] * alpha + sum;
             m_run[r] = m_new;
+            if (alpha != 1.0f) {  // the running maximum settles after the first tiles
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                oacc[i][2 * r] *= alpha;
-                oacc[i][2 * r + 1] *= alpha;
+                for (int i = 0; i < 32; ++i) {
+                    oacc[i][2 * r] *= alpha;
+                    oacc[i][2 * r + 1] *= alpha;
+                }
             }
             // A fragment of P: a0 (row g, k 2t..) / a1 (row g+8) from n-tile 0, a2 / a3 from n-tile 1
             split_bf16(ps[0], ps[1], p_hi[r], p_lo[r]);
@@ -701,25 +742,36 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     }
     __syncthreads();
     float *out = ws + ((size_t)(kh * splits + sp) * NQ) * (kFaHd + 2);
-    for (uint32_t i = tid; i < 16 * GROUPS * kFaHd; i += NT) {
-        const uint32_t qi = i / kFaHd, d = i % kFaHd;
+    // weights of the four warps per query row, once; they go where the rows kept (max, sum)
+    if (tid < 16 * GROUPS && tid < NQ) {
+        const uint32_t gg = tid / 16, rr = tid % 16;
+        float mx = -INFINITY, den = 0.f, wgt[4];
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mo[((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2) + kFaHd]);
+        for (int w = 0; w < 4; ++w) {
+            float *row = mo + ((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2);
+            wgt[w] = row[kFaHd] > -INFINITY ? expf(row[kFaHd] - mx) : 0.f;
+            den += row[kFaHd + 1] * wgt[w];
+        }
+        for (int w = 0; w < 4; ++w) mo[((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2) + kFaHd] = wgt[w];
+        out[(size_t)tid * (kFaHd + 2) + kFaHd] = mx;
+        out[(size_t)tid * (kFaHd + 2) + kFaHd + 1] = den;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (uint32_t i = tid; i < 16 * GROUPS * (kFaHd / 2); i += NT) {
+        const uint32_t qi = i / (kFaHd / 2), d = (i % (kFaHd / 2)) * 2;
         if (qi >= NQ) continue;
         const uint32_t gg = qi / 16, rr = qi % 16;
-        float mx = -INFINITY;
-        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mo[((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2) + kFaHd]);
-        float acc = 0.f, den = 0.f;
+        float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float *row = mo + ((size_t)(gg * 4 + w) * 16 + rr) * (kFaHd + 2);
-            if (!(row[kFaHd] > -INFINITY)) continue;
-            const float wgt = expf(row[kFaHd] - mx);
-            acc += row[d] * wgt;
-            den += row[kFaHd + 1] * wgt;
+            const float wgt = row[kFaHd];
+            const float2 v = *reinterpret_cast<const float2 *>(row + d);
+            acc.x += v.x * wgt;
+            acc.y += v.y * wgt;
         }
-        out[(size_t)qi * (kFaHd + 2) + d] = acc;
-        if (d == 0) {
-            out[(size_t)qi * (kFaHd + 2) + kFaHd] = mx;
-            out[(size_t)qi * (kFaHd + 2) + kFaHd + 1] = den;
-        }
+        *reinterpret_cast<float2 *>(out + (size_t)qi * (kFaHd + 2) + d) = acc;
     }
 }
 
