@@ -811,9 +811,21 @@ ctox_status group_sum(ctox_exec *e, ctox_matvec *mv, uint32_t m, MvOut *o) {
     return CTOX_OK;
 }
 
-// One decoder layer for m positions. The fragments of the layer's fused input projection are
-// already in place; on return h holds the layer output and the fragments of `next` (if any) hold
-// rmsnorm(h, next_norm); xn_out (if any) receives that normalised vector.
+// Up to this many positions the input norm of a projection runs inside the streaming kernel's
+// prologue; with more positions the prologue (every CTA repeats its slice's fragments for every
+// position) costs more than the separate kernel it replaces (measured on the 5-position verify pass).
+constexpr uint32_t kFuseNormMaxPos = 2;
+
+NormSource norm_of(const ctox_exec *e, const float *h, const float *w) {
+    return NormSource{h, e->norm_scratch, w, residual_parts(e->cfg.hidden_size), e->cfg.hidden_size,
+                      e->cfg.rms_norm_epsilon};
+}
+
+// One decoder layer for m positions. Up to kFuseNormMaxPos positions the projections normalise h
+// in their own prologue: on entry norm_scratch holds the sums of squares of h, and unless
+// xn_out/next ask for the final norm as a kernel (xn_out receives the normalised vector, `next`
+// its fragments) it holds those of the output on return. With more positions the fragments of the
+// layer's input projection are in place on entry and `next`/next_norm name the next projection.
 ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t rope_pos0, uint64_t slot0,
                        const uint32_t *page_table, const float *next_norm, float *xn_out, ctox_matvec *next) {
     ctox_ctx *ctx = e->ctx;
@@ -821,7 +833,9 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
     const ctox_model_config &c = e->cfg;
     LayerW &lw = e->w[l];
     LayerS &ls = e->s[l];
-    EX(matvec_stream_prepared(lw.in_fan, 0, m));
+    const bool fuse = m <= kFuseNormMaxPos;
+    const NormSource in_norm = norm_of(e, h, lw.in_ln);
+    EX(matvec_stream_prepared(lw.in_fan, 0, m, fuse ? &in_norm : nullptr));
     const MvOut fan = mv_out(lw.in_fan, m);
     const MvIn out_in = mv_in(lw.out);
     if (!lw.full) {
@@ -844,18 +858,25 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
     EX(matvec_stream_prepared(lw.out, 0, m));
     MvOut o = mv_out(lw.out, m);
     EX(group_sum(e, lw.out, m, &o));
-    const MvIn gu_in = mv_in(lw.gate_up);
-    launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in, e->norm_scratch);
-    EX(matvec_stream_prepared(lw.gate_up, 0, m));
+    const NormSource post_norm = norm_of(e, h, lw.post_ln);
+    if (fuse) {
+        launch_residual_add(st, h, &o, c.hidden_size, m, e->norm_scratch);
+    } else {
+        const MvIn gu_in = mv_in(lw.gate_up);
+        launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in,
+                                  e->norm_scratch);
+    }
+    EX(matvec_stream_prepared(lw.gate_up, 0, m, fuse ? &post_norm : nullptr));
     launch_swiglu_prep(st, mv_out(lw.gate_up, m), c.intermediate_size, m, mv_in(lw.down));
     EX(matvec_stream_prepared(lw.down, 0, m));
     MvOut d = mv_out(lw.down, m);
     EX(group_sum(e, lw.down, m, &d));
-    if (next) {
-        const MvIn nin = mv_in(next);
-        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, &nin, e->norm_scratch);
+    if (xn_out || next) {
+        const MvIn nin = next ? mv_in(next) : MvIn{};
+        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out,
+                                  next ? &nin : nullptr, e->norm_scratch);
     } else {
-        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out, nullptr, e->norm_scratch);
+        launch_residual_add(st, h, &d, c.hidden_size, m, e->norm_scratch);
     }
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
@@ -867,13 +888,19 @@ ctox_status target_pass(ctox_exec *e, uint32_t m, uint64_t pos0) {
     ctox_ctx *ctx = e->ctx;
     const ctox_model_config &c = e->cfg;
     EX(matvec_embed_rows(e->embed, e->tokens_dev, m, e->h));
-    const MvIn first = mv_in(e->w[0].in_fan);
-    launch_residual_norm_prep(ctx->stream, e->h, nullptr, e->w[0].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
-                              nullptr, &first, e->norm_scratch);
+    const bool fuse = m <= kFuseNormMaxPos;
+    if (fuse) {
+        launch_residual_add(ctx->stream, e->h, nullptr, c.hidden_size, m, e->norm_scratch);
+    } else {
+        const MvIn first = mv_in(e->w[0].in_fan);
+        launch_residual_norm_prep(ctx->stream, e->h, nullptr, e->w[0].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
+                                  nullptr, &first, e->norm_scratch);
+    }
     for (uint32_t l = 0; l < e->n_layers; ++l) {
         const bool last = l + 1 == e->n_layers;
-        EX(layer_body(e, l, e->h, m, pos0, pos0, e->page_table, last ? e->final_norm : e->w[l + 1].in_ln,
-                      last ? e->final_hidden : nullptr, last ? e->lm_head : e->w[l + 1].in_fan));
+        const float *next_norm = last ? e->final_norm : (fuse ? nullptr : e->w[l + 1].in_ln);
+        ctox_matvec *next = last ? e->lm_head : (fuse ? nullptr : e->w[l + 1].in_fan);
+        EX(layer_body(e, l, e->h, m, pos0, pos0, e->page_table, next_norm, last ? e->final_hidden : nullptr, next));
     }
     return CTOX_OK;
 }
@@ -913,9 +940,13 @@ ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const float *h
     EX(matvec_stream_prepared(e->mtp_fc, 0, m));
     CTOX_CUDA(ctx, cudaMemsetAsync(e->mtp_h, 0, (size_t)m * c.hidden_size * 4, ctx->stream));
     const MvOut fc = mv_out(e->mtp_fc, m);
-    const MvIn lin = mv_in(e->w[L].in_fan);
-    launch_residual_norm_prep(ctx->stream, e->mtp_h, &fc, e->w[L].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
-                              nullptr, &lin, e->norm_scratch);
+    if (m <= kFuseNormMaxPos) {
+        launch_residual_add(ctx->stream, e->mtp_h, &fc, c.hidden_size, m, e->norm_scratch);
+    } else {
+        const MvIn lin = mv_in(e->w[L].in_fan);
+        launch_residual_norm_prep(ctx->stream, e->mtp_h, &fc, e->w[L].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
+                                  nullptr, &lin, e->norm_scratch);
+    }
     EX(layer_body(e, L, e->mtp_h, m, abs_pos0, abs_pos0 - 1, e->mtp_page_table, e->mtp_norm, e->mtp_hidden,
                   nullptr));
     if (draft_slot >= 0) {

@@ -91,6 +91,11 @@ __global__ void k_norm_prep(const float *__restrict__ h, const float *__restrict
     }
 }
 
+void launch_residual_add(cudaStream_t st, float *h, const MvOut *add, uint32_t hidden, uint32_t m, float *scratch) {
+    MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0, nullptr, 0};
+    launch_pdl(k_residual_add, dim3(residual_parts(hidden), m), dim3(256), 0, st, h, a, add != nullptr, hidden, scratch);
+}
+
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
                                uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch) {
     MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0, nullptr, 0};

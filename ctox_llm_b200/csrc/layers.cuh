@@ -41,6 +41,10 @@ struct AttnGeom {
 // scratch: m * ceil(hidden / 256) floats.
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
                                uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch);
+// h[m] (+= matvec output) and the partial sums of squares of the result: scratch[m][ceil(hidden/256)],
+// the form NormSource takes.
+void launch_residual_add(cudaStream_t st, float *h, const MvOut *add, uint32_t hidden, uint32_t m, float *scratch);
+inline uint32_t residual_parts(uint32_t hidden) { return (hidden + 255) / 256; }
 // MTP input: fragments of concat(rmsnorm_1p(embed(tok[m])), rmsnorm_1p(prev_hidden[m])) * s_in.
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next);

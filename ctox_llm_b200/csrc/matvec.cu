@@ -236,6 +236,14 @@ struct StreamParams {
     uint32_t ctas_per_slice;
     uint32_t warps_per_slice;  // warps that take work (<= units per slice)
     uint32_t npos, max_pieces;
+    // When norm_h is set the activations are not read from xfrag/meta: every CTA builds the
+    // fragments of its column slice itself from x = rmsnorm_1p(norm_h) * s_in.
+    const float *norm_h;      // [npos][norm_hidden]
+    const float *norm_sumsq;  // [npos][norm_parts] partial sums of squares of norm_h
+    const float *norm_w;      // [norm_hidden]
+    const float *norm_s_in;   // [norm_hidden] or null
+    uint32_t norm_parts, norm_hidden;
+    float norm_eps;
 };
 
 // Four MMAs of one 16-row x 64-column block; cw = this lane's code vector(s).
@@ -278,6 +286,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     uint8_t *ms = xs + xfrag_bytes;
     uint8_t *zero = ms + ((meta_bytes + 15) & ~15u);  // 16 zero bytes for lanes without operands
     uint64_t *bars = reinterpret_cast<uint64_t *>(zero + 16);
+    float *inv_rms = reinterpret_cast<float *>(&bars[WARPS * STAGES + 1]);  // [kMaxPosPerPass]
     const uint32_t xbar = smem_u32(&bars[WARPS * STAGES]);
     const uint32_t my_bars = smem_u32(&bars[warp * STAGES]);
     const uint32_t my_stage = smem_u32(stages + warp * STAGES * kChunkBytes);
@@ -317,7 +326,37 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     // The activations come from the kernels before this one: wait for them here, with the first
     // STAGES chunks of every warp already on their way.
     pdl_wait();
-    if (threadIdx.x == 0) {
+    if (p.norm_h) {
+        // Fused input norm: xn = h * rsqrt(mean(h^2) + eps) * (1 + w), x = xn * s_in, written as
+        // fragments straight into shared memory while the first weight chunks are in flight.
+        if (threadIdx.x < p.npos) {
+            float sq = 0.f;
+            for (uint32_t q = 0; q < p.norm_parts; ++q) sq += p.norm_sumsq[threadIdx.x * p.norm_parts + q];
+            inv_rms[threadIdx.x] = 1.0f / sqrtf(sq / (float)p.norm_hidden + p.norm_eps);
+        }
+        __syncthreads();
+        const int i = threadIdx.x & 15;
+        const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+        const uint32_t first_block = slice * slice_blocks;
+        for (uint32_t task = threadIdx.x >> 4; task < slice_blocks * p.npos; task += (WARPS * 32) >> 4) {
+            const uint32_t b = task / p.npos, m = task % p.npos;
+            const uint32_t c = (first_block + b) * 64 + i * 4;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (c < p.norm_hidden) {  // norm_hidden is a multiple of 64: whole blocks
+                const float4 hv = *reinterpret_cast<const float4 *>(p.norm_h + (size_t)m * p.norm_hidden + c);
+                const float4 wv = *reinterpret_cast<const float4 *>(p.norm_w + c);
+                float4 sv = make_float4(1.f, 1.f, 1.f, 1.f);
+                if (p.norm_s_in) sv = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
+                const float inv = inv_rms[m];
+                v[0] = hv.x * inv * (1.0f + wv.x) * sv.x;
+                v[1] = hv.y * inv * (1.0f + wv.y) * sv.y;
+                v[2] = hv.z * inv * (1.0f + wv.z) * sv.z;
+                v[3] = hv.w * inv * (1.0f + wv.w) * sv.w;
+            }
+            prep_block(v, i, gmask, (int)b, (int)m, (int)p.npos, DT, xs, reinterpret_cast<float2 *>(ms));
+        }
+        __syncthreads();
+    } else if (threadIdx.x == 0) {
         fence_proxy_async();
         mbar_expect_tx(xbar, xfrag_bytes + meta_bytes);
         const uint8_t *xsrc = p.xfrag + (size_t)slice * xfrag_bytes;
@@ -331,7 +370,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
                  meta_bytes, xbar);
     }
     if (!active || nchunks == 0) return;  // warp 0 of every CTA is active and waits for xbar below
-    bool ok = mbar_wait(xbar, 0);
+    bool ok = p.norm_h ? true : mbar_wait(xbar, 0);
 
     // lanes whose B column / position does not exist read zeros with stride 0
     uint32_t b_base[NT], b_stride[NT], b_half[NT], m_base[NT], m_stride[NT];
@@ -725,7 +764,7 @@ size_t stream_smem_bytes(int dt, StreamCfg cfg, uint32_t slice_blocks, uint32_t 
     const size_t stage = (size_t)cfg.warps * cfg.stages * chunk;
     const size_t xfrag = (size_t)slice_blocks * 2 * npos * 128;
     const size_t meta = ((size_t)slice_blocks * npos * 8 + 15) & ~(size_t)15;
-    return stage + xfrag + meta + 16 + ((size_t)cfg.warps * cfg.stages + 1) * 8;
+    return stage + xfrag + meta + 16 + ((size_t)cfg.warps * cfg.stages + 1) * 8 + kMaxPosPerPass * 4;
 }
 
 // The widest launch shape whose shared memory fits; warps == 0 when none does.
@@ -927,7 +966,7 @@ uint32_t matvec_positions_per_pass(ctox_matvec *mv) {
     return per_pass;
 }
 
-ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos) {
+ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos, const NormSource *norm) {
     ctox_ctx *ctx = mv->ctx;
     MatvecPart &p = mv->parts[part_index];
     const MatvecPart::Split &split = p.split[npos > 4 ? 1 : 0];
@@ -951,6 +990,19 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     sp.warps_per_slice = split.warps_per_slice;
     sp.npos = npos;
     sp.max_pieces = p.max_pieces;
+    sp.norm_h = nullptr;
+    if (norm) {
+        if (norm->hidden != mv->columns || norm->hidden % 64)
+            return fail(ctx, CTOX_SHAPE, "fused norm: %u values for a matrix of %llu columns", norm->hidden,
+                        (unsigned long long)mv->columns);
+        sp.norm_h = norm->h;
+        sp.norm_sumsq = norm->sumsq;
+        sp.norm_w = norm->w;
+        sp.norm_s_in = mv->s_in;
+        sp.norm_parts = norm->parts;
+        sp.norm_hidden = norm->hidden;
+        sp.norm_eps = norm->eps;
+    }
     const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
     const unsigned grid = split.ctas_per_slice * p.slices;
     timing_begin(ctx);
@@ -1477,6 +1529,7 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             sp.warps_per_slice = split.warps_per_slice;
             sp.npos = npos;
             sp.max_pieces = p.max_pieces;
+            sp.norm_h = nullptr;
             const StreamCfg cfg{split.warps, split.stages};
             const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
             const unsigned grid = split.ctas_per_slice * p.slices;
