@@ -235,7 +235,7 @@ struct StreamParams {
     uint32_t slices;           // column slices (each CTA works inside one slice)
     uint32_t ctas_per_slice;
     uint32_t warps_per_slice;  // warps that take work (<= units per slice)
-    uint32_t npos, max_pieces;
+    uint32_t npos, max_pieces, trace_slot;
     // When norm_h is set the activations are not read from xfrag/meta: every CTA builds the
     // fragments of its column slice itself from x = rmsnorm_1p(norm_h) * s_in.
     const float *norm_h;      // [npos][norm_hidden]
@@ -268,9 +268,30 @@ __device__ __forceinline__ void block_mma(float (&c)[4], uint32_t w0, uint32_t w
     }
 }
 
+// Build with -DCTOX_TRACE to record, per launch of the streaming kernel, the global timer at
+// entry, when its dependency was met, when its activations were ready and when its last warp
+// finished (ctox_debug_trace_dump reads the ring): the timeline with dependent launches
+// overlapping, which a profiler that serialises kernels cannot show.
+#ifdef CTOX_TRACE
+__device__ unsigned long long g_trace[4 * 16384];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define CTOX_TRACE_MARK(cond, idx, slot) \
+    if (cond) g_trace[4 * (slot) + (idx)] = gtime()
+#define CTOX_TRACE_END(cond, slot) \
+    if (cond) atomicMax(&g_trace[4 * (slot) + 3], gtime())
+#else
+#define CTOX_TRACE_MARK(cond, idx, slot)
+#define CTOX_TRACE_END(cond, slot)
+#endif
 template <int DT, int WARPS, int STAGES, int NT>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamParams p) {
     pdl_launch();
+    [[maybe_unused]] const bool tracer = blockIdx.x == 0 && threadIdx.x == 0;
+    CTOX_TRACE_MARK(tracer, 0, p.trace_slot);
     using F = Fmt<DT>;
     constexpr uint32_t kST = F::kSuperTileBytes;
     constexpr uint32_t kUnitBytes = 2 * kST;                      // one tile pair
@@ -326,6 +347,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     // The activations come from the kernels before this one: wait for them here, with the first
     // STAGES chunks of every warp already on their way.
     pdl_wait();
+    CTOX_TRACE_MARK(tracer, 1, p.trace_slot);
     if (p.norm_h) {
         // Fused input norm: xn = h * rsqrt(mean(h^2) + eps) * (1 + w), x = xn * s_in, written as
         // fragments straight into shared memory while the first weight chunks are in flight.
@@ -369,6 +391,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         bulk_g2s(smem_u32(ms), reinterpret_cast<const uint8_t *>(p.meta) + (size_t)slice * meta_bytes,
                  meta_bytes, xbar);
     }
+    CTOX_TRACE_MARK(tracer, 2, p.trace_slot);
     if (!active || nchunks == 0) return;  // warp 0 of every CTA is active and waits for xbar below
     bool ok = p.norm_h ? true : mbar_wait(xbar, 0);
 
@@ -513,6 +536,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         return;
     }
     close_pair(cur_pair, cur_ks == p.kst_s);
+    CTOX_TRACE_END(lane == 0, p.trace_slot);
 }
 
 // y[pos][row] = act((sum over slices and pieces + bias[row]) * s_out[row]); one thread per (row, pos).
@@ -990,6 +1014,8 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     sp.warps_per_slice = split.warps_per_slice;
     sp.npos = npos;
     sp.max_pieces = p.max_pieces;
+    static uint32_t trace_counter = 0;
+    sp.trace_slot = trace_counter++ % 16384;
     sp.norm_h = nullptr;
     if (norm) {
         if (norm->hidden != mv->columns || norm->hidden % 64)
@@ -1530,6 +1556,7 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             sp.npos = npos;
             sp.max_pieces = p.max_pieces;
             sp.norm_h = nullptr;
+            sp.trace_slot = 16383;
             const StreamCfg cfg{split.warps, split.stages};
             const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
             const unsigned grid = split.ctas_per_slice * p.slices;
@@ -1547,3 +1574,9 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
+
+#ifdef CTOX_TRACE
+extern "C" int ctox_debug_trace_dump(unsigned long long *out, int n) {
+    return (int)cudaMemcpyFromSymbol(out, g_trace, (size_t)n * 4 * 8);
+}
+#endif
