@@ -77,23 +77,14 @@ __global__ void __launch_bounds__(kHeadThreads) k_head_stats(
 #pragma unroll
         for (int m = 0; m < kMaxPosPerPass; ++m) lg[m] = 0.f;
         for (uint32_t sl = 0; sl < slices; ++sl) {
-            const float4 *base = reinterpret_cast<const float4 *>(
-                partial + ((size_t)pr * slices + sl) * max_pieces * (kPairRows * kMaxPosPerPass) +
-                rl * kMaxPosPerPass);
+            // a slot is [position][32 rows]: the 32 rows of a pair are one coalesced line per position
+            const float *base = partial + ((size_t)pr * slices + sl) * max_pieces * (kPairRows * kMaxPosPerPass) + rl;
             const uint32_t n = pieces[pr * slices + sl];
             for (uint32_t q = 0; q < n; ++q) {
-                const float4 v0 = base[q * (kPairRows * kMaxPosPerPass / 4)];
-                lg[0] += v0.x;
-                lg[1] += v0.y;
-                lg[2] += v0.z;
-                lg[3] += v0.w;
-                if (npos > 4) {
-                    const float4 v1 = base[q * (kPairRows * kMaxPosPerPass / 4) + 1];
-                    lg[4] += v1.x;
-                    lg[5] += v1.y;
-                    lg[6] += v1.z;
-                    lg[7] += v1.w;
-                }
+                const float *sl_q = base + q * (kPairRows * kMaxPosPerPass);
+#pragma unroll
+                for (int m = 0; m < kMaxPosPerPass; ++m)
+                    if ((uint32_t)m < npos) lg[m] += sl_q[m * kPairRows];
             }
         }
         const float so = s_out ? s_out[row] : 1.0f, bi = bias ? bias[row] : 0.0f;

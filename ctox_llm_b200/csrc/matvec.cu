@@ -228,7 +228,7 @@ struct StreamParams {
     const uint8_t *wprep;
     const uint8_t *xfrag;   // prepared activations (k_prep_x), [block][half][column][quarter][8 fp16]
     const float2 *meta;     // [block][position]
-    float *partial;         // [pair][slice][piece][32][kMaxPosPerPass] raw sums
+    float *partial;         // [pair][slice][piece][kMaxPosPerPass][32 rows] raw sums
     int32_t *error_flag;
     uint32_t pairs;            // 32-row tile pairs
     uint32_t kst_s;            // 256-column super-tiles per column slice
@@ -435,10 +435,11 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
             if (has_m[nt]) {  // hi + lo columns of position 4*nt + t
-                slot[rloc[0] * kMaxPosPerPass + 4 * nt + t] = acc[nt][0] + acc[nt][1];
-                slot[rloc[1] * kMaxPosPerPass + 4 * nt + t] = acc[nt][2] + acc[nt][3];
-                slot[rloc[2] * kMaxPosPerPass + 4 * nt + t] = acc[nt][4] + acc[nt][5];
-                slot[rloc[3] * kMaxPosPerPass + 4 * nt + t] = acc[nt][6] + acc[nt][7];
+                float *col = slot + (4 * nt + t) * kPairRows;  // a slot is [position][32 rows]
+                col[rloc[0]] = acc[nt][0] + acc[nt][1];
+                col[rloc[1]] = acc[nt][2] + acc[nt][3];
+                col[rloc[2]] = acc[nt][4] + acc[nt][5];
+                col[rloc[3]] = acc[nt][6] + acc[nt][7];
             }
         }
     };
@@ -554,7 +555,7 @@ __global__ void k_matvec_finish(const float *__restrict__ partial, const uint8_t
     float v = 0.f;
     for (uint32_t sl = 0; sl < slices; ++sl) {
         const float *base = partial + ((size_t)pr * slices + sl) * max_pieces * (kPairRows * kMaxPosPerPass) +
-                            rl * kMaxPosPerPass + pos;
+                            pos * kPairRows + rl;
         const uint32_t n = pieces[pr * slices + sl];
         for (uint32_t q = 0; q < n; ++q) v += base[q * (kPairRows * kMaxPosPerPass)];
     }

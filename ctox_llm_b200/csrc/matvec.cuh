@@ -57,7 +57,7 @@ namespace ctox {
 // Positions one pass of the streaming kernel can take for this matrix (shared-memory bound).
 uint32_t matvec_positions_per_pass(ctox_matvec *mv);
 // Enqueues activation preparation + streaming kernel for `npos` positions of one part; raw sums
-// land in part.partial ([pairs][max_pieces][32][kMaxPosPerPass]); no finish kernel is run.
+// land in part.partial ([pairs][slices][max_pieces][kMaxPosPerPass][32 rows]); no finish kernel is run.
 ctox_status matvec_stream_pass(ctox_matvec *mv, size_t part_index, const void *x, uint32_t x_dtype,
                                uint32_t npos, uint64_t x_stride);
 // Input of a matvec given as "rmsnorm_1p of h": the streaming kernel normalises and builds the

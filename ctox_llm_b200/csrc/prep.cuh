@@ -60,7 +60,7 @@ __device__ __forceinline__ float matvec_output(const float *__restrict__ partial
     const uint32_t pr = row >> 5, rl = row & 31;
     float v = 0.f;
     for (uint32_t sl = 0; sl < slices; ++sl) {
-        const float *base = partial + ((size_t)pr * slices + sl) * max_pieces * (32 * 8) + rl * 8 + pos;
+        const float *base = partial + ((size_t)pr * slices + sl) * max_pieces * (32 * 8) + pos * 32 + rl;
         const uint32_t n = pieces[pr * slices + sl];
         for (uint32_t q = 0; q < n; ++q) v += base[q * (32 * 8)];
     }
