@@ -16,7 +16,11 @@ namespace ctox {
 
 MvOut mv_out(ctox_matvec *mv, uint32_t npos) {
     MatvecPart &p = mv->parts[0];
-    return MvOut{p.partial, p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, p.slices, p.max_pieces, nullptr, 0};
+    const MatvecPart::Split &sp = p.split[npos > 4 ? 1 : 0];
+    const uint64_t units = (uint64_t)p.pairs * p.kst_s;
+    const bool fits = (units + 1) * sp.warps_per_slice + units < (1ull << 32);  // piece_count() in 32 bits
+    return MvOut{p.partial, sp.pieces, mv->s_out, p.slices, p.max_pieces, nullptr, 0,
+                 p.kst_s, fits ? sp.warps_per_slice : 0, p.pairs};
 }
 MvIn mv_in(ctox_matvec *mv) {
     return MvIn{mv->xfrag, mv->meta, mv->s_in, (uint32_t)mv->columns, mv->blocks_padded, mv->parts[0].dt};
@@ -24,6 +28,9 @@ MvIn mv_in(ctox_matvec *mv) {
 
 __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t pos) {
     if (o.plain) return o.plain[(size_t)pos * o.plain_stride + row];
+    if (o.warps_per_slice)
+        return matvec_output_n(o.partial, piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs), o.slices,
+                               o.max_pieces, o.s_out, row, pos);
     return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
 }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
@@ -92,13 +99,13 @@ __global__ void k_norm_prep(const float *__restrict__ h, const float *__restrict
 }
 
 void launch_residual_add(cudaStream_t st, float *h, const MvOut *add, uint32_t hidden, uint32_t m, float *scratch) {
-    MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0, nullptr, 0};
+    MvOut a = add ? *add : MvOut{};
     launch_pdl(k_residual_add, dim3(residual_parts(hidden), m), dim3(256), 0, st, h, a, add != nullptr, hidden, scratch);
 }
 
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
                                uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch) {
-    MvOut a = add ? *add : MvOut{nullptr, nullptr, nullptr, 0, 0, nullptr, 0};
+    MvOut a = add ? *add : MvOut{};
     MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
     const uint32_t nparts = (hidden + 255) / 256;
     launch_pdl(k_residual_add, dim3(nparts, m), dim3(256), 0, st, h, a, add != nullptr, hidden, scratch);

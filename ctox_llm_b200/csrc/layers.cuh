@@ -19,6 +19,10 @@ struct MvOut {
     // column-split matvec has after its partial results were summed over the tensor-parallel group.
     const float *plain;
     uint32_t plain_stride;
+    // The work split that produced the partial sums (units of a slice = pairs * kst_s, warps per
+    // slice): consumers compute the piece count of a row pair instead of loading it.
+    // warps_per_slice == 0: use the table.
+    uint32_t kst_s, warps_per_slice, pairs;
 };
 // Input of the next matvec: where to write the activation fragments.
 struct MvIn {

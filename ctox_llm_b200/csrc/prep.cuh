@@ -51,6 +51,18 @@ __device__ __forceinline__ void prep_block(const float (&v)[4], int i, unsigned 
             make_float2(-code_offset(dt) * code_scale(dt) * sum, inv * code_unit(dt) / code_scale(dt));
 }
 
+// Pieces of row pair pr of a streamed matvec: the warps (warps_per_slice of them, over
+// units = pairs * kst_s per slice) whose ranges [w * units / nw, (w + 1) * units / nw) meet the
+// pair's units. Same formula as the host's table (matvec.cu, prepare_part); computing it saves the
+// consumer a dependent load. 32-bit: the caller checks that (units + 1) * nw + units fits.
+__device__ __forceinline__ uint32_t piece_count(uint32_t pr, uint32_t kst_s, uint32_t nw, uint32_t pairs) {
+    const uint32_t units = pairs * kst_s;
+    const uint32_t u_first = pr * kst_s, u_last = u_first + kst_s - 1;
+    const uint32_t w_first = ((u_first + 1) * nw + units - 1) / units - 1;
+    const uint32_t w_last = ((u_last + 1) * nw + units - 1) / units - 1;
+    return w_last - w_first + 1;
+}
+
 // Sum of the raw partial sums the streaming kernel left for (row, pos), times s_out (+ bias):
 // the value of one matvec output. pieces: [pair][slice].
 __device__ __forceinline__ float matvec_output(const float *__restrict__ partial,
@@ -65,6 +77,38 @@ __device__ __forceinline__ float matvec_output(const float *__restrict__ partial
         for (uint32_t q = 0; q < n; ++q) v += base[q * (32 * 8)];
     }
     return s_out ? v * s_out[row] : v;
+}
+
+// The same value with the piece count computed (n pieces in every slice) and the loads of up to
+// eight pieces issued before the first addition: one trip to L2 instead of one per piece plus the
+// table lookup. Same order of additions.
+__device__ __forceinline__ float matvec_output_n(const float *__restrict__ partial, uint32_t n, uint32_t slices,
+                                                 uint32_t max_pieces, const float *__restrict__ s_out,
+                                                 uint32_t row, uint32_t pos) {
+    const uint32_t pr = row >> 5, rl = row & 31;
+    const float *first = partial + (size_t)pr * slices * max_pieces * (32 * 8) + pos * 32 + rl;
+    const float so = s_out ? s_out[row] : 1.0f;
+    const uint32_t total = slices * n;
+    float v = 0.f;
+    uint32_t sl = 0, q = 0;
+    for (uint32_t k0 = 0; k0 < total; k0 += 8) {
+        float buf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            buf[j] = 0.f;
+            if (k0 + j < total) {
+                buf[j] = first[((size_t)sl * max_pieces + q) * (32 * 8)];
+                if (++q == n) {
+                    q = 0;
+                    ++sl;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (k0 + j < total) v += buf[j];
+    }
+    return s_out ? v * so : v;
 }
 
 }  // namespace ctox
