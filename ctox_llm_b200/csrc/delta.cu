@@ -16,6 +16,7 @@
 // state_in and state_out may differ, which is how a speculative verify pass
 // leaves the committed state untouched.
 #include "common.cuh"
+#include "layers.cuh"
 
 #include <cmath>
 
@@ -163,6 +164,163 @@ __global__ void k_gated_delta_prepare(const float *__restrict__ a, const float *
     const float x = a[idx] + dt_bias[h];
     const float sp = x > 20.0f ? x : log1pf(expf(x));
     log_decay[idx] = -expf(a_log[h]) * sp;
+}
+
+
+// ------------------------------------------------------------------ one kernel per linear-attention layer
+// Everything between the fused input projection and out_proj of a linear-attention layer
+// (decoder.rs:806-938) for one value head per CTA, 512 threads:
+//   1. causal conv + SiLU (reference.rs:159-187) over the head's 128 q, 128 k and 128 v channels for
+//      the m positions, the head's z, and decay / beta from a, b (decoder.rs:29-35,881,897-902);
+//   2. the recurrence above, four 32-column slices side by side (warp = slice * 4 + row group), with
+//      exactly the arithmetic and the order of k_gated_delta_scan128, so that a later re-scan of an
+//      accepted prefix from the kept (q, k, v, g, beta) reproduces this pass bit for bit;
+//   3. rms_norm_gated (reference.rs:66-93) and the two 64-column fragments of out_proj's input.
+// The q and k channels are shared by the value heads of a key head; the first of them stores them.
+constexpr int kLaMaxPos = 8;
+
+__global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int npos) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float qs[kLaMaxPos][kDeltaDim], ks[kLaMaxPos][kDeltaDim], vs[kLaMaxPos][kDeltaDim];
+    __shared__ float zs[kLaMaxPos][kDeltaDim], core[kLaMaxPos][kDeltaDim];
+    __shared__ float gs[kLaMaxPos], bs[kLaMaxPos], q_inv[kLaMaxPos], k_inv[kLaMaxPos];
+    __shared__ float nred[2][4];
+    __shared__ float red[4][4][kDeltaSlice];  // [slice][row group][column]
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t head = blockIdx.x, rep = a.value_heads / a.qk_heads, khead = head / rep;
+    const bool owns_qk = head % rep == 0;
+    const uint32_t channels = 2 * a.key_width + a.value_width;
+
+    // ---- 1. conv + SiLU, z, decay, beta
+    if (tid < 384) {
+        const uint32_t part = tid >> 7, d = tid & 127;
+        const uint32_t ch = part == 0 ? khead * kDeltaDim + d
+                            : part == 1 ? a.key_width + khead * kDeltaDim + d
+                                        : 2 * a.key_width + head * kDeltaDim + d;
+        const bool store = part == 2 || owns_qk;
+        float st[8], cw[8];
+        for (uint32_t j = 0; j < a.conv_kernel; ++j) {
+            st[j] = a.conv_state[(size_t)ch * a.conv_kernel + j];
+            cw[j] = a.conv_w[(size_t)ch * a.conv_kernel + j];
+        }
+        for (int m = 0; m < npos; ++m) {
+            const float x = out_of(a.fan, ch, m);
+            if (store) a.conv_in[(size_t)m * channels + ch] = x;
+            for (uint32_t j = 0; j + 1 < a.conv_kernel; ++j) st[j] = st[j + 1];
+            st[a.conv_kernel - 1] = x;
+            float sum = 0.f;
+            for (uint32_t j = 0; j < a.conv_kernel; ++j) sum += st[j] * cw[j];
+            const float y = silu_f(sum);
+            if (part == 0) {
+                qs[m][d] = y;
+                if (store) a.q[(size_t)m * a.key_width + khead * kDeltaDim + d] = y;
+            } else if (part == 1) {
+                ks[m][d] = y;
+                if (store) a.k[(size_t)m * a.key_width + khead * kDeltaDim + d] = y;
+            } else {
+                vs[m][d] = y;
+                a.v[(size_t)m * a.value_width + head * kDeltaDim + d] = y;
+            }
+        }
+    } else {
+        const uint32_t d = tid - 384;
+        for (int m = 0; m < npos; ++m) zs[m][d] = out_of(a.fan, channels + head * kDeltaDim + d, m);
+        if (d < (uint32_t)npos) {
+            const float x = out_of(a.fan, channels + a.value_width + head, d) + a.dt_bias[head];
+            const float sp = x > 20.0f ? x : log1pf(expf(x));  // decoder.rs:29-35
+            const float g = -expf(a.a_log[head]) * sp;
+            gs[d] = g;
+            a.log_decay[(size_t)d * a.value_heads + head] = g;
+        } else if (d >= 32 && d < 32 + (uint32_t)npos) {
+            const uint32_t m = d - 32;
+            const float b = 1.0f / (1.0f + expf(-out_of(a.fan, channels + a.value_width + a.value_heads + head, m)));
+            bs[m] = b;
+            a.beta[(size_t)m * a.value_heads + head] = b;
+        }
+    }
+    // the recurrent state of this thread: rows rg * 32 .. + 32 of column slice * 32 + lane
+    const uint32_t slice = warp >> 2, rg = warp & 3, col = slice * kDeltaSlice + lane;
+    float s[32];
+    {
+        const float *sin_ = a.state_in + ((size_t)head * kDeltaDim + rg * 32) * kDeltaDim + col;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = sin_[(size_t)i * kDeltaDim];
+    }
+    __syncthreads();
+    // L2 norms of q and k per position, with the reduction tree of the stand-alone scan: value d in
+    // lane d % 32 of warp d / 32, butterfly, then the four warp sums in order
+    for (int m = 0; m < npos; ++m) {
+        if (warp < 8) {
+            const float x = warp < 4 ? qs[m][warp * 32 + lane] : ks[m][(warp - 4) * 32 + lane];
+            float x2 = x * x;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) x2 += __shfl_xor_sync(0xffffffffu, x2, o);
+            if (lane == 0) nred[warp >> 2][warp & 3] = x2;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            q_inv[m] = 1.0f / sqrtf(nred[0][0] + nred[0][1] + nred[0][2] + nred[0][3] + kL2Eps);
+            k_inv[m] = 1.0f / sqrtf(nred[1][0] + nred[1][1] + nred[1][2] + nred[1][3] + kL2Eps);
+        }
+        __syncthreads();
+    }
+
+    // ---- 2. recurrence
+    const float query_scale = 1.0f / sqrtf((float)kDeltaDim);
+    for (int m = 0; m < npos; ++m) {
+        const float qi = q_inv[m], ki = k_inv[m];
+        const float decay = expf(gs[m]), b = bs[m], vj = vs[m][col];
+        float mem = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            s[i] *= decay;
+            mem += s[i] * ks[m][rg * 32 + i] * ki;
+        }
+        red[slice][rg][lane] = mem;
+        __syncthreads();
+        const float delta = (vj - (red[slice][0][lane] + red[slice][1][lane] + red[slice][2][lane] + red[slice][3][lane])) * b;
+        __syncthreads();
+        float o = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            s[i] += ks[m][rg * 32 + i] * ki * delta;
+            o += s[i] * qs[m][rg * 32 + i] * qi * query_scale;
+        }
+        red[slice][rg][lane] = o;
+        __syncthreads();
+        if (rg == 0)
+            core[m][col] = red[slice][0][lane] + red[slice][1][lane] + red[slice][2][lane] + red[slice][3][lane];
+        __syncthreads();
+    }
+    {
+        float *sout = a.state_out + ((size_t)head * kDeltaDim + rg * 32) * kDeltaDim + col;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sout[(size_t)i * kDeltaDim] = s[i];
+    }
+
+    // ---- 3. gated norm and fragments: warp m takes position m, four values per lane
+    if (warp < (uint32_t)npos) {
+        const int m = warp;
+        const float4 c = *reinterpret_cast<const float4 *>(&core[m][lane * 4]);
+        const float4 g = *reinterpret_cast<const float4 *>(&zs[m][lane * 4]);
+        float sq = c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        const float inv = 1.0f / sqrtf(sq / 128.0f + a.eps);
+        const uint32_t ocol = head * kDeltaDim + lane * 4;
+        const float cs[4] = {c.x, c.y, c.z, c.w}, gz[4] = {g.x, g.y, g.z, g.w};
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            v[j] = cs[j] * inv * a.norm_w[lane * 4 + j] * silu_f(gz[j]) * (a.next.s_in ? a.next.s_in[ocol + j] : 1.0f);
+        const unsigned gmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+        prep_block(v, lane & 15, gmask, (int)(head * 2 + (lane >> 4)), m, npos, a.next.dt, a.next.xfrag, a.next.meta);
+    }
+}
+
+void launch_linear_attention(cudaStream_t st, const LinearAttnArgs &a, uint32_t m) {
+    launch_pdl(k_linear_attention, dim3(a.value_heads), dim3(512), 0, st, a, (int)m);
 }
 
 }  // namespace ctox

@@ -839,13 +839,11 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
     const MvOut fan = mv_out(lw.in_fan, m);
     const MvIn out_in = mv_in(lw.out);
     if (!lw.full) {
-        launch_linear_mid(st, fan, e->key_width, e->value_width, c.linear_num_value_heads,
-                          c.linear_conv_kernel_dim, ls.conv_state, lw.conv_w, lw.a_log, lw.dt_bias, m, ls.conv_in,
-                          ls.q, ls.k, ls.v, e->lz, ls.g, ls.beta);
-        EX(ctox_gated_delta_scan(ctx, ls.q, ls.k, ls.v, ls.g, ls.beta, ls.delta[ls.cur], ls.delta[ls.cur ^ 1],
-                                 e->lcore, m, c.linear_num_value_heads, c.linear_num_key_heads, 128, 128));
-        launch_gated_norm_prep(st, e->lcore, e->lz, lw.lin_norm, c.rms_norm_epsilon, c.linear_num_value_heads, 128,
-                               m, out_in);
+        LinearAttnArgs la{fan, e->key_width, e->value_width, c.linear_num_value_heads, c.linear_num_key_heads,
+                          c.linear_conv_kernel_dim, ls.conv_state, lw.conv_w, lw.a_log, lw.dt_bias, lw.lin_norm,
+                          c.rms_norm_epsilon, ls.delta[ls.cur], ls.delta[ls.cur ^ 1], ls.conv_in, ls.q, ls.k, ls.v,
+                          ls.g, ls.beta, out_in};
+        launch_linear_attention(st, la, m);
     } else {
         const AttnGeom g = attn_geom(e);
         launch_attn_pre(st, fan, g, lw.q_norm, lw.k_norm, rope_pos0, slot0, m, e->aq, e->agate, ls.k_cache,

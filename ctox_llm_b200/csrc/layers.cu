@@ -26,15 +26,6 @@ MvIn mv_in(ctox_matvec *mv) {
     return MvIn{mv->xfrag, mv->meta, mv->s_in, (uint32_t)mv->columns, mv->blocks_padded, mv->parts[0].dt};
 }
 
-__device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t pos) {
-    if (o.plain) return o.plain[(size_t)pos * o.plain_stride + row];
-    if (o.warps_per_slice)
-        return matvec_output_n(o.partial, piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs), o.slices,
-                               o.max_pieces, o.s_out, row, pos);
-    return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
-}
-__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
-
 __device__ __forceinline__ float block_sum(float v, float *red) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -787,41 +778,68 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     }
 }
 
-// Merge of the splits, sigmoid gate (reference.rs:502-515) and fragments for o_proj: one
-// 16-lane group per (position, query head, 64-dimension block).
-__global__ void k_attn_combine_prep(AttnGeom g, const float *__restrict__ ws, const float *__restrict__ gate,
-                                    int npos, uint32_t splits, MvIn next) {
+// Merge of the splits, sigmoid gate (reference.rs:502-515) and fragments for o_proj: one CTA per
+// (position, query head), one thread per head dimension. The weights of the splits are formed once
+// per CTA; every thread then adds its dimension over the splits, eight loads at a time.
+__global__ void __launch_bounds__(256) k_attn_combine_prep(AttnGeom g, const float *__restrict__ ws,
+                                                         const float *__restrict__ gate, int npos, uint32_t splits,
+                                                         MvIn next) {
     pdl_launch();
     pdl_wait();
-    const uint32_t gid = (blockIdx.x * blockDim.x + threadIdx.x) >> 4;
-    const int i = threadIdx.x & 15;
-    const uint32_t hd = g.head_dim, bph = hd / 64, G = g.q_heads / g.kv_heads, NQ = G * npos;
-    if (gid >= (uint32_t)npos * g.q_heads * bph) return;
-    const uint32_t blk = gid % bph, hq = (gid / bph) % g.q_heads;
-    const int m = gid / (bph * g.q_heads);
-    const uint32_t kh = hq / G, qi = m * G + hq % G;
-    const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-    float mx = -INFINITY;
-    for (uint32_t sp = 0; sp < splits; ++sp)
-        mx = fmaxf(mx, ws[((size_t)(kh * splits + sp) * NQ + qi) * (hd + 2) + hd]);
-    float den = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (uint32_t sp = 0; sp < splits; ++sp) {
-        const float *r = ws + ((size_t)(kh * splits + sp) * NQ + qi) * (hd + 2);
-        const float ms = r[hd];
-        if (!(ms > -INFINITY)) continue;
-        const float wgt = expf(ms - mx);
-        den += r[hd + 1] * wgt;
+    __shared__ float wgt[64];    // per split: exp(max_s - max) / denominator
+    __shared__ float vals[256];  // the head's output, gated and scaled
+    const uint32_t hd = g.head_dim, G = g.q_heads / g.kv_heads, NQ = G * npos;
+    const uint32_t hq = blockIdx.x % g.q_heads;
+    const int m = blockIdx.x / g.q_heads;
+    const uint32_t kh = hq / G, qi = m * G + hq % G, d = threadIdx.x;  // blockDim.x == head_dim
+    const float *base = ws + ((size_t)kh * splits * NQ + qi) * (hd + 2);
+    const size_t split_stride = (size_t)NQ * (hd + 2);
+    if (threadIdx.x < 32) {  // splits <= 64: two per lane
+        float ms[2], ls[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[j] += r[blk * 64 + i * 4 + j] * wgt;
-    }
-    float v[4];
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t sp = threadIdx.x + 32 * j;
+            ms[j] = sp < splits ? base[sp * split_stride + hd] : -INFINITY;
+            ls[j] = sp < splits ? base[sp * split_stride + hd + 1] : 0.f;
+        }
+        float mx = fmaxf(ms[0], ms[1]);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t d = blk * 64 + i * 4 + j, col = hq * hd + d;
-        const float gt = gate[((size_t)m * g.q_heads + hq) * hd + d];
-        v[j] = acc[j] / den * (1.0f / (1.0f + expf(-gt))) * (next.s_in ? next.s_in[col] : 1.0f);
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float w[2], den = 0.f;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            w[j] = ms[j] > -INFINITY ? expf(ms[j] - mx) : 0.f;
+            den += ls[j] * w[j];
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+            if (threadIdx.x + 32 * j < splits) wgt[threadIdx.x + 32 * j] = w[j] / den;
     }
-    prep_block(v, i, gmask, (int)(hq * bph + blk), m, npos, next.dt, next.xfrag, next.meta);
+    __syncthreads();
+    float acc = 0.f;
+    for (uint32_t s0 = 0; s0 < splits; s0 += 8) {
+        float buf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) buf[j] = s0 + j < splits ? base[(s0 + j) * split_stride + d] : 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (s0 + j < splits) acc += buf[j] * wgt[s0 + j];
+    }
+    const float gt = gate[((size_t)m * g.q_heads + hq) * hd + d];
+    const uint32_t col = hq * hd + d;
+    vals[d] = acc * (1.0f / (1.0f + expf(-gt))) * (next.s_in ? next.s_in[col] : 1.0f);
+    __syncthreads();
+    const uint32_t bph = hd / 64;
+    if (threadIdx.x < bph * 16) {
+        const int i = threadIdx.x & 15;
+        const uint32_t blk = threadIdx.x >> 4;
+        const float v[4] = {vals[blk * 64 + i * 4], vals[blk * 64 + i * 4 + 1], vals[blk * 64 + i * 4 + 2],
+                            vals[blk * 64 + i * 4 + 3]};
+        const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
+        prep_block(v, i, gmask, (int)(hq * bph + blk), m, npos, next.dt, next.xfrag, next.meta);
+    }
 }
 
 size_t attn_workspace_bytes(const AttnGeom &g, uint32_t m, uint32_t max_splits) {
@@ -864,8 +882,8 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
             launch_pdl(k_attention_mma<2>, dim3(g.kv_heads * splits), dim3(256), smem, st, 
                 g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
                 cache_slot, (int)m, splits, workspace);
-        const uint32_t groups = m * g.q_heads * (g.head_dim / 64);
-        launch_pdl(k_attn_combine_prep, dim3((groups * 16 + 255) / 256), dim3(256), 0, st, g, workspace, gate, (int)m, splits, next);
+        launch_pdl(k_attn_combine_prep, dim3(m * g.q_heads), dim3(g.head_dim), 0, st, g, workspace, gate, (int)m, splits,
+                   next);
         return;
     }
 #define CTOX_ATTN(T)                                                                                        \
@@ -885,8 +903,7 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
     else
         CTOX_ATTN(float);
 #undef CTOX_ATTN
-    const uint32_t groups = m * g.q_heads * (g.head_dim / 64);
-    launch_pdl(k_attn_combine_prep, dim3((groups * 16 + 255) / 256), dim3(256), 0, st, g, workspace, gate, (int)m, splits, next);
+    launch_pdl(k_attn_combine_prep, dim3(m * g.q_heads), dim3(g.head_dim), 0, st, g, workspace, gate, (int)m, splits, next);
 }
 
 }  // namespace ctox

@@ -78,4 +78,34 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
                       uint32_t page_tokens, uint64_t cache_slot, uint32_t m, uint32_t splits, float *workspace,
                       const MvIn &next);
 
+// Linear attention of one layer in one kernel: causal conv + SiLU over this head's channels of the
+// fused projection, decay/beta, the gated-delta recurrence over the m positions, rms_norm_gated and
+// the fragments for out_proj. One CTA per value head. The pass's conv inputs and (q, k, v, g,
+// beta) are kept so that a commit of any accepted prefix can re-scan (delta.cu).
+struct LinearAttnArgs {
+    MvOut fan;
+    uint32_t key_width, value_width, value_heads, qk_heads, conv_kernel;
+    const float *conv_state, *conv_w, *a_log, *dt_bias, *norm_w;
+    float eps;
+    const float *state_in;
+    float *state_out, *conv_in, *q, *k, *v, *log_decay, *beta;
+    MvIn next;
+};
+void launch_linear_attention(cudaStream_t st, const LinearAttnArgs &a, uint32_t m);
+
 }  // namespace ctox
+
+#ifdef __CUDACC__
+#include "prep.cuh"
+namespace ctox {
+// One output value of an earlier matvec.
+__device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t pos) {
+    if (o.plain) return o.plain[(size_t)pos * o.plain_stride + row];
+    if (o.warps_per_slice)
+        return matvec_output_n(o.partial, piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs), o.slices,
+                               o.max_pieces, o.s_out, row, pos);
+    return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
+}
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+}  // namespace ctox
+#endif
