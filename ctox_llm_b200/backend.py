@@ -189,6 +189,14 @@ class B200Backend:
         return tok.value
 
     # -- housekeeping ----------------------------------------------------------------------
+    def sample_topk_topp(self, logits_ptr: int, n: int, temperature: float, top_k: int, top_p: float,
+                         draw: float) -> int:
+        """Sampler::sample_with_draw (sampler.rs:65-144) over device logits."""
+        tok = C.c_uint32()
+        self._check(self._lib.ctox_sample_topk_topp(self._ctx, C.c_void_p(logits_ptr), n, C.c_float(temperature),
+                                                    top_k, C.c_float(top_p), C.c_float(draw), C.byref(tok)))
+        return tok.value
+
     def synchronize(self) -> None:
         self._check(self._lib.ctox_ctx_synchronize(self._ctx))
 

@@ -13,6 +13,9 @@
 
 #include "../../include/ctox_b200.h"
 
+namespace ctox {
+struct TpPeer;
+}
 struct ctox_ctx {
     int device = 0;
     cudaStream_t stream = nullptr;
@@ -30,6 +33,7 @@ struct ctox_ctx {
     // tensor parallelism: NCCL communicator over the GPUs of one box (tp.cu); world 1 = none
     int tp_rank = 0, tp_world = 1;
     void *nccl_comm = nullptr;
+    ctox::TpPeer *tp_peer = nullptr;  // peer-memory all-reduce state (tp.cu); null = NCCL only
     // optional per-kernel timing of the dominant kernel (benchmark support)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timing_events;
@@ -70,6 +74,11 @@ ctox_status ensure_scratch(ctox_ctx *ctx, size_t bytes);
 // Collectives over the tensor-parallel group, enqueued on the context's stream (tp.cu).
 ctox_status tp_all_reduce_sum_f32(ctox_ctx *ctx, float *buf, size_t n);
 ctox_status tp_all_gather(ctox_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank);
+// Sets up the peer-memory all-reduce for vectors of up to `elems` floats per rank (buffers and
+// flags every rank can address); falls back to NCCL (returns CTOX_OK with ctx->tp_peer null) when
+// peer mapping is unavailable or CTOX_TP_P2P=0.
+ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems);
+void tp_peer_destroy(ctox_ctx *ctx);
 // When timing is enabled, brackets the next launches with a CUDA event pair on
 // the context's stream; both are no-ops otherwise.
 void timing_begin(ctox_ctx *ctx);

@@ -669,7 +669,11 @@ ctox_status ctox_exec_warmup(ctox_exec *e) {
     WALLOC(e->lcore, P * e->value_width * 4);
     WALLOC(e->norm_scratch, P * ((H + 255) / 256) * 4);
     WALLOC(e->draft_logits, (size_t)(c.draft_vocab ? (e->draft_n ? e->draft_n : 1) : e->vocab_l) * 4);
-    if (e->tp_world > 1) WALLOC(e->tp_buf, P * H * 4);
+    if (e->tp_world > 1) {
+        WALLOC(e->tp_buf, P * H * 4);
+        rc = tp_peer_init(ctx, (size_t)P * H);
+        if (rc) return rc;
+    }
     WALLOC(e->tokens_dev, (P + 1) * 4);
     WALLOC(e->mtp_tokens_dev, (P + 1) * 4);
     const uint32_t slots = (c.max_context_tokens + c.kv_page_tokens - 1) / c.kv_page_tokens * c.kv_page_tokens;
@@ -821,6 +825,28 @@ NormSource norm_of(const ctox_exec *e, const float *h, const float *w) {
                       e->cfg.rms_norm_epsilon};
 }
 
+// h += output of a projection back to the hidden width (summed over the tensor-parallel group when
+// there is one: through peer memory, else NCCL), with the partial sums of squares in norm_scratch;
+// then, unless the next projection normalises in its own prologue (`fused_norm`), the norm kernel.
+ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, const float *norm_w, float *xn_out,
+                         ctox_matvec *next, bool fused_norm) {
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    MvOut o = mv_out(mv, m);
+    if (ctx->tp_peer) {
+        EX(tp_peer_reduce_add(ctx, o, c.hidden_size, m, h, e->norm_scratch));
+    } else {
+        EX(group_sum(e, mv, m, &o));
+        launch_residual_add(ctx->stream, h, &o, c.hidden_size, m, e->norm_scratch);
+    }
+    if (!fused_norm) {
+        const MvIn nin = next ? mv_in(next) : MvIn{};
+        launch_norm_prep(ctx->stream, h, norm_w, c.rms_norm_epsilon, c.hidden_size, m, xn_out, next ? &nin : nullptr,
+                         e->norm_scratch);
+    }
+    return CTOX_OK;
+}
+
 // One decoder layer for m positions. Up to kFuseNormMaxPos positions the projections normalise h
 // in their own prologue: on entry norm_scratch holds the sums of squares of h, and unless
 // xn_out/next ask for the final norm as a kernel (xn_out receives the normalised vector, `next`
@@ -854,28 +880,12 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
                          c.kv_page_tokens, slot0, m, splits, e->attn_ws, out_in);
     }
     EX(matvec_stream_prepared(lw.out, 0, m));
-    MvOut o = mv_out(lw.out, m);
-    EX(group_sum(e, lw.out, m, &o));
+    EX(add_and_norm(e, h, lw.out, m, lw.post_ln, nullptr, lw.gate_up, fuse));
     const NormSource post_norm = norm_of(e, h, lw.post_ln);
-    if (fuse) {
-        launch_residual_add(st, h, &o, c.hidden_size, m, e->norm_scratch);
-    } else {
-        const MvIn gu_in = mv_in(lw.gate_up);
-        launch_residual_norm_prep(st, h, &o, lw.post_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr, &gu_in,
-                                  e->norm_scratch);
-    }
     EX(matvec_stream_prepared(lw.gate_up, 0, m, fuse ? &post_norm : nullptr));
     launch_swiglu_prep(st, mv_out(lw.gate_up, m), c.intermediate_size, m, mv_in(lw.down));
     EX(matvec_stream_prepared(lw.down, 0, m));
-    MvOut d = mv_out(lw.down, m);
-    EX(group_sum(e, lw.down, m, &d));
-    if (xn_out || next) {
-        const MvIn nin = next ? mv_in(next) : MvIn{};
-        launch_residual_norm_prep(st, h, &d, next_norm, c.rms_norm_epsilon, c.hidden_size, m, xn_out,
-                                  next ? &nin : nullptr, e->norm_scratch);
-    } else {
-        launch_residual_add(st, h, &d, c.hidden_size, m, e->norm_scratch);
-    }
+    EX(add_and_norm(e, h, lw.down, m, next_norm, xn_out, next, !(xn_out || next)));
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
@@ -1102,6 +1112,18 @@ ctox_status ctox_exec_last_logits(ctox_exec *e, uint32_t position, float *out) {
                                    cudaMemcpyDeviceToHost, ctx->stream));
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return CTOX_OK;
+}
+
+ctox_status ctox_exec_select_target(ctox_exec *e, uint32_t position, float temperature, uint32_t top_k,
+                                    float top_p, float draw, uint32_t *token) {
+    if (!e || !token) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (!e->keep_logits || !e->logits || position >= kMaxPass)
+        return fail(ctx, CTOX_INVALID_STATE, "logits are not kept (ctox_exec_keep_logits) or position out of range");
+    if (e->tp_world > 1)
+        return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "select_target: the kept logits are a vocabulary shard");
+    return ctox_sample_topk_topp(ctx, e->logits + (size_t)position * e->vocab_l, e->vocab_l, temperature, top_k, top_p,
+                                 draw, token);
 }
 
 }  // extern "C"

@@ -350,6 +350,164 @@ __global__ void k_argmax_ranks(const ArgmaxPartial *__restrict__ gathered, uint3
     if (status_out) *status_out = a.nonfinite;
 }
 
+// ------------------------------------------------------------------ top-k / top-p sampling with a supplied draw
+// Sampler::sample_with_draw (sampler.rs:65-144): z = logit / T; candidates ordered by z descending,
+// ties by token id descending; the first top_k; weights exp(z - z_max); the nucleus ends at the first
+// candidate whose running sum reaches top_p * total; the token is the first whose running sum
+// reaches draw * nucleus_total. All sums are sequential fp32 in candidate order, as in the
+// reference. The reference's CUDA sampler takes top_k in 1..=256
+// (backend/cuda_runtime.rs:2828, kernels/cuda/q2q4_fused_matvec_sm86.cu:2648-2667); this one 1..=1024.
+// One CTA: radix select of the top_k-th largest key (then of the largest ids among equal keys),
+// gather, bitonic sort of the <= 1024 candidates, one thread for the sequential part.
+constexpr uint32_t kSampleMaxTopK = 1024, kSampleThreads = 1024;
+
+// result: [0] token, [1] status (0 ok, 1 invalid arguments, 2 non-finite value), [2] nucleus size
+__global__ void __launch_bounds__(kSampleThreads) k_sample_topk_topp(const float *__restrict__ logits, uint32_t n,
+                                                                    uint32_t top_k, float inv_t, float top_p,
+                                                                    float draw, uint32_t *__restrict__ result) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ uint32_t hist[256];
+    __shared__ unsigned long long cand[kSampleMaxTopK];  // (key << 32) | id, sorted descending
+    __shared__ uint32_t sh_prefix, sh_need, sh_count, sh_bad;
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) {
+        sh_bad = 0;
+        sh_count = 0;
+    }
+    __syncthreads();
+    if (n == 0 || top_k == 0 || top_k > kSampleMaxTopK || !isfinite(inv_t) || inv_t <= 0.f || !isfinite(top_p) ||
+        top_p <= 0.f || top_p > 1.f || !isfinite(draw) || draw < 0.f || draw >= 1.f) {
+        if (tid == 0) {
+            result[0] = 0;
+            result[1] = 1;
+            result[2] = 0;
+        }
+        return;
+    }
+    const uint32_t k = top_k < n ? top_k : n;
+    auto key_of = [&](uint32_t i) {
+        const float z = logits[i] * inv_t;
+        if (!isfinite(logits[i]) || !isfinite(z)) sh_bad = 1;
+        return total_order_key(z);
+    };
+    // ---- the k-th largest key, 8 bits at a time from the top
+    uint32_t prefix = 0, need = k;  // among keys matching `prefix` on the bits fixed so far, `need` more
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t mask_hi = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+        for (uint32_t i = tid; i < n; i += kSampleThreads) {
+            const uint32_t key = key_of(i);
+            if ((key & mask_hi) == (prefix & mask_hi)) atomicAdd(&hist[(key >> shift) & 0xff], 1u);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t acc = 0, b = 255;
+            for (;; --b) {  // from the largest digit down
+                if (acc + hist[b] >= need || b == 0) break;
+                acc += hist[b];
+            }
+            sh_prefix = prefix | (b << shift);
+            sh_need = need - acc;
+        }
+        __syncthreads();
+        prefix = sh_prefix;
+        need = sh_need;
+        __syncthreads();
+    }
+    const uint32_t kth_key = prefix;  // `need` of the candidates carry exactly this key: the largest ids
+    // ---- among keys == kth_key, the need-th largest id (same select over the ids)
+    uint32_t id_prefix = 0, id_need = need;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t mask_hi = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+        for (uint32_t i = tid; i < n; i += kSampleThreads)
+            if (key_of(i) == kth_key && (i & mask_hi) == (id_prefix & mask_hi)) atomicAdd(&hist[(i >> shift) & 0xff], 1u);
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t acc = 0, b = 255;
+            for (;; --b) {
+                if (acc + hist[b] >= id_need || b == 0) break;
+                acc += hist[b];
+            }
+            sh_prefix = id_prefix | (b << shift);
+            sh_need = id_need - acc;
+        }
+        __syncthreads();
+        id_prefix = sh_prefix;
+        id_need = sh_need;
+        __syncthreads();
+    }
+    const uint32_t min_tie_id = id_prefix;
+    // ---- gather the k candidates, pad, sort descending
+    for (uint32_t i = tid; i < kSampleMaxTopK; i += kSampleThreads) cand[i] = 0ull;
+    __syncthreads();
+    for (uint32_t i = tid; i < n; i += kSampleThreads) {
+        const uint32_t key = key_of(i);
+        if (key > kth_key || (key == kth_key && i >= min_tie_id)) {
+            const uint32_t slot = atomicAdd(&sh_count, 1u);
+            if (slot < kSampleMaxTopK) cand[slot] = ((unsigned long long)key << 32) | i;
+        }
+    }
+    __syncthreads();
+    for (uint32_t size = 2; size <= kSampleMaxTopK; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            const uint32_t partner = tid ^ stride;
+            if (partner > tid) {
+                const bool descending = (tid & size) == 0;
+                const unsigned long long a = cand[tid], b = cand[partner];
+                if ((a < b) == descending) {
+                    cand[tid] = b;
+                    cand[partner] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    // ---- the sequential part (sampler.rs:108-143)
+    if (tid == 0) {
+        uint32_t status = sh_bad ? 2u : 0u, token = 0, nucleus = 0;
+        if (status == 0 && sh_count != k) status = 2;  // cannot happen for finite input
+        if (status == 0) {
+            const float maximum = logits[(uint32_t)(cand[0] & 0xffffffffull)] * inv_t;
+            float normalization = 0.f;
+            for (uint32_t i = 0; i < k; ++i)
+                normalization += expf(logits[(uint32_t)(cand[i] & 0xffffffffull)] * inv_t - maximum);
+            if (!isfinite(normalization) || normalization <= 0.f) {
+                status = 2;
+            } else {
+                float cumulative = 0.f;
+                nucleus = k;
+                for (uint32_t i = 0; i < k; ++i) {
+                    cumulative += expf(logits[(uint32_t)(cand[i] & 0xffffffffull)] * inv_t - maximum);
+                    if (cumulative >= top_p * normalization) {
+                        nucleus = i + 1;
+                        break;
+                    }
+                }
+                float nucleus_total = 0.f;
+                for (uint32_t i = 0; i < nucleus; ++i)
+                    nucleus_total += expf(logits[(uint32_t)(cand[i] & 0xffffffffull)] * inv_t - maximum);
+                const float threshold = draw * nucleus_total;
+                cumulative = 0.f;
+                token = (uint32_t)(cand[nucleus - 1] & 0xffffffffull);
+                for (uint32_t i = 0; i < nucleus; ++i) {
+                    cumulative += expf(logits[(uint32_t)(cand[i] & 0xffffffffull)] * inv_t - maximum);
+                    if (threshold <= cumulative) {
+                        token = (uint32_t)(cand[i] & 0xffffffffull);
+                        break;
+                    }
+                }
+            }
+        }
+        result[0] = token;
+        result[1] = status;
+        result[2] = nucleus;
+    }
+}
+
 }  // namespace ctox
 
 using namespace ctox;
@@ -439,6 +597,39 @@ ctox_status ctox_argmax_f32_host(ctox_ctx *ctx, const float *logits_dev, uint32_
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     const uint32_t *r = (const uint32_t *)ctx->pinned;
     if (r[1]) return fail(ctx, CTOX_INVALID_STATE, "argmax input contains a non-finite logit");
+    *token = r[0];
+    return CTOX_OK;
+}
+
+ctox_status ctox_sample_topk_topp(ctox_ctx *ctx, const float *logits_dev, uint32_t n, float temperature,
+                                  uint32_t top_k, float top_p, float draw, uint32_t *token) {
+    if (!ctx || !token) return CTOX_INVALID_STATE;
+    if (!logits_dev || n == 0) return fail(ctx, CTOX_INVALID_ARTIFACT, "sampler logits are empty");
+    if (!std::isfinite(draw) || !(draw >= 0.f && draw < 1.f))
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "sampler draw must lie in [0, 1)");
+    if (!std::isfinite(temperature) || temperature < 0.f)
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "temperature must be finite and non-negative");
+    if (!(std::isfinite(top_p) && top_p > 0.f && top_p <= 1.f))
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "top_p must lie in (0, 1]");
+    if (temperature == 0.f) return ctox_argmax_f32_host(ctx, logits_dev, n, nullptr, token);  // sampler.rs:76-82
+    if (top_k == 0 || top_k > kSampleMaxTopK)
+        return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "device sampler takes top_k in 1..=%u", kSampleMaxTopK);
+    const float inv_t = 1.0f / temperature;
+    if (!std::isfinite(inv_t)) return fail(ctx, CTOX_INVALID_ARTIFACT, "temperature is too small");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    HeadScratch hs;
+    ctox_status rc = head_scratch(ctx, hs);
+    if (rc) return rc;
+    launch_pdl(k_sample_topk_topp, dim3(1), dim3(kSampleThreads), 0, ctx->stream, logits_dev, n, top_k, inv_t, top_p,
+               draw, hs.tokens);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    rc = ensure_pinned(ctx, 16);
+    if (rc) return rc;
+    CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, hs.tokens, 12, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const uint32_t *r = (const uint32_t *)ctx->pinned;
+    if (r[1] == 2) return fail(ctx, CTOX_INVALID_ARTIFACT, "sampler input or normalisation is not finite");
+    if (r[1]) return fail(ctx, CTOX_INVALID_ARTIFACT, "sampler arguments rejected on the device");
     *token = r[0];
     return CTOX_OK;
 }

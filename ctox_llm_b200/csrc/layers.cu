@@ -94,16 +94,20 @@ void launch_residual_add(cudaStream_t st, float *h, const MvOut *add, uint32_t h
     launch_pdl(k_residual_add, dim3(residual_parts(hidden), m), dim3(256), 0, st, h, a, add != nullptr, hidden, scratch);
 }
 
-void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
-                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch) {
-    MvOut a = add ? *add : MvOut{};
+void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps, uint32_t hidden, uint32_t m,
+                      float *xn_out, const MvIn *next, const float *scratch) {
     MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
     const uint32_t nparts = (hidden + 255) / 256;
-    launch_pdl(k_residual_add, dim3(nparts, m), dim3(256), 0, st, h, a, add != nullptr, hidden, scratch);
     const uint32_t nblocks = next ? next->blocks_padded : (hidden + 63) / 64;
     const uint32_t groups = nblocks * m;
-    launch_pdl(k_norm_prep, dim3((groups * 16 + 127) / 128), dim3(128), 0, st, h, scratch, nparts, w, eps, hidden, (int)m, xn_out, n,
-                                                          next != nullptr, nblocks);
+    launch_pdl(k_norm_prep, dim3((groups * 16 + 127) / 128), dim3(128), 0, st, h, scratch, nparts, w, eps, hidden,
+               (int)m, xn_out, n, next != nullptr, nblocks);
+}
+
+void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
+                               uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch) {
+    launch_residual_add(st, h, add, hidden, m, scratch);
+    launch_norm_prep(st, h, w, eps, hidden, m, xn_out, next, scratch);
 }
 
 // [rmsnorm(embed) | rmsnorm(prev_hidden)] -> fragments (2 * hidden columns). One CTA per

@@ -49,6 +49,12 @@ void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, cons
 // the form NormSource takes.
 void launch_residual_add(cudaStream_t st, float *h, const MvOut *add, uint32_t hidden, uint32_t m, float *scratch);
 inline uint32_t residual_parts(uint32_t hidden) { return (hidden + 255) / 256; }
+// The norm half of launch_residual_norm_prep alone (scratch already holds the sums of squares of h).
+void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps, uint32_t hidden, uint32_t m,
+                      float *xn_out, const MvIn *next, const float *scratch);
+// h += sum over the tensor-parallel group of a matvec's output, through peer memory (tp.cu);
+// scratch receives the partial sums of squares like launch_residual_add.
+ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *scratch);
 // MTP input: fragments of concat(rmsnorm_1p(embed(tok[m])), rmsnorm_1p(prev_hidden[m])) * s_in.
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next);

@@ -4,6 +4,7 @@
 // dependency on it; the rendezvous (sharing the unique id) is the caller's, e.g.
 // torch.distributed.
 #include "common.cuh"
+#include "layers.cuh"
 
 #include <dlfcn.h>
 
@@ -66,6 +67,207 @@ ctox_status tp_all_gather(ctox_ctx *ctx, const void *send, void *recv, size_t by
 
 }  // namespace ctox
 
+// ------------------------------------------------------------------ one-shot all-reduce over peer memory
+// The sum of a column-split projection over the group without a library collective: every rank
+// finishes its partial vector into a buffer its peers can address, raises a flag in every peer's
+// memory, and the residual kernel of every rank adds the W buffers itself, in rank order (all
+// ranks get identical bits). Chunked by 256 columns so a consumer CTA only waits for the chunk it
+// needs. Plain peer stores and loads over NVLink; no multicast. Waits are bounded: a peer that
+// never signals makes the kernel set the device error word and carry on.
+namespace ctox {
+
+constexpr uint32_t kTpChunk = 256, kTpMaxWorld = 8;
+
+struct TpPeer {
+    uint32_t world = 0, rank = 0, seq = 0;
+    size_t elems = 0;         // floats per buffer
+    uint32_t chunks = 0;      // flag slots per source rank
+    float *buf = nullptr;     // own: [2 parities][elems]
+    uint32_t *flags = nullptr;  // own: [world][chunks], written by the peers
+    float *peer_buf[kTpMaxWorld] = {nullptr};
+    uint32_t *peer_flags[kTpMaxWorld] = {nullptr};
+};
+struct TpPeerPtrs {  // by value into the kernels
+    float *buf[kTpMaxWorld];
+    uint32_t *flags[kTpMaxWorld];
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_relaxed_sys(const float *p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// y[pos][row] of this rank's partial result for one chunk of 256 rows -> own buffer, then the
+// chunk's flag in every rank's memory (own included) takes the value seq.
+__global__ void __launch_bounds__(kTpChunk) k_tp_finish_signal(MvOut o, uint32_t rows, int npos, float *own,
+                                                             TpPeerPtrs peers, uint32_t rank, uint32_t world,
+                                                             uint32_t chunks, uint32_t seq) {
+    pdl_launch();
+    pdl_wait();
+    const uint32_t row = blockIdx.x * kTpChunk + threadIdx.x;
+    if (row < rows)
+        for (int m = 0; m < npos; ++m) own[(size_t)m * rows + row] = out_of(o, row, m);
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + rank * chunks + blockIdx.x, seq);
+}
+
+// h[m][c] += sum over ranks of their partial vectors (rank order); partial sums of squares of the
+// result per 256-column part, like k_residual_add. flags: this rank's [world][chunks].
+__global__ void __launch_bounds__(kTpChunk) k_tp_residual_add(float *__restrict__ h, TpPeerPtrs peers,
+                                                            const uint32_t *flags, uint32_t world, uint32_t chunks,
+                                                            uint32_t seq, uint32_t hidden, float *__restrict__ sumsq,
+                                                            int32_t *error_flag) {
+    pdl_launch();
+    pdl_wait();
+    __shared__ float red[kTpChunk / 32];
+    const int m = blockIdx.y;
+    if (threadIdx.x < world) {
+        const uint32_t *f = flags + threadIdx.x * chunks + blockIdx.x;
+        const long long t0 = clock64();
+        while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
+            if (clock64() - t0 > 2000000000ll) {  // ~1 s: a peer is gone
+                atomicExch(error_flag, DEV_ERR_WAIT_TIMEOUT);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    const uint32_t c = blockIdx.x * kTpChunk + threadIdx.x;
+    float v = 0.f;
+    if (c < hidden) {
+        v = h[(size_t)m * hidden + c];
+        for (uint32_t r = 0; r < world; ++r) v += ld_relaxed_sys(peers.buf[r] + (size_t)m * hidden + c);
+        h[(size_t)m * hidden + c] = v;
+    }
+    float s = v * v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (unsigned w = 0; w < kTpChunk / 32; ++w) t += red[w];  // fixed order
+        sumsq[m * gridDim.x + blockIdx.x] = t;
+    }
+}
+
+ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
+    if (ctx->tp_world <= 1 || ctx->tp_peer) return CTOX_OK;
+    const char *env = getenv("CTOX_TP_P2P");
+    if (env && env[0] == '0') return CTOX_OK;
+    const uint32_t W = (uint32_t)ctx->tp_world, R = (uint32_t)ctx->tp_rank;
+    if (W > kTpMaxWorld) return CTOX_OK;
+    TpPeer *tp = new TpPeer();
+    tp->world = W;
+    tp->rank = R;
+    tp->elems = elems;
+    tp->chunks = (uint32_t)((elems + kTpChunk - 1) / kTpChunk);  // an upper bound for every vector width
+    struct Card {
+        cudaIpcMemHandle_t buf, flags;
+        int device, ok;
+    } mine{}, all[kTpMaxWorld];
+    mine.device = ctx->device;
+    bool ok = cudaMalloc((void **)&tp->buf, 2 * elems * sizeof(float)) == cudaSuccess &&
+              cudaMalloc((void **)&tp->flags, (size_t)W * tp->chunks * 4) == cudaSuccess &&
+              cudaMemset(tp->flags, 0, (size_t)W * tp->chunks * 4) == cudaSuccess &&
+              cudaMemset(tp->buf, 0, 2 * elems * sizeof(float)) == cudaSuccess &&
+              cudaIpcGetMemHandle(&mine.buf, tp->buf) == cudaSuccess &&
+              cudaIpcGetMemHandle(&mine.flags, tp->flags) == cudaSuccess;
+    mine.ok = ok ? 1 : 0;
+    // exchange the cards through the communicator the group already has
+    Card *dev = nullptr;
+    ctox_status rc = CTOX_OK;
+    if (cudaMalloc((void **)&dev, sizeof(Card) * (W + 1)) != cudaSuccess) {
+        rc = fail(ctx, CTOX_MEMORY_BUDGET, "tp: no memory for the peer exchange");
+    } else {
+        cudaMemcpyAsync(dev + W, &mine, sizeof(Card), cudaMemcpyHostToDevice, ctx->stream);
+        rc = tp_all_gather(ctx, dev + W, dev, sizeof(Card));
+        if (!rc) {
+            cudaMemcpyAsync(all, dev, sizeof(Card) * W, cudaMemcpyDeviceToHost, ctx->stream);
+            if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(ctx, CTOX_INVALID_STATE, "tp: peer exchange failed");
+        }
+        cudaFree(dev);
+    }
+    if (rc) {
+        cudaFree(tp->buf);
+        cudaFree(tp->flags);
+        delete tp;
+        return rc;
+    }
+    for (uint32_t r = 0; r < W && ok; ++r) ok = all[r].ok != 0;
+    for (uint32_t r = 0; r < W && ok; ++r) {
+        if (r == R) {
+            tp->peer_buf[r] = tp->buf;
+            tp->peer_flags[r] = tp->flags;
+            continue;
+        }
+        ok = cudaIpcOpenMemHandle((void **)&tp->peer_buf[r], all[r].buf, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess &&
+             cudaIpcOpenMemHandle((void **)&tp->peer_flags[r], all[r].flags, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+    }
+    // every rank must take the same path: agree through one more exchange
+    int agree = ok ? 1 : 0, *agree_dev = nullptr, votes[kTpMaxWorld] = {0};
+    if (cudaMalloc((void **)&agree_dev, sizeof(int) * (W + 1)) == cudaSuccess) {
+        cudaMemcpyAsync(agree_dev + W, &agree, sizeof(int), cudaMemcpyHostToDevice, ctx->stream);
+        if (!tp_all_gather(ctx, agree_dev + W, agree_dev, sizeof(int))) {
+            cudaMemcpyAsync(votes, agree_dev, sizeof(int) * W, cudaMemcpyDeviceToHost, ctx->stream);
+            cudaStreamSynchronize(ctx->stream);
+        }
+        cudaFree(agree_dev);
+    }
+    for (uint32_t r = 0; r < W; ++r) ok = ok && votes[r] == 1;
+    cudaGetLastError();  // a refused mapping is not an error of the context: NCCL serves instead
+    ctx->tp_peer = tp;
+    if (!ok) tp_peer_destroy(ctx);
+    return CTOX_OK;
+}
+
+void tp_peer_destroy(ctox_ctx *ctx) {
+    TpPeer *tp = ctx->tp_peer;
+    if (!tp) return;
+    cudaStreamSynchronize(ctx->stream);
+    for (uint32_t r = 0; r < tp->world; ++r) {
+        if (r == tp->rank) continue;
+        if (tp->peer_buf[r]) cudaIpcCloseMemHandle(tp->peer_buf[r]);
+        if (tp->peer_flags[r]) cudaIpcCloseMemHandle(tp->peer_flags[r]);
+    }
+    if (tp->buf) cudaFree(tp->buf);
+    if (tp->flags) cudaFree(tp->flags);
+    delete tp;
+    ctx->tp_peer = nullptr;
+}
+
+// Enqueues "h += sum over the group of this matvec's output" for m positions through peer memory.
+ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *sumsq) {
+    TpPeer *tp = ctx->tp_peer;
+    if (!tp) return fail(ctx, CTOX_INVALID_STATE, "tp: peer all-reduce is not set up");
+    if ((size_t)m * rows > tp->elems) return fail(ctx, CTOX_SHAPE, "tp: vector of %u x %u exceeds the peer buffer", m, rows);
+    const uint32_t seq = ++tp->seq, parity = seq & 1;
+    const uint32_t chunks_used = (rows + kTpChunk - 1) / kTpChunk;
+    TpPeerPtrs pp{};
+    for (uint32_t r = 0; r < tp->world; ++r) {
+        pp.buf[r] = tp->peer_buf[r] + (size_t)parity * tp->elems;
+        pp.flags[r] = tp->peer_flags[r];
+    }
+    launch_pdl(k_tp_finish_signal, dim3(chunks_used), dim3(kTpChunk), 0, ctx->stream, o, rows, (int)m,
+               tp->buf + (size_t)parity * tp->elems, pp, tp->rank, tp->world, tp->chunks, seq);
+    launch_pdl(k_tp_residual_add, dim3(chunks_used, m), dim3(kTpChunk), 0, ctx->stream, h, pp, tp->flags, tp->world,
+               tp->chunks, seq, rows, sumsq, ctx->dev_error);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+}  // namespace ctox
+
 using namespace ctox;
 
 extern "C" {
@@ -104,6 +306,7 @@ ctox_status ctox_tp_init(ctox_ctx *ctx, const char *nccl_path, int32_t rank, int
 
 ctox_status ctox_tp_destroy(ctox_ctx *ctx) {
     if (!ctx) return CTOX_OK;
+    tp_peer_destroy(ctx);
     if (ctx->nccl_comm) {
         cudaStreamSynchronize(ctx->stream);
         g_nccl.CommDestroy(ctx->nccl_comm);

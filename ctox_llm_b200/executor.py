@@ -135,6 +135,14 @@ class B200Executor:
                                                        out.ctypes.data_as(C.c_void_p)))
         return out
 
+    def select_target_token(self, temperature: float, top_k: int, top_p: float, draw: float,
+                            position: int = 0) -> int:
+        """ModelExecutor::select_target_token over the logits kept by the last decode call."""
+        tok = C.c_uint32()
+        self._b._check(self._lib.ctox_exec_select_target(self._h, position, C.c_float(temperature), top_k,
+                                                         C.c_float(top_p), C.c_float(draw), C.byref(tok)))
+        return tok.value
+
     def unload(self) -> None:
         if self._h:
             self._lib.ctox_exec_destroy(self._h)

@@ -256,6 +256,16 @@ ctox_status ctox_argmax_f32(ctox_ctx *ctx, const float *logits_dev, uint32_t n,
  * logit is CTOX_INVALID_STATE (backend/cuda_runtime.rs:2790-2794). */
 ctox_status ctox_argmax_f32_host(ctox_ctx *ctx, const float *logits_dev, uint32_t n,
                                  const uint32_t *row_ids_dev, uint32_t *token);
+/* Sampler::sample_with_draw (sampler.rs:65-144; CUDA candidate ctox_topk_topp_sample_f32_sm86,
+ * kernels/cuda/q2q4_fused_matvec_sm86.cu:2648, prepared by backend/cuda_runtime.rs:2728-2910):
+ * temperature, top-k, top-p over n device logits with the caller's uniform draw in [0, 1).
+ * temperature 0 = greedy. The device path takes top_k in 1..=1024 (the reference's 1..=256);
+ * other values are CTOX_UNSUPPORTED_OPERATION. Host form: synchronises, returns the token.
+ * Invalid draw / temperature / top_p and non-finite logits are CTOX_INVALID_ARTIFACT like the
+ * reference's fail-closed sampler (sampler.rs:66-99). */
+ctox_status ctox_sample_topk_topp(ctox_ctx *ctx, const float *logits_dev, uint32_t n,
+                                  float temperature, uint32_t top_k, float top_p, float draw,
+                                  uint32_t *token);
 /* Fused lm_head -> softmax statistics -> acceptance for the n_nodes verify
  * positions of a draft tree (a chain is the tree parent[i] = i-1). hidden_dev:
  * n_nodes rows of the lm_head's input (CTOX_F32 or CTOX_BF16), row i being the
@@ -371,6 +381,12 @@ ctox_status ctox_exec_last_hidden(ctox_exec *exec, float *out);
  * enabled with ctox_exec_keep_logits). */
 ctox_status ctox_exec_keep_logits(ctox_exec *exec, int32_t enable);
 ctox_status ctox_exec_last_logits(ctox_exec *exec, uint32_t position, float *out);
+/* ModelExecutor::select_target_token (engine.rs:322-362): samples the target token of verify
+ * position `position` of the last decode call from the logits the executor kept on the device
+ * (ctox_exec_keep_logits must be on), with the same rules as ctox_sample_topk_topp. In a
+ * tensor-parallel group the kept logits are a vocabulary shard: CTOX_UNSUPPORTED_OPERATION. */
+ctox_status ctox_exec_select_target(ctox_exec *exec, uint32_t position, float temperature,
+                                    uint32_t top_k, float top_p, float draw, uint32_t *token);
 ctox_status ctox_exec_allocated_bytes(const ctox_exec *exec, uint64_t *model, uint64_t *session);
 
 #ifdef __cplusplus
