@@ -360,12 +360,26 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         const int i = threadIdx.x & 15;
         const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
         const uint32_t first_block = slice * slice_blocks;
-        for (uint32_t task = threadIdx.x >> 4; task < slice_blocks * p.npos; task += (WARPS * 32) >> 4) {
+        // tasks = (block, position) pairs, one per 16-lane group and round; the h values of the next
+        // round are requested before this round's fragments are built (one L2 trip in flight)
+        const uint32_t n_tasks = slice_blocks * p.npos, stride = (WARPS * 32) >> 4;
+        auto load_h = [&](uint32_t task) {
+            float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (task < n_tasks) {
+                const uint32_t b = task / p.npos, m = task % p.npos;
+                const uint32_t c = (first_block + b) * 64 + i * 4;
+                if (c < p.norm_hidden)  // norm_hidden is a multiple of 64: whole blocks
+                    hv = *reinterpret_cast<const float4 *>(p.norm_h + (size_t)m * p.norm_hidden + c);
+            }
+            return hv;
+        };
+        float4 hv = load_h(threadIdx.x >> 4);
+        for (uint32_t task = threadIdx.x >> 4; task < n_tasks; task += stride) {
+            const float4 hn = load_h(task + stride);
             const uint32_t b = task / p.npos, m = task % p.npos;
             const uint32_t c = (first_block + b) * 64 + i * 4;
             float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (c < p.norm_hidden) {  // norm_hidden is a multiple of 64: whole blocks
-                const float4 hv = *reinterpret_cast<const float4 *>(p.norm_h + (size_t)m * p.norm_hidden + c);
+            if (c < p.norm_hidden) {
                 const float4 wv = *reinterpret_cast<const float4 *>(p.norm_w + c);
                 float4 sv = make_float4(1.f, 1.f, 1.f, 1.f);
                 if (p.norm_s_in) sv = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
@@ -376,6 +390,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
                 v[3] = hv.w * inv * (1.0f + wv.w) * sv.w;
             }
             prep_block(v, i, gmask, (int)b, (int)m, (int)p.npos, DT, xs, reinterpret_cast<float2 *>(ms));
+            hv = hn;
         }
         __syncthreads();
     } else if (threadIdx.x == 0) {
