@@ -153,7 +153,8 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit,
         "n_gpus": args.gpus, "steps": steps, "warmup": max(args.warmup, 1),
-        "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": dt / steps * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.workload == "decode" else "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload},
         "cpu_baseline": {"value": value, "unit": unit, "cores": cores, "kind": "port",
