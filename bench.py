@@ -216,6 +216,8 @@ def run_decode(args):
         be.tp_init_from_torch()
     context = args.context
     cfg = ctox.qwen38_27b_config(max_context_tokens=context + 4096)
+    if args.layers:  # a shallower model of the same layer shapes: small cases for profiler captures
+        cfg.num_hidden_layers = args.layers
     ex = ctox.B200Executor(be, cfg)
     ex.fill_synthetic(seed=0)
     ex.warmup()
@@ -288,8 +290,9 @@ def run_decode(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"qwen3.8-27b-shaped decode, 64 layers, batch 1, context {context}, MTP k=4 "
-                                   "(BASELINE config 4)",
+            "config": {"workload": f"qwen3.8-27b-shaped decode, {cfg.num_hidden_layers} layers, batch 1, "
+                                   f"context {context}, MTP k=4 (BASELINE config 4"
+                                   f"{'' if cfg.num_hidden_layers == 64 else ', reduced depth: profiling case'})",
                        "weights": "Q4_B64 attention/embedding, Q2_B64 FFN, random init",
                        "kv": "bf16, 16-token pages", "l2": "11.8 GB streamed per pass (>> 126 MB L2)",
                        "parallelism": f"tp{world} (one sequence; heads, FFN width and vocabulary split, "
@@ -445,6 +448,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "q4_matvec"])
     ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="decode: number of layers (default: the model's 64); fewer = a small profiling case")
     ap.add_argument("--quick", action="store_true",
                     help="decode: only the timed region and one kernel-timing block (for launch lists)")
     args = ap.parse_args()
