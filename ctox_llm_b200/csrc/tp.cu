@@ -68,85 +68,81 @@ ctox_status tp_all_gather(ctox_ctx *ctx, const void *send, void *recv, size_t by
 }  // namespace ctox
 
 // ------------------------------------------------------------------ one-shot all-reduce over peer memory
-// The sum of a column-split projection over the group without a library collective: every rank
-// finishes its partial vector into a buffer its peers can address, raises a flag in every peer's
-// memory, and the residual kernel of every rank adds the W buffers itself, in rank order (all
-// ranks get identical bits). Chunked by 256 columns so a consumer CTA only waits for the chunk it
-// needs. Plain peer stores and loads over NVLink; no multicast. Waits are bounded: a peer that
-// never signals makes the kernel set the device error word and carry on.
+// The sum of a column-split projection over the group without a library collective, in the
+// low-latency style: every rank PUSHES its finished partial vector into a receive buffer in each
+// peer's memory as 8-byte words {value, sequence number}; an 8-byte store is single-copy atomic,
+// so the word itself says when it has arrived and no fence or separate flag is needed. The
+// residual kernel of every rank polls its own (local) receive buffer, one word per source rank and
+// element, and adds the W values in rank order: all ranks get identical bits, and the residual add,
+// the sum over the group and the partial sums of squares are one kernel. Plain peer stores over
+// NVLink only (no multicast, no reads of peer memory). Waits are bounded: a peer that never
+// delivers makes the kernel set the device error word and carry on.
 namespace ctox {
 
 constexpr uint32_t kTpChunk = 256, kTpMaxWorld = 8;
 
 struct TpPeer {
     uint32_t world = 0, rank = 0, seq = 0;
-    size_t elems = 0;         // floats per buffer
-    uint32_t chunks = 0;      // flag slots per source rank
-    float *buf = nullptr;     // own: [2 parities][elems]
-    uint32_t *flags = nullptr;  // own: [world][chunks], written by the peers
-    float *peer_buf[kTpMaxWorld] = {nullptr};
-    uint32_t *peer_flags[kTpMaxWorld] = {nullptr};
+    size_t elems = 0;          // floats per vector
+    uint2 *recv = nullptr;     // own: [2 parities][world sources][elems] of {value bits, seq}
+    uint2 *peer_recv[kTpMaxWorld] = {nullptr};
 };
-struct TpPeerPtrs {  // by value into the kernels
-    float *buf[kTpMaxWorld];
-    uint32_t *flags[kTpMaxWorld];
+struct TpPeerPtrs {  // by value into the kernels: where each rank receives THIS rank's vector
+    uint2 *dst[kTpMaxWorld];
 };
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// One aligned 64-bit scalar access (single-copy atomic): low word = value bits, high word = seq.
+__device__ __forceinline__ void st_word_sys(uint2 *p, uint32_t value, uint32_t seq) {
+    const unsigned long long w = ((unsigned long long)seq << 32) | value;
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ float ld_relaxed_sys(const float *p) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-    return v;
+__device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 
-// y[pos][row] of this rank's partial result for one chunk of 256 rows -> own buffer, then the
-// chunk's flag in every rank's memory (own included) takes the value seq.
-__global__ void __launch_bounds__(kTpChunk) k_tp_finish_signal(MvOut o, uint32_t rows, int npos, float *own,
-                                                             TpPeerPtrs peers, uint32_t rank, uint32_t world,
-                                                             uint32_t chunks, uint32_t seq) {
+// y[pos][row] of this rank's partial result -> every rank's receive slot for this rank.
+__global__ void __launch_bounds__(kTpChunk) k_tp_finish_push(MvOut o, uint32_t rows, int npos, TpPeerPtrs peers,
+                                                           uint32_t world, uint32_t seq) {
     pdl_launch();
     pdl_wait();
     const uint32_t row = blockIdx.x * kTpChunk + threadIdx.x;
-    if (row < rows)
-        for (int m = 0; m < npos; ++m) own[(size_t)m * rows + row] = out_of(o, row, m);
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world) st_release_sys(peers.flags[threadIdx.x] + rank * chunks + blockIdx.x, seq);
+    if (row >= rows) return;
+    for (int m = 0; m < npos; ++m) {
+        const uint32_t bits = __float_as_uint(out_of(o, row, m));
+        for (uint32_t r = 0; r < world; ++r) st_word_sys(peers.dst[r] + (size_t)m * rows + row, bits, seq);
+    }
 }
 
-// h[m][c] += sum over ranks of their partial vectors (rank order); partial sums of squares of the
-// result per 256-column part, like k_residual_add. flags: this rank's [world][chunks].
-__global__ void __launch_bounds__(kTpChunk) k_tp_residual_add(float *__restrict__ h, TpPeerPtrs peers,
-                                                            const uint32_t *flags, uint32_t world, uint32_t chunks,
-                                                            uint32_t seq, uint32_t hidden, float *__restrict__ sumsq,
+// h[m][c] += sum over ranks of their partial vectors (rank order), from this rank's receive
+// buffer recv[source][m][c]; partial sums of squares of the result per 256-column part, like
+// k_residual_add.
+__global__ void __launch_bounds__(kTpChunk) k_tp_residual_add(float *__restrict__ h, const uint2 *recv,
+                                                            size_t source_stride, uint32_t world, uint32_t seq,
+                                                            uint32_t hidden, float *__restrict__ sumsq,
                                                             int32_t *error_flag) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[kTpChunk / 32];
     const int m = blockIdx.y;
-    if (threadIdx.x < world) {
-        const uint32_t *f = flags + threadIdx.x * chunks + blockIdx.x;
-        const long long t0 = clock64();
-        while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
-            if (clock64() - t0 > 2000000000ll) {  // ~1 s: a peer is gone
-                atomicExch(error_flag, DEV_ERR_WAIT_TIMEOUT);
-                break;
-            }
-        }
-    }
-    __syncthreads();
     const uint32_t c = blockIdx.x * kTpChunk + threadIdx.x;
     float v = 0.f;
     if (c < hidden) {
         v = h[(size_t)m * hidden + c];
-        for (uint32_t r = 0; r < world; ++r) v += ld_relaxed_sys(peers.buf[r] + (size_t)m * hidden + c);
+        const long long t0 = clock64();
+        for (uint32_t r = 0; r < world; ++r) {
+            const uint2 *p = recv + r * source_stride + (size_t)m * hidden + c;
+            uint2 word = ld_word_sys(p);
+            while (word.y != seq) {
+                if (clock64() - t0 > 2000000000ll) {  // ~1 s: a peer is gone
+                    atomicExch(error_flag, DEV_ERR_WAIT_TIMEOUT);
+                    break;
+                }
+                word = ld_word_sys(p);
+            }
+            v += __uint_as_float(word.x);
+        }
         h[(size_t)m * hidden + c] = v;
     }
     float s = v * v;
@@ -171,18 +167,13 @@ ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
     tp->world = W;
     tp->rank = R;
     tp->elems = elems;
-    tp->chunks = (uint32_t)((elems + kTpChunk - 1) / kTpChunk);  // an upper bound for every vector width
+    const size_t bytes = 2 * (size_t)W * elems * sizeof(uint2);
     struct Card {
-        cudaIpcMemHandle_t buf, flags;
-        int device, ok;
+        cudaIpcMemHandle_t recv;
+        int ok;
     } mine{}, all[kTpMaxWorld];
-    mine.device = ctx->device;
-    bool ok = cudaMalloc((void **)&tp->buf, 2 * elems * sizeof(float)) == cudaSuccess &&
-              cudaMalloc((void **)&tp->flags, (size_t)W * tp->chunks * 4) == cudaSuccess &&
-              cudaMemset(tp->flags, 0, (size_t)W * tp->chunks * 4) == cudaSuccess &&
-              cudaMemset(tp->buf, 0, 2 * elems * sizeof(float)) == cudaSuccess &&
-              cudaIpcGetMemHandle(&mine.buf, tp->buf) == cudaSuccess &&
-              cudaIpcGetMemHandle(&mine.flags, tp->flags) == cudaSuccess;
+    bool ok = cudaMalloc((void **)&tp->recv, bytes) == cudaSuccess && cudaMemset(tp->recv, 0, bytes) == cudaSuccess &&
+              cudaIpcGetMemHandle(&mine.recv, tp->recv) == cudaSuccess;
     mine.ok = ok ? 1 : 0;
     // exchange the cards through the communicator the group already has
     Card *dev = nullptr;
@@ -199,20 +190,17 @@ ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
         cudaFree(dev);
     }
     if (rc) {
-        cudaFree(tp->buf);
-        cudaFree(tp->flags);
+        cudaFree(tp->recv);
         delete tp;
         return rc;
     }
     for (uint32_t r = 0; r < W && ok; ++r) ok = all[r].ok != 0;
     for (uint32_t r = 0; r < W && ok; ++r) {
         if (r == R) {
-            tp->peer_buf[r] = tp->buf;
-            tp->peer_flags[r] = tp->flags;
+            tp->peer_recv[r] = tp->recv;
             continue;
         }
-        ok = cudaIpcOpenMemHandle((void **)&tp->peer_buf[r], all[r].buf, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess &&
-             cudaIpcOpenMemHandle((void **)&tp->peer_flags[r], all[r].flags, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
+        ok = cudaIpcOpenMemHandle((void **)&tp->peer_recv[r], all[r].recv, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess;
     }
     // every rank must take the same path: agree through one more exchange
     int agree = ok ? 1 : 0, *agree_dev = nullptr, votes[kTpMaxWorld] = {0};
@@ -235,33 +223,30 @@ void tp_peer_destroy(ctox_ctx *ctx) {
     TpPeer *tp = ctx->tp_peer;
     if (!tp) return;
     cudaStreamSynchronize(ctx->stream);
-    for (uint32_t r = 0; r < tp->world; ++r) {
-        if (r == tp->rank) continue;
-        if (tp->peer_buf[r]) cudaIpcCloseMemHandle(tp->peer_buf[r]);
-        if (tp->peer_flags[r]) cudaIpcCloseMemHandle(tp->peer_flags[r]);
-    }
-    if (tp->buf) cudaFree(tp->buf);
-    if (tp->flags) cudaFree(tp->flags);
+    for (uint32_t r = 0; r < tp->world; ++r)
+        if (r != tp->rank && tp->peer_recv[r]) cudaIpcCloseMemHandle(tp->peer_recv[r]);
+    if (tp->recv) cudaFree(tp->recv);
     delete tp;
     ctx->tp_peer = nullptr;
 }
 
 // Enqueues "h += sum over the group of this matvec's output" for m positions through peer memory.
+// Receive buffers alternate with the parity of the sequence number: a rank's next-but-one push runs
+// after its own next residual kernel, which has consumed every peer's next push, which those peers
+// issued after consuming the current one.
 ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *sumsq) {
     TpPeer *tp = ctx->tp_peer;
     if (!tp) return fail(ctx, CTOX_INVALID_STATE, "tp: peer all-reduce is not set up");
     if ((size_t)m * rows > tp->elems) return fail(ctx, CTOX_SHAPE, "tp: vector of %u x %u exceeds the peer buffer", m, rows);
     const uint32_t seq = ++tp->seq, parity = seq & 1;
-    const uint32_t chunks_used = (rows + kTpChunk - 1) / kTpChunk;
+    if (seq == 0) return fail(ctx, CTOX_INVALID_STATE, "tp: sequence numbers exhausted");
+    const uint32_t chunks = (rows + kTpChunk - 1) / kTpChunk;
+    const size_t parity_off = (size_t)parity * tp->world * tp->elems;
     TpPeerPtrs pp{};
-    for (uint32_t r = 0; r < tp->world; ++r) {
-        pp.buf[r] = tp->peer_buf[r] + (size_t)parity * tp->elems;
-        pp.flags[r] = tp->peer_flags[r];
-    }
-    launch_pdl(k_tp_finish_signal, dim3(chunks_used), dim3(kTpChunk), 0, ctx->stream, o, rows, (int)m,
-               tp->buf + (size_t)parity * tp->elems, pp, tp->rank, tp->world, tp->chunks, seq);
-    launch_pdl(k_tp_residual_add, dim3(chunks_used, m), dim3(kTpChunk), 0, ctx->stream, h, pp, tp->flags, tp->world,
-               tp->chunks, seq, rows, sumsq, ctx->dev_error);
+    for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
+    launch_pdl(k_tp_finish_push, dim3(chunks), dim3(kTpChunk), 0, ctx->stream, o, rows, (int)m, pp, tp->world, seq);
+    launch_pdl(k_tp_residual_add, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, h, tp->recv + parity_off, tp->elems,
+               tp->world, seq, rows, sumsq, ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
