@@ -26,14 +26,12 @@ constexpr int kDeltaDim = 128;    // key_dim == value_dim of the fast path
 constexpr int kDeltaSlice = 32;   // value columns per CTA
 constexpr float kL2Eps = 1e-6f;   // reference.rs:11
 
-__global__ void __launch_bounds__(128) k_gated_delta_scan128(
+// The scan of one (head, 32-column slice) by one CTA of 128 threads; out may be null (state only).
+__device__ __forceinline__ void delta_scan128_body(
     const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
     const float *__restrict__ log_decay, const float *__restrict__ beta,
     const float *__restrict__ state_in, float *__restrict__ state_out, float *__restrict__ out,
-    int tokens, int heads, int qk_heads) {
-    pdl_launch();
-    pdl_wait();
-    const int head = blockIdx.x >> 2, slice = blockIdx.x & 3;
+    int tokens, int heads, int qk_heads, int head, int slice) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = slice * kDeltaSlice + lane;
     const int src = head / (heads / qk_heads);  // repeat_heads: decoder.rs:47-65
@@ -92,7 +90,7 @@ __global__ void __launch_bounds__(128) k_gated_delta_scan128(
         }
         red[0][warp][lane] = o;
         __syncthreads();
-        if (warp == 0)
+        if (warp == 0 && out)
             out[((size_t)tok * heads + head) * kDeltaDim + col] =
                 red[0][0][lane] + red[0][1][lane] + red[0][2][lane] + red[0][3][lane];
         // red[0] is rewritten by the next token's norm partials only after the
@@ -102,6 +100,54 @@ __global__ void __launch_bounds__(128) k_gated_delta_scan128(
     float *sout = state_out + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
 #pragma unroll
     for (int i = 0; i < 32; ++i) sout[(size_t)i * kDeltaDim] = s[i];
+}
+
+__global__ void __launch_bounds__(128) k_gated_delta_scan128(
+    const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+    const float *__restrict__ log_decay, const float *__restrict__ beta,
+    const float *__restrict__ state_in, float *__restrict__ state_out, float *__restrict__ out,
+    int tokens, int heads, int qk_heads) {
+    pdl_launch();
+    pdl_wait();
+    delta_scan128_body(q, k, v, log_decay, beta, state_in, state_out, out, tokens, heads, qk_heads, blockIdx.x >> 2,
+                       blockIdx.x & 3);
+}
+
+// Commit of the first n positions of a pass for ALL linear-attention layers in one launch:
+// blockIdx.y = layer; the first heads * 4 CTAs of a layer re-scan the recurrence from the committed
+// state over the kept (q, k, v, g, beta) when only a prefix was accepted, the others shift the first
+// n kept conv inputs into the conv state. `cur` says which state buffer of a layer is committed.
+__global__ void __launch_bounds__(128) k_commit_batch(const CommitLayer *__restrict__ layers, CommitCur cur, int n,
+                                                    int rescan, int heads, int qk_heads, uint32_t channels,
+                                                    uint32_t conv_kernel) {
+    pdl_launch();
+    pdl_wait();
+    const CommitLayer L = layers[blockIdx.y];
+    const int scan_ctas = heads * 4;
+    if ((int)blockIdx.x < scan_ctas) {
+        if (!rescan) return;
+        const int c = cur.v[blockIdx.y];
+        delta_scan128_body(L.q, L.k, L.v, L.g, L.beta, L.state[c], L.state[c ^ 1], nullptr, n, heads, qk_heads,
+                           blockIdx.x >> 2, blockIdx.x & 3);
+        return;
+    }
+    const uint32_t r = (blockIdx.x - scan_ctas) * blockDim.x + threadIdx.x;
+    if (r >= channels) return;
+    float st[8];
+    for (uint32_t j = 0; j < conv_kernel; ++j) st[j] = L.conv_state[(size_t)r * conv_kernel + j];
+    for (int m = 0; m < n; ++m) {
+        for (uint32_t j = 0; j + 1 < conv_kernel; ++j) st[j] = st[j + 1];
+        st[conv_kernel - 1] = L.conv_in[(size_t)m * channels + r];
+    }
+    for (uint32_t j = 0; j < conv_kernel; ++j) L.conv_state[(size_t)r * conv_kernel + j] = st[j];
+}
+
+void launch_commit_batch(cudaStream_t st, const CommitLayer *layers_dev, const CommitCur &cur, uint32_t n_layers,
+                         uint32_t n, bool rescan, uint32_t heads, uint32_t qk_heads, uint32_t channels,
+                         uint32_t conv_kernel) {
+    const uint32_t conv_ctas = (channels + 127) / 128;
+    launch_pdl(k_commit_batch, dim3(heads * 4 + conv_ctas, n_layers), dim3(128), 0, st, layers_dev, cur, (int)n,
+               rescan ? 1 : 0, (int)heads, (int)qk_heads, channels, conv_kernel);
 }
 
 // Any head geometry: one thread per (head, value column), the reference's loop order.

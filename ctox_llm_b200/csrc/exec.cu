@@ -69,6 +69,8 @@ struct ctox_exec {
     ctox_matvec *embed = nullptr, *lm_head = nullptr, *mtp_fc = nullptr, *draft_head = nullptr;
     float *final_norm = nullptr, *mtp_norm_e = nullptr, *mtp_norm_h = nullptr, *mtp_norm = nullptr;
     uint32_t *draft_ids = nullptr;  // device, [draft_vocab]
+    CommitLayer *commit_table = nullptr;  // device, one entry per linear-attention layer
+    uint32_t n_linear = 0;
     bool lm_head_is_embed = false;
     // session
     uint64_t position = 0;     // tokens consumed by the target so far
@@ -700,6 +702,22 @@ ctox_status ctox_exec_warmup(ctox_exec *e) {
             WALLOC(ls.beta, P * c.linear_num_value_heads * 4);
         }
     }
+    {   // pointer table of the batched commit kernel
+        std::vector<CommitLayer> table;
+        for (uint32_t l = 0; l < e->n_layers; ++l) {
+            if (e->w[l].full) continue;
+            LayerS &ls = e->s[l];
+            table.push_back(CommitLayer{ls.q, ls.k, ls.v, ls.g, ls.beta, {ls.delta[0], ls.delta[1]}, ls.conv_state,
+                                        ls.conv_in});
+        }
+        e->n_linear = (uint32_t)table.size();
+        if (e->n_linear && e->n_linear <= 128) {
+            WALLOC(e->commit_table, table.size() * sizeof(CommitLayer));
+            CTOX_CUDA(ctx, cudaMemcpyAsync(e->commit_table, table.data(), table.size() * sizeof(CommitLayer),
+                                           cudaMemcpyHostToDevice, ctx->stream));
+            CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `table` is a local
+        }
+    }
 #undef WALLOC
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     e->warmed = true;
@@ -917,14 +935,26 @@ ctox_status target_pass(ctox_exec *e, uint32_t m, uint64_t pos0) {
 ctox_status commit_positions(ctox_exec *e, uint32_t m, uint32_t n) {
     ctox_ctx *ctx = e->ctx;
     const ctox_model_config &c = e->cfg;
-    for (uint32_t l = 0; l < e->n_layers; ++l) {
-        if (e->w[l].full) continue;
-        LayerS &ls = e->s[l];
-        if (n < m)  // partial acceptance: re-scan the recurrence alone from the committed state
-            EX(ctox_gated_delta_scan(ctx, ls.q, ls.k, ls.v, ls.g, ls.beta, ls.delta[ls.cur], ls.delta[ls.cur ^ 1],
-                                     e->lcore, n, c.linear_num_value_heads, c.linear_num_key_heads, 128, 128));
-        ls.cur ^= 1;
-        launch_conv_commit(ctx->stream, ls.conv_state, ls.conv_in, e->channels, c.linear_conv_kernel_dim, n);
+    if (e->commit_table) {  // all linear-attention layers in one launch
+        CommitCur cur{};
+        uint32_t j = 0;
+        for (uint32_t l = 0; l < e->n_layers; ++l)
+            if (!e->w[l].full) cur.v[j++] = (uint8_t)e->s[l].cur;
+        // partial acceptance: re-scan the recurrence alone from the committed state
+        launch_commit_batch(ctx->stream, e->commit_table, cur, e->n_linear, n, n < m, c.linear_num_value_heads,
+                            c.linear_num_key_heads, e->channels, c.linear_conv_kernel_dim);
+        for (uint32_t l = 0; l < e->n_layers; ++l)
+            if (!e->w[l].full) e->s[l].cur ^= 1;
+    } else {
+        for (uint32_t l = 0; l < e->n_layers; ++l) {
+            if (e->w[l].full) continue;
+            LayerS &ls = e->s[l];
+            if (n < m)
+                EX(ctox_gated_delta_scan(ctx, ls.q, ls.k, ls.v, ls.g, ls.beta, ls.delta[ls.cur], ls.delta[ls.cur ^ 1],
+                                         e->lcore, n, c.linear_num_value_heads, c.linear_num_key_heads, 128, 128));
+            ls.cur ^= 1;
+            launch_conv_commit(ctx->stream, ls.conv_state, ls.conv_in, e->channels, c.linear_conv_kernel_dim, n);
+        }
     }
     CTOX_CUDA(ctx, cudaMemcpyAsync(e->hist_hidden, e->final_hidden, (size_t)n * c.hidden_size * 4,
                                    cudaMemcpyDeviceToDevice, ctx->stream));

@@ -166,7 +166,8 @@ __global__ void __launch_bounds__(256) k_swiglu_prep(MvOut gu, uint32_t inter, i
     const uint32_t c = blockIdx.x * 256 + threadIdx.x;
     float v = 0.f;
     if (c < inter) {
-        const float gate = out_of(gu, c, m), up = out_of(gu, inter + c, m);
+        float gate, up;
+        out_of2(gu, c, inter + c, m, gate, up);
         v = silu_f(gate) * up * (next.s_in ? next.s_in[c] : 1.0f);
     }
     vals[threadIdx.x] = v;

@@ -99,6 +99,20 @@ struct LinearAttnArgs {
 };
 void launch_linear_attention(cudaStream_t st, const LinearAttnArgs &a, uint32_t m);
 
+// Commit of an accepted prefix for all linear-attention layers in one launch (delta.cu).
+struct CommitLayer {
+    const float *q, *k, *v, *g, *beta;  // kept inputs of the last pass
+    float *state[2];                    // recurrent state double buffer
+    float *conv_state;
+    const float *conv_in;
+};
+struct CommitCur {
+    uint8_t v[128];  // per linear layer: index of the committed state buffer
+};
+void launch_commit_batch(cudaStream_t st, const CommitLayer *layers_dev, const CommitCur &cur, uint32_t n_layers,
+                         uint32_t n, bool rescan, uint32_t heads, uint32_t qk_heads, uint32_t channels,
+                         uint32_t conv_kernel);
+
 }  // namespace ctox
 
 #ifdef __CUDACC__
@@ -113,5 +127,50 @@ __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t p
     return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
 }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+// Two output values of the same matvec and position with the loads of both issued together
+// (each up to four pieces per trip; same order of additions as out_of).
+__device__ __forceinline__ void out_of2(const MvOut &o, uint32_t row_a, uint32_t row_b, uint32_t pos, float &a,
+                                        float &b) {
+    if (o.plain || !o.warps_per_slice) {
+        a = out_of(o, row_a, pos);
+        b = out_of(o, row_b, pos);
+        return;
+    }
+    const uint32_t na = piece_count(row_a >> 5, o.kst_s, o.warps_per_slice, o.pairs);
+    const uint32_t nb = piece_count(row_b >> 5, o.kst_s, o.warps_per_slice, o.pairs);
+    const float *fa = o.partial + (size_t)(row_a >> 5) * o.slices * o.max_pieces * 256 + pos * 32 + (row_a & 31);
+    const float *fb = o.partial + (size_t)(row_b >> 5) * o.slices * o.max_pieces * 256 + pos * 32 + (row_b & 31);
+    const uint32_t ta = o.slices * na, tb = o.slices * nb;
+    float va = 0.f, vb = 0.f;
+    uint32_t sla = 0, qa = 0, slb = 0, qb = 0;
+    for (uint32_t k0 = 0; k0 < max(ta, tb); k0 += 4) {
+        float ba[4], bb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            ba[j] = bb[j] = 0.f;
+            if (k0 + j < ta) {
+                ba[j] = fa[((size_t)sla * o.max_pieces + qa) * 256];
+                if (++qa == na) {
+                    qa = 0;
+                    ++sla;
+                }
+            }
+            if (k0 + j < tb) {
+                bb[j] = fb[((size_t)slb * o.max_pieces + qb) * 256];
+                if (++qb == nb) {
+                    qb = 0;
+                    ++slb;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (k0 + j < ta) va += ba[j];
+            if (k0 + j < tb) vb += bb[j];
+        }
+    }
+    a = o.s_out ? va * o.s_out[row_a] : va;
+    b = o.s_out ? vb * o.s_out[row_b] : vb;
+}
 }  // namespace ctox
 #endif
