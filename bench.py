@@ -216,6 +216,8 @@ def run_decode(args):
         be.tp_init_from_torch()
     context = args.context
     cfg = ctox.qwen38_27b_config(max_context_tokens=context + 4096)
+    if args.drafts:  # chained MTP drafts per block (the reference's candidate path uses 4: a 5-row verify pass)
+        cfg.max_draft_tokens = args.drafts
     if args.layers:  # a shallower model of the same layer shapes: small cases for profiler captures
         cfg.num_hidden_layers = args.layers
     ex = ctox.B200Executor(be, cfg)
@@ -255,7 +257,7 @@ def run_decode(args):
     clocks = sampler.stop() if rank == 0 else None
     buckets, plain = {}, None
     if not args.quick:
-        for force in (0, 2, 4):
+        for force in sorted({0, min(2, cfg.max_draft_tokens), cfg.max_draft_tokens}):
             bms, _, bem, _ = run_blocks(max(args.steps // 8, 8), True, force, False)
             buckets[f"accept_{force}"] = bem / (bms * 1e-3)
         pms, _, pem, _ = run_blocks(max(args.steps // 8, 8), False, -1, False)
@@ -291,7 +293,7 @@ def run_decode(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": f"qwen3.8-27b-shaped decode, {cfg.num_hidden_layers} layers, batch 1, "
-                                   f"context {context}, MTP k=4 (BASELINE config 4"
+                                   f"context {context}, MTP k={cfg.max_draft_tokens} (BASELINE config 4"
                                    f"{'' if cfg.num_hidden_layers == 64 else ', reduced depth: profiling case'})",
                        "weights": "Q4_B64 attention/embedding, Q2_B64 FFN, random init",
                        "kv": "bf16, 16-token pages", "l2": "11.8 GB streamed per pass (>> 126 MB L2)",
@@ -448,6 +450,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "q4_matvec"])
     ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--drafts", type=int, default=0,
+                    help="decode: chained MTP drafts per block (default: the configuration's 4)")
     ap.add_argument("--layers", type=int, default=0,
                     help="decode: number of layers (default: the model's 64); fewer = a small profiling case")
     ap.add_argument("--quick", action="store_true",

@@ -81,7 +81,7 @@ struct ctox_exec {
     bool warmed = false, keep_logits = false;
     // buffers ([kMaxPass] rows each)
     float *h = nullptr, *final_hidden = nullptr, *hist_hidden = nullptr, *embed_rows = nullptr;
-    float *mtp_h = nullptr, *mtp_hidden = nullptr, *mtp_prev = nullptr;
+    float *mtp_h = nullptr, *mtp_hidden = nullptr;
     float *aq = nullptr, *agate = nullptr, *attn_ws = nullptr;
     float *lz = nullptr, *lcore = nullptr, *norm_scratch = nullptr;
     float *draft_logits = nullptr, *logits = nullptr;
@@ -661,7 +661,6 @@ ctox_status ctox_exec_warmup(ctox_exec *e) {
     WALLOC(e->embed_rows, P * H * 4);
     WALLOC(e->mtp_h, P * H * 4);
     WALLOC(e->mtp_hidden, P * H * 4);
-    WALLOC(e->mtp_prev, P * H * 4);
     WALLOC(e->aq, P * e->q_width * 4);
     WALLOC(e->agate, P * e->q_width * 4);
     AttnGeom g{c.num_attention_heads, c.num_key_value_heads, c.head_dim, c.rotary_dim, c.rope_theta,
@@ -964,14 +963,15 @@ ctox_status commit_positions(ctox_exec *e, uint32_t m, uint32_t n) {
     return CTOX_OK;
 }
 
-// MTP layer over m (token, previous final hidden) pairs; tokens in mtp_tokens_dev, the pair of
+// MTP layer over m (token, previous final hidden) pairs; tokens in device memory, the pair of
 // absolute position p uses cache slot p - 1 (decoder.rs:1009-1046). With draft_slot >= 0 the greedy
 // draft of the last pair goes to tokens_dev[draft_slot].
-ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const float *hidden_rows, int draft_slot) {
+ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const uint32_t *tokens, const float *hidden_rows,
+                     int draft_slot) {
     ctox_ctx *ctx = e->ctx;
     const ctox_model_config &c = e->cfg;
     const uint32_t L = e->n_layers;
-    EX(matvec_embed_rows(e->embed, e->mtp_tokens_dev, m, e->embed_rows));
+    EX(matvec_embed_rows(e->embed, tokens, m, e->embed_rows));
     const MvIn fc_in = mv_in(e->mtp_fc);
     launch_mtp_pre(ctx->stream, e->embed_rows, hidden_rows, e->mtp_norm_e, e->mtp_norm_h, c.rms_norm_epsilon,
                    c.hidden_size, m, &fc_in);
@@ -1034,7 +1034,7 @@ ctox_status ctox_exec_prefill(ctox_exec *e, const uint32_t *tokens, uint64_t n) 
         if (e->cfg.mtp_num_hidden_layers && !last_chunk) {
             // keep the MTP cache exact: pairs (token p+1, final hidden p) of this chunk
             EX(upload_u32(e, e->mtp_tokens_dev, tokens + a + 1, m));
-            EX(mtp_pass(e, m, a + 1, e->hist_hidden, -1));
+            EX(mtp_pass(e, m, a + 1, e->mtp_tokens_dev, e->hist_hidden, -1));
         }
         CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `tokens` may be pageable host memory
     }
@@ -1069,14 +1069,13 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
         for (uint32_t j = 0; j + 1 < n; ++j) mt[j] = e->hist_tokens[j];
         mt[n - 1] = token;
         EX(upload_u32(e, e->mtp_tokens_dev, mt, n));
-        EX(mtp_pass(e, n, P - n + 1, e->hist_hidden, 1));
+        EX(mtp_pass(e, n, P - n + 1, e->mtp_tokens_dev, e->hist_hidden, 1));
         for (uint32_t i = 1; i < k; ++i) {
-            CTOX_CUDA(ctx, cudaMemcpyAsync(e->mtp_tokens_dev, e->tokens_dev + i, 4, cudaMemcpyDeviceToDevice,
-                                           ctx->stream));
+            // the draft just written to tokens_dev[i] and the MTP's own hidden of the last pair, in
+            // place: the pass reads both in its first kernels and rewrites mtp_hidden in its last
             const uint32_t prev_rows = i == 1 ? n : 1;
-            CTOX_CUDA(ctx, cudaMemcpyAsync(e->mtp_prev, e->mtp_hidden + (size_t)(prev_rows - 1) * c.hidden_size,
-                                           (size_t)c.hidden_size * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-            EX(mtp_pass(e, 1, P + i, e->mtp_prev, (int)(1 + i)));
+            EX(mtp_pass(e, 1, P + i, e->tokens_dev + i, e->mtp_hidden + (size_t)(prev_rows - 1) * c.hidden_size,
+                        (int)(1 + i)));
         }
     }
     const uint32_t m = k + 1;
