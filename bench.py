@@ -142,7 +142,7 @@ def run_reference(args):
         weights, kv, state = decode_config_bytes(cfg, args.context)
         value = 1.0 / ((weights + kv + state) / (gbs * 1e9))
         metric, unit = "decode_tokens_per_s_mtp", "tokens/s"
-        workload = (f"qwen3.8-27b-shaped decode, 64 layers, batch 1, context {args.context}, MTP k=4 "
+        workload = (f"qwen3.8-27b-shaped decode, 64 layers, batch 1, context {args.context}, MTP k={args.drafts} "
                     "(BASELINE config 4)")
         sample = (f"one 17408x5120 Q4 fused matvec per step at {gbs:.2f} GB/s, scaled to the "
                   f"{(weights + kv + state) / 1e9:.1f} GB of one target pass (one token per pass)")
@@ -199,7 +199,9 @@ def launches_per_block(cfg, world=1):
 def run_decode(args):
     """BASELINE config 4: random-init Qwen3.8-27B-shaped hybrid decode, Q4 attention/embedding and
     Q2 FFN weights, bf16 paged KV (16-token pages) prefilled to 32768 tokens with random K/V,
-    batch 1, MTP speculation (4 chained drafts, restricted 40000-row draft head)."""
+    batch 1, MTP speculation (restricted 40000-row draft head). Chained drafts per block: 3 by
+    default, i.e. k + 1 = 4 verify positions as BASELINE config 2 states them; `--drafts 4` gives
+    the 5-row verify pass of the reference's CUDA candidate (backend/cuda_graph.rs:4565)."""
     import torch
     import torch.distributed as dist
     import ctox_llm_b200 as ctox
@@ -216,8 +218,7 @@ def run_decode(args):
         be.tp_init_from_torch()
     context = args.context
     cfg = ctox.qwen38_27b_config(max_context_tokens=context + 4096)
-    if args.drafts:  # chained MTP drafts per block (the reference's candidate path uses 4: a 5-row verify pass)
-        cfg.max_draft_tokens = args.drafts
+    cfg.max_draft_tokens = args.drafts
     if args.layers:  # a shallower model of the same layer shapes: small cases for profiler captures
         cfg.num_hidden_layers = args.layers
     ex = ctox.B200Executor(be, cfg)
@@ -293,7 +294,7 @@ def run_decode(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
             "config": {"workload": f"qwen3.8-27b-shaped decode, {cfg.num_hidden_layers} layers, batch 1, "
-                                   f"context {context}, MTP k={cfg.max_draft_tokens} (BASELINE config 4"
+                                   f"context {context}, MTP k={cfg.max_draft_tokens} (k + 1 verify positions; BASELINE config 4"
                                    f"{'' if cfg.num_hidden_layers == 64 else ', reduced depth: profiling case'})",
                        "weights": "Q4_B64 attention/embedding, Q2_B64 FFN, random init",
                        "kv": "bf16, 16-token pages", "l2": "11.8 GB streamed per pass (>> 126 MB L2)",
@@ -450,8 +451,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "q4_matvec"])
     ap.add_argument("--context", type=int, default=32768)
-    ap.add_argument("--drafts", type=int, default=0,
-                    help="decode: chained MTP drafts per block (default: the configuration's 4)")
+    ap.add_argument("--drafts", type=int, default=3,
+                    help="decode: chained MTP drafts per block (3 = 4 verify positions, BASELINE config 2; "
+                         "4 = the reference candidate's 5-row verify pass)")
     ap.add_argument("--layers", type=int, default=0,
                     help="decode: number of layers (default: the model's 64); fewer = a small profiling case")
     ap.add_argument("--quick", action="store_true",
