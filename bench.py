@@ -115,6 +115,12 @@ def cpu_baseline(threads: int, avx2: bool, repeats: int):
     return ALGO_BYTES / statistics.median(times) / 1e9, statistics.median(times)
 
 
+def decode_workload_name(context, layers, drafts):
+    depth = "" if layers == 64 else ", reduced depth: profiling case"
+    return (f"qwen3.8-27b-shaped decode, {layers} layers, batch 1, context {context}, MTP k={drafts} "
+            f"(k + 1 verify positions; BASELINE config 4{depth})")
+
+
 def run_reference(args):
     """The reference's CPU path (C restatement of backend/cpu.rs, AVX2 arm, rows split over all host
     threads). Each step is one bounded sample: a 17408x5120 Q4 fused matvec. For the decode workload
@@ -142,8 +148,7 @@ def run_reference(args):
         weights, kv, state = decode_config_bytes(cfg, args.context)
         value = 1.0 / ((weights + kv + state) / (gbs * 1e9))
         metric, unit = "decode_tokens_per_s_mtp", "tokens/s"
-        workload = (f"qwen3.8-27b-shaped decode, 64 layers, batch 1, context {args.context}, MTP k={args.drafts} "
-                    "(BASELINE config 4)")
+        workload = decode_workload_name(args.context, args.layers or 64, args.drafts)
         sample = (f"one 17408x5120 Q4 fused matvec per step at {gbs:.2f} GB/s, scaled to the "
                   f"{(weights + kv + state) / 1e9:.1f} GB of one target pass (one token per pass)")
     else:
@@ -293,9 +298,7 @@ def run_decode(args):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": f"qwen3.8-27b-shaped decode, {cfg.num_hidden_layers} layers, batch 1, "
-                                   f"context {context}, MTP k={cfg.max_draft_tokens} (k + 1 verify positions; BASELINE config 4"
-                                   f"{'' if cfg.num_hidden_layers == 64 else ', reduced depth: profiling case'})",
+            "config": {"workload": decode_workload_name(context, cfg.num_hidden_layers, cfg.max_draft_tokens),
                        "weights": "Q4_B64 attention/embedding, Q2_B64 FFN, random init",
                        "kv": "bf16, 16-token pages", "l2": "11.8 GB streamed per pass (>> 126 MB L2)",
                        "parallelism": f"tp{world} (one sequence; heads, FFN width and vocabulary split, "
