@@ -159,6 +159,9 @@ SIGNATURES = {
     "ctox_argmax_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
     "ctox_argmax_f32_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                          C.POINTER(C.c_uint32)]),
+    "ctox_matvec_fanout_dispatch": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint32, C.c_uint32,
+                                                C.c_uint64, C.c_void_p, C.c_void_p]),
+    "ctox_matvec_recovered_rows": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p]),
     "ctox_sample_topk_topp": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_float, C.c_uint32, C.c_float,
                                           C.c_float, C.POINTER(C.c_uint32)]),
     "ctox_exec_select_target": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_float, C.c_uint32, C.c_float, C.c_float,

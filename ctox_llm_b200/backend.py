@@ -197,6 +197,16 @@ class B200Backend:
                                                     top_k, C.c_float(top_p), C.c_float(draw), C.byref(tok)))
         return tok.value
 
+    def fanout_dispatch_device(self, prepared, x_ptr: int, x_dtype: int, positions: int, x_stride: int,
+                               y_ptrs, y_strides) -> None:
+        """Backend::fused_matvec_fanout over prepared matrices: one set of activation fragments."""
+        n = len(prepared)
+        handles = (C.c_void_p * n)(*[p._h for p in prepared])
+        ys = (C.c_void_p * n)(*[C.c_void_p(int(y)) for y in y_ptrs])
+        strides = (C.c_uint64 * n)(*[int(v) for v in y_strides])
+        self._check(self._lib.ctox_matvec_fanout_dispatch(handles, n, C.c_void_p(x_ptr), x_dtype, positions,
+                                                          x_stride, ys, strides))
+
     def synchronize(self) -> None:
         self._check(self._lib.ctox_ctx_synchronize(self._ctx))
 
@@ -281,6 +291,11 @@ class PreparedMatVec:
         self._h = handle
         self.rows = rows
         self.columns = columns
+
+    def recovered_rows_device(self, row_ids_ptr: int, n: int, out_ptr: int) -> None:
+        """Rows of the matrix times both recovery scales, for row ids in device memory."""
+        self._b._check(self._b._lib.ctox_matvec_recovered_rows(self._h, C.c_void_p(row_ids_ptr), n,
+                                                               C.c_void_p(out_ptr)))
 
     def dispatch_host(self, x, positions: int = 1, kernel: int = N.KERNEL_AUTO) -> np.ndarray:
         x = _f32(x)

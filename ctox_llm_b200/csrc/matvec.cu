@@ -1006,7 +1006,9 @@ uint32_t matvec_positions_per_pass(ctox_matvec *mv) {
     return per_pass;
 }
 
-ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos, const NormSource *norm) {
+// fragments_of: another matrix of the same fan-out group whose fragment buffers hold the activations.
+ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos, const NormSource *norm,
+                                   const ctox_matvec *fragments_of) {
     ctox_ctx *ctx = mv->ctx;
     MatvecPart &p = mv->parts[part_index];
     const MatvecPart::Split &split = p.split[npos > 4 ? 1 : 0];
@@ -1019,8 +1021,8 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     }
     StreamParams sp;
     sp.wprep = p.prep;
-    sp.xfrag = mv->xfrag;
-    sp.meta = mv->meta;
+    sp.xfrag = fragments_of ? fragments_of->xfrag : mv->xfrag;
+    sp.meta = fragments_of ? fragments_of->meta : mv->meta;
     sp.partial = p.partial;
     sp.error_flag = ctx->dev_error;
     sp.pairs = p.pairs;
@@ -1156,6 +1158,13 @@ ctox_status ctox_matvec_prepare(ctox_ctx *ctx, const ctox_fused_matvec_op *op, u
         rc = widen_scales(ctx, op->s_out_kind, op->s_out, op->s_out_len, s_out);
         if (rc) return rc;
     }
+    uint64_t s_in_digest = 0;
+    if (!s_in.empty()) {
+        s_in_digest = 1469598103934665603ull;  // FNV-1a over the widened values
+        const uint8_t *b = reinterpret_cast<const uint8_t *>(s_in.data());
+        for (size_t i = 0; i < s_in.size() * sizeof(float); ++i) s_in_digest = (s_in_digest ^ b[i]) * 1099511628211ull;
+        if (s_in_digest == 0) s_in_digest = 1;
+    }
     CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
     rc = set_smem_attr(ctx);
     if (rc) return rc;
@@ -1167,6 +1176,7 @@ ctox_status ctox_matvec_prepare(ctox_ctx *ctx, const ctox_fused_matvec_op *op, u
     mv->blocks = (uint32_t)(op->columns / kBlockLen);
     mv->blocks_padded = (mv->blocks + kTileBlocks - 1) / kTileBlocks * kTileBlocks;
     mv->activation = op->activation;
+    mv->s_in_digest = s_in_digest;
 #define PREP_TRY(expr)          \
     do {                        \
         rc = (expr);            \
@@ -1301,6 +1311,65 @@ ctox_status ctox_matvec_dispatch(ctox_matvec *mv, const void *x_dev, uint32_t x_
     }
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
+}
+
+ctox_status ctox_matvec_fanout_dispatch(ctox_matvec *const *mvs, uint64_t n, const void *x_dev, uint32_t x_dtype,
+                                        uint32_t positions, uint64_t x_stride, float *const *y_devs,
+                                        const uint64_t *y_strides) {
+    if (!mvs || n == 0 || !mvs[0]) return CTOX_INVALID_STATE;
+    ctox_matvec *first = mvs[0];
+    ctox_ctx *ctx = first->ctx;
+    if (!x_dev || !y_devs || !y_strides) return fail(ctx, CTOX_SHAPE, "fan-out: null pointer");
+    if (positions == 0 || positions > 16) return fail(ctx, CTOX_SHAPE, "fan-out: positions must be 1..16, got %u", positions);
+    if (x_dtype != CTOX_F32 && x_dtype != CTOX_BF16) return fail(ctx, CTOX_UNSUPPORTED_DTYPE, "fan-out: activation dtype %u", x_dtype);
+    if (x_stride < first->columns) return fail(ctx, CTOX_SHAPE, "fan-out: stride shorter than a row");
+    // fanout.rs:31-70: one corrected input serves matrices with the same input and identical s_in;
+    // here also the same code format, which fixes the fragment layout
+    uint32_t per_pass = kMaxPosPerPass;
+    for (uint64_t i = 0; i < n; ++i) {
+        ctox_matvec *mv = mvs[i];
+        if (!mv || mv->ctx != ctx || !y_devs[i]) return fail(ctx, CTOX_INVALID_STATE, "fan-out: member %llu is unusable", (unsigned long long)i);
+        if (mv->parts.size() != 1 || mv->parts[0].dt != first->parts[0].dt)
+            return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "fan-out: members must be pure and of one code format");
+        if (mv->columns != first->columns || mv->s_in_digest != first->s_in_digest)
+            return fail(ctx, CTOX_SHAPE, "fan-out: members must share the input width and s_in");
+        if (y_strides[i] < mv->rows) return fail(ctx, CTOX_SHAPE, "fan-out: output stride shorter than a row");
+        const uint32_t pp = matvec_positions_per_pass(mv);
+        if (pp == 0) return fail(ctx, CTOX_MEMORY_BUDGET, "fan-out: columns exceed the shared-memory budget");
+        per_pass = pp < per_pass ? pp : per_pass;
+    }
+    const size_t esz = x_dtype == CTOX_BF16 ? 2 : 4;
+    for (uint32_t m0 = 0; m0 < positions; m0 += per_pass) {
+        const uint32_t npos = positions - m0 < per_pass ? positions - m0 : per_pass;
+        const uint8_t *xp = (const uint8_t *)x_dev + (size_t)m0 * x_stride * esz;
+        const int groups = (int)(first->blocks_padded * npos);
+        launch_pdl(k_prep_x, dim3((groups * 16 + 255) / 256), dim3(256), 0, ctx->stream, (const void *)xp,
+                   (int)(x_dtype == CTOX_BF16), (long long)x_stride, (const float *)first->s_in, (int)first->columns,
+                   (int)first->blocks_padded, (int)npos, first->parts[0].dt, first->xfrag, first->meta);
+        for (uint64_t i = 0; i < n; ++i) {
+            ctox_matvec *mv = mvs[i];
+            ctox_status rc = matvec_stream_prepared(mv, 0, npos, nullptr, first);
+            if (rc) return rc;
+            float *y = y_devs[i] + (size_t)m0 * y_strides[i];
+            MatvecPart &p = mv->parts[0];
+            const unsigned n_out = (unsigned)(p.rows * npos);
+            launch_pdl(k_matvec_finish, dim3((n_out + 255) / 256), dim3(256), 0, ctx->stream, p.partial,
+                       p.split[npos > 4 ? 1 : 0].pieces, mv->s_out, mv->bias, y, (long long)y_strides[i],
+                       (uint32_t)p.rows, npos, p.slices, p.max_pieces, mv->activation);
+        }
+    }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status ctox_matvec_recovered_rows(ctox_matvec *mv, const uint32_t *row_ids_dev, uint32_t n, float *out_dev) {
+    if (!mv) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = mv->ctx;
+    if (!row_ids_dev || !out_dev || n == 0) return fail(ctx, CTOX_SHAPE, "recovered rows: null pointer or no rows");
+    if (mv->parts.size() != 1) return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "recovered rows: mixed matrices are served by the host form");
+    if (!mv->s_in || !mv->s_out) return fail(ctx, CTOX_SHAPE, "recovered rows need both recovery scales (backend/cpu.rs:312-370)");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    return matvec_embed_rows(mv, row_ids_dev, n, out_dev);
 }
 
 ctox_status ctox_matvec_dispatch_host(ctox_matvec *mv, const float *x_host, uint32_t positions,

@@ -46,6 +46,7 @@ struct ctox_matvec {
     size_t xfrag_bytes = 0;
     float2 *meta = nullptr;
     size_t meta_bytes = 0;
+    uint64_t s_in_digest = 0;  // FNV-1a of the widened s_in values (0 = none): fan-out groups must agree
     float *xtmp = nullptr;  // f32 staging (bf16 input to the row-warp kernel, host form)
     size_t xtmp_bytes = 0;
     float *ytmp = nullptr;
@@ -72,7 +73,7 @@ struct NormSource {
 // Same, for activations that are already in fragment form in mv->xfrag / mv->meta, or (norm set)
 // for x = rmsnorm_1p(norm->h) * s_in computed inside the kernel.
 ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos,
-                                   const NormSource *norm = nullptr);
+                                   const NormSource *norm = nullptr, const ctox_matvec *fragments_of = nullptr);
 // Takes ownership of tracked device buffers: canonical bytes, widened s_in [columns], s_out [rows].
 ctox_status matvec_create_device(ctox_ctx *ctx, int dt, uint64_t rows, uint64_t columns, uint8_t *canon,
                                  size_t canon_bytes, float *s_in, float *s_out, uint32_t flags,

@@ -201,6 +201,21 @@ ctox_status ctox_matvec_dispatch_host(ctox_matvec *mv, const float *x_host, uint
 ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *x_dev, uint32_t x_dtype,
                                         uint32_t positions, uint64_t x_stride, float *y_dev,
                                         uint64_t y_stride);
+/* Backend::fused_matvec_fanout on prepared, device-resident matrices (backend/cpu.rs:444-472;
+ * policy fanout.rs:31-70: members read the same input and carry identical s_in). The activation
+ * fragments are built once and every member streams against them. Members must be pure (one code
+ * format, the same for all) and have the same column count; otherwise CTOX_SHAPE /
+ * CTOX_UNSUPPORTED_OPERATION. y_devs[i] receives [positions][y_strides[i]] like
+ * ctox_matvec_dispatch. */
+ctox_status ctox_matvec_fanout_dispatch(ctox_matvec *const *mvs, uint64_t n, const void *x_dev,
+                                        uint32_t x_dtype, uint32_t positions, uint64_t x_stride,
+                                        float *const *y_devs, const uint64_t *y_strides);
+/* Device form of recovered rows (backend/cpu.rs:312-370; CUDA candidate
+ * ctox_q{2,4}_b64_recovered_rows_sm86): out_dev[i][c] = W[row_ids[i]][c] * s_in[c] *
+ * s_out[row_ids[i]] for n row ids in device memory. Needs CTOX_PREPARE_KEEP_CANONICAL and both
+ * recovery scales; a row id out of range sets the device error word. */
+ctox_status ctox_matvec_recovered_rows(ctox_matvec *mv, const uint32_t *row_ids_dev, uint32_t n,
+                                       float *out_dev);
 /* Geometry of the prepared operation. */
 ctox_status ctox_matvec_info(const ctox_matvec *mv, uint64_t *rows, uint64_t *columns,
                              uint64_t *packed_bytes, uint64_t *device_bytes);

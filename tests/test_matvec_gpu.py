@@ -231,3 +231,61 @@ def test_recovered_row_and_row_matvec(be, orc):
     with pytest.raises(ctox.CtoxError) as e:
         be.recovered_row_matvec(ctox.RecoveredRowMatVec(ctox.F32, w, x, 1.0))
     assert e.value.kind == "UnsupportedDType"
+
+
+def test_device_fanout_matches_independent_dispatches(orc):
+    """Backend::fused_matvec_fanout on prepared matrices (cpu.rs:444-472, fanout.rs:31-70): one set of
+    activation fragments, every member bit-identical to its own dispatch; members with a different
+    s_in are refused."""
+    import torch
+    be = ctox.B200Backend(0)
+    rng = np.random.default_rng(21)
+    cols, positions = 1024, 3
+    s_in = synthetic.recovery_scales_f16(cols, 5, 1)
+    mats = []
+    for rows, seed in ((512, 1), (96, 2), (2048, 3)):
+        mats.append(be.prepare_fused_matvec(ctox.FusedMatVec(
+            ctox.Q4B64, synthetic.packed_weights(ctox.Q4B64, rows, cols, seed), rows, cols, None, s_in=s_in,
+            s_out=synthetic.recovery_scales_f16(rows, seed, 2))))
+    x = torch.from_numpy(rng.standard_normal((positions, cols)).astype(np.float32)).cuda()
+    ys = [torch.zeros(positions, m.rows, device="cuda") for m in mats]
+    be.fanout_dispatch_device(mats, x.data_ptr(), ctox.F32, positions, cols, [y.data_ptr() for y in ys],
+                              [m.rows for m in mats])
+    be.synchronize()
+    for m, y in zip(mats, ys):
+        single = torch.zeros(positions, m.rows, device="cuda")
+        m.dispatch_device(x.data_ptr(), ctox.F32, positions, cols, single.data_ptr(), m.rows)
+        be.synchronize()
+        assert torch.equal(y, single)
+    other = be.prepare_fused_matvec(ctox.FusedMatVec(
+        ctox.Q4B64, synthetic.packed_weights(ctox.Q4B64, 64, cols, 9), 64, cols, None,
+        s_in=synthetic.recovery_scales_f16(cols, 6, 1)))
+    with pytest.raises(ctox.CtoxError) as e:
+        be.fanout_dispatch_device([mats[0], other], x.data_ptr(), ctox.F32, 1, cols,
+                                  [ys[0].data_ptr(), ys[1].data_ptr()], [mats[0].rows, 64])
+    assert e.value.kind == "Shape"
+    for m in mats + [other]:
+        m.destroy()
+    assert be.allocated_bytes() == 0
+    be.close()
+
+
+def test_device_recovered_rows_match_the_oracle(orc):
+    import torch
+    be = ctox.B200Backend(0)
+    rows, cols = 300, 512
+    w = synthetic.packed_weights(ctox.Q2B64, rows, cols, 4)
+    s_in, s_out = synthetic.recovery_scales_f16(cols, 4, 1), synthetic.recovery_scales_f16(rows, 4, 2)
+    mv = be.prepare_fused_matvec(ctox.FusedMatVec(ctox.Q2B64, w, rows, cols, None, s_in=s_in, s_out=s_out),
+                                 keep_canonical=True)
+    ids = np.array([0, 299, 17, 17, 128], dtype=np.uint32)
+    out = torch.zeros(ids.size, cols, device="cuda")
+    mv.recovered_rows_device(torch.from_numpy(ids.view(np.int32)).cuda().data_ptr(), ids.size, out.data_ptr())
+    be.synchronize()
+    rb = cols // 64 * 18
+    so = np.frombuffer(s_out.tobytes(), dtype=np.float16).astype(np.float32)
+    for i, r in enumerate(ids):
+        exp = orc.recovered_row(orc.Q2B64, w[r * rb:(r + 1) * rb], cols, s_in, float(so[r]))
+        assert np.array_equal(out[i].cpu().numpy(), exp), (i, r)
+    mv.destroy()
+    be.close()
