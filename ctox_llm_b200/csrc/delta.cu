@@ -227,7 +227,6 @@ constexpr int kLaMaxPos = 8;
 
 __global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int npos) {
     pdl_launch();
-    pdl_wait();
     __shared__ float qs[kLaMaxPos][kDeltaDim], ks[kLaMaxPos][kDeltaDim], vs[kLaMaxPos][kDeltaDim];
     __shared__ float zs[kLaMaxPos][kDeltaDim], core[kLaMaxPos][kDeltaDim];
     __shared__ float gs[kLaMaxPos], bs[kLaMaxPos], q_inv[kLaMaxPos], k_inv[kLaMaxPos];
@@ -238,18 +237,34 @@ __global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int 
     const bool owns_qk = head % rep == 0;
     const uint32_t channels = 2 * a.key_width + a.value_width;
 
-    // ---- 1. conv + SiLU, z, decay, beta
+    // Before the dependency wait: what the pass itself does not write. The committed recurrent
+    // state and conv state were last written by the commit of the previous block, which a host
+    // copy separates from this pass; the weights never change. These loads overlap the tail of
+    // the input projection.
+    const uint32_t slice = warp >> 2, rg = warp & 3, col = slice * kDeltaSlice + lane;
+    float s[32];  // rows rg * 32 .. + 32 of column slice * 32 + lane
+    {
+        const float *sin_ = a.state_in + ((size_t)head * kDeltaDim + rg * 32) * kDeltaDim + col;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[i] = sin_[(size_t)i * kDeltaDim];
+    }
+    const uint32_t part = tid >> 7, cd = tid & 127;
+    const uint32_t ch = part == 0 ? khead * kDeltaDim + cd
+                        : part == 1 ? a.key_width + khead * kDeltaDim + cd
+                                    : 2 * a.key_width + head * kDeltaDim + cd;
+    float st[8], cw[8];
     if (tid < 384) {
-        const uint32_t part = tid >> 7, d = tid & 127;
-        const uint32_t ch = part == 0 ? khead * kDeltaDim + d
-                            : part == 1 ? a.key_width + khead * kDeltaDim + d
-                                        : 2 * a.key_width + head * kDeltaDim + d;
-        const bool store = part == 2 || owns_qk;
-        float st[8], cw[8];
         for (uint32_t j = 0; j < a.conv_kernel; ++j) {
             st[j] = a.conv_state[(size_t)ch * a.conv_kernel + j];
             cw[j] = a.conv_w[(size_t)ch * a.conv_kernel + j];
         }
+    }
+    pdl_wait();
+
+    // ---- 1. conv + SiLU, z, decay, beta
+    if (tid < 384) {
+        const uint32_t d = cd;
+        const bool store = part == 2 || owns_qk;
         for (int m = 0; m < npos; ++m) {
             const float x = out_of(a.fan, ch, m);
             if (store) a.conv_in[(size_t)m * channels + ch] = x;
@@ -284,14 +299,6 @@ __global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int 
             bs[m] = b;
             a.beta[(size_t)m * a.value_heads + head] = b;
         }
-    }
-    // the recurrent state of this thread: rows rg * 32 .. + 32 of column slice * 32 + lane
-    const uint32_t slice = warp >> 2, rg = warp & 3, col = slice * kDeltaSlice + lane;
-    float s[32];
-    {
-        const float *sin_ = a.state_in + ((size_t)head * kDeltaDim + rg * 32) * kDeltaDim + col;
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = sin_[(size_t)i * kDeltaDim];
     }
     __syncthreads();
     // L2 norms of q and k per position, with the reduction tree of the stand-alone scan: value d in
