@@ -545,7 +545,6 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     const __nv_bfloat16 *__restrict__ v_cache, const uint32_t *__restrict__ page_table, uint32_t page_tokens,
     uint64_t cache_slot, int npos, uint32_t splits, float *__restrict__ ws) {
     pdl_launch();
-    pdl_wait();
     extern __shared__ __align__(128) uint8_t smraw[];
     constexpr int NT = GROUPS * 128;
     const uint32_t G = g.q_heads / g.kv_heads, NQ = G * npos;
@@ -561,28 +560,6 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     const uint64_t tiles = (total + kFaTile - 1) / kFaTile;
     const uint64_t tile_beg = tiles * sp / splits, tile_end = tiles * (sp + 1) / splits;
     const float scale = 1.0f / sqrtf((float)kFaHd);
-    {   // Q as bf16 hi + lo: 8 float4 per thread, all loads issued before the first conversion
-        constexpr int kQRows = 16 * GROUPS, kVec = kQRows * kFaHd / 4 / NT;
-        float4 qv[kVec];
-#pragma unroll
-        for (int it = 0; it < kVec; ++it) {
-            const uint32_t i = (tid + it * NT) * 4, qi = i / kFaHd, d = i % kFaHd;
-            qv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (qi < NQ)
-                qv[it] = *reinterpret_cast<const float4 *>(
-                    q + ((size_t)(qi / G) * g.q_heads + kh * G + qi % G) * kFaHd + d);
-        }
-#pragma unroll
-        for (int it = 0; it < kVec; ++it) {
-            const uint32_t i = (tid + it * NT) * 4, qi = i / kFaHd, d = i % kFaHd;
-            const float v[4] = {qv[it].x * scale, qv[it].y * scale, qv[it].z * scale, qv[it].w * scale};
-            uint32_t hi[2], lo[2];
-            split_bf16(v[0], v[1], hi[0], lo[0]);
-            split_bf16(v[2], v[3], hi[1], lo[1]);
-            *reinterpret_cast<uint2 *>(q_s + qi * kFaStride + d) = make_uint2(hi[0], hi[1]);
-            *reinterpret_cast<uint2 *>(q_s + (32 + qi) * kFaStride + d) = make_uint2(lo[0], lo[1]);
-        }
-    }
     // Tile loads. Thread (warp, lane) copies the 16-byte chunk `lane` of rows warp, warp + NT/32, ...
     // of the K and of the V tile. The cache slots of a tile (page-table lookups) are fetched one
     // tile ahead of the copies that use them, so the lookups never sit between two copies.
@@ -640,10 +617,35 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     uint64_t limit[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) limit[r] = cache_slot + (qrow[r] < NQ ? qrow[r] / G : 0);
+    // The page table does not change after warm-up: the lookups of the first tile go out before the
+    // wait for the kernels in front (which write q and the new K/V rows).
+    if (tile_beg < tile_end) fetch_slots(tile_beg);
+    pdl_wait();
     if (tile_beg < tile_end) {
-        fetch_slots(tile_beg);
         issue_tile(0);
         if (tile_beg + 1 < tile_end) fetch_slots(tile_beg + 1);
+    }
+    {   // Q as bf16 hi + lo: 8 float4 per thread, all loads issued before the first conversion
+        constexpr int kQRows = 16 * GROUPS, kVec = kQRows * kFaHd / 4 / NT;
+        float4 qv[kVec];
+#pragma unroll
+        for (int it = 0; it < kVec; ++it) {
+            const uint32_t i = (tid + it * NT) * 4, qi = i / kFaHd, d = i % kFaHd;
+            qv[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (qi < NQ)
+                qv[it] = *reinterpret_cast<const float4 *>(
+                    q + ((size_t)(qi / G) * g.q_heads + kh * G + qi % G) * kFaHd + d);
+        }
+#pragma unroll
+        for (int it = 0; it < kVec; ++it) {
+            const uint32_t i = (tid + it * NT) * 4, qi = i / kFaHd, d = i % kFaHd;
+            const float v[4] = {qv[it].x * scale, qv[it].y * scale, qv[it].z * scale, qv[it].w * scale};
+            uint32_t hi[2], lo[2];
+            split_bf16(v[0], v[1], hi[0], lo[0]);
+            split_bf16(v[2], v[3], hi[1], lo[1]);
+            *reinterpret_cast<uint2 *>(q_s + qi * kFaStride + d) = make_uint2(hi[0], hi[1]);
+            *reinterpret_cast<uint2 *>(q_s + (32 + qi) * kFaStride + d) = make_uint2(lo[0], lo[1]);
+        }
     }
     for (uint64_t tile = tile_beg; tile < tile_end; ++tile) {
         const uint32_t b = (uint32_t)(tile - tile_beg) & 1;
