@@ -108,11 +108,10 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_finish_push(MvOut o, uint32_t r
     pdl_launch();
     pdl_wait();
     const uint32_t row = blockIdx.x * kTpChunk + threadIdx.x;
-    if (row >= rows) return;
-    for (int m = 0; m < npos; ++m) {
-        const uint32_t bits = __float_as_uint(out_of(o, row, m));
-        for (uint32_t r = 0; r < world; ++r) st_word_sys(peers.dst[r] + (size_t)m * rows + row, bits, seq);
-    }
+    const int m = blockIdx.y;  // one position per CTA row: the piece loads of all positions go out together
+    if (row >= rows || m >= npos) return;
+    const uint32_t bits = __float_as_uint(out_of(o, row, m));
+    for (uint32_t r = 0; r < world; ++r) st_word_sys(peers.dst[r] + (size_t)m * rows + row, bits, seq);
 }
 
 // h[m][c] += sum over ranks of their partial vectors (rank order), from this rank's receive
@@ -244,7 +243,7 @@ ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uin
     const size_t parity_off = (size_t)parity * tp->world * tp->elems;
     TpPeerPtrs pp{};
     for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
-    launch_pdl(k_tp_finish_push, dim3(chunks), dim3(kTpChunk), 0, ctx->stream, o, rows, (int)m, pp, tp->world, seq);
+    launch_pdl(k_tp_finish_push, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, o, rows, (int)m, pp, tp->world, seq);
     launch_pdl(k_tp_residual_add, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, h, tp->recv + parity_off, tp->elems,
                tp->world, seq, rows, sumsq, ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());

@@ -79,7 +79,7 @@ def main():
     be.tp_all_reduce(x.data_ptr(), x.numel())
     be.synchronize()
     assert float(x[0]) == world * (world + 1) / 2 and float(x[-1]) == float(x[0])
-    heads = 8 if world <= 4 else 16
+    heads = 4 * world  # 4 query heads of 64 per rank: a 256-wide o_proj shard
     acc = run(orc, be, rank, world, tiny_config(num_attention_heads=heads, linear_num_key_heads=world,
                                                 linear_num_value_heads=2 * world), 16)
     acc2 = run(orc, be, rank, world, tiny_config(num_attention_heads=heads, linear_num_key_heads=world,
