@@ -346,22 +346,26 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     // Everything above touched only this matrix's weights, which nothing in the stream writes.
     // The activations come from the kernels before this one: wait for them here, with the first
     // STAGES chunks of every warp already on their way.
+    // fused norm: the norm weight and s_in of this thread's first block are constants too
+    float4 wv_first = make_float4(0.f, 0.f, 0.f, 0.f), sv_first = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (p.norm_h) {
+        const uint32_t c = (slice * slice_blocks + (threadIdx.x >> 4) / p.npos) * 64 + (threadIdx.x & 15) * 4;
+        if ((threadIdx.x >> 4) < slice_blocks * p.npos && c < p.norm_hidden) {
+            wv_first = *reinterpret_cast<const float4 *>(p.norm_w + c);
+            if (p.norm_s_in) sv_first = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
+        }
+    }
     pdl_wait();
     CTOX_TRACE_MARK(tracer, 1, p.trace_slot);
     if (p.norm_h) {
         // Fused input norm: xn = h * rsqrt(mean(h^2) + eps) * (1 + w), x = xn * s_in, written as
         // fragments straight into shared memory while the first weight chunks are in flight.
-        if (threadIdx.x < p.npos) {
-            float sq = 0.f;
-            for (uint32_t q = 0; q < p.norm_parts; ++q) sq += p.norm_sumsq[threadIdx.x * p.norm_parts + q];
-            inv_rms[threadIdx.x] = 1.0f / sqrtf(sq / (float)p.norm_hidden + p.norm_eps);
-        }
-        __syncthreads();
         const int i = threadIdx.x & 15;
         const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
         const uint32_t first_block = slice * slice_blocks;
         // tasks = (block, position) pairs, one per 16-lane group and round; the h values of the next
-        // round are requested before this round's fragments are built (one L2 trip in flight)
+        // round are requested before this round's fragments are built (one L2 trip in flight), and
+        // those of the first round together with the partial sums of squares
         const uint32_t n_tasks = slice_blocks * p.npos, stride = (WARPS * 32) >> 4;
         auto load_h = [&](uint32_t task) {
             float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -374,15 +378,24 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
             return hv;
         };
         float4 hv = load_h(threadIdx.x >> 4);
+        if (threadIdx.x < p.npos) {
+            float sq = 0.f;
+            for (uint32_t q = 0; q < p.norm_parts; ++q) sq += p.norm_sumsq[threadIdx.x * p.norm_parts + q];
+            inv_rms[threadIdx.x] = 1.0f / sqrtf(sq / (float)p.norm_hidden + p.norm_eps);
+        }
+        __syncthreads();
         for (uint32_t task = threadIdx.x >> 4; task < n_tasks; task += stride) {
             const float4 hn = load_h(task + stride);
             const uint32_t b = task / p.npos, m = task % p.npos;
             const uint32_t c = (first_block + b) * 64 + i * 4;
             float v[4] = {0.f, 0.f, 0.f, 0.f};
             if (c < p.norm_hidden) {
-                const float4 wv = *reinterpret_cast<const float4 *>(p.norm_w + c);
-                float4 sv = make_float4(1.f, 1.f, 1.f, 1.f);
-                if (p.norm_s_in) sv = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
+                float4 wv = wv_first, sv = sv_first;
+                if (task != (threadIdx.x >> 4)) {
+                    wv = *reinterpret_cast<const float4 *>(p.norm_w + c);
+                    sv = make_float4(1.f, 1.f, 1.f, 1.f);
+                    if (p.norm_s_in) sv = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
+                }
                 const float inv = inv_rms[m];
                 v[0] = hv.x * inv * (1.0f + wv.x) * sv.x;
                 v[1] = hv.y * inv * (1.0f + wv.y) * sv.y;
