@@ -102,25 +102,17 @@ __device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
     return make_uint2((uint32_t)w, (uint32_t)(w >> 32));
 }
 
-// y[pos][row] of this rank's partial result -> every rank's receive slot for this rank.
-__global__ void __launch_bounds__(kTpChunk) k_tp_finish_push(MvOut o, uint32_t rows, int npos, TpPeerPtrs peers,
-                                                           uint32_t world, uint32_t seq) {
-    pdl_launch();
-    pdl_wait();
-    const uint32_t row = blockIdx.x * kTpChunk + threadIdx.x;
-    const int m = blockIdx.y;  // one position per CTA row: the piece loads of all positions go out together
-    if (row >= rows || m >= npos) return;
-    const uint32_t bits = __float_as_uint(out_of(o, row, m));
-    for (uint32_t r = 0; r < world; ++r) st_word_sys(peers.dst[r] + (size_t)m * rows + row, bits, seq);
-}
-
-// h[m][c] += sum over ranks of their partial vectors (rank order), from this rank's receive
-// buffer recv[source][m][c]; partial sums of squares of the result per 256-column part, like
-// k_residual_add.
-__global__ void __launch_bounds__(kTpChunk) k_tp_residual_add(float *__restrict__ h, const uint2 *recv,
-                                                            size_t source_stride, uint32_t world, uint32_t seq,
-                                                            uint32_t hidden, float *__restrict__ sumsq,
-                                                            int32_t *error_flag) {
+// One kernel per sum: y[pos][row] of this rank's partial result goes to every PEER's receive slot
+// for this rank; then the same thread collects the peers' values for its (row, position) from this
+// rank's own receive buffer and adds all W values to h in rank order (its own from the register:
+// the same bits the peers receive). Pushes never wait, so two ranks cannot wait on each other
+// without one of them having pushed. Partial sums of squares of the result per 256-column part,
+// like k_residual_add.
+__global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float *__restrict__ h, TpPeerPtrs peers,
+                                                               const uint2 *recv, size_t source_stride,
+                                                               uint32_t rank, uint32_t world, uint32_t seq,
+                                                               uint32_t hidden, float *__restrict__ sumsq,
+                                                               int32_t *error_flag) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[kTpChunk / 32];
@@ -128,10 +120,18 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_residual_add(float *__restrict_
     const uint32_t c = blockIdx.x * kTpChunk + threadIdx.x;
     float v = 0.f;
     if (c < hidden) {
-        v = h[(size_t)m * hidden + c];
+        const float mine = out_of(o, c, m);
+        const size_t at = (size_t)m * hidden + c;
+        for (uint32_t r = 0; r < world; ++r)
+            if (r != rank) st_word_sys(peers.dst[r] + at, __float_as_uint(mine), seq);
+        v = h[at];
         const long long t0 = clock64();
         for (uint32_t r = 0; r < world; ++r) {
-            const uint2 *p = recv + r * source_stride + (size_t)m * hidden + c;
+            if (r == rank) {
+                v += mine;
+                continue;
+            }
+            const uint2 *p = recv + r * source_stride + at;
             uint2 word = ld_word_sys(p);
             while (word.y != seq) {
                 if (clock64() - t0 > 2000000000ll) {  // ~1 s: a peer is gone
@@ -142,11 +142,11 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_residual_add(float *__restrict_
             }
             v += __uint_as_float(word.x);
         }
-        h[(size_t)m * hidden + c] = v;
+        h[at] = v;
     }
     float s = v * v;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -243,9 +243,8 @@ ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uin
     const size_t parity_off = (size_t)parity * tp->world * tp->elems;
     TpPeerPtrs pp{};
     for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
-    launch_pdl(k_tp_finish_push, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, o, rows, (int)m, pp, tp->world, seq);
-    launch_pdl(k_tp_residual_add, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, h, tp->recv + parity_off, tp->elems,
-               tp->world, seq, rows, sumsq, ctx->dev_error);
+    launch_pdl(k_tp_reduce_residual, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, o, h, pp, tp->recv + parity_off,
+               tp->elems, tp->rank, tp->world, seq, rows, sumsq, ctx->dev_error);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }

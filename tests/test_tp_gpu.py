@@ -1,4 +1,4 @@
-"""Tensor-parallel decode on 2 and 4 GPUs against the CPU oracle: each rank holds a shard of the tiny
+"""Tensor-parallel decode on 2, 4 and 8 GPUs against the CPU oracle: each rank holds a shard of the tiny
 model; tokens and logits must match the unsharded oracle, and every rank must resolve the same
 speculative blocks. Skipped on a box with one GPU."""
 import os
@@ -17,7 +17,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_sharded_decode_matches_the_oracle(orc, world):
     import torch
     if torch.cuda.device_count() < world:
