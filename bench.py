@@ -190,14 +190,22 @@ def decode_config_bytes(cfg, positions):
 
 
 def launches_per_block(cfg, world=1):
-    """Kernels of this library launched by one speculative block on one GPU (counted from the
-    executor's structure: 12 per decoder layer, 3 to start a pass, 5 for the head, 1-2 per linear
-    layer to commit; an MTP pass is one layer plus 4 around the fc and 5 for the draft head; in a
-    tensor-parallel group 2 more per layer finish the partial results that NCCL then sums)."""
-    n_lin = cfg.num_hidden_layers - cfg.num_hidden_layers // cfg.full_attention_interval
-    per_layer = 12 + (2 if world > 1 else 0)
-    target = 3 + per_layer * cfg.num_hidden_layers + 5 + 2 * n_lin
-    mtp = cfg.max_draft_tokens * (4 + per_layer + 5)
+    """Kernels of this library launched by one speculative block on one GPU, counted from the
+    executor's structure. A pass of m positions: per linear-attention layer 8 (input projection, the
+    layer's one linear-attention kernel, out_proj, residual, gate/up, SwiGLU, down, residual), per
+    full-attention layer 10 (attention pre, attention, split merge instead of the one kernel), plus
+    2 norm kernels per layer when m > 2 (with fewer positions the projections normalise in their
+    prologue); 3 to start and end a pass. Head: 4 (lm_head, statistics, merge, acceptance); commit: 1.
+    An MTP draft pass: that layer plus 11 around it (embedding rows, input norm, fc, residual, final
+    norm, fragments, draft head, finish, 2 argmax). A tensor-parallel group adds nothing: the group
+    sum is the residual kernel."""
+    del world
+    n_full = cfg.num_hidden_layers // cfg.full_attention_interval
+    n_lin = cfg.num_hidden_layers - n_full
+    m = cfg.max_draft_tokens + 1
+    norm = 2 if m > 2 else 0
+    target = n_lin * (8 + norm) + n_full * (10 + norm) + 3 + 4 + 1
+    mtp = cfg.max_draft_tokens * (10 + 11)
     return target + mtp
 
 
