@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdlib>
 #include <vector>
@@ -1056,6 +1057,7 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
     if (mtp_enabled && !c.mtp_num_hidden_layers)
         return fail(ctx, CTOX_INVALID_STATE, "decode enabled MTP but the model has no MTP layer");
     CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    const auto t_decode_begin = std::chrono::steady_clock::now();
     memset(step, 0, sizeof *step);
     const uint32_t k = (mtp_enabled && e->have_hidden && e->position > 0) ? c.max_draft_tokens : 0;
     const uint64_t P = e->position;
@@ -1097,7 +1099,15 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
                                    ctx->stream));
     CTOX_CUDA(ctx, cudaMemcpyAsync((uint8_t *)ctx->pinned + sizeof(ctox_spec_record), ctx->dev_error, 4,
                                    cudaMemcpyDeviceToHost, ctx->stream));
+    static const bool host_timing = getenv("CTOX_HOST_TIMING") != nullptr;  // diagnostic: launch path cost
+    const auto t_enqueued = std::chrono::steady_clock::now();
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the one host read of the block
+    if (host_timing) {
+        const auto t_done = std::chrono::steady_clock::now();
+        fprintf(stderr, "decode: host enqueue %.0f us, then waited %.0f us for the device\n",
+                std::chrono::duration<double, std::micro>(t_enqueued - t_decode_begin).count(),
+                std::chrono::duration<double, std::micro>(t_done - t_enqueued).count());
+    }
     ctox_spec_record rec;
     memcpy(&rec, ctx->pinned, sizeof rec);
     int32_t dev_err;
