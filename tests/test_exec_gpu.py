@@ -150,3 +150,20 @@ def test_bf16_cache_tensor_core_attention_matches_oracle(orc):
     finally:
         ex.unload()
         be.close()
+
+
+def test_select_target_token_samples_from_the_kept_logits(setup, orc):
+    """ModelExecutor::select_target_token (engine.rs:322-362): the sampler runs on the logits the
+    executor kept on the device; same token as Sampler::sample_with_draw on those logits."""
+    be, ex, model = setup
+    ex.keep_logits(True)
+    ex.prefill(PROMPT)
+    ex.decode(PROMPT[-1], mtp_enabled=False)
+    logits = ex.last_logits(0)
+    for draw in (0.0, 0.37, 0.93):
+        got = ex.select_target_token(0.8, 40, 0.9, draw)
+        assert got == orc.sample_with_draw(logits, 0.8, 40, 0.9, draw)
+    assert ex.select_target_token(0.0, 40, 0.9, 0.5) == orc.greedy_token(logits)
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.select_target_token(0.8, 0, 0.9, 0.5)
+    assert e.value.kind == "UnsupportedOperation"
