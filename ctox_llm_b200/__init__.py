@@ -9,11 +9,11 @@ from ._native import (ACT_IDENTITY, ACT_SILU, BF16, F16, F32, KERNEL_AUTO, KERNE
                       KERNEL_STREAM, MIXED_Q2Q4B64, PREPARE_KEEP_CANONICAL, Q2B64, Q4B64, CtoxError,
                       Segment, load)
 from .backend import B200Backend, FusedMatVec, PreparedMatVec, RecoveredRow, RecoveredRowMatVec
-from .executor import B200Executor, GeneratedBlock, qwen38_27b_config
+from .executor import B200Executor, CancellationToken, GeneratedBlock, qwen38_27b_config
 from . import _native as native
 
 __all__ = [
-    "B200Backend", "B200Executor", "GeneratedBlock", "qwen38_27b_config", "native", "FusedMatVec", "PreparedMatVec", "RecoveredRow", "RecoveredRowMatVec", "Segment",
+    "B200Backend", "B200Executor", "CancellationToken", "GeneratedBlock", "qwen38_27b_config", "native", "FusedMatVec", "PreparedMatVec", "RecoveredRow", "RecoveredRowMatVec", "Segment",
     "CtoxError", "load", "Q2B64", "Q4B64", "MIXED_Q2Q4B64", "F16", "F32", "BF16", "ACT_IDENTITY",
     "ACT_SILU", "KERNEL_AUTO", "KERNEL_STREAM", "KERNEL_ROWWARP", "PREPARE_KEEP_CANONICAL",
 ]

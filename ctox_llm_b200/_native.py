@@ -132,6 +132,8 @@ SIGNATURES = {
     "ctox_tp_init": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_int32, C.c_int32, C.c_void_p]),
     "ctox_tp_destroy": (C.c_int32, [C.c_void_p]),
     "ctox_tp_all_reduce_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "ctox_tp_collective": (C.c_int32, [C.c_void_p, C.POINTER(C.c_char_p)]),
+    "ctox_tp_debug_silent_peers": (C.c_int32, [C.c_void_p, C.c_int32, C.c_uint64]),
     "ctox_ctx_allocated_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "ctox_ctx_device_error": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32)]),
     "ctox_ctx_kernel_timing": (C.c_int32, [C.c_void_p, C.c_int32]),
@@ -177,10 +179,15 @@ SIGNATURES = {
     "ctox_exec_fill_synthetic": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_float, C.c_float]),
     "ctox_exec_warmup": (C.c_int32, [C.c_void_p]),
     "ctox_exec_reset_session": (C.c_int32, [C.c_void_p]),
-    "ctox_exec_prefill": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64]),
+    "ctox_exec_prefill": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
     "ctox_exec_prefill_synthetic": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_uint64]),
     "ctox_exec_decode": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_int32, C.c_float, C.c_uint64, C.c_int32,
-                                     C.POINTER(ExecStep)]),
+                                     C.c_void_p, C.POINTER(ExecStep)]),
+    "ctox_exec_commit_speculative": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p]),
+    "ctox_exec_session_state": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "ctox_exec_last_mtp_hidden": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32)]),
+    "ctox_exec_last_draft_logits": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32),
+                                                C.POINTER(C.c_uint32)]),
     "ctox_exec_position": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "ctox_exec_last_hidden": (C.c_int32, [C.c_void_p, C.c_void_p]),
     "ctox_exec_keep_logits": (C.c_int32, [C.c_void_p, C.c_int32]),

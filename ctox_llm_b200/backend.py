@@ -264,6 +264,17 @@ class B200Backend:
         dist.broadcast_object_list(box, src=0)
         self.tp_init(rank, world, box[0])
 
+    def tp_collective(self) -> str:
+        """"none", "p2p_push" (peer-memory one-shot all-reduce) or "nccl": what sums the group."""
+        name = C.c_char_p()
+        self._check(self._lib.ctox_tp_collective(self._ctx, C.byref(name)))
+        return name.value.decode()
+
+    def tp_debug_silent_peers(self, world: int, wait_limit_cycles: int = 0) -> None:
+        """Failure-detection tests: rank 0 of a group whose other ranks never answer."""
+        self._check(self._lib.ctox_tp_debug_silent_peers(self._ctx, world, wait_limit_cycles))
+        self.tp_rank, self.tp_world = 0, world
+
     def tp_all_reduce(self, buf_ptr: int, n: int) -> None:
         self._check(self._lib.ctox_tp_all_reduce_f32(self._ctx, C.c_void_p(buf_ptr), n))
 

@@ -34,6 +34,10 @@ struct ctox_ctx {
     int tp_rank = 0, tp_world = 1;
     void *nccl_comm = nullptr;
     ctox::TpPeer *tp_peer = nullptr;  // peer-memory all-reduce state (tp.cu); null = NCCL only
+    // Limit of the bounded device waits on a peer, in SM clock cycles (~1 s by default).
+    long long wait_limit_cycles = 2000000000ll;
+    // Test mode: a group whose other ranks never answer (ctox_tp_debug_silent_peers).
+    bool tp_silent = false;
     // optional per-kernel timing of the dominant kernel (benchmark support)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timing_events;

@@ -23,7 +23,6 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
-#include <chrono>
 #include <cmath>
 #include <cstdlib>
 #include <vector>
@@ -80,6 +79,16 @@ struct ctox_exec {
     uint32_t hist_tokens[kMaxPass] = {0};  // tokens at positions position-hist_n+1 .. position-1 (drafts accepted)
     uint64_t step_counter = 0;
     bool warmed = false, keep_logits = false;
+    // Speculative transaction (engine.rs:322-362): an MTP decode resolves and commits its accepted
+    // prefix on the device and leaves the count here until commit_speculative confirms it.
+    int32_t pending = -1;
+    // A device error or a failed call after work was enqueued leaves the session state undefined:
+    // every call fails until reset_session (engine.rs:594-611 invalidates the session the same way).
+    bool poisoned = false;
+    // evidence of the last decode call (with keep_logits): the MTP layer's final hidden of every
+    // (token, hidden) pair it ran, in order, and the logits of every draft
+    float *mtp_trace = nullptr, *draft_trace = nullptr;
+    uint32_t mtp_trace_n = 0, draft_trace_n = 0, draft_rows = 0;
     // buffers ([kMaxPass] rows each)
     float *h = nullptr, *final_hidden = nullptr, *hist_hidden = nullptr, *embed_rows = nullptr;
     float *mtp_h = nullptr, *mtp_hidden = nullptr;
@@ -745,6 +754,12 @@ ctox_status ctox_exec_reset_session(ctox_exec *e) {
     e->have_hidden = false;
     e->hist_n = 0;
     e->step_counter = 0;
+    e->pending = -1;
+    if (e->poisoned) {  // the error word may still be set by kernels that ran after the failure
+        CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        CTOX_CUDA(ctx, cudaMemsetAsync(ctx->dev_error, 0, sizeof(int32_t), ctx->stream));
+        e->poisoned = false;
+    }
     return CTOX_OK;
 }
 
@@ -799,8 +814,17 @@ ctox_status ctox_exec_position(const ctox_exec *e, uint64_t *position) {
 ctox_status ctox_exec_keep_logits(ctox_exec *e, int32_t enable) {
     if (!e) return CTOX_INVALID_STATE;
     e->keep_logits = enable != 0;
-    if (e->keep_logits && !e->logits)
-        return xalloc(e, (void **)&e->logits, (size_t)kMaxPass * e->vocab_l * 4, true);
+    if (e->keep_logits && !e->logits) {
+        ctox_status rc = xalloc(e, (void **)&e->logits, (size_t)kMaxPass * e->vocab_l * 4, true);
+        if (rc) return rc;
+    }
+    if (e->keep_logits && e->cfg.mtp_num_hidden_layers && !e->mtp_trace) {
+        ctox_status rc = xalloc(e, (void **)&e->mtp_trace, (size_t)2 * kMaxPass * e->cfg.hidden_size * 4, true);
+        if (rc) return rc;
+        e->draft_rows = e->cfg.draft_vocab ? (e->draft_n ? e->draft_n : 1) : e->vocab_l;
+        rc = xalloc(e, (void **)&e->draft_trace, (size_t)kMaxPass * e->draft_rows * 4, true);
+        if (rc) return rc;
+    }
     return CTOX_OK;
 }
 
@@ -988,6 +1012,11 @@ ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const uint32_t
     }
     EX(layer_body(e, L, e->mtp_h, m, abs_pos0, abs_pos0 - 1, e->mtp_page_table, e->mtp_norm, e->mtp_hidden,
                   nullptr));
+    if (e->keep_logits && e->mtp_trace && e->mtp_trace_n + m <= 2 * kMaxPass) {
+        CTOX_CUDA(ctx, cudaMemcpyAsync(e->mtp_trace + (size_t)e->mtp_trace_n * c.hidden_size, e->mtp_hidden,
+                                       (size_t)m * c.hidden_size * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        e->mtp_trace_n += m;
+    }
     if (draft_slot >= 0) {
         const bool restricted = c.draft_vocab != 0;
         ctox_matvec *head = restricted ? e->draft_head : e->lm_head;  // null: no draft row on this rank
@@ -995,6 +1024,12 @@ ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const uint32_t
             EX(matvec_stream_pass(head, 0, e->mtp_hidden + (size_t)(m - 1) * c.hidden_size, CTOX_F32, 1,
                                   c.hidden_size));
             matvec_finish_enqueue(head, 1, e->draft_logits, head->rows);
+            if (e->keep_logits && e->draft_trace && e->draft_trace_n < kMaxPass && head->rows <= e->draft_rows) {
+                CTOX_CUDA(ctx, cudaMemcpyAsync(e->draft_trace + (size_t)e->draft_trace_n * e->draft_rows,
+                                               e->draft_logits, (size_t)head->rows * 4, cudaMemcpyDeviceToDevice,
+                                               ctx->stream));
+                e->draft_trace_n += 1;
+            }
         }
         EX(argmax_enqueue(ctx, e->draft_logits, head ? (uint32_t)head->rows : 0,
                           restricted ? e->draft_ids + e->draft_lo : nullptr, e->vocab_off,
@@ -1010,23 +1045,24 @@ ctox_status upload_u32(ctox_exec *e, uint32_t *dst, const uint32_t *src, uint32_
     return CTOX_OK;
 }
 
-}  // namespace
+bool cancelled(const volatile int32_t *cancel) { return cancel && *cancel != 0; }
 
-extern "C" {
+ctox_status session_usable(ctox_exec *e, const char *what) {
+    if (e->poisoned)
+        return fail(e->ctx, CTOX_INVALID_STATE,
+                    "%s: the session was invalidated by an earlier device error; reset_session first", what);
+    return CTOX_OK;
+}
 
-ctox_status ctox_exec_prefill(ctox_exec *e, const uint32_t *tokens, uint64_t n) {
-    if (!e || !tokens) return CTOX_INVALID_STATE;
+ctox_status prefill_impl(ctox_exec *e, const uint32_t *tokens, uint64_t n, const volatile int32_t *cancel,
+                         bool *began) {
     ctox_ctx *ctx = e->ctx;
-    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "prefill: executor is not warm");
-    if (n == 0 || n + 2 * kMaxPass > e->cfg.max_context_tokens)
-        return fail(ctx, CTOX_SHAPE, "prefill: %llu tokens do not fit the context", (unsigned long long)n);
-    for (uint64_t i = 0; i < n; ++i)
-        if (tokens[i] >= e->cfg.vocab_size) return fail(ctx, CTOX_SHAPE, "prefill: token %u out of range", tokens[i]);
-    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
     EX(ctox_exec_reset_session(e));
     const uint64_t consume = n - 1;  // the last token is the input of the first decode
     for (uint64_t a = 0; a < consume; a += kMaxPass) {
+        if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "prefill cancelled at token %llu", (unsigned long long)a);
         const uint32_t m = (uint32_t)(consume - a < kMaxPass ? consume - a : kMaxPass);
+        *began = true;
         EX(upload_u32(e, e->tokens_dev, tokens + a, m));
         EX(target_pass(e, m, a));
         EX(commit_positions(e, m, m));
@@ -1037,32 +1073,32 @@ ctox_status ctox_exec_prefill(ctox_exec *e, const uint32_t *tokens, uint64_t n) 
             EX(upload_u32(e, e->mtp_tokens_dev, tokens + a + 1, m));
             EX(mtp_pass(e, m, a + 1, e->mtp_tokens_dev, e->hist_hidden, -1));
         }
-        CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // `tokens` may be pageable host memory
+        // `tokens` may be pageable host memory: finish the chunk, and read the device error word
+        int32_t dev_err = 0;
+        EX(ctox_ctx_device_error(ctx, &dev_err));
+        if (dev_err)
+            return fail(ctx, CTOX_INVALID_STATE,
+                        dev_err == DEV_ERR_WAIT_TIMEOUT ? "prefill: a bounded device wait ran out (device error %d)"
+                                                        : "prefill: device error %d",
+                        dev_err);
     }
     return CTOX_OK;
 }
 
-ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float temperature, uint64_t seed,
-                             int32_t force_accept, ctox_exec_step *step) {
-    if (!e || !step) return CTOX_INVALID_STATE;
+ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float temperature, uint64_t seed,
+                        int32_t force_accept, const volatile int32_t *cancel, ctox_exec_step *step, bool *began) {
     ctox_ctx *ctx = e->ctx;
     const ctox_model_config &c = e->cfg;
-    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "decode: executor is not warm");
-    if (token >= c.vocab_size) return fail(ctx, CTOX_SHAPE, "decode: token %u out of range", token);
-    if (!std::isfinite(temperature) || temperature < 0.f)
-        return fail(ctx, CTOX_INVALID_ARTIFACT, "temperature must be finite and non-negative");
-    if (e->position + 2 * kMaxPass >= c.max_context_tokens)
-        return fail(ctx, CTOX_SHAPE, "decode: context capacity exhausted at position %llu",
-                    (unsigned long long)e->position);
-    if (mtp_enabled && !c.mtp_num_hidden_layers)
-        return fail(ctx, CTOX_INVALID_STATE, "decode enabled MTP but the model has no MTP layer");
-    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
-    const auto t_decode_begin = std::chrono::steady_clock::now();
     memset(step, 0, sizeof *step);
     const uint32_t k = (mtp_enabled && e->have_hidden && e->position > 0) ? c.max_draft_tokens : 0;
     const uint64_t P = e->position;
     uint32_t host_tokens[kMaxPass + 1] = {0};
     host_tokens[0] = token;
+    e->mtp_trace_n = e->draft_trace_n = 0;
+    // Nothing below changes the committed session before the acceptance is known: a cancellation
+    // between passes leaves the session where it was (the MTP cache slots written so far belong to
+    // committed positions or lie beyond them and are rewritten by the next call).
+    *began = true;
     EX(upload_u32(e, e->tokens_dev, host_tokens, 1));
     if (k > 0) {
         // catch-up over the pairs of the last block (true target hiddens), then the chained drafts
@@ -1073,6 +1109,7 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
         EX(upload_u32(e, e->mtp_tokens_dev, mt, n));
         EX(mtp_pass(e, n, P - n + 1, e->mtp_tokens_dev, e->hist_hidden, 1));
         for (uint32_t i = 1; i < k; ++i) {
+            if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "decode cancelled while drafting");
             // the draft just written to tokens_dev[i] and the MTP's own hidden of the last pair, in
             // place: the pass reads both in its first kernels and rewrites mtp_hidden in its last
             const uint32_t prev_rows = i == 1 ? n : 1;
@@ -1080,6 +1117,7 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
                         (int)(1 + i)));
         }
     }
+    if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "decode cancelled before the target pass");
     const uint32_t m = k + 1;
     EX(target_pass(e, m, P));
     EX(matvec_stream_prepared(e->lm_head, 0, m));
@@ -1099,22 +1137,18 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
                                    ctx->stream));
     CTOX_CUDA(ctx, cudaMemcpyAsync((uint8_t *)ctx->pinned + sizeof(ctox_spec_record), ctx->dev_error, 4,
                                    cudaMemcpyDeviceToHost, ctx->stream));
-    static const bool host_timing = getenv("CTOX_HOST_TIMING") != nullptr;  // diagnostic: launch path cost
-    const auto t_enqueued = std::chrono::steady_clock::now();
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the one host read of the block
-    if (host_timing) {
-        const auto t_done = std::chrono::steady_clock::now();
-        fprintf(stderr, "decode: host enqueue %.0f us, then waited %.0f us for the device\n",
-                std::chrono::duration<double, std::micro>(t_enqueued - t_decode_begin).count(),
-                std::chrono::duration<double, std::micro>(t_done - t_enqueued).count());
-    }
     ctox_spec_record rec;
     memcpy(&rec, ctx->pinned, sizeof rec);
     int32_t dev_err;
     memcpy(&dev_err, (uint8_t *)ctx->pinned + sizeof(ctox_spec_record), 4);
     if (dev_err) {
         cudaMemsetAsync(ctx->dev_error, 0, 4, ctx->stream);
-        return fail(ctx, CTOX_INVALID_STATE, "decode: device error %d", dev_err);
+        e->poisoned = true;  // kernels carried on past the failure: the residual stream and caches are undefined
+        return fail(ctx, CTOX_INVALID_STATE,
+                    dev_err == DEV_ERR_WAIT_TIMEOUT ? "decode: a bounded device wait ran out (device error %d)"
+                                                    : "decode: device error %d",
+                    dev_err);
     }
     if (rec.status) return fail(ctx, CTOX_INVALID_STATE, "decode: the target produced a non-finite logit");
     if (rec.n_emitted == 0 || rec.n_emitted > m)
@@ -1129,6 +1163,103 @@ ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, 
     step->next_token = rec.emitted[n_acc];
     for (uint32_t j = 0; j < k; ++j) step->draft_tokens[j] = rec.node_token[1 + j];
     for (uint32_t j = 0; j < m; ++j) step->target_tokens[j] = rec.node_argmax[j];
+    if (k > 0) e->pending = (int32_t)n_acc;
+    return CTOX_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+ctox_status ctox_exec_prefill(ctox_exec *e, const uint32_t *tokens, uint64_t n, const volatile int32_t *cancel) {
+    if (!e || !tokens) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "prefill cancelled");
+    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "prefill: executor is not warm");
+    if (n == 0 || n + 2 * kMaxPass > e->cfg.max_context_tokens)
+        return fail(ctx, CTOX_SHAPE, "prefill: %llu tokens do not fit the context", (unsigned long long)n);
+    for (uint64_t i = 0; i < n; ++i)
+        if (tokens[i] >= e->cfg.vocab_size) return fail(ctx, CTOX_SHAPE, "prefill: token %u out of range", tokens[i]);
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    bool began = false;
+    const ctox_status rc = prefill_impl(e, tokens, n, cancel, &began);
+    // a prefill that stopped half way (cancelled or failed) leaves no usable session
+    if (rc && began) e->poisoned = true;
+    return rc;
+}
+
+ctox_status ctox_exec_decode(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float temperature, uint64_t seed,
+                             int32_t force_accept, const volatile int32_t *cancel, ctox_exec_step *step) {
+    if (!e || !step) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    const ctox_model_config &c = e->cfg;
+    if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "decode cancelled");  // decoder.rs:1284-1292
+    if (!e->warmed) return fail(ctx, CTOX_INVALID_STATE, "decode: executor is not warm");
+    EX(session_usable(e, "decode"));
+    if (e->pending >= 0)  // decoder.rs:1293-1297
+        return fail(ctx, CTOX_INVALID_STATE, "decode requires the previous speculative branch to be committed");
+    if (token >= c.vocab_size) return fail(ctx, CTOX_SHAPE, "decode: token %u out of range", token);
+    if (!std::isfinite(temperature) || temperature < 0.f)
+        return fail(ctx, CTOX_INVALID_ARTIFACT, "temperature must be finite and non-negative");
+    if (e->position + 2 * kMaxPass >= c.max_context_tokens)
+        return fail(ctx, CTOX_SHAPE, "decode: context capacity exhausted at position %llu",
+                    (unsigned long long)e->position);
+    if (mtp_enabled && !c.mtp_num_hidden_layers)
+        return fail(ctx, CTOX_INVALID_STATE, "decode enabled MTP but the model has no MTP layer");
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    bool began = false;
+    const ctox_status rc = decode_impl(e, token, mtp_enabled, temperature, seed, force_accept, cancel, step, &began);
+    if (rc && rc != CTOX_CANCELLED && began) e->poisoned = true;
+    return rc;
+}
+
+ctox_status ctox_exec_commit_speculative(ctox_exec *e, uint32_t accepted_drafts, const volatile int32_t *cancel) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    EX(session_usable(e, "commit_speculative"));
+    if (e->pending < 0)  // decoder.rs:1401-1403
+        return fail(ctx, CTOX_INVALID_STATE, "executor has no pending speculative branch");
+    if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "commit_speculative cancelled");
+    // The device resolved the acceptance and committed exactly that prefix (the resolved form,
+    // engine.rs:110-136); any other depth would name a state this executor does not hold.
+    if ((int32_t)accepted_drafts != e->pending)
+        return fail(ctx, CTOX_INVALID_STATE, "accepted MTP depth %u differs from the device-resolved prefix %d",
+                    accepted_drafts, e->pending);
+    e->pending = -1;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_session_state(const ctox_exec *e, int32_t *pending_accepted, int32_t *poisoned) {
+    if (!e) return CTOX_INVALID_STATE;
+    if (pending_accepted) *pending_accepted = e->pending;
+    if (poisoned) *poisoned = e->poisoned ? 1 : 0;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_last_mtp_hidden(ctox_exec *e, uint32_t index, float *out, uint32_t *count) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (count) *count = e->mtp_trace_n;
+    if (!out) return CTOX_OK;
+    if (!e->keep_logits || !e->mtp_trace || index >= e->mtp_trace_n)
+        return fail(ctx, CTOX_INVALID_STATE, "MTP hidden states are not kept (ctox_exec_keep_logits) or index out of range");
+    CTOX_CUDA(ctx, cudaMemcpyAsync(out, e->mtp_trace + (size_t)index * e->cfg.hidden_size,
+                                   (size_t)e->cfg.hidden_size * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_last_draft_logits(ctox_exec *e, uint32_t draft, float *out, uint32_t *rows, uint32_t *count) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    if (rows) *rows = e->draft_rows;
+    if (count) *count = e->draft_trace_n;
+    if (!out) return CTOX_OK;
+    if (!e->keep_logits || !e->draft_trace || draft >= e->draft_trace_n)
+        return fail(ctx, CTOX_INVALID_STATE, "draft logits are not kept (ctox_exec_keep_logits) or index out of range");
+    CTOX_CUDA(ctx, cudaMemcpyAsync(out, e->draft_trace + (size_t)draft * e->draft_rows, (size_t)e->draft_rows * 4,
+                                   cudaMemcpyDeviceToHost, ctx->stream));
+    CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return CTOX_OK;
 }
 

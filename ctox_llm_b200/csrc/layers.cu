@@ -189,66 +189,9 @@ void launch_swiglu_prep(cudaStream_t st, const MvOut &gate_up, uint32_t inter, u
 }
 
 // ------------------------------------------------------------------ linear attention
-// Rows of the fused projection: [q | k | v] (conv channels), z, a, b (decoder.rs:832-867).
-// One thread per output row; the conv state of a channel is walked over the m positions
-// (causal_conv_silu_update, reference.rs:159-187: shift left, append, dot, SiLU). The
-// committed conv state is only read; the inputs are kept so that a commit of any prefix can
-// rebuild it.
-__global__ void k_linear_mid(MvOut fan, uint32_t key_width, uint32_t value_width, uint32_t value_heads,
-                             uint32_t conv_kernel, const float *__restrict__ conv_state,
-                             const float *__restrict__ conv_w, const float *__restrict__ a_log,
-                             const float *__restrict__ dt_bias, int npos, float *__restrict__ conv_in,
-                             float *__restrict__ q, float *__restrict__ k, float *__restrict__ v,
-                             float *__restrict__ z, float *__restrict__ log_decay, float *__restrict__ beta) {
-    pdl_launch();
-    pdl_wait();
-    const uint32_t channels = 2 * key_width + value_width;
-    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
-    if (r < channels) {
-        float st[8];
-        for (uint32_t j = 0; j < conv_kernel; ++j) st[j] = conv_state[(size_t)r * conv_kernel + j];
-        for (int m = 0; m < npos; ++m) {
-            const float x = out_of(fan, r, m);
-            conv_in[(size_t)m * channels + r] = x;
-            for (uint32_t j = 0; j + 1 < conv_kernel; ++j) st[j] = st[j + 1];
-            st[conv_kernel - 1] = x;
-            float sum = 0.f;
-            for (uint32_t j = 0; j < conv_kernel; ++j) sum += st[j] * conv_w[(size_t)r * conv_kernel + j];
-            const float y = silu_f(sum);
-            if (r < key_width)
-                q[(size_t)m * key_width + r] = y;
-            else if (r < 2 * key_width)
-                k[(size_t)m * key_width + (r - key_width)] = y;
-            else
-                v[(size_t)m * value_width + (r - 2 * key_width)] = y;
-        }
-    } else if (r < channels + value_width) {
-        const uint32_t c = r - channels;
-        for (int m = 0; m < npos; ++m) z[(size_t)m * value_width + c] = out_of(fan, r, m);
-    } else if (r < channels + value_width + value_heads) {
-        const uint32_t hh = r - channels - value_width;
-        for (int m = 0; m < npos; ++m) {
-            const float x = out_of(fan, r, m) + dt_bias[hh];
-            const float sp = x > 20.0f ? x : log1pf(expf(x));  // decoder.rs:29-35
-            log_decay[(size_t)m * value_heads + hh] = -expf(a_log[hh]) * sp;
-        }
-    } else if (r < channels + value_width + 2 * value_heads) {
-        const uint32_t hh = r - channels - value_width - value_heads;
-        for (int m = 0; m < npos; ++m)
-            beta[(size_t)m * value_heads + hh] = 1.0f / (1.0f + expf(-out_of(fan, r, m)));
-    }
-}
-
-void launch_linear_mid(cudaStream_t st, const MvOut &fan, uint32_t key_width, uint32_t value_width,
-                       uint32_t value_heads, uint32_t conv_kernel, const float *conv_state,
-                       const float *conv_w, const float *a_log, const float *dt_bias, uint32_t m,
-                       float *conv_in, float *q, float *k, float *v, float *z, float *log_decay, float *beta) {
-    const uint32_t rows = 2 * key_width + 2 * value_width + 2 * value_heads;
-    launch_pdl(k_linear_mid, dim3((rows + 127) / 128), dim3(128), 0, st, fan, key_width, value_width, value_heads, conv_kernel,
-                                                    conv_state, conv_w, a_log, dt_bias, (int)m, conv_in, q, k,
-                                                    v, z, log_decay, beta);
-}
-
+// conv_state <- conv_state shifted by the first n kept inputs of a pass (causal_conv_silu_update,
+// reference.rs:159-187: shift left, append): the commit of n positions when the batched commit
+// kernel is not in use.
 __global__ void k_conv_commit(float *__restrict__ conv_state, const float *__restrict__ conv_in,
                               uint32_t channels, uint32_t conv_kernel, uint32_t n) {
     pdl_launch();
@@ -267,41 +210,6 @@ __global__ void k_conv_commit(float *__restrict__ conv_state, const float *__res
 void launch_conv_commit(cudaStream_t st, float *conv_state, const float *conv_in, uint32_t channels,
                         uint32_t conv_kernel, uint32_t n) {
     launch_pdl(k_conv_commit, dim3((channels + 127) / 128), dim3(128), 0, st, conv_state, conv_in, channels, conv_kernel, n);
-}
-
-// rms_norm_gated (reference.rs:66-93) per (position, value head) of 128 values: one warp,
-// four values per lane, two 64-column blocks of the out_proj input.
-__global__ void k_gated_norm_prep(const float *__restrict__ core, const float *__restrict__ z,
-                                  const float *__restrict__ w, float eps, uint32_t value_heads, int npos,
-                                  MvIn next) {
-    pdl_launch();
-    pdl_wait();
-    const uint32_t wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (wid >= value_heads * (uint32_t)npos) return;
-    const uint32_t head = wid / npos;
-    const int m = wid % npos;
-    const size_t off = ((size_t)m * value_heads + head) * 128 + lane * 4;
-    const float4 c = *reinterpret_cast<const float4 *>(core + off);
-    const float4 g = *reinterpret_cast<const float4 *>(z + off);
-    float sq = c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-    const float inv = 1.0f / sqrtf(sq / 128.0f + eps);
-    const uint32_t col = head * 128 + lane * 4;
-    const float cs[4] = {c.x, c.y, c.z, c.w}, gs[4] = {g.x, g.y, g.z, g.w};
-    float v[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j)
-        v[j] = cs[j] * inv * w[lane * 4 + j] * silu_f(gs[j]) * (next.s_in ? next.s_in[col + j] : 1.0f);
-    const unsigned gmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
-    prep_block(v, lane & 15, gmask, (int)(head * 2 + (lane >> 4)), m, npos, next.dt, next.xfrag, next.meta);
-}
-
-void launch_gated_norm_prep(cudaStream_t st, const float *core, const float *z, const float *w, float eps,
-                            uint32_t value_heads, uint32_t value_dim, uint32_t m, const MvIn &next) {
-    (void)value_dim;  // 128: checked by the executor
-    const uint32_t warps = value_heads * m;
-    launch_pdl(k_gated_norm_prep, dim3((warps * 32 + 255) / 256), dim3(256), 0, st, core, z, w, eps, value_heads, (int)m, next);
 }
 
 // ------------------------------------------------------------------ full attention
@@ -859,11 +767,14 @@ static void launch_attention_t(cudaStream_t st, const AttnGeom &g, const float *
                                uint64_t cache_slot, uint32_t m, uint32_t splits, float *ws) {
     const size_t smem = (size_t)NQMAX * g.head_dim * 4 + (size_t)NQMAX * kAttnTile * 4 + 3 * NQMAX * 4 +
                         (size_t)kAttnTile * (g.head_dim + 16 / sizeof(T)) * sizeof(T) + 16;
-    static bool attr_done = false;
-    if (!attr_done) {
-        cudaFuncSetAttribute(k_attention<T, NQMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_done = true;
-    }
+    // the attribute belongs to the device, not to the process: once per device
+    static thread_local unsigned long long attr_devices = 0;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 64 && !(attr_devices >> dev & 1ull) &&
+        cudaFuncSetAttribute(k_attention<T, NQMAX>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) ==
+            cudaSuccess)
+        attr_devices |= 1ull << dev;
     launch_pdl(k_attention<T, NQMAX>, dim3(g.kv_heads * splits), dim3(kAttnThreads), smem, st, 
         g, q, (const T *)k_cache, (const T *)v_cache, page_table, page_tokens, cache_slot, (int)m, splits, ws);
 }
@@ -875,12 +786,15 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
     const uint32_t nq = g.q_heads / g.kv_heads * m;
     if (kv_bf16 && g.head_dim == kFaHd && nq <= 32) {
         const size_t smem = 2 * 32 * kFaStride * 2 + 4 * (size_t)kFaTile * kFaStride * 2;
-        static bool attr_done = false;
-        if (!attr_done) {
-            cudaFuncSetAttribute(k_attention_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(k_attention_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr_done = true;
-        }
+        static thread_local unsigned long long attr_devices = 0;  // per device, like above
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev < 64 && !(attr_devices >> dev & 1ull) &&
+            cudaFuncSetAttribute(k_attention_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) ==
+                cudaSuccess &&
+            cudaFuncSetAttribute(k_attention_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) ==
+                cudaSuccess)
+            attr_devices |= 1ull << dev;
         if (nq <= 16)
             launch_pdl(k_attention_mma<1>, dim3(g.kv_heads * splits), dim3(128), smem, st, 
                 g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,

@@ -60,17 +60,9 @@ void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next);
 // silu(gate) * up of a fused [gate; up] projection -> fragments for the down projection.
 void launch_swiglu_prep(cudaStream_t st, const MvOut &gate_up, uint32_t inter, uint32_t m, const MvIn &next);
-// Linear-attention middle: conv + SiLU over [q|k|v], z, decay and beta from a, b.
-void launch_linear_mid(cudaStream_t st, const MvOut &fan, uint32_t key_width, uint32_t value_width,
-                       uint32_t value_heads, uint32_t conv_kernel, const float *conv_state,
-                       const float *conv_w, const float *a_log, const float *dt_bias, uint32_t m,
-                       float *conv_in, float *q, float *k, float *v, float *z, float *log_decay, float *beta);
 // conv_state <- conv_state shifted by the first n inputs of the pass (commit of n positions).
 void launch_conv_commit(cudaStream_t st, float *conv_state, const float *conv_in, uint32_t channels,
                         uint32_t conv_kernel, uint32_t n);
-// rms_norm_gated(core, z) per value head -> fragments for out_proj.
-void launch_gated_norm_prep(cudaStream_t st, const float *core, const float *z, const float *w, float eps,
-                            uint32_t value_heads, uint32_t value_dim, uint32_t m, const MvIn &next);
 // Full attention, before the cache: split q/gate, per-head norms, partial RoPE, K/V append.
 void launch_attn_pre(cudaStream_t st, const MvOut &fan, const AttnGeom &g, const float *q_norm,
                      const float *k_norm, uint64_t rope_position, uint64_t cache_slot, uint32_t m, float *q,

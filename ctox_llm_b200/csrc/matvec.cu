@@ -235,7 +235,7 @@ struct StreamParams {
     uint32_t slices;           // column slices (each CTA works inside one slice)
     uint32_t ctas_per_slice;
     uint32_t warps_per_slice;  // warps that take work (<= units per slice)
-    uint32_t npos, max_pieces, trace_slot;
+    uint32_t npos, max_pieces;
     // When norm_h is set the activations are not read from xfrag/meta: every CTA builds the
     // fragments of its column slice itself from x = rmsnorm_1p(norm_h) * s_in.
     const float *norm_h;      // [npos][norm_hidden]
@@ -268,30 +268,9 @@ __device__ __forceinline__ void block_mma(float (&c)[4], uint32_t w0, uint32_t w
     }
 }
 
-// Build with -DCTOX_TRACE to record, per launch of the streaming kernel, the global timer at
-// entry, when its dependency was met, when its activations were ready and when its last warp
-// finished (ctox_debug_trace_dump reads the ring): the timeline with dependent launches
-// overlapping, which a profiler that serialises kernels cannot show.
-#ifdef CTOX_TRACE
-__device__ unsigned long long g_trace[4 * 16384];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return t;
-}
-#define CTOX_TRACE_MARK(cond, idx, slot) \
-    if (cond) g_trace[4 * (slot) + (idx)] = gtime()
-#define CTOX_TRACE_END(cond, slot) \
-    if (cond) atomicMax(&g_trace[4 * (slot) + 3], gtime())
-#else
-#define CTOX_TRACE_MARK(cond, idx, slot)
-#define CTOX_TRACE_END(cond, slot)
-#endif
 template <int DT, int WARPS, int STAGES, int NT>
 __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamParams p) {
     pdl_launch();
-    [[maybe_unused]] const bool tracer = blockIdx.x == 0 && threadIdx.x == 0;
-    CTOX_TRACE_MARK(tracer, 0, p.trace_slot);
     using F = Fmt<DT>;
     constexpr uint32_t kST = F::kSuperTileBytes;
     constexpr uint32_t kUnitBytes = 2 * kST;                      // one tile pair
@@ -356,7 +335,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         }
     }
     pdl_wait();
-    CTOX_TRACE_MARK(tracer, 1, p.trace_slot);
     if (p.norm_h) {
         // Fused input norm: xn = h * rsqrt(mean(h^2) + eps) * (1 + w), x = xn * s_in, written as
         // fragments straight into shared memory while the first weight chunks are in flight.
@@ -419,7 +397,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         bulk_g2s(smem_u32(ms), reinterpret_cast<const uint8_t *>(p.meta) + (size_t)slice * meta_bytes,
                  meta_bytes, xbar);
     }
-    CTOX_TRACE_MARK(tracer, 2, p.trace_slot);
     if (!active || nchunks == 0) return;  // warp 0 of every CTA is active and waits for xbar below
     bool ok = p.norm_h ? true : mbar_wait(xbar, 0);
 
@@ -565,7 +542,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
         return;
     }
     close_pair(cur_pair, cur_ks == p.kst_s);
-    CTOX_TRACE_END(lane == 0, p.trace_slot);
 }
 
 // y[pos][row] = act((sum over slices and pieces + bias[row]) * s_out[row]); one thread per (row, pos).
@@ -1045,8 +1021,6 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     sp.warps_per_slice = split.warps_per_slice;
     sp.npos = npos;
     sp.max_pieces = p.max_pieces;
-    static uint32_t trace_counter = 0;
-    sp.trace_slot = trace_counter++ % 16384;
     sp.norm_h = nullptr;
     if (norm) {
         if (norm->hidden != mv->columns || norm->hidden % 64)
@@ -1621,6 +1595,7 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
                     "dispatch_static: this %llux%llu operation needs %zu bytes of scratch, the built-in array "
                     "holds %zu; use ctox_matvec_dispatch",
                     (unsigned long long)mv->rows, (unsigned long long)mv->columns, need, kStaticScratchBytes);
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));  // every call: the launches below go to the current device
     unsigned char *base = nullptr;
     ctox_status rc = static_scratch_address(ctx, &base);
     if (rc) return rc;
@@ -1654,14 +1629,15 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             sp.npos = npos;
             sp.max_pieces = p.max_pieces;
             sp.norm_h = nullptr;
-            sp.trace_slot = 16383;
             const StreamCfg cfg{split.warps, split.stages};
             const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
             const unsigned grid = split.ctas_per_slice * p.slices;
+            timing_begin(ctx);
             if (p.dt)
                 launch_stream<1>(cfg, grid, smem, st, sp);
             else
                 launch_stream<0>(cfg, grid, smem, st, sp);
+            timing_end(ctx);
             const unsigned n_out = (unsigned)(p.rows * npos);
             launch_pdl(k_matvec_finish, dim3((n_out + 255) / 256), dim3(256), 0, st, 
                 partial, split.pieces, mv->s_out ? mv->s_out + p.row_start : nullptr,
@@ -1672,9 +1648,3 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
-
-#ifdef CTOX_TRACE
-extern "C" int ctox_debug_trace_dump(unsigned long long *out, int n) {
-    return (int)cudaMemcpyFromSymbol(out, g_trace, (size_t)n * 4 * 8);
-}
-#endif

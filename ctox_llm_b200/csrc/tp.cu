@@ -49,13 +49,21 @@ constexpr int kNcclFloat32 = 7, kNcclInt8 = 0, kNcclSum = 0;
 namespace ctox {
 
 ctox_status tp_all_reduce_sum_f32(ctox_ctx *ctx, float *buf, size_t n) {
-    if (ctx->tp_world <= 1) return CTOX_OK;
+    if (ctx->tp_world <= 1 || ctx->tp_silent) return CTOX_OK;
     const int rc = g_nccl.AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, ctx->nccl_comm, ctx->stream);
     if (rc) return fail(ctx, CTOX_INVALID_STATE, "ncclAllReduce failed: %s", g_nccl.GetErrorString(rc));
     return CTOX_OK;
 }
 
 ctox_status tp_all_gather(ctox_ctx *ctx, const void *send, void *recv, size_t bytes_per_rank) {
+    if (ctx->tp_silent) {  // the other ranks never answer: their slots read as zeros
+        uint8_t *own = (uint8_t *)recv + (size_t)ctx->tp_rank * bytes_per_rank;
+        if (send != own) CTOX_CUDA(ctx, cudaMemcpyAsync(own, send, bytes_per_rank, cudaMemcpyDeviceToDevice, ctx->stream));
+        for (int r = 0; r < ctx->tp_world; ++r)
+            if (r != ctx->tp_rank)
+                CTOX_CUDA(ctx, cudaMemsetAsync((uint8_t *)recv + (size_t)r * bytes_per_rank, 0, bytes_per_rank, ctx->stream));
+        return CTOX_OK;
+    }
     if (ctx->tp_world <= 1) {
         if (send != recv) CTOX_CUDA(ctx, cudaMemcpyAsync(recv, send, bytes_per_rank, cudaMemcpyDeviceToDevice, ctx->stream));
         return CTOX_OK;
@@ -86,6 +94,7 @@ struct TpPeer {
     size_t elems = 0;          // floats per vector
     uint2 *recv = nullptr;     // own: [2 parities][world sources][elems] of {value bits, seq}
     uint2 *peer_recv[kTpMaxWorld] = {nullptr};
+    uint2 *sink = nullptr;     // test mode only: where pushes to the silent peers go
 };
 struct TpPeerPtrs {  // by value into the kernels: where each rank receives THIS rank's vector
     uint2 *dst[kTpMaxWorld];
@@ -112,7 +121,7 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
                                                                const uint2 *recv, size_t source_stride,
                                                                uint32_t rank, uint32_t world, uint32_t seq,
                                                                uint32_t hidden, float *__restrict__ sumsq,
-                                                               int32_t *error_flag) {
+                                                               int32_t *error_flag, long long wait_limit) {
     pdl_launch();
     pdl_wait();
     __shared__ float red[kTpChunk / 32];
@@ -126,6 +135,9 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
             if (r != rank) st_word_sys(peers.dst[r] + at, __float_as_uint(mine), seq);
         v = h[at];
         const long long t0 = clock64();
+        // once a wait has run out anywhere (this kernel or an earlier one of the same call), nobody
+        // waits again: the call is lost anyway and the kernels behind it must not each spend the limit
+        bool gave_up = *reinterpret_cast<volatile int32_t *>(error_flag) != 0;
         for (uint32_t r = 0; r < world; ++r) {
             if (r == rank) {
                 v += mine;
@@ -133,11 +145,13 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
             }
             const uint2 *p = recv + r * source_stride + at;
             uint2 word = ld_word_sys(p);
-            while (word.y != seq) {
-                if (clock64() - t0 > 2000000000ll) {  // ~1 s: a peer is gone
+            while (word.y != seq && !gave_up) {
+                if (clock64() - t0 > wait_limit) {  // a peer is gone
                     atomicExch(error_flag, DEV_ERR_WAIT_TIMEOUT);
+                    gave_up = true;
                     break;
                 }
+                if (*reinterpret_cast<volatile int32_t *>(error_flag) != 0) gave_up = true;
                 word = ld_word_sys(p);
             }
             v += __uint_as_float(word.x);
@@ -167,6 +181,21 @@ ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
     tp->rank = R;
     tp->elems = elems;
     const size_t bytes = 2 * (size_t)W * elems * sizeof(uint2);
+    if (ctx->tp_silent) {
+        // test mode: this rank's pushes land in a local sink, nothing is ever pushed to it
+        uint2 *sink = nullptr;
+        if (cudaMalloc((void **)&tp->recv, bytes) != cudaSuccess || cudaMemset(tp->recv, 0, bytes) != cudaSuccess ||
+            cudaMalloc((void **)&sink, bytes) != cudaSuccess) {
+            cudaFree(tp->recv);
+            delete tp;
+            cudaGetLastError();
+            return fail(ctx, CTOX_MEMORY_BUDGET, "tp: no memory for the silent-peer buffers");
+        }
+        for (uint32_t r = 0; r < W; ++r) tp->peer_recv[r] = r == R ? tp->recv : sink;
+        tp->sink = sink;
+        ctx->tp_peer = tp;
+        return CTOX_OK;
+    }
     struct Card {
         cudaIpcMemHandle_t recv;
         int ok;
@@ -180,12 +209,12 @@ ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
     if (cudaMalloc((void **)&dev, sizeof(Card) * (W + 1)) != cudaSuccess) {
         rc = fail(ctx, CTOX_MEMORY_BUDGET, "tp: no memory for the peer exchange");
     } else {
-        cudaMemcpyAsync(dev + W, &mine, sizeof(Card), cudaMemcpyHostToDevice, ctx->stream);
-        rc = tp_all_gather(ctx, dev + W, dev, sizeof(Card));
-        if (!rc) {
-            cudaMemcpyAsync(all, dev, sizeof(Card) * W, cudaMemcpyDeviceToHost, ctx->stream);
-            if (cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = fail(ctx, CTOX_INVALID_STATE, "tp: peer exchange failed");
-        }
+        if (cudaMemcpyAsync(dev + W, &mine, sizeof(Card), cudaMemcpyHostToDevice, ctx->stream) != cudaSuccess)
+            rc = fail(ctx, CTOX_INVALID_STATE, "tp: peer exchange failed (upload)");
+        if (!rc) rc = tp_all_gather(ctx, dev + W, dev, sizeof(Card));
+        if (!rc && (cudaMemcpyAsync(all, dev, sizeof(Card) * W, cudaMemcpyDeviceToHost, ctx->stream) != cudaSuccess ||
+                    cudaStreamSynchronize(ctx->stream) != cudaSuccess))
+            rc = fail(ctx, CTOX_INVALID_STATE, "tp: peer exchange failed (download)");
         cudaFree(dev);
     }
     if (rc) {
@@ -204,10 +233,13 @@ ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
     // every rank must take the same path: agree through one more exchange
     int agree = ok ? 1 : 0, *agree_dev = nullptr, votes[kTpMaxWorld] = {0};
     if (cudaMalloc((void **)&agree_dev, sizeof(int) * (W + 1)) == cudaSuccess) {
-        cudaMemcpyAsync(agree_dev + W, &agree, sizeof(int), cudaMemcpyHostToDevice, ctx->stream);
-        if (!tp_all_gather(ctx, agree_dev + W, agree_dev, sizeof(int))) {
-            cudaMemcpyAsync(votes, agree_dev, sizeof(int) * W, cudaMemcpyDeviceToHost, ctx->stream);
-            cudaStreamSynchronize(ctx->stream);
+        // a failed copy leaves the votes at zero: every rank then falls back to NCCL together
+        if (cudaMemcpyAsync(agree_dev + W, &agree, sizeof(int), cudaMemcpyHostToDevice, ctx->stream) == cudaSuccess &&
+            !tp_all_gather(ctx, agree_dev + W, agree_dev, sizeof(int))) {
+            int got[kTpMaxWorld] = {0};
+            if (cudaMemcpyAsync(got, agree_dev, sizeof(int) * W, cudaMemcpyDeviceToHost, ctx->stream) == cudaSuccess &&
+                cudaStreamSynchronize(ctx->stream) == cudaSuccess)
+                memcpy(votes, got, sizeof(int) * W);
         }
         cudaFree(agree_dev);
     }
@@ -223,7 +255,8 @@ void tp_peer_destroy(ctox_ctx *ctx) {
     if (!tp) return;
     cudaStreamSynchronize(ctx->stream);
     for (uint32_t r = 0; r < tp->world; ++r)
-        if (r != tp->rank && tp->peer_recv[r]) cudaIpcCloseMemHandle(tp->peer_recv[r]);
+        if (!tp->sink && r != tp->rank && tp->peer_recv[r]) cudaIpcCloseMemHandle(tp->peer_recv[r]);
+    if (tp->sink) cudaFree(tp->sink);
     if (tp->recv) cudaFree(tp->recv);
     delete tp;
     ctx->tp_peer = nullptr;
@@ -244,7 +277,7 @@ ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uin
     TpPeerPtrs pp{};
     for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
     launch_pdl(k_tp_reduce_residual, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, o, h, pp, tp->recv + parity_off,
-               tp->elems, tp->rank, tp->world, seq, rows, sumsq, ctx->dev_error);
+               tp->elems, tp->rank, tp->world, seq, rows, sumsq, ctx->dev_error, ctx->wait_limit_cycles);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
@@ -287,9 +320,27 @@ ctox_status ctox_tp_init(ctox_ctx *ctx, const char *nccl_path, int32_t rank, int
     return CTOX_OK;
 }
 
+ctox_status ctox_tp_debug_silent_peers(ctox_ctx *ctx, int32_t world, uint64_t wait_limit_cycles) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    if (world < 2 || world > (int32_t)kTpMaxWorld) return fail(ctx, CTOX_SHAPE, "silent peers: world %d", world);
+    if (ctx->nccl_comm || ctx->tp_world > 1) return fail(ctx, CTOX_INVALID_STATE, "tp: the context already belongs to a group");
+    ctx->tp_rank = 0;
+    ctx->tp_world = world;
+    ctx->tp_silent = true;
+    if (wait_limit_cycles) ctx->wait_limit_cycles = (long long)wait_limit_cycles;
+    return CTOX_OK;
+}
+
+ctox_status ctox_tp_collective(const ctox_ctx *ctx, const char **name) {
+    if (!ctx || !name) return CTOX_INVALID_STATE;
+    *name = ctx->tp_world <= 1 ? "none" : (ctx->tp_peer ? "p2p_push" : "nccl");
+    return CTOX_OK;
+}
+
 ctox_status ctox_tp_destroy(ctox_ctx *ctx) {
     if (!ctx) return CTOX_OK;
     tp_peer_destroy(ctx);
+    ctx->tp_silent = false;
     if (ctx->nccl_comm) {
         cudaStreamSynchronize(ctx->stream);
         g_nccl.CommDestroy(ctx->nccl_comm);

@@ -3,8 +3,9 @@ C ABI: load / warmup / prefill / decode / commit_speculative / reset_session / u
 
 ``decode`` returns the device-resolved form of a speculative block (engine.rs:110-116,
 ``ResolvedGreedyMtpVerification``): proposed and verified draft counts, the accepted draft tokens
-and the next token. The state is committed on the device for exactly that prefix, so
-``commit_speculative`` only checks that the engine agrees.
+and the next token. The state is committed on the device for exactly that prefix and the block
+stays pending until ``commit_speculative`` names the same depth (the library refuses any other).
+Every call that the trait gives a ``CancellationToken`` takes one here (engine.rs:364-377).
 """
 from __future__ import annotations
 
@@ -16,6 +17,26 @@ import numpy as np
 
 from . import _native as N
 from .backend import B200Backend, FusedMatVec, _marshal
+
+
+class CancellationToken:
+    """engine.rs:364-377: a flag another thread may raise; the library reads it between passes."""
+
+    def __init__(self):
+        self._word = C.c_int32(0)
+
+    def cancel(self) -> None:
+        self._word.value = 1
+
+    def is_cancelled(self) -> bool:
+        return self._word.value != 0
+
+    def _ptr(self):
+        return C.cast(C.byref(self._word), C.c_void_p)
+
+
+def _cancel_ptr(token: Optional["CancellationToken"]):
+    return token._ptr() if token is not None else None
 
 
 def qwen38_27b_config(**overrides) -> N.ModelConfig:
@@ -57,7 +78,6 @@ class B200Executor:
         handle = C.c_void_p()
         backend._check(self._lib.ctox_exec_create(backend._ctx, C.byref(config), C.byref(handle)))
         self._h = handle
-        self._pending: Optional[int] = None
 
     # -- load ------------------------------------------------------------------------------
     def load_matrix(self, layer: int, tensor: int, op: FusedMatVec) -> None:
@@ -77,21 +97,27 @@ class B200Executor:
     def warmup(self) -> None:
         self._b._check(self._lib.ctox_exec_warmup(self._h))
 
-    def prefill(self, tokens: Sequence[int]) -> None:
+    def prefill(self, tokens: Sequence[int], cancellation: Optional[CancellationToken] = None) -> None:
         t = np.ascontiguousarray(tokens, dtype=np.uint32)
-        self._b._check(self._lib.ctox_exec_prefill(self._h, t.ctypes.data_as(C.c_void_p), t.size))
+        self._b._check(self._lib.ctox_exec_prefill(self._h, t.ctypes.data_as(C.c_void_p), t.size,
+                                                   _cancel_ptr(cancellation)))
 
     def prefill_synthetic(self, n: int, seed: int = 0) -> None:
         self._b._check(self._lib.ctox_exec_prefill_synthetic(self._h, n, seed))
 
     def decode(self, token: int, mtp_enabled: bool = True, temperature: float = 0.0, seed: int = 0,
-               force_accept: int = -1) -> GeneratedBlock:
+               force_accept: int = -1, cancellation: Optional[CancellationToken] = None,
+               commit: bool = True) -> GeneratedBlock:
+        """One decode call. ``commit=True`` (the default) confirms the device-resolved prefix
+        right away, which is what ``Engine::decode`` does with a resolved block (engine.rs:583-640);
+        ``commit=False`` leaves the block pending for an explicit ``commit_speculative``."""
         step = N.ExecStep()
         self._b._check(self._lib.ctox_exec_decode(self._h, token, int(mtp_enabled),
                                                   C.c_float(temperature), seed, force_accept,
-                                                  C.byref(step)))
-        self._pending = step.n_accepted
+                                                  _cancel_ptr(cancellation), C.byref(step)))
         k = step.proposed_drafts
+        if commit and k > 0:
+            self.commit_speculative(step.n_accepted, cancellation)
         return GeneratedBlock(
             token_id=step.next_token, draft_tokens_proposed=k,
             draft_tokens_verified=step.verified_drafts,
@@ -99,12 +125,15 @@ class B200Executor:
             draft_tokens=[int(x) for x in step.draft_tokens[:k]],
             target_tokens=[int(x) for x in step.target_tokens[:k + 1]])
 
-    def commit_speculative(self, accepted_drafts: int) -> None:
-        if self._pending is None:
-            raise N.CtoxError(6, "executor has no pending speculative branch")
-        if accepted_drafts != self._pending:
-            raise N.CtoxError(6, "accepted MTP depth differs from the device-resolved prefix")
-        self._pending = None
+    def commit_speculative(self, accepted_drafts: int,
+                           cancellation: Optional[CancellationToken] = None) -> None:
+        self._b._check(self._lib.ctox_exec_commit_speculative(self._h, accepted_drafts,
+                                                              _cancel_ptr(cancellation)))
+
+    def session_state(self) -> dict:
+        pending, poisoned = C.c_int32(), C.c_int32()
+        self._b._check(self._lib.ctox_exec_session_state(self._h, C.byref(pending), C.byref(poisoned)))
+        return {"pending_accepted": pending.value, "poisoned": bool(poisoned.value)}
 
     def reset_session(self) -> None:
         self._b._check(self._lib.ctox_exec_reset_session(self._h))
@@ -133,6 +162,25 @@ class B200Executor:
         out = np.zeros(self.config.vocab_size // self._b.tp_world, dtype=np.float32)
         self._b._check(self._lib.ctox_exec_last_logits(self._h, position,
                                                        out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def last_mtp_hidden(self) -> np.ndarray:
+        """[pairs][hidden]: the MTP layer's final hidden of every pair the last decode ran."""
+        n = C.c_uint32()
+        self._b._check(self._lib.ctox_exec_last_mtp_hidden(self._h, 0, None, C.byref(n)))
+        out = np.zeros((n.value, self.config.hidden_size), dtype=np.float32)
+        for i in range(n.value):
+            self._b._check(self._lib.ctox_exec_last_mtp_hidden(self._h, i, out[i].ctypes.data_as(C.c_void_p), None))
+        return out
+
+    def last_draft_logits(self) -> np.ndarray:
+        """[drafts][rows of the draft head]: the logits every draft of the last decode was taken from."""
+        rows, n = C.c_uint32(), C.c_uint32()
+        self._b._check(self._lib.ctox_exec_last_draft_logits(self._h, 0, None, C.byref(rows), C.byref(n)))
+        out = np.zeros((n.value, rows.value), dtype=np.float32)
+        for i in range(n.value):
+            self._b._check(self._lib.ctox_exec_last_draft_logits(self._h, i, out[i].ctypes.data_as(C.c_void_p),
+                                                                 None, None))
         return out
 
     def select_target_token(self, temperature: float, top_k: int, top_p: float, draw: float,

@@ -129,6 +129,16 @@ ctox_status ctox_tp_init(ctox_ctx *ctx, const char *nccl_path, int32_t rank, int
 ctox_status ctox_tp_destroy(ctox_ctx *ctx);
 /* Sum of an fp32 device buffer over the group, in place (the collective the executor uses). */
 ctox_status ctox_tp_all_reduce_f32(ctox_ctx *ctx, float *buf_dev, uint64_t n);
+/* Which collective sums the column-split projections: "none" (one GPU), "p2p_push" (one-shot
+ * all-reduce through peer memory, set up at warmup) or "nccl" (the fall-back). Static string. */
+ctox_status ctox_tp_collective(const ctox_ctx *ctx, const char **name);
+/* Failure-detection test support (no counterpart in the reference): makes the context rank 0 of a
+ * group of `world` ranks whose other ranks never answer, without NCCL or a second GPU, and sets the
+ * limit of the bounded device waits on a peer (SM clock cycles; 0 keeps the default of ~1 s). An
+ * executor created afterwards holds rank 0's shard; its first group sum runs out of time, the
+ * kernels set the device error word and return, and the call reports CTOX_INVALID_STATE. Nothing
+ * hangs: every later wait of the same call is skipped once the word is set. */
+ctox_status ctox_tp_debug_silent_peers(ctox_ctx *ctx, int32_t world, uint64_t wait_limit_cycles);
 /* Never NULL; empty when no call has failed. ctx may be NULL (creation errors). */
 const char *ctox_last_error_message(const ctox_ctx *ctx);
 /* Bytes of device memory currently owned through this context
@@ -291,7 +301,7 @@ ctox_status ctox_sample_topk_topp(ctox_ctx *ctx, const float *logits_dev, uint32
  * draws keyed by (seed, step) - no counterpart in the reference. vocab limits
  * selection to the first `vocab` rows (0 = all rows). logits_out_dev (may be
  * NULL): [n_nodes][rows] materialised logits for evidence paths. The weight
- * matrix is streamed once per four positions. Synchronises; one small
+ * matrix is streamed once per pass of up to sixteen positions. Synchronises; one small
  * device-to-host read, like backend/cuda_runtime.rs:2707-2726. */
 ctox_status ctox_lmhead_verify(ctox_matvec *lm_head, const void *hidden_dev, uint32_t hidden_dtype,
                                uint64_t hidden_stride, uint32_t n_nodes, const int32_t *parent,
@@ -376,19 +386,50 @@ ctox_status ctox_exec_fill_synthetic(ctox_exec *exec, uint64_t seed, float scale
 /* warmup(): checks that every tensor is present and builds launch plans. */
 ctox_status ctox_exec_warmup(ctox_exec *exec);
 ctox_status ctox_exec_reset_session(ctox_exec *exec);
+/* Cancellation (engine.rs:364-377 CancellationToken = Arc<AtomicBool>): `cancel` points to a
+ * word another thread may set to non-zero at any time, or is NULL. It is read on the host at
+ * entry and between passes; a call that sees it returns CTOX_CANCELLED (error.rs:5-29). A
+ * cancelled decode leaves the session as it was before the call; a cancelled prefill leaves no
+ * usable session (reset_session or a new prefill). */
+
 /* prefill(): runs the tokens through the target (and the MTP cache) in chunks;
  * the last token is NOT consumed: it is the input of the first decode. */
-ctox_status ctox_exec_prefill(ctox_exec *exec, const uint32_t *tokens, uint64_t n);
+ctox_status ctox_exec_prefill(ctox_exec *exec, const uint32_t *tokens, uint64_t n,
+                              const volatile int32_t *cancel);
 /* Benchmark prefill: fills `n` cache positions with random K/V ~ N(0,1) and random
  * recurrent state instead of running the model, and sets the position. */
 ctox_status ctox_exec_prefill_synthetic(ctox_exec *exec, uint64_t n, uint64_t seed);
 /* decode(): consumes `token` at the current position. With mtp_enabled, drafts
  * max_draft_tokens tokens, verifies them in one target pass and resolves the
  * acceptance on the device (temperature 0: engine.rs:939-962). The state is
- * committed for the accepted prefix before returning. force_accept >= 0 accepts
- * exactly that many drafts regardless of the target (throughput buckets). */
+ * committed on the device for the accepted prefix before returning, and the block
+ * stays pending until ctox_exec_commit_speculative confirms it (a second decode
+ * before that is CTOX_INVALID_STATE, like decoder.rs:1293-1297). force_accept >= 0
+ * accepts exactly that many drafts regardless of the target (throughput buckets).
+ *
+ * The three forms of ExecutorStep (engine.rs:77-150,240-319) map onto the result so:
+ *  - resolved (ResolvedGreedyMtpVerification): proposed_drafts, verified_drafts,
+ *    accepted_draft_tokens[0..n_accepted), next_token: the form this executor reports;
+ *  - compact (GreedyMtpVerification): draft_tokens[0..k), target_tokens[0..k) and
+ *    bonus_token = target_tokens[k], k = proposed_drafts;
+ *  - logit form: with ctox_exec_keep_logits on, target_logits / target_verification_logits[i] /
+ *    bonus_logits are ctox_exec_last_logits(i) for i = 0 / 0..k-1 / k, and the restricted
+ *    draft distributions are ctox_exec_last_draft_logits(i) over the draft id table.
+ * A device error (a bounded wait that ran out, a non-finite scale) invalidates the session:
+ * every later call fails with CTOX_INVALID_STATE until ctox_exec_reset_session or a prefill
+ * (engine.rs:594-611). */
 ctox_status ctox_exec_decode(ctox_exec *exec, uint32_t token, int32_t mtp_enabled, float temperature,
-                             uint64_t seed, int32_t force_accept, ctox_exec_step *step);
+                             uint64_t seed, int32_t force_accept, const volatile int32_t *cancel,
+                             ctox_exec_step *step);
+/* commit_speculative() (engine.rs:322-362, decoder.rs:1396-1458): resolves the branch an MTP
+ * decode left pending. accepted_drafts must equal the n_accepted the decode reported: the
+ * device already holds exactly that state; any other depth is CTOX_INVALID_STATE, as is a call
+ * with no pending branch. */
+ctox_status ctox_exec_commit_speculative(ctox_exec *exec, uint32_t accepted_drafts,
+                                         const volatile int32_t *cancel);
+/* pending_accepted: -1, or the accepted depth of the block awaiting commit_speculative;
+ * poisoned: 1 after a device error until reset_session. Either pointer may be NULL. */
+ctox_status ctox_exec_session_state(const ctox_exec *exec, int32_t *pending_accepted, int32_t *poisoned);
 ctox_status ctox_exec_position(const ctox_exec *exec, uint64_t *position);
 /* Final hidden state of the last committed position (device -> host), for parity tests. */
 ctox_status ctox_exec_last_hidden(ctox_exec *exec, float *out);
@@ -396,6 +437,15 @@ ctox_status ctox_exec_last_hidden(ctox_exec *exec, float *out);
  * enabled with ctox_exec_keep_logits). */
 ctox_status ctox_exec_keep_logits(ctox_exec *exec, int32_t enable);
 ctox_status ctox_exec_last_logits(ctox_exec *exec, uint32_t position, float *out);
+/* Evidence of the MTP layer (decoder.rs:1009-1046), kept while ctox_exec_keep_logits is on: the
+ * final hidden state (after mtp.norm) of every (token, previous hidden) pair the last decode ran,
+ * in order (first the pairs of the previous block with the target's own hidden states, then the
+ * chained drafts), and the logits of draft `draft` over the rows of the draft head (the draft id
+ * table's entries on this rank, or the vocabulary shard when draft_vocab is 0). `count` receives
+ * how many are held; `out` may be NULL to query the counts only. */
+ctox_status ctox_exec_last_mtp_hidden(ctox_exec *exec, uint32_t index, float *out, uint32_t *count);
+ctox_status ctox_exec_last_draft_logits(ctox_exec *exec, uint32_t draft, float *out, uint32_t *rows,
+                                        uint32_t *count);
 /* ModelExecutor::select_target_token (engine.rs:322-362): samples the target token of verify
  * position `position` of the last decode call from the logits the executor kept on the device
  * (ctox_exec_keep_logits must be on), with the same rules as ctox_sample_topk_topp. In a

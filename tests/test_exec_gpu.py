@@ -39,7 +39,6 @@ def test_plain_greedy_decode_matches_oracle(setup):
     tok, got = PROMPT[-1], []
     for i in range(n_new):
         blk = ex.decode(tok, mtp_enabled=False)
-        ex.commit_speculative(0)
         assert blk.draft_tokens_proposed == 0 and blk.accepted_draft_tokens == []
         err = rel_l2(ex.last_logits(0), exp_logits[i])
         assert err <= 1e-3, (i, err)
@@ -56,7 +55,8 @@ def test_mtp_greedy_emits_the_same_sequence(setup):
     ex.prefill(PROMPT)
     tok, got, proposed, accepted = PROMPT[-1], [], 0, 0
     while len(got) < n_new:
-        blk = ex.decode(tok, mtp_enabled=True)
+        blk = ex.decode(tok, mtp_enabled=True, commit=False)
+        assert ex.session_state()["pending_accepted"] == len(blk.accepted_draft_tokens)
         ex.commit_speculative(len(blk.accepted_draft_tokens))
         assert blk.draft_tokens_proposed == 4
         # engine.rs:118-136
@@ -167,3 +167,77 @@ def test_select_target_token_samples_from_the_kept_logits(setup, orc):
     with pytest.raises(ctox.CtoxError) as e:
         ex.select_target_token(0.8, 0, 0.9, 0.5)
     assert e.value.kind == "UnsupportedOperation"
+
+
+def test_speculative_transaction_and_cancellation(setup):
+    """trait ModelExecutor (engine.rs:322-377): a pending block must be committed with the depth the
+    device resolved before the next decode; a raised cancellation token fails the call with
+    Cancelled and leaves a decode's session untouched."""
+    be, ex, model = setup
+    ex.prefill(PROMPT)
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.commit_speculative(0)  # decoder.rs:1401-1403: nothing pending
+    assert e.value.kind == "InvalidState"
+    blk = ex.decode(PROMPT[-1], mtp_enabled=True, force_accept=2, commit=False)
+    assert ex.session_state() == {"pending_accepted": 2, "poisoned": False}
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.decode(blk.token_id, mtp_enabled=True)  # decoder.rs:1293-1297
+    assert e.value.kind == "InvalidState" and "committed" in str(e.value)
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.commit_speculative(1)  # not the prefix the device holds
+    assert e.value.kind == "InvalidState"
+    token = ctox.CancellationToken()
+    token.cancel()
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.commit_speculative(2, token)
+    assert e.value.kind == "Cancelled"
+    ex.commit_speculative(2)
+    assert ex.session_state()["pending_accepted"] == -1
+    # a cancelled decode changes nothing: the same call without the token gives the oracle's token
+    position = ex.position()
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.decode(blk.token_id, mtp_enabled=True, cancellation=token)
+    assert e.value.kind == "Cancelled" and ex.position() == position
+    seq = PROMPT + blk.accepted_draft_tokens + [blk.token_id]
+    model.reset()
+    for t in seq[:-1]:
+        model.decode_target_step(int(t))
+    _, logits = model.decode_target_step(int(seq[-1]))
+    nxt = ex.decode(blk.token_id, mtp_enabled=True)
+    assert nxt.emitted[0] == model.orc.greedy_token(logits)
+    with pytest.raises(ctox.CtoxError) as e:
+        ex.prefill(PROMPT, token)
+    assert e.value.kind == "Cancelled"
+
+
+def test_a_peer_that_never_answers_runs_out_the_bounded_wait_and_poisons_the_session(orc):
+    """Failure detection without a fault: rank 0 of a two-rank group whose peer never pushes its
+    partial sums (host-side set-up, one GPU, no NCCL). The group sum waits for at most the limit
+    given here (~10 ms), sets the device error word and returns; the decode call reports
+    InvalidState, the session is poisoned until reset_session (engine.rs:594-611), and the context
+    stays usable."""
+    import time
+    be = ctox.B200Backend(0)
+    be.tp_debug_silent_peers(2, wait_limit_cycles=20_000_000)
+    cfg = tiny_config(num_attention_heads=8, linear_num_key_heads=2, linear_num_value_heads=4)
+    model = OracleModel(orc, cfg, seed=3)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex, rank=0, world=2)
+        ex.warmup()
+        assert be.tp_collective() == "p2p_push"
+        t0 = time.time()
+        with pytest.raises(ctox.CtoxError) as e:
+            ex.prefill(PROMPT)
+        assert e.value.kind == "InvalidState" and "wait" in str(e.value)
+        assert time.time() - t0 < 5.0, "later waits of the same call must be skipped"
+        assert ex.session_state()["poisoned"]
+        with pytest.raises(ctox.CtoxError) as e:
+            ex.decode(5, mtp_enabled=False)
+        assert e.value.kind == "InvalidState" and "reset_session" in str(e.value)
+        ex.reset_session()
+        assert not ex.session_state()["poisoned"]
+        assert be.device_error() == 0  # cleared: the context is usable again
+    finally:
+        ex.unload()
+        be.close()

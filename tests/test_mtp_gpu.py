@@ -1,0 +1,117 @@
+"""GPU parity of the MTP draft path (decoder.rs:1009-1113 and the device feeding rule
+backend/cuda_graph.rs:4258-4262) against the oracle restatement (oracle_model.DeviceChainOracle,
+itself pinned to the reference CPU executor's restatement in test_oracle_model.py).
+
+Per speculative block: the MTP layer's final hidden of EVERY pair the device ran (the catch-up
+pairs with true target hiddens, then the chained drafts) within rel-L2 1e-3; the draft logits
+within rel-L2 1e-3; every draft token equal to the oracle's (or, where the oracle's top two draft
+logits lie within 1e-4 of each other relative to their size, either of the two: the oracle then
+follows the device's token so that the comparison stays aligned); the accepted count, the emitted
+tokens and the committed final hidden equal. The model's lm_head has two loud rows so that
+unforced acceptance is non-zero; forced acceptance depths cover the catch-up pass over 1..4 pairs.
+"""
+import numpy as np
+import pytest
+
+import ctox_llm_b200 as ctox
+from gpu_util import rel_l2
+from oracle_model import DeviceChainOracle, OracleModel, tiny_config
+
+pytestmark = pytest.mark.gpu
+
+PROMPT = [5, 17, 900, 3, 3, 41, 512, 77, 1001, 64, 9]
+LOUD = (3, 17)
+FORCE = [-1, 2, -1, 0, 3, 1, -1, -1, 3, -1, 2, -1]  # -1: the target decides
+
+
+def near_tie(logits, a, b):
+    return abs(float(logits[a]) - float(logits[b])) <= 1e-4 * max(abs(float(logits[a])), abs(float(logits[b])), 1e-6)
+
+
+def run_blocks(orc, cfg, draft_ids, seed):
+    be = ctox.B200Backend(0)
+    model = OracleModel(orc, cfg, seed=seed, loud_tokens=LOUD)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex)
+        if draft_ids is not None:
+            ex.load_vector(ctox.native.LAYER_GLOBAL, ctox.native.T_DRAFT_IDS, draft_ids.astype(np.uint32))
+        ex.warmup()
+        ex.keep_logits(True)
+        k = cfg.max_draft_tokens
+        dev = DeviceChainOracle(model, k, draft_ids)
+        ex.prefill(PROMPT)
+        dev.prefill(PROMPT)
+        tok, natural_accepts, catch_up_sizes = PROMPT[-1], 0, set()
+        for block, force in enumerate(FORCE):
+            blk = ex.decode(tok, mtp_enabled=True, force_accept=force)
+            assert blk.draft_tokens_proposed == k
+            want = dev.decode(tok, force_accept=force, given_drafts=blk.draft_tokens)
+            got_h = ex.last_mtp_hidden()
+            assert got_h.shape[0] == len(want["mtp_hidden"]), (block, got_h.shape)
+            catch_up_sizes.add(got_h.shape[0] - (k - 1))
+            for j, (g, w) in enumerate(zip(got_h, want["mtp_hidden"])):
+                assert rel_l2(g, w) <= 1e-3, ("mtp hidden", block, j, rel_l2(g, w))
+            got_l = ex.last_draft_logits()
+            assert got_l.shape[0] == k
+            for i in range(k):
+                assert rel_l2(got_l[i][:want["draft_logits"][i].size], want["draft_logits"][i]) <= 1e-3, (block, i)
+                if blk.draft_tokens[i] != want["drafts"][i]:
+                    lg = want["draft_logits"][i]
+                    ids = draft_ids if draft_ids is not None else np.arange(cfg.vocab_size)
+                    a = int(np.searchsorted(ids, blk.draft_tokens[i]))
+                    b = int(np.searchsorted(ids, want["drafts"][i]))
+                    assert ids[a] == blk.draft_tokens[i] and near_tie(lg, a, b), \
+                        ("draft token", block, i, blk.draft_tokens, want["drafts"])
+            assert blk.accepted_draft_tokens == want["accepted"], (block, blk, want["accepted"])
+            assert blk.token_id == want["next_token"], (block, blk.token_id, want["next_token"])
+            assert blk.target_tokens[:len(want["target_tokens"])] == want["target_tokens"]
+            assert rel_l2(ex.last_hidden(), want["final_hidden"]) <= 1e-3
+            if force < 0:
+                natural_accepts += len(blk.accepted_draft_tokens)
+            tok = blk.token_id
+        assert natural_accepts > 0, "no draft was accepted on the target's own decision"
+        assert {1, 2, 3, 4} <= catch_up_sizes, catch_up_sizes
+    finally:
+        ex.unload()
+        assert be.allocated_bytes() == 0
+        be.close()
+
+
+def test_mtp_hiddens_drafts_and_acceptance_match_the_oracle_full_vocabulary_head(orc):
+    run_blocks(orc, tiny_config(max_draft_tokens=3), None, seed=7)
+
+
+def test_mtp_with_the_restricted_draft_head_on_one_gpu(orc):
+    cfg = tiny_config(max_draft_tokens=3, draft_vocab=258)
+    ids = np.sort(np.random.default_rng(11).choice(cfg.vocab_size, 256, replace=False))
+    ids = np.union1d(ids, LOUD)
+    cfg.draft_vocab = int(ids.size)
+    run_blocks(orc, cfg, ids, seed=7)
+
+
+def test_mtp_with_four_drafts_and_bf16_cache(orc):
+    """Five verify positions (two n-tiles in the matvec) and the tensor-core attention kernel."""
+    cfg = tiny_config(max_draft_tokens=4, num_attention_heads=4, num_key_value_heads=1, head_dim=256,
+                      rotary_dim=64, kv_dtype=ctox.BF16, max_context_tokens=512)
+    be = ctox.B200Backend(0)
+    model = OracleModel(orc, cfg, seed=5, loud_tokens=LOUD)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex)
+        ex.warmup()
+        ex.keep_logits(True)
+        dev = DeviceChainOracle(model, 4, None)
+        ex.prefill(PROMPT)
+        dev.prefill(PROMPT)
+        tok = PROMPT[-1]
+        for block, force in enumerate([-1, 4, 1, -1, 0, -1]):
+            blk = ex.decode(tok, mtp_enabled=True, force_accept=force)
+            want = dev.decode(tok, force_accept=force, given_drafts=blk.draft_tokens)
+            for j, (g, w) in enumerate(zip(ex.last_mtp_hidden(), want["mtp_hidden"])):
+                assert rel_l2(g, w) <= 1e-3, (block, j)
+            assert blk.accepted_draft_tokens == want["accepted"] and blk.token_id == want["next_token"]
+            tok = blk.token_id
+    finally:
+        ex.unload()
+        be.close()

@@ -43,6 +43,38 @@ def test_static_scratch_dispatch_matches_ordinary_dispatch_twice():
                 assert be.allocated_bytes() == before, "the static dispatch must not allocate"
             finally:
                 mv.destroy()
+        # The places where the built-in array is shared more than once per call: every part of a
+        # mixed Q2/Q4 matrix uses the same fragment and partial-sum regions; 16 positions run as
+        # two passes through them; bf16 activations take the other input path; and two different
+        # handles called back to back leave each other's contents behind.
+        columns = 512
+        q2 = synthetic.packed_weights(ctox.Q2B64, 96, columns, 94)
+        q4 = synthetic.packed_weights(ctox.Q4B64, 160, columns, 95)
+        segs = [ctox.Segment(0, ctox.Q2B64, 0, 96, 0, q2.size),
+                ctox.Segment(1, ctox.Q4B64, 96, 256, q2.size, q4.size)]
+        mixed = be.prepare_fused_matvec(ctox.FusedMatVec(
+            ctox.MIXED_Q2Q4B64, np.concatenate([q2, q4]), 256, columns, None, segments=segs,
+            s_in=synthetic.recovery_scales_f16(columns, 94, 3), s_out=synthetic.recovery_scales_f16(256, 94, 4)))
+        pure = be.prepare_fused_matvec(ctox.FusedMatVec(
+            ctox.Q4B64, synthetic.packed_weights(ctox.Q4B64, 320, columns, 96), 320, columns, None))
+        try:
+            before = be.allocated_bytes()
+            for call, (positions, bf16) in enumerate(((16, False), (3, True), (16, True), (9, False))):
+                x = torch.from_numpy(synthetic.activations(columns, 97 + call, positions=positions)
+                                     .reshape(positions, columns)).cuda()
+                xd, dt = (x.to(torch.bfloat16), ctox.BF16) if bf16 else (x, ctox.F32)
+                for mv, rows in ((mixed, 256), (pure, 320), (mixed, 256)):  # handles interleaved
+                    want = torch.empty(positions, rows, device="cuda")
+                    got = torch.full((positions, rows), float("nan"), device="cuda")
+                    torch.cuda.synchronize()
+                    mv.dispatch_device(xd.data_ptr(), dt, positions, columns, want.data_ptr(), rows)
+                    mv.dispatch_static(xd.data_ptr(), dt, positions, columns, got.data_ptr(), rows)
+                    be.synchronize()
+                    assert torch.equal(got, want), (positions, bf16, rows)
+            assert be.allocated_bytes() == before, "the static dispatch must not allocate"
+        finally:
+            mixed.destroy()
+            pure.destroy()
         # an operation whose scratch exceeds the built-in array is refused with a clear error
         rows, columns = 262144, 512
         big = be.prepare_fused_matvec(ctox.FusedMatVec(
