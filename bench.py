@@ -34,8 +34,31 @@ REPLICAS = 8
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one k_matvec_stream launch over its algorithmic
-# bytes, from the ncu capture summarised in profiles/ (47.3907 MB for 47.3498 MB).
-NCU_TRAFFIC_RATIO = 47.3907 / 47.3498
+# bytes: read from the committed ncu summary of the kernel (the line "dram bytes per algorithmic byte").
+TRAFFIC_PROFILE = "profiles/k_matvec_stream_q4_17408x5120.md"
+
+
+def load_traffic_ratio():
+    import re
+    try:
+        with open(os.path.join(ROOT, TRAFFIC_PROFILE)) as f:
+            m = re.search(r"dram bytes per algorithmic byte:\s*([0-9.]+)", f.read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
+
+
+def roofline_report(phase, elapsed_s, accepted_tokens, bytes_read, bytes_written, flops, bandwidth,
+                    theoretical_bandwidth=None, compute=1383.2e12, dispatch_floor_s=0.0):
+    """The reference's roofline gate record for this run (src/roofline.rs:82-142)."""
+    from ctox_llm_b200.roofline import RooflineMeasurement
+    return RooflineMeasurement(
+        hardware_profile="cuda-sm100a-b200", phase=phase, traffic_source="exact_tensor_schedule",
+        elapsed_seconds=elapsed_s, accepted_tokens=accepted_tokens, bytes_read=int(bytes_read),
+        bytes_written=int(bytes_written), floating_point_operations=flops,
+        sustainable_bandwidth_bytes_per_second=bandwidth, sustainable_compute_flops_per_second=compute,
+        dispatch_floor_seconds=dispatch_floor_s, theoretical_bandwidth_bytes_per_second=theoretical_bandwidth,
+        theoretical_compute_flops_per_second=2250e12 if theoretical_bandwidth else None).evaluate()
 
 
 def load_peaks():
@@ -113,6 +136,65 @@ def cpu_baseline(threads: int, avx2: bool, repeats: int):
         oracle.fused_matvec(op, threads=threads, avx2=avx2)
         times.append(time.perf_counter() - t0)
     return ALGO_BYTES / statistics.median(times) / 1e9, statistics.median(times)
+
+
+
+BLOCK_BYTES = {"q4": 34, "q2": 18}
+
+
+def matvec_algo_bytes(dtype, rows, cols, positions=1):
+    """Packed weights once + activations in + outputs out (f32), as BASELINE.md section 3 counts them."""
+    return rows * (cols // 64) * BLOCK_BYTES[dtype] + positions * (cols + rows) * 4
+
+
+def measure_matvec(be, stream, local, dtype, rows, cols, positions, steps, warmup=20, static=False):
+    """Device-resident timing of one prepared matvec shape: `steps` dispatches over enough weight
+    replicas to exceed twice the L2, CUDA events around the whole loop (launches overlap through
+    programmatic dependent launch, as in a decode pass) and an event pair around every launch of the
+    streaming kernel (serialised: the figure the roofline fraction uses)."""
+    import torch
+    import ctox_llm_b200 as ctox
+    from ctox_llm_b200 import synthetic
+    dt = ctox.Q4B64 if dtype == "q4" else ctox.Q2B64
+    wbytes = rows * (cols // 64) * BLOCK_BYTES[dtype]
+    n_rep = max(2, min(16, -(-300_000_000 // wbytes)))
+    reps = [be.prepare_fused_matvec(ctox.FusedMatVec(dt, synthetic.packed_weights(dt, rows, cols, seed=100 + r),
+                                                     rows, cols, None)) for r in range(n_rep)]
+    x = torch.from_numpy(synthetic.activations(cols, 0, positions=positions).reshape(positions, cols)).cuda(local)
+    y = torch.empty(positions, rows, dtype=torch.float32, device=f"cuda:{local}")
+    torch.cuda.synchronize()
+
+    def step(i):
+        if static:
+            reps[i % n_rep].dispatch_static(x.data_ptr(), ctox.F32, positions, cols, y.data_ptr(), rows)
+        else:
+            reps[i % n_rep].dispatch_device(x.data_ptr(), ctox.F32, positions, cols, y.data_ptr(), rows)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(steps):
+        step(i)
+    ev1.record(stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    be.kernel_timing(True)
+    for i in range(steps):
+        step(i)
+    kernel_ms, launches = be.kernel_timing_read()
+    be.kernel_timing(False)
+    for r in reps:
+        r.destroy()
+    peak, peak_kind = load_peaks()
+    algo = matvec_algo_bytes(dtype, rows, cols, positions)
+    kernel_us = kernel_ms / max(launches, 1) * 1e3 * (launches / steps)  # all passes of one dispatch
+    return {"shape": f"{dtype} {rows}x{cols} x{positions}", "algo_bytes": algo, "replicas": n_rep,
+            "us_per_dispatch": ms / steps * 1e3, "gbs": algo / (ms / steps * 1e-3) / 1e9,
+            "kernel_us": kernel_us, "kernel_gbs": algo / (kernel_us * 1e-6) / 1e9,
+            "frac": algo / (kernel_us * 1e-6) / 1e9 / peak, "frac_pipelined": algo / (ms / steps * 1e-3) / 1e9 / peak,
+            "peak_kind": f"of {peak_kind}"}
 
 
 def decode_workload_name(context, layers, drafts):
@@ -209,6 +291,57 @@ def launches_per_block(cfg, world=1):
     return target + mtp
 
 
+
+def tp_parity_check(be, local, rank, world, drafts):
+    """Outside the timed region: a 4-layer model of the full widths, sharded over the group, against
+    the same model unsharded on rank 0 (synthetic tensors are functions of the global index, so the
+    shards are slices of the one-GPU model). Real prefill of a short prompt, then speculative blocks:
+    every rank must resolve the same blocks as the unsharded run, and its vocabulary shard of the
+    logits must lie within rel-L2 1e-3 of the unsharded logits. Raises on mismatch."""
+    import torch
+    import torch.distributed as dist
+    import ctox_llm_b200 as ctox
+    cfg = ctox.qwen38_27b_config(max_context_tokens=512, num_hidden_layers=4, max_draft_tokens=drafts)
+    prompt = [int(t) for t in np.random.default_rng(5).integers(0, cfg.vocab_size, 21)]
+    n_blocks = 5
+
+    def run(backend):
+        ex = ctox.B200Executor(backend, cfg)
+        ex.fill_synthetic(seed=7)
+        ex.warmup()
+        ex.keep_logits(True)
+        ex.prefill(prompt)
+        tok, blocks, logits = prompt[-1], [], []
+        for _ in range(n_blocks):
+            blk = ex.decode(tok, mtp_enabled=True)
+            blocks.append((tuple(blk.draft_tokens), tuple(blk.accepted_draft_tokens), blk.token_id))
+            logits.append(ex.last_logits(0).copy())
+            tok = blk.token_id
+        ex.unload()
+        return blocks, logits
+
+    blocks, logits = run(be)
+    ref = [None, None]
+    if rank == 0:
+        solo = ctox.B200Backend(local)
+        ref = list(run(solo))
+        solo.close()
+    dist.broadcast_object_list(ref, src=0)
+    ref_blocks, ref_logits = ref
+    n = cfg.vocab_size // world
+    worst = 0.0
+    for got, want in zip(logits, ref_logits):
+        w = want[rank * n:(rank + 1) * n]
+        worst = max(worst, float(np.linalg.norm(got - w) / max(np.linalg.norm(w), 1e-30)))
+    ok = blocks == ref_blocks and worst <= 1e-3
+    flags = [None] * world
+    dist.all_gather_object(flags, (ok, worst, blocks == ref_blocks))
+    if not all(f[0] for f in flags):
+        raise SystemExit(f"tensor-parallel parity check failed: per rank (ok, logits rel-L2, blocks equal) = {flags}; "
+                         f"rank {rank} blocks {blocks} reference {ref_blocks}")
+    return {"tp_check": "green", "tp_check_blocks": n_blocks, "tp_check_logits_rel_l2_max": max(f[1] for f in flags)}
+
+
 def run_decode(args):
     """BASELINE config 4: random-init Qwen3.8-27B-shaped hybrid decode, Q4 attention/embedding and
     Q2 FFN weights, bf16 paged KV (16-token pages) prefilled to 32768 tokens with random K/V,
@@ -227,8 +360,10 @@ def run_decode(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     stream = torch.cuda.Stream(device=local)
     be = ctox.B200Backend(local, stream=stream.cuda_stream)
+    tp_report = {}
     if world > 1:  # tensor parallel: every rank holds 1/world of the heads, FFN width and vocabulary
         be.tp_init_from_torch()
+        tp_report = tp_parity_check(be, local, rank, world, args.drafts)
     context = args.context
     cfg = ctox.qwen38_27b_config(max_context_tokens=context + 4096)
     cfg.max_draft_tokens = args.drafts
@@ -255,6 +390,7 @@ def run_decode(args):
         ev0.record(stream)
         t0 = time.perf_counter()
         for _ in range(n_blocks):
+            # decode + commit_speculative: the two calls of the executor interface per block
             blk = ex.decode(tok, mtp_enabled=mtp, force_accept=force)
             tok = blk.token_id
             emitted += len(blk.emitted)
@@ -290,6 +426,15 @@ def run_decode(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, wall = float(t[0]), float(t[1])
     emitted, accepted = float(cnt[0]), float(cnt[1])
+    collective = be.tp_collective()
+    sub = {}
+    if rank == 0 and world == 1 and not args.quick:
+        # the other half of the headline metric in the same record: BASELINE config 0 (a) and (b)
+        ex.unload()
+        ex = None
+        sub["q4_matvec"] = measure_matvec(be, stream, local, "q4", Q4_ROWS, Q4_COLS, 1, 400)
+        sub["q2_matvec"] = measure_matvec(be, stream, local, "q2", 5120, 17408, 1, 400)
+    traffic_ratio = load_traffic_ratio()
     if rank == 0:
         peak, peak_kind = load_peaks()
         weights, kv, state = decode_config_bytes(cfg, context)
@@ -309,9 +454,10 @@ def run_decode(args):
             "config": {"workload": decode_workload_name(context, cfg.num_hidden_layers, cfg.max_draft_tokens),
                        "weights": "Q4_B64 attention/embedding, Q2_B64 FFN, random init",
                        "kv": "bf16, 16-token pages", "l2": "11.8 GB streamed per pass (>> 126 MB L2)",
-                       "parallelism": f"tp{world} (one sequence; heads, FFN width and vocabulary split, "
-                                      "NCCL all-reduce after every column-split projection)" if world > 1
-                                      else "single",
+                       "parallelism": f"tp{world} (one sequence; heads, FFN width and vocabulary split; partial "
+                                      f"results of every column-split projection summed by: {collective})"
+                                      if world > 1 else "single",
+                       "collective": collective,
                        "acceptance": "as measured on random-init weights"},
             "mean_accepted_drafts_per_block": accepted / args.steps,
             "tokens_per_s_without_mtp": plain,
@@ -321,22 +467,35 @@ def run_decode(args):
                          "frac": achieved / peak, "frac_of_8000_nominal": achieved / 8000.0,
                          "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (all launches of a block, per GPU)",
                          "bytes_per_block": stream_bytes, "launches_per_block": launches / blocks_timed,
-                         "traffic": stream_bytes * NCU_TRAFFIC_RATIO,
-                         "traffic_note": "per block; dram bytes of the ncu capture of one 47.35 MB launch "
-                                         "(47.39 MB read, 0 written) scaled by the bytes streamed"},
+                         "timing_note": "event pair around every launch: serialised, without the overlap of "
+                                        "dependent launches that the headline number has",
+                         "traffic": stream_bytes * traffic_ratio if traffic_ratio else None,
+                         "traffic_note": "per block; dram bytes per algorithmic byte of the ncu capture in "
+                                         f"{TRAFFIC_PROFILE} scaled by the bytes streamed"},
+            "roofline_gate": roofline_report(
+                "speculative_verify", elapsed_s=ms * 1e-3 / args.steps, accepted_tokens=emitted / args.steps,
+                bytes_read=(weights + kv + state // 2) // world + (stream_bytes - weights // world),
+                bytes_written=state // 2 // world, flops=0.0, bandwidth=peak * 1e9,
+                theoretical_bandwidth=8000e9),
             "pass_bytes": {"weights": weights, "kv": kv, "state": state},
             "cpu_baseline": {"value": cpu_tok_s, "unit": "tokens/s", "cores": 1, "kind": "port",
                              "sample": f"scalar-verifier matvec on one 17408x5120 Q4 matrix ({cpu_val:.3f} GB/s, "
                                        f"{cpu_s * 1e3:.0f} ms), scaled to the {(weights + kv + state) / 1e9:.1f} GB "
                                        "of one target pass"},
             "e2e": {"value": emitted / wall, "unit": "tokens/s",
-                    "h2d_bytes_per_step": 4 * (1 + 5), "d2h_bytes_per_step": 292,
-                    "note": "decode() takes a host token and returns a host record; same calls, wall clock"},
+                    # uploads per block: the token (4 B) and the tokens of the MTP catch-up pairs
+                    # (4 B per position committed by the previous block); read back: record + error word
+                    "h2d_bytes_per_step": 4 + 4 * (emitted / args.steps), "d2h_bytes_per_step": 292 + 4,
+                    "note": "decode() + commit_speculative() take a host token and return a host record; "
+                            "same calls, wall clock"},
             "gpu_launches": launches_per_block(cfg, world) * args.steps,
             "clocks": clocks,
         }
+        line.update(tp_report)
+        line.update(sub)
         print(json.dumps(line), flush=True)
-    ex.unload()
+    if ex is not None:
+        ex.unload()
     be.close()
     if world > 1:
         dist.destroy_process_group()
@@ -436,7 +595,7 @@ def run_b200(args):
                          "frac": achieved / peak, "frac_of_8000_nominal": achieved / 8000.0,
                          "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream<Q4>",
                          "kernel_us": kernel_ms / max(launches, 1) * 1e3,
-                         "traffic": ALGO_BYTES * NCU_TRAFFIC_RATIO},
+                         "traffic": ALGO_BYTES * load_traffic_ratio() if load_traffic_ratio() else None},
             "cpu_baseline": {"value": cpu_val, "unit": "GB/s", "cores": 1, "kind": "port",
                              "sample": f"whole 17408x5120 matvec, scalar-verifier arm, median of 5 "
                                        f"({cpu_s * 1e3:.1f} ms each)"},
@@ -454,13 +613,133 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+
+CONFIG1_LAYER = [  # BASELINE config 1 (q_proj with the interleaved gate rows, as the reference holds it)
+    ("q_proj", "q4", 12288, 5120), ("k_proj", "q4", 1024, 5120), ("v_proj", "q4", 1024, 5120),
+    ("o_proj", "q4", 5120, 6144), ("gate_proj", "q2", 17408, 5120), ("up_proj", "q2", 17408, 5120),
+    ("down_proj", "q2", 5120, 17408)]
+
+
+def run_micro(args):
+    """Single-kernel workloads on one GPU: `matvec` (any shape), `q2_matvec` (BASELINE config 0b),
+    `verify_layer` (config 1: the seven projections of one layer at M = 1, 2, 4, 8, 16 positions) and
+    `gated_delta` (config 2: 48 layers, T = 4 then T = 1). Inputs are resident in HBM; weights or
+    states are rotated over more than twice the L2."""
+    import torch
+    import ctox_llm_b200 as ctox
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    torch.cuda.set_device(local)
+    stream = torch.cuda.Stream(device=local)
+    be = ctox.B200Backend(local, stream=stream.cuda_stream)
+    peak, peak_kind = load_peaks()
+    sampler = ClockSampler(local)
+    sampler.start()
+    line = {"n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+    with torch.cuda.stream(stream):
+        if args.workload in ("matvec", "q2_matvec"):
+            dtype, rows, cols, pos = (("q2", 5120, 17408, 1) if args.workload == "q2_matvec"
+                                      else (args.dtype, args.rows, args.cols, args.positions))
+            r = measure_matvec(be, stream, local, dtype, rows, cols, pos, args.steps, args.warmup, args.static)
+            line.update(metric=f"{dtype}_matvec_hbm_gbs", value=r["gbs"], unit="GB/s",
+                        ms_per_step=r["us_per_dispatch"] * 1e-3,
+                        config={"workload": f"matvec {r['shape']} positions, f32 activations",
+                                "l2": f"{r['replicas']} weight replicas rotated"},
+                        roofline={"bound": "hbm", "achieved": r["kernel_gbs"], "peak": peak, "unit": "GB/s",
+                                  "frac": r["frac"], "peak_kind": r["peak_kind"], "kernel": "k_matvec_stream",
+                                  "kernel_us": r["kernel_us"], "frac_pipelined": r["frac_pipelined"],
+                                  "traffic": None},
+                        gpu_launches=2 * args.steps * (1 + (pos > 8)))
+        elif args.workload == "verify_layer":
+            sweep = {}
+            for m in (1, 2, 4, 8, 16):
+                us = kus = 0.0
+                for name, dtype, rows, cols in CONFIG1_LAYER:
+                    r = measure_matvec(be, stream, local, dtype, rows, cols, m, max(args.steps // 10, 40), 10)
+                    us += r["us_per_dispatch"]
+                    kus += r["kernel_us"]
+                wbytes = sum(rows * (cols // 64) * BLOCK_BYTES[d] for _, d, rows, cols in CONFIG1_LAYER)
+                sweep[f"M{m}"] = {"us_per_layer": us, "gbs": wbytes / (us * 1e-6) / 1e9,
+                                  "kernel_us_per_layer": kus, "kernel_frac": wbytes / (kus * 1e-6) / 1e9 / peak,
+                                  "gflop": 2 * m * sum(r * c for _, _, r, c in CONFIG1_LAYER) / 1e9}
+            ref = sweep["M4"]
+            line.update(metric="verify_layer_hbm_gbs", value=ref["gbs"], unit="GB/s",
+                        ms_per_step=ref["us_per_layer"] * 1e-3,
+                        config={"workload": "BASELINE config 1: q/k/v/o (Q4) and gate/up/down (Q2) of one layer, "
+                                            "M verify positions, weights 130 908 160 B read once per M <= 16"},
+                        sweep=sweep,
+                        roofline={"bound": "hbm", "achieved": 130908160 / (ref["kernel_us_per_layer"] * 1e-6) / 1e9,
+                                  "peak": peak, "unit": "GB/s", "frac": ref["kernel_frac"],
+                                  "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (M = 4)", "traffic": None},
+                        gpu_launches=0)
+        else:  # gated_delta
+            heads, qk, layers = 48, 16, 48
+            dev = f"cuda:{local}"
+            g = torch.Generator(device=dev).manual_seed(2)
+            state = [torch.randn(layers, heads, 128, 128, device=dev, generator=g) * 0.02 for _ in range(2)]
+            T = 4
+            q = torch.nn.functional.normalize(torch.randn(T, qk, 128, device=dev, generator=g), dim=-1)
+            k = torch.nn.functional.normalize(torch.randn(T, qk, 128, device=dev, generator=g), dim=-1)
+            v = torch.randn(T, heads, 128, device=dev, generator=g)
+            gate = torch.log(torch.sigmoid(torch.randn(T, heads, device=dev, generator=g) + 2.0))
+            beta = torch.sigmoid(torch.randn(T, heads, device=dev, generator=g))
+            out = torch.empty(T, heads, 128, device=dev)
+            torch.cuda.synchronize()
+
+            def step(tokens, a, b):
+                for l in range(layers):
+                    be.gated_delta_scan(q.data_ptr(), k.data_ptr(), v.data_ptr(), gate.data_ptr(), beta.data_ptr(),
+                                        state[a][l].data_ptr(), state[b][l].data_ptr(), out.data_ptr(), tokens,
+                                        heads, qk)
+
+            res = {}
+            for tokens in (4, 1):
+                for i in range(args.warmup):
+                    step(tokens, i & 1, (i & 1) ^ 1)
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record(stream)
+                for i in range(args.steps):
+                    step(tokens, i & 1, (i & 1) ^ 1)
+                ev1.record(stream)
+                torch.cuda.synchronize()
+                ms = ev0.elapsed_time(ev1) / args.steps
+                nbytes = layers * (2 * heads * 128 * 128 * 4 + tokens * ((2 * qk + heads) * 128 + 2 * heads) * 4
+                                   + tokens * heads * 128 * 4)
+                res[f"T{tokens}"] = {"ms_per_48_layers": ms, "us_per_layer": ms * 1e3 / layers, "bytes": nbytes,
+                                     "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+            line.update(metric="gated_delta_hbm_gbs", value=res["T4"]["gbs"], unit="GB/s",
+                        ms_per_step=res["T4"]["ms_per_48_layers"],
+                        config={"workload": "BASELINE config 2: gated-delta recurrence, 16 key / 48 value heads, "
+                                            "dim 128, fp32 state, 48 layers back to back, T = 4 then T = 1",
+                                "l2": "302 MB of state (two buffers of 48 layers) > 2x L2"},
+                        sweep=res,
+                        roofline={"bound": "hbm", "achieved": res["T4"]["gbs"], "peak": peak, "unit": "GB/s",
+                                  "frac": res["T4"]["frac"], "peak_kind": f"of {peak_kind}",
+                                  "kernel": "k_gated_delta_scan128 (48 launches per step)", "traffic": None},
+                        gpu_launches=48 * args.steps * 2)
+    line["clocks"] = sampler.stop()
+    line["e2e"] = None
+    line["cpu_baseline"] = None
+    print(json.dumps(line), flush=True)
+    be.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "q4_matvec"])
+    ap.add_argument("--workload", default="decode",
+                    choices=["decode", "q4_matvec", "q2_matvec", "matvec", "verify_layer", "gated_delta"])
+    ap.add_argument("--dtype", default="q4", choices=["q4", "q2"], help="matvec: code format")
+    ap.add_argument("--rows", type=int, default=17408)
+    ap.add_argument("--cols", type=int, default=5120)
+    ap.add_argument("--positions", type=int, default=1)
+    ap.add_argument("--static", action="store_true", help="matvec: use the allocation-free dispatch")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--drafts", type=int, default=3,
                     help="decode: chained MTP drafts per block (3 = 4 verify positions, BASELINE config 2; "
@@ -471,15 +750,17 @@ def main():
                     help="decode: only the timed region and one kernel-timing block (for launch lists)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 256 if args.workload == "decode" else 2000
+        args.steps = {"decode": 256, "verify_layer": 400, "gated_delta": 50}.get(args.workload, 2000)
     if args.warmup is None:
-        args.warmup = 4 if args.workload == "decode" else 50
+        args.warmup = {"decode": 4, "gated_delta": 5}.get(args.workload, 50)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode":
         run_decode(args)
-    else:
+    elif args.workload == "q4_matvec":
         run_b200(args)
+    else:
+        run_micro(args)
 
 
 if __name__ == "__main__":

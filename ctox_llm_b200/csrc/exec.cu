@@ -59,6 +59,7 @@ struct ctox_exec {
     ctox_model_config cfg{};  // this rank's shard: heads and FFN width divided by the group size
     uint32_t tp_world = 1, tp_rank = 0;
     uint32_t vocab_l = 0, vocab_off = 0;      // rows of lm_head on this rank
+    uint32_t kv_heads_global = 0;             // KV heads of the unsharded model
     uint32_t draft_lo = 0, draft_n = 0;       // this rank's range of the draft id table
     std::vector<uint32_t> draft_ids_host;
     float *tp_buf = nullptr;                  // [kMaxPass][hidden] vector being summed over the group
@@ -168,6 +169,7 @@ ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c_global, c
     e->n_layers = c->num_hidden_layers;
     e->tp_world = W;
     e->tp_rank = R;
+    e->kv_heads_global = c_global->num_key_value_heads;
     e->vocab_l = c->vocab_size / W;
     e->vocab_off = R * e->vocab_l;
     e->key_width = c->linear_num_key_heads * 128;
@@ -379,13 +381,30 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
     return x ^ (x >> 31);
 }
 
+// Where the rows of a rank's shard sit in the unsharded matrix: up to 6 runs of consecutive rows
+// (fan-out groups are several matrices, each split by heads). A single GPU uses one identity run.
+struct RowMap {
+    uint32_t n;
+    uint64_t local_start[6], global_start[6];
+};
+__device__ __forceinline__ uint64_t global_row(const RowMap &map, uint64_t row) {
+    uint32_t seg = 0;
+    for (uint32_t i = 1; i < map.n; ++i)
+        if (row >= map.local_start[i]) seg = i;
+    return map.global_start[seg] + (row - map.local_start[seg]);
+}
+
 // Canonical blocks [f16 scale][codes]: codes uniform, scale drawn from a 4096-entry quantile table.
+// Every block is a function of its position in the UNSHARDED matrix (global row, global column
+// block), so the shards of a tensor-parallel group are slices of the one-GPU model.
 __global__ void k_fill_canonical(uint8_t *__restrict__ out, uint64_t blocks, uint32_t block_bytes,
-                                 const uint16_t *__restrict__ table, uint64_t seed) {
+                                 const uint16_t *__restrict__ table, uint64_t seed, uint32_t blocks_per_row,
+                                 uint32_t global_blocks_per_row, uint32_t col_block0, RowMap map) {
     const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= blocks) return;
     uint8_t *p = out + b * block_bytes;
-    uint64_t r = mix64(seed ^ (b * 0x100000001B3ull));
+    const uint64_t gid = global_row(map, b / blocks_per_row) * global_blocks_per_row + col_block0 + b % blocks_per_row;
+    uint64_t r = mix64(seed ^ (gid * 0x100000001B3ull));
     const uint16_t sc = table[r & 4095];
     p[0] = (uint8_t)(sc & 0xff);
     p[1] = (uint8_t)(sc >> 8);
@@ -395,10 +414,13 @@ __global__ void k_fill_canonical(uint8_t *__restrict__ out, uint64_t blocks, uin
     }
 }
 
-__global__ void k_fill_uniform_f16(float *__restrict__ out, uint64_t n, float lo, float hi, uint64_t seed) {
+// out[i] for the global index offset + i (columns) or the mapped row (rows, use_map).
+__global__ void k_fill_uniform_f16(float *__restrict__ out, uint64_t n, float lo, float hi, uint64_t seed,
+                                   uint64_t offset, int use_map, RowMap map) {
     const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float u = (float)(mix64(seed ^ (i * 0x9E3779B1ull)) >> 40) * (1.0f / 16777216.0f);
+    const uint64_t gi = use_map ? global_row(map, i) : offset + i;
+    const float u = (float)(mix64(seed ^ (gi * 0x9E3779B1ull)) >> 40) * (1.0f / 16777216.0f);
     out[i] = __half2float(__float2half_rn(lo + (hi - lo) * u));  // what an f16 payload would hold
 }
 
@@ -415,6 +437,18 @@ __global__ void k_fill_normal(T *__restrict__ out, uint64_t n, float mean, float
         reinterpret_cast<__nv_bfloat16 *>(out)[i] = __float2bfloat16_rn(v);
     else
         reinterpret_cast<float *>(out)[i] = v;
+}
+
+// Values of a per-item vector (per_item values per row of `map`), a function of the global index.
+__global__ void k_fill_normal_mapped(float *__restrict__ out, uint64_t n, uint32_t per_item, float mean, float std,
+                                     uint64_t seed, RowMap map) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const uint64_t gi = global_row(map, i / per_item) * per_item + i % per_item;
+    const uint64_t r = mix64(seed ^ (gi * 0xD6E8FEB86659FD93ull));
+    const float u1 = ((float)(r >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = (float)((r >> 16) & 0xffffff) * (1.0f / 16777216.0f);
+    out[i] = mean + std * sqrtf(-2.0f * logf(u1)) * cosf(6.28318530718f * u2);
 }
 
 __global__ void k_gather_rows(const uint8_t *__restrict__ src, const uint32_t *__restrict__ ids,
@@ -470,11 +504,26 @@ uint16_t f32_to_f16_bits(float f) {
     return u;
 }
 
-// `sharded`: this rank's slice of a matrix that is split over the group; its codes differ per rank,
-// the recovery scales follow the rank-independent seed.
-ctox_status synth_matrix(ctox_exec *e, int dt, uint64_t rows, uint64_t cols, const uint16_t *table_dev,
-                         uint64_t seed, bool sharded, uint32_t flags, ctox_matvec **out) {
+// One run of rows: local rows [.., ..+count) are global rows [global, global+count).
+struct RowRun {
+    uint64_t global, count;
+};
+
+// A matrix of `rows` x `cols` that is the slice (row runs, columns [col0, col0 + cols)) of an unsharded
+// matrix with global_cols columns: codes and recovery scales follow the global indices.
+ctox_status synth_matrix(ctox_exec *e, int dt, uint64_t cols, uint64_t global_cols, uint64_t col0,
+                         std::initializer_list<RowRun> runs, const uint16_t *table_dev, uint64_t seed, uint32_t flags,
+                         ctox_matvec **out) {
     ctox_ctx *ctx = e->ctx;
+    RowMap map{};
+    uint64_t rows = 0;
+    for (const RowRun &r : runs) {
+        if (map.n >= 6) return fail(ctx, CTOX_SHAPE, "synthetic matrix: too many row runs");
+        map.local_start[map.n] = rows;
+        map.global_start[map.n] = r.global;
+        rows += r.count;
+        ++map.n;
+    }
     const uint32_t bb = dt ? 34 : 18;
     const uint64_t blocks = rows * (cols / 64);
     uint8_t *canon = nullptr;
@@ -483,13 +532,12 @@ ctox_status synth_matrix(ctox_exec *e, int dt, uint64_t rows, uint64_t cols, con
     if (!rc) rc = dev_alloc(ctx, (void **)&s_in, cols * 4);
     if (!rc) rc = dev_alloc(ctx, (void **)&s_out, rows * 4);
     if (rc) return rc;
-    const uint64_t code_seed = sharded ? seed ^ (0xC2B2AE3D27D4EB4Full * (e->tp_rank + 1)) : seed;
-    k_fill_canonical<<<(unsigned)((blocks + 255) / 256), 256, 0, ctx->stream>>>(canon, blocks, bb, table_dev,
-                                                                               code_seed);
+    k_fill_canonical<<<(unsigned)((blocks + 255) / 256), 256, 0, ctx->stream>>>(
+        canon, blocks, bb, table_dev, seed, (uint32_t)(cols / 64), (uint32_t)(global_cols / 64), (uint32_t)(col0 / 64), map);
     k_fill_uniform_f16<<<(unsigned)((cols + 255) / 256), 256, 0, ctx->stream>>>(s_in, cols, 0.75f, 1.25f,
-                                                                             seed ^ 0x5151);
+                                                                             seed ^ 0x5151, col0, 0, map);
     k_fill_uniform_f16<<<(unsigned)((rows + 255) / 256), 256, 0, ctx->stream>>>(s_out, rows, 0.75f, 1.25f,
-                                                                             seed ^ 0xA0A0);
+                                                                             seed ^ 0xA0A0, 0, 1, map);
     CTOX_CUDA(ctx, cudaGetLastError());
     return matvec_create_device(ctx, dt, rows, cols, canon, blocks * bb, s_in, s_out, flags, out);
 }
@@ -500,6 +548,25 @@ ctox_status synth_vector(ctox_exec *e, float **slot, uint64_t n, float mean, flo
         if (rc) return rc;
     }
     k_fill_normal<float><<<(unsigned)((n + 255) / 256), 256, 0, e->ctx->stream>>>(*slot, n, mean, std, seed);
+    return CTOX_OK;
+}
+
+ctox_status synth_vector_sharded(ctox_exec *e, float **slot, uint32_t per_item, std::initializer_list<RowRun> runs,
+                                 float mean, float std, uint64_t seed) {
+    RowMap map{};
+    uint64_t items = 0;
+    for (const RowRun &r : runs) {
+        map.local_start[map.n] = items;
+        map.global_start[map.n] = r.global;
+        items += r.count;
+        ++map.n;
+    }
+    const uint64_t n = items * per_item;
+    if (!*slot) {
+        ctox_status rc = xalloc(e, (void **)slot, n * 4, false);
+        if (rc) return rc;
+    }
+    k_fill_normal_mapped<<<(unsigned)((n + 255) / 256), 256, 0, e->ctx->stream>>>(*slot, n, per_item, mean, std, seed, map);
     return CTOX_OK;
 }
 
@@ -571,17 +638,27 @@ ctox_status ctox_exec_fill_synthetic(ctox_exec *e, uint64_t seed, float mu, floa
     };
     if (e->lm_head && !e->lm_head_is_embed) replace(&e->lm_head);
     replace(&e->embed);
+    // Shard geometry: this rank's heads, FFN columns and vocabulary rows inside the unsharded model
+    // (world 1: everything). Seeds are drawn in the same order on every rank, and every tensor is a
+    // function of (seed, global index), so a group's shards are slices of the one-GPU model.
+    const uint64_t W = e->tp_world, R = e->tp_rank;
+    const uint64_t hd = c.head_dim, QWl = e->q_width, KVl = e->kv_width, QW = QWl * W;
+    const uint64_t kv_heads_global = e->kv_heads_global, KV = kv_heads_global * hd;
+    const uint64_t kv_head0 = kv_heads_global >= W ? R * c.num_key_value_heads : R * kv_heads_global / W;
+    const uint64_t KWl = e->key_width, VWl = e->value_width, KW = KWl * W, VW = VWl * W;
+    const uint64_t VHl = c.linear_num_value_heads, VH = VHl * W, CH = 2 * KW + VW, Fl = F, FG = F * W;
     // attention / embedding weights Q4, FFN weights Q2 (the benchmark configuration)
-    SYNTH(synth_matrix(e, 1, c.vocab_size, H, table_dev, next_seed(), false, CTOX_PREPARE_KEEP_CANONICAL,
+    const uint64_t embed_seed = next_seed();
+    SYNTH(synth_matrix(e, 1, H, H, 0, {{0, c.vocab_size}}, table_dev, embed_seed, CTOX_PREPARE_KEEP_CANONICAL,
                        &e->embed));
     if (e->tp_world == 1) {
         e->lm_head = e->embed;  // tied: one resident copy serves row gathers and the head
         e->lm_head_is_embed = true;
-    } else {  // the embedding is replicated, the head holds this rank's vocabulary rows
+    } else {  // the embedding is replicated, the head holds this rank's vocabulary rows of the same matrix
         e->lm_head = nullptr;
         e->lm_head_is_embed = false;
-        SYNTH(synth_matrix(e, 1, e->vocab_l, H, table_dev, next_seed(), true, CTOX_PREPARE_KEEP_CANONICAL,
-                           &e->lm_head));
+        SYNTH(synth_matrix(e, 1, H, H, 0, {{e->vocab_off, e->vocab_l}}, table_dev, embed_seed,
+                           CTOX_PREPARE_KEEP_CANONICAL, &e->lm_head));
     }
     SYNTH(synth_vector(e, &e->final_norm, H, 0.f, 0.02f, next_seed()));
     for (uint32_t l = 0; l < e->w.size(); ++l) {
@@ -593,27 +670,34 @@ ctox_status ctox_exec_fill_synthetic(ctox_exec *e, uint64_t seed, float mu, floa
         SYNTH(synth_vector(e, &lw.in_ln, H, 0.f, 0.02f, next_seed()));
         SYNTH(synth_vector(e, &lw.post_ln, H, 0.f, 0.02f, next_seed()));
         if (lw.full) {
-            SYNTH(synth_matrix(e, 1, 2ull * e->q_width + 2ull * e->kv_width, H, table_dev, next_seed(), true, 0,
-                               &lw.in_fan));
-            SYNTH(synth_matrix(e, 1, H, e->q_width, table_dev, next_seed(), true, 0, &lw.out));
+            // [q + gate per head | k | v]: this rank's query heads and its KV head(s)
+            SYNTH(synth_matrix(e, 1, H, H, 0,
+                               {{R * 2 * QWl, 2 * QWl}, {2 * QW + kv_head0 * hd, KVl}, {2 * QW + KV + kv_head0 * hd, KVl}},
+                               table_dev, next_seed(), 0, &lw.in_fan));
+            SYNTH(synth_matrix(e, 1, QWl, QW, R * QWl, {{0, H}}, table_dev, next_seed(), 0, &lw.out));
             SYNTH(synth_vector(e, &lw.q_norm, c.head_dim, 0.f, 0.02f, next_seed()));
             SYNTH(synth_vector(e, &lw.k_norm, c.head_dim, 0.f, 0.02f, next_seed()));
         } else {
-            SYNTH(synth_matrix(e, 1, (uint64_t)e->channels + e->value_width + 2ull * c.linear_num_value_heads, H,
-                               table_dev, next_seed(), true, 0, &lw.in_fan));
-            SYNTH(synth_matrix(e, 1, H, e->value_width, table_dev, next_seed(), true, 0, &lw.out));
-            SYNTH(synth_vector(e, &lw.conv_w, (uint64_t)e->channels * c.linear_conv_kernel_dim, 0.f, 0.3f,
-                               next_seed()));
-            SYNTH(synth_vector(e, &lw.a_log, c.linear_num_value_heads, 0.f, 0.5f, next_seed()));
-            SYNTH(synth_vector(e, &lw.dt_bias, c.linear_num_value_heads, 0.f, 0.5f, next_seed()));
+            // [q | k | v] conv channels, z, a, b: this rank's key heads and value heads
+            SYNTH(synth_matrix(e, 1, H, H, 0,
+                               {{R * KWl, KWl}, {KW + R * KWl, KWl}, {2 * KW + R * VWl, VWl}, {CH + R * VWl, VWl},
+                                {CH + VW + R * VHl, VHl}, {CH + VW + VH + R * VHl, VHl}},
+                               table_dev, next_seed(), 0, &lw.in_fan));
+            SYNTH(synth_matrix(e, 1, VWl, VW, R * VWl, {{0, H}}, table_dev, next_seed(), 0, &lw.out));
+            // per-channel / per-head vectors: generated for the whole model, this rank keeps its part
+            SYNTH(synth_vector_sharded(e, &lw.conv_w, c.linear_conv_kernel_dim,
+                                       {{R * KWl, KWl}, {KW + R * KWl, KWl}, {2 * KW + R * VWl, VWl}}, 0.f, 0.3f,
+                                       next_seed()));
+            SYNTH(synth_vector_sharded(e, &lw.a_log, 1, {{R * VHl, VHl}}, 0.f, 0.5f, next_seed()));
+            SYNTH(synth_vector_sharded(e, &lw.dt_bias, 1, {{R * VHl, VHl}}, 0.f, 0.5f, next_seed()));
             SYNTH(synth_vector(e, &lw.lin_norm, 128, 1.f, 0.02f, next_seed()));
         }
-        SYNTH(synth_matrix(e, 0, 2 * F, H, table_dev, next_seed(), true, 0, &lw.gate_up));
-        SYNTH(synth_matrix(e, 0, H, F, table_dev, next_seed(), true, 0, &lw.down));
+        SYNTH(synth_matrix(e, 0, H, H, 0, {{R * Fl, Fl}, {FG + R * Fl, Fl}}, table_dev, next_seed(), 0, &lw.gate_up));
+        SYNTH(synth_matrix(e, 0, Fl, FG, R * Fl, {{0, H}}, table_dev, next_seed(), 0, &lw.down));
     }
     if (c.mtp_num_hidden_layers) {
         replace(&e->mtp_fc);
-        SYNTH(synth_matrix(e, 1, H, 2 * H, table_dev, next_seed(), false, 0, &e->mtp_fc));
+        SYNTH(synth_matrix(e, 1, 2 * H, 2 * H, 0, {{0, H}}, table_dev, next_seed(), 0, &e->mtp_fc));
         SYNTH(synth_vector(e, &e->mtp_norm_e, H, 0.f, 0.02f, next_seed()));
         SYNTH(synth_vector(e, &e->mtp_norm_h, H, 0.f, 0.02f, next_seed()));
         SYNTH(synth_vector(e, &e->mtp_norm, H, 0.f, 0.02f, next_seed()));
