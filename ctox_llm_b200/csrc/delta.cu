@@ -225,7 +225,7 @@ __global__ void k_gated_delta_prepare(const float *__restrict__ a, const float *
 // The q and k channels are shared by the value heads of a key head; the first of them stores them.
 constexpr int kLaMaxPos = 8;
 
-__global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int npos) {
+__global__ void __launch_bounds__(512, 1) k_linear_attention(LinearAttnArgs a, int npos) {
     pdl_launch();
     __shared__ float qs[kLaMaxPos][kDeltaDim], ks[kLaMaxPos][kDeltaDim], vs[kLaMaxPos][kDeltaDim];
     __shared__ float zs[kLaMaxPos][kDeltaDim], core[kLaMaxPos][kDeltaDim];
@@ -252,11 +252,16 @@ __global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int 
     const uint32_t ch = part == 0 ? khead * kDeltaDim + cd
                         : part == 1 ? a.key_width + khead * kDeltaDim + cd
                                     : 2 * a.key_width + head * kDeltaDim + cd;
+    // taps in registers for any kernel width <= 8: every loop over them is fully unrolled with
+    // predicates (a run-time trip count would put the arrays on the local-memory stack)
+    const uint32_t K = a.conv_kernel;
     float st[8], cw[8];
-    if (tid < 384) {
-        for (uint32_t j = 0; j < a.conv_kernel; ++j) {
-            st[j] = a.conv_state[(size_t)ch * a.conv_kernel + j];
-            cw[j] = a.conv_w[(size_t)ch * a.conv_kernel + j];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        st[j] = cw[j] = 0.f;
+        if (tid < 384 && (uint32_t)j < K) {
+            st[j] = a.conv_state[(size_t)ch * K + j];
+            cw[j] = a.conv_w[(size_t)ch * K + j];
         }
     }
     pdl_wait();
@@ -268,10 +273,16 @@ __global__ void __launch_bounds__(512) k_linear_attention(LinearAttnArgs a, int 
         for (int m = 0; m < npos; ++m) {
             const float x = out_of(a.fan, ch, m);
             if (store) a.conv_in[(size_t)m * channels + ch] = x;
-            for (uint32_t j = 0; j + 1 < a.conv_kernel; ++j) st[j] = st[j + 1];
-            st[a.conv_kernel - 1] = x;
+#pragma unroll
+            for (int j = 0; j < 7; ++j)
+                if ((uint32_t)j + 1 < K) st[j] = st[j + 1];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((uint32_t)j + 1 == K) st[j] = x;
             float sum = 0.f;
-            for (uint32_t j = 0; j < a.conv_kernel; ++j) sum += st[j] * cw[j];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if ((uint32_t)j < K) sum += st[j] * cw[j];
             const float y = silu_f(sum);
             if (part == 0) {
                 qs[m][d] = y;

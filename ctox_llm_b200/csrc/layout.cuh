@@ -51,9 +51,9 @@ struct Fmt<1> {  // Q4_B64
 //   Q4: registers are the nibble pairs (0,4)(1,5)(2,6)(3,7) of each 8-code word.
 //   Q2: registers are the field pairs (0,8)(1,9)...(7,15) of the 16-code word.
 __host__ __device__ inline int inv_perm(int dt, int q) {
-    const int q4[16] = {0, 2, 4, 6, 1, 3, 5, 7, 8, 10, 12, 14, 9, 11, 13, 15};
-    const int q2[16] = {0, 2, 4, 6, 8, 10, 12, 14, 1, 3, 5, 7, 9, 11, 13, 15};
-    return dt ? q4[q] : q2[q];
+    // Q4 {0,2,4,6,1,3,5,7, 8,10,12,14,9,11,13,15}; Q2 {0,2,..,14, 1,3,..,15}: as arithmetic, so that a
+    // run-time q does not turn a table into a local-memory array
+    return dt ? ((q & 8) | ((q & 3) << 1) | ((q >> 2) & 1)) : (((q & 7) << 1) | (q >> 3));
 }
 
 // The kernels feed the tensor cores the masked code bits themselves: a code at
@@ -65,8 +65,9 @@ __host__ __device__ inline int inv_perm(int dt, int q) {
 //   Q2: fields at p = 0,2,4,6,8 -> x256,x64,x16,x4,x1; product scale 2^-16.
 __host__ __device__ inline float column_multiplier(int dt, int column) {
     if (dt) return (column & 1) ? 1.0f : 16.0f;
-    const float q2[8] = {256.f, 64.f, 16.f, 4.f, 1.f, 256.f, 64.f, 16.f};
-    return q2[column & 7];
+    // Q2 {256, 64, 16, 4, 1, 256, 64, 16}: 2^(8 - 2 k), k = position of the field in its half word
+    const int idx = column & 7, k = idx >= 5 ? idx - 5 : idx;
+    return (float)(1 << (8 - 2 * k));
 }
 __host__ __device__ inline float code_scale(int dt) { return dt ? 9.5367431640625e-07f /* 2^-20 */
                                                                : 1.52587890625e-05f /* 2^-16 */; }

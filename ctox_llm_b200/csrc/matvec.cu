@@ -113,6 +113,14 @@ __device__ __forceinline__ void mma_f16_init(float (&d)[4], uint32_t a0, uint32_
         : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(c0), "f"(c1));
 }
+// Four f16 values packed in two 32-bit words -> four floats, in registers.
+__device__ __forceinline__ void h2x2_to_f32(uint32_t a, uint32_t b, float (&out)[4]) {
+    asm("{\n\t.reg .b16 l0, h0, l1, h1;\n\t"
+        "mov.b32 {l0, h0}, %4;\n\tmov.b32 {l1, h1}, %5;\n\t"
+        "cvt.f32.f16 %0, l0;\n\tcvt.f32.f16 %1, h0;\n\tcvt.f32.f16 %2, l1;\n\tcvt.f32.f16 %3, h1;\n\t}"
+        : "=f"(out[0]), "=f"(out[1]), "=f"(out[2]), "=f"(out[3])
+        : "r"(a), "r"(b));
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -471,19 +479,13 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
             const uint32_t tile0 = my_stage + st * kChunkBytes + i * kUnitBytes, tile1 = tile0 + kST;
             // scales of both tiles: rows g, g+8 (tile 0) and 16+g, 24+g (tile 1), blocks 0..3
             const uint4 sv0 = lds128(tile0 + g * 16), sv1 = lds128(tile1 + g * 16);
+            // row r of the pair: two words = four f16 block scales (no address is taken of a register
+            // array here: that would put it on the local-memory stack, a round trip per unit)
             float sc[4][4];
-            {
-                const uint32_t raw[8] = {sv0.x, sv0.y, sv0.z, sv0.w, sv1.x, sv1.y, sv1.z, sv1.w};
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float2 lo2 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[2 * r]));
-                    const float2 hi2 = __half22float2(*reinterpret_cast<const __half2 *>(&raw[2 * r + 1]));
-                    sc[r][0] = lo2.x;
-                    sc[r][1] = lo2.y;
-                    sc[r][2] = hi2.x;
-                    sc[r][3] = hi2.y;
-                }
-            }
+            h2x2_to_f32(sv0.x, sv0.y, sc[0]);
+            h2x2_to_f32(sv0.z, sv0.w, sc[1]);
+            h2x2_to_f32(sv1.x, sv1.y, sc[2]);
+            h2x2_to_f32(sv1.z, sv1.w, sc[3]);
             uint4 q0 = make_uint4(0, 0, 0, 0), q1 = make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {

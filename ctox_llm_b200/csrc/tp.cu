@@ -131,8 +131,11 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
     if (c < hidden) {
         const float mine = out_of(o, c, m);
         const size_t at = (size_t)m * hidden + c;
-        for (uint32_t r = 0; r < world; ++r)
-            if (r != rank) st_word_sys(peers.dst[r] + at, __float_as_uint(mine), seq);
+        // (unrolled with predicates: a run-time index into the by-value pointer table would copy it
+        // to the local-memory stack first)
+#pragma unroll
+        for (uint32_t r = 0; r < kTpMaxWorld; ++r)
+            if (r < world && r != rank) st_word_sys(peers.dst[r] + at, __float_as_uint(mine), seq);
         v = h[at];
         const long long t0 = clock64();
         // once a wait has run out anywhere (this kernel or an earlier one of the same call), nobody
