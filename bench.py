@@ -147,7 +147,7 @@ def matvec_algo_bytes(dtype, rows, cols, positions=1):
     return rows * (cols // 64) * BLOCK_BYTES[dtype] + positions * (cols + rows) * 4
 
 
-def measure_matvec(be, stream, local, dtype, rows, cols, positions, steps, warmup=20, static=False):
+def measure_matvec(be, stream, local, dtype, rows, cols, positions, steps, warmup=20, static=False, replicas=0):
     """Device-resident timing of one prepared matvec shape: `steps` dispatches over enough weight
     replicas to exceed twice the L2, CUDA events around the whole loop (launches overlap through
     programmatic dependent launch, as in a decode pass) and an event pair around every launch of the
@@ -157,7 +157,7 @@ def measure_matvec(be, stream, local, dtype, rows, cols, positions, steps, warmu
     from ctox_llm_b200 import synthetic
     dt = ctox.Q4B64 if dtype == "q4" else ctox.Q2B64
     wbytes = rows * (cols // 64) * BLOCK_BYTES[dtype]
-    n_rep = max(2, min(16, -(-300_000_000 // wbytes)))
+    n_rep = replicas if replicas > 0 else max(2, min(16, -(-300_000_000 // wbytes)))
     reps = [be.prepare_fused_matvec(ctox.FusedMatVec(dt, synthetic.packed_weights(dt, rows, cols, seed=100 + r),
                                                      rows, cols, None)) for r in range(n_rep)]
     x = torch.from_numpy(synthetic.activations(cols, 0, positions=positions).reshape(positions, cols)).cuda(local)
@@ -642,7 +642,8 @@ def run_micro(args):
         if args.workload in ("matvec", "q2_matvec"):
             dtype, rows, cols, pos = (("q2", 5120, 17408, 1) if args.workload == "q2_matvec"
                                       else (args.dtype, args.rows, args.cols, args.positions))
-            r = measure_matvec(be, stream, local, dtype, rows, cols, pos, args.steps, args.warmup, args.static)
+            r = measure_matvec(be, stream, local, dtype, rows, cols, pos, args.steps, args.warmup, args.static,
+                               args.replicas)
             line.update(metric=f"{dtype}_matvec_hbm_gbs", value=r["gbs"], unit="GB/s",
                         ms_per_step=r["us_per_dispatch"] * 1e-3,
                         config={"workload": f"matvec {r['shape']} positions, f32 activations",
@@ -740,6 +741,9 @@ def main():
     ap.add_argument("--cols", type=int, default=5120)
     ap.add_argument("--positions", type=int, default=1)
     ap.add_argument("--static", action="store_true", help="matvec: use the allocation-free dispatch")
+    ap.add_argument("--replicas", type=int, default=0,
+                    help="matvec: weight replicas to rotate (default: enough to exceed twice the L2; 1 = weights "
+                         "stay in L2, a diagnostic that separates the instruction cost from the HBM stream)")
     ap.add_argument("--context", type=int, default=32768)
     ap.add_argument("--drafts", type=int, default=3,
                     help="decode: chained MTP drafts per block (3 = 4 verify positions, BASELINE config 2; "
