@@ -378,6 +378,8 @@ def run_decode(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_enqueue_ms = [0.0]
+
     def run_blocks(n_blocks, mtp, force, timed):
         """Returns (device ms, wall s, tokens emitted, drafts accepted) for n_blocks decode calls."""
         ex.prefill_synthetic(context, seed=1)
@@ -387,6 +389,7 @@ def run_decode(args):
         barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         emitted = accepted = 0
+        enqueue_us = 0.0
         ev0.record(stream)
         t0 = time.perf_counter()
         for _ in range(n_blocks):
@@ -395,6 +398,8 @@ def run_decode(args):
             tok = blk.token_id
             emitted += len(blk.emitted)
             accepted += len(blk.accepted_draft_tokens)
+            enqueue_us += ex.last_enqueue_us()
+        host_enqueue_ms[0] = enqueue_us / n_blocks * 1e-3
         wall = time.perf_counter() - t0
         ev1.record(stream)
         barrier()
@@ -404,6 +409,7 @@ def run_decode(args):
     if rank == 0:
         sampler.start()
     ms, wall, emitted, accepted = run_blocks(args.steps, True, -1, True)
+    enqueue_ms = host_enqueue_ms[0]
     clocks = sampler.stop() if rank == 0 else None
     buckets, plain = {}, None
     if not args.quick:
@@ -463,6 +469,7 @@ def run_decode(args):
             "tokens_per_s_without_mtp": plain,
             "tokens_per_s_forced_acceptance": buckets,
             "host_reads_per_block": 1,
+            "host_enqueue_ms_per_block": enqueue_ms,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "frac_of_8000_nominal": achieved / 8000.0,
                          "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (all launches of a block, per GPU)",

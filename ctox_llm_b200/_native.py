@@ -157,6 +157,7 @@ SIGNATURES = {
     "ctox_matvec_dispatch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                               C.c_uint32]),
     "ctox_gated_delta_scan": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
+    "ctox_gated_delta_scan_f16_state": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
     "ctox_gated_delta_prepare": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_uint32] * 2),
     "ctox_argmax_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),
     "ctox_argmax_f32_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
@@ -185,6 +186,7 @@ SIGNATURES = {
                                      C.c_void_p, C.POINTER(ExecStep)]),
     "ctox_exec_commit_speculative": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p]),
     "ctox_exec_session_state": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "ctox_exec_last_enqueue_us": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double)]),
     "ctox_exec_last_mtp_hidden": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32)]),
     "ctox_exec_last_draft_logits": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32),
                                                 C.POINTER(C.c_uint32)]),

@@ -172,6 +172,14 @@ class B200Backend:
             self._ctx, *(C.c_void_p(a) for a in (q, k, v, log_decay, beta, state_in, state_out, out)),
             tokens, heads, qk_heads, key_dim, value_dim))
 
+    def gated_delta_scan_f16_state(self, q: int, k: int, v: int, log_decay: int, beta: int, state_in: int,
+                                   state_out: int, out: int, tokens: int, heads: int, qk_heads: int) -> None:
+        """recurrent_gated_delta_step_f16_state (reference.rs:299-373) over `tokens` tokens: the state
+        buffers hold binary16 values, everything else is fp32."""
+        self._check(self._lib.ctox_gated_delta_scan_f16_state(
+            self._ctx, *(C.c_void_p(a) for a in (q, k, v, log_decay, beta, state_in, state_out, out)),
+            tokens, heads, qk_heads, 128, 128))
+
     def gated_delta_prepare(self, a: int, b: int, a_log: int, dt_bias: int, log_decay: int,
                             beta: int, tokens: int, heads: int) -> None:
         self._check(self._lib.ctox_gated_delta_prepare(

@@ -18,6 +18,8 @@
 #include "common.cuh"
 #include "layers.cuh"
 
+#include <cuda_fp16.h>
+
 #include <cmath>
 
 namespace ctox {
@@ -26,11 +28,34 @@ constexpr int kDeltaDim = 128;    // key_dim == value_dim of the fast path
 constexpr int kDeltaSlice = 32;   // value columns per CTA
 constexpr float kL2Eps = 1e-6f;   // reference.rs:11
 
+// State element types: fp32, or FP16-resident (reference.rs:299-373: dot products and update
+// arithmetic stay fp32, every persistent state element is rounded to binary16 when it is written,
+// i.e. after the decay and after the delta update of every token).
+template <typename S>
+__device__ __forceinline__ float state_load(const S *p);
+template <>
+__device__ __forceinline__ float state_load<float>(const float *p) { return *p; }
+template <>
+__device__ __forceinline__ float state_load<__half>(const __half *p) { return __half2float(*p); }
+template <typename S>
+__device__ __forceinline__ float state_round(float v);
+template <>
+__device__ __forceinline__ float state_round<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float state_round<__half>(float v) { return __half2float(__float2half_rn(v)); }
+template <typename S>
+__device__ __forceinline__ void state_store(S *p, float v);
+template <>
+__device__ __forceinline__ void state_store<float>(float *p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void state_store<__half>(__half *p, float v) { *p = __float2half_rn(v); }
+
 // The scan of one (head, 32-column slice) by one CTA of 128 threads; out may be null (state only).
+template <typename S>
 __device__ __forceinline__ void delta_scan128_body(
     const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
     const float *__restrict__ log_decay, const float *__restrict__ beta,
-    const float *__restrict__ state_in, float *__restrict__ state_out, float *__restrict__ out,
+    const S *__restrict__ state_in, S *__restrict__ state_out, float *__restrict__ out,
     int tokens, int heads, int qk_heads, int head, int slice) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int col = slice * kDeltaSlice + lane;
@@ -40,9 +65,9 @@ __device__ __forceinline__ void delta_scan128_body(
     __shared__ float norms[2];
 
     float s[32];
-    const float *sin_ = state_in + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
+    const S *sin_ = state_in + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) s[i] = sin_[(size_t)i * kDeltaDim];
+    for (int i = 0; i < 32; ++i) s[i] = state_load<S>(sin_ + (size_t)i * kDeltaDim);
 
     const float query_scale = 1.0f / sqrtf((float)kDeltaDim);
     for (int tok = 0; tok < tokens; ++tok) {
@@ -76,7 +101,7 @@ __device__ __forceinline__ void delta_scan128_body(
         float mem = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            s[i] *= decay;
+            s[i] = state_round<S>(s[i] * decay);
             mem += s[i] * ks[warp * 32 + i] * k_inv;
         }
         red[1][warp][lane] = mem;
@@ -85,7 +110,7 @@ __device__ __forceinline__ void delta_scan128_body(
         float o = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            s[i] += ks[warp * 32 + i] * k_inv * delta;
+            s[i] = state_round<S>(s[i] + ks[warp * 32 + i] * k_inv * delta);
             o += s[i] * qs[warp * 32 + i] * q_inv * query_scale;
         }
         red[0][warp][lane] = o;
@@ -97,20 +122,21 @@ __device__ __forceinline__ void delta_scan128_body(
         // barrier that follows the qs/ks stores, which every warp reaches after this read
         __syncthreads();
     }
-    float *sout = state_out + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
+    S *sout = state_out + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
 #pragma unroll
-    for (int i = 0; i < 32; ++i) sout[(size_t)i * kDeltaDim] = s[i];
+    for (int i = 0; i < 32; ++i) state_store<S>(sout + (size_t)i * kDeltaDim, s[i]);
 }
 
+template <typename S>
 __global__ void __launch_bounds__(128) k_gated_delta_scan128(
     const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
     const float *__restrict__ log_decay, const float *__restrict__ beta,
-    const float *__restrict__ state_in, float *__restrict__ state_out, float *__restrict__ out,
+    const S *__restrict__ state_in, S *__restrict__ state_out, float *__restrict__ out,
     int tokens, int heads, int qk_heads) {
     pdl_launch();
     pdl_wait();
-    delta_scan128_body(q, k, v, log_decay, beta, state_in, state_out, out, tokens, heads, qk_heads, blockIdx.x >> 2,
-                       blockIdx.x & 3);
+    delta_scan128_body<S>(q, k, v, log_decay, beta, state_in, state_out, out, tokens, heads, qk_heads,
+                          blockIdx.x >> 2, blockIdx.x & 3);
 }
 
 // Commit of the first n positions of a pass for ALL linear-attention layers in one launch:
@@ -127,8 +153,8 @@ __global__ void __launch_bounds__(128) k_commit_batch(const CommitLayer *__restr
     if ((int)blockIdx.x < scan_ctas) {
         if (!rescan) return;
         const int c = cur.v[blockIdx.y];
-        delta_scan128_body(L.q, L.k, L.v, L.g, L.beta, L.state[c], L.state[c ^ 1], nullptr, n, heads, qk_heads,
-                           blockIdx.x >> 2, blockIdx.x & 3);
+        delta_scan128_body<float>(L.q, L.k, L.v, L.g, L.beta, L.state[c], L.state[c ^ 1], nullptr, n, heads, qk_heads,
+                                  blockIdx.x >> 2, blockIdx.x & 3);
         return;
     }
     const uint32_t r = (blockIdx.x - scan_ctas) * blockDim.x + threadIdx.x;
@@ -405,14 +431,33 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
                     tokens, heads, qk_heads, key_dim, value_dim);
     CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
     if (key_dim == kDeltaDim && value_dim == kDeltaDim) {
-        launch_pdl(k_gated_delta_scan128, dim3(heads * 4), dim3(128), 0, ctx->stream, q, k, v, log_decay, beta, state_in, state_out,
-                                                                 out, (int)tokens, (int)heads, (int)qk_heads);
+        launch_pdl(k_gated_delta_scan128<float>, dim3(heads * 4), dim3(128), 0, ctx->stream, q, k, v, log_decay, beta,
+                   state_in, state_out, out, (int)tokens, (int)heads, (int)qk_heads);
     } else {
         const unsigned n = heads * value_dim;
         launch_pdl(k_gated_delta_scan_generic, dim3((n + 127) / 128), dim3(128), 0, ctx->stream, 
             q, k, v, log_decay, beta, state_in, state_out, out, (int)tokens, (int)heads, (int)qk_heads,
             (int)key_dim, (int)value_dim);
     }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status ctox_gated_delta_scan_f16_state(ctox_ctx *ctx, const float *q, const float *k, const float *v,
+                                            const float *log_decay, const float *beta, const void *state_in,
+                                            void *state_out, float *out, uint32_t tokens, uint32_t heads,
+                                            uint32_t qk_heads, uint32_t key_dim, uint32_t value_dim) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    if (!q || !k || !v || !log_decay || !beta || !state_in || !state_out || !out)
+        return fail(ctx, CTOX_SHAPE, "gated delta (f16 state): null device pointer");
+    if (tokens == 0 || heads == 0 || qk_heads == 0 || heads % qk_heads)
+        return fail(ctx, CTOX_SHAPE, "gated delta (f16 state): tokens %u heads %u qk_heads %u", tokens, heads, qk_heads);
+    if (key_dim != kDeltaDim || value_dim != kDeltaDim)
+        return fail(ctx, CTOX_UNSUPPORTED_OPERATION, "gated delta (f16 state): only 128 x 128 heads, got %u x %u", key_dim,
+                    value_dim);
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    launch_pdl(k_gated_delta_scan128<__half>, dim3(heads * 4), dim3(128), 0, ctx->stream, q, k, v, log_decay, beta,
+               (const __half *)state_in, (__half *)state_out, out, (int)tokens, (int)heads, (int)qk_heads);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }

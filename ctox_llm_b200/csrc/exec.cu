@@ -23,6 +23,7 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdlib>
 #include <vector>
@@ -83,6 +84,7 @@ struct ctox_exec {
     // Speculative transaction (engine.rs:322-362): an MTP decode resolves and commits its accepted
     // prefix on the device and leaves the count here until commit_speculative confirms it.
     int32_t pending = -1;
+    double last_enqueue_us = 0.0;  // host time the last decode spent enqueuing before it waited for the device
     // A device error or a failed call after work was enqueued leaves the session state undefined:
     // every call fails until reset_session (engine.rs:594-611 invalidates the session the same way).
     bool poisoned = false;
@@ -1179,6 +1181,7 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
     uint32_t host_tokens[kMaxPass + 1] = {0};
     host_tokens[0] = token;
     e->mtp_trace_n = e->draft_trace_n = 0;
+    const auto t_begin = std::chrono::steady_clock::now();
     // Nothing below changes the committed session before the acceptance is known: a cancellation
     // between passes leaves the session where it was (the MTP cache slots written so far belong to
     // committed positions or lie beyond them and are rewritten by the next call).
@@ -1221,6 +1224,7 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
                                    ctx->stream));
     CTOX_CUDA(ctx, cudaMemcpyAsync((uint8_t *)ctx->pinned + sizeof(ctox_spec_record), ctx->dev_error, 4,
                                    cudaMemcpyDeviceToHost, ctx->stream));
+    e->last_enqueue_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_begin).count();
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the one host read of the block
     ctox_spec_record rec;
     memcpy(&rec, ctx->pinned, sizeof rec);
@@ -1317,6 +1321,12 @@ ctox_status ctox_exec_session_state(const ctox_exec *e, int32_t *pending_accepte
     if (!e) return CTOX_INVALID_STATE;
     if (pending_accepted) *pending_accepted = e->pending;
     if (poisoned) *poisoned = e->poisoned ? 1 : 0;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_last_enqueue_us(const ctox_exec *e, double *microseconds) {
+    if (!e || !microseconds) return CTOX_INVALID_STATE;
+    *microseconds = e->last_enqueue_us;
     return CTOX_OK;
 }
 

@@ -130,6 +130,12 @@ class B200Executor:
         self._b._check(self._lib.ctox_exec_commit_speculative(self._h, accepted_drafts,
                                                               _cancel_ptr(cancellation)))
 
+    def last_enqueue_us(self) -> float:
+        """Host microseconds the last decode spent enqueuing kernels before waiting for the device."""
+        v = C.c_double()
+        self._b._check(self._lib.ctox_exec_last_enqueue_us(self._h, C.byref(v)))
+        return v.value
+
     def session_state(self) -> dict:
         pending, poisoned = C.c_int32(), C.c_int32()
         self._b._check(self._lib.ctox_exec_session_state(self._h, C.byref(pending), C.byref(poisoned)))

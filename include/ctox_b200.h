@@ -243,6 +243,16 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
                                   const float *log_decay, const float *beta, const float *state_in,
                                   float *state_out, float *out, uint32_t tokens, uint32_t heads,
                                   uint32_t qk_heads, uint32_t key_dim, uint32_t value_dim);
+/* The same scan with the FP16-resident state of the reference's CUDA candidate
+ * (recurrent_gated_delta_step_f16_state, reference.rs:299-373; backend/cuda_runtime.rs:3514-3900
+ * dispatch_gated_delta_f16[_scan]_device): state_in / state_out are [heads][128][128] binary16;
+ * dot products and update arithmetic stay fp32, every state element is rounded to binary16 when
+ * it is written (after the decay and after the update of every token). 128 x 128 heads only. */
+ctox_status ctox_gated_delta_scan_f16_state(ctox_ctx *ctx, const float *q, const float *k, const float *v,
+                                            const float *log_decay, const float *beta,
+                                            const void *state_in, void *state_out, float *out,
+                                            uint32_t tokens, uint32_t heads, uint32_t qk_heads,
+                                            uint32_t key_dim, uint32_t value_dim);
 /* beta = sigmoid(b), log_decay = -exp(A_log) * softplus(a + dt_bias)
  * (decoder.rs:29-35,881,897-902). a, b, log_decay, beta: [tokens][heads]. */
 ctox_status ctox_gated_delta_prepare(ctox_ctx *ctx, const float *a, const float *b,
@@ -430,6 +440,10 @@ ctox_status ctox_exec_commit_speculative(ctox_exec *exec, uint32_t accepted_draf
 /* pending_accepted: -1, or the accepted depth of the block awaiting commit_speculative;
  * poisoned: 1 after a device error until reset_session. Either pointer may be NULL. */
 ctox_status ctox_exec_session_state(const ctox_exec *exec, int32_t *pending_accepted, int32_t *poisoned);
+/* Host time, in microseconds, that the last decode call spent enqueuing its kernels before it
+ * waited for the device: the launch path's cost, which bounds a block when the shards are small
+ * (the reference bench reports the same split, src/bin/cuda_target_mtp4_graph_bench.rs:36-64). */
+ctox_status ctox_exec_last_enqueue_us(const ctox_exec *exec, double *microseconds);
 ctox_status ctox_exec_position(const ctox_exec *exec, uint64_t *position);
 /* Final hidden state of the last committed position (device -> host), for parity tests. */
 ctox_status ctox_exec_last_hidden(ctox_exec *exec, float *out);

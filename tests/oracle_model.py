@@ -192,6 +192,53 @@ class OracleModel:
             ex.load_vector(G, N.T_MTP_NORM_H, self.mtp_norm_h)
             ex.load_vector(G, N.T_MTP_NORM, self.mtp_norm)
 
+    # ---- the model as a CTOXQ container (tensor names of tensor_contract.rs:70-249)
+    def packed_tensors(self):
+        from ctox_llm_b200.artifact import PackedTensor
+        c = self.cfg
+        code = {self.orc.Q2B64: "q2_b64", self.orc.Q4B64: "q4_b64"}
+        out = []
+
+        def matrix(name, m):
+            out.append(PackedTensor(name, code[m.dtype], [m.rows, m.cols], m.packed.tobytes()))
+            out.append(PackedTensor(f"{name}.s_in", "f16", [m.cols], np.asarray(m.s_in, np.uint8).tobytes()))
+            out.append(PackedTensor(f"{name}.s_out", "f16", [m.rows], np.asarray(m.s_out, np.uint8).tobytes()))
+
+        def vector(name, v, dtype="f32"):
+            v = np.asarray(v, np.float32)
+            data = v.astype("<f2").tobytes() if dtype == "f16" else v.astype("<f4").tobytes()
+            out.append(PackedTensor(name, dtype, [v.size], data))
+
+        matrix("model.language_model.embed_tokens.weight", self.embed)
+        matrix("lm_head.weight", self.lm_head)
+        vector("model.language_model.norm.weight", self.final_norm)
+        for l, L in enumerate(self.layers):
+            prefix = "mtp.layers.0" if l >= c.num_hidden_layers else f"model.language_model.layers.{l}"
+            vector(f"{prefix}.input_layernorm.weight", L["in_ln"])
+            vector(f"{prefix}.post_attention_layernorm.weight", L["post_ln"])
+            if L["full"]:
+                for p in ("q", "k", "v", "o"):
+                    matrix(f"{prefix}.self_attn.{p}_proj.weight", L[p])
+                vector(f"{prefix}.self_attn.q_norm.weight", L["q_norm"])
+                vector(f"{prefix}.self_attn.k_norm.weight", L["k_norm"])
+            else:
+                a = f"{prefix}.linear_attn"
+                for p, key in (("in_proj_qkv", "qkv"), ("in_proj_z", "z"), ("in_proj_a", "a"), ("in_proj_b", "b"),
+                               ("out_proj", "out")):
+                    matrix(f"{a}.{p}.weight", L[key])
+                vector(f"{a}.conv1d.weight", L["conv_w"])
+                vector(f"{a}.A_log", L["a_log"])
+                vector(f"{a}.dt_bias", L["dt_bias"])
+                vector(f"{a}.norm.weight", L["lin_norm"])
+            for p in ("gate", "up", "down"):
+                matrix(f"{prefix}.mlp.{p}_proj.weight", L[p])
+        if c.mtp_num_hidden_layers:
+            matrix("mtp.fc.weight", self.mtp_fc)
+            vector("mtp.pre_fc_norm_embedding.weight", self.mtp_norm_e)
+            vector("mtp.pre_fc_norm_hidden.weight", self.mtp_norm_h)
+            vector("mtp.norm.weight", self.mtp_norm)
+        return out
+
     # ---- scalar evaluation (decoder.rs)
     def reset(self):
         c = self.cfg

@@ -241,3 +241,32 @@ def test_a_peer_that_never_answers_runs_out_the_bounded_wait_and_poisons_the_ses
     finally:
         ex.unload()
         be.close()
+
+
+def test_model_loaded_from_a_ctoxq_container_decodes_like_the_oracle(orc, tmp_path):
+    """ModelExecutor::load from a container file (format.rs / loader.rs): the tiny model written as
+    CTOXQ, opened with checksums on, loaded by tensor name with the fan-out groups joined, must
+    emit the oracle's greedy tokens with speculation on."""
+    from ctox_llm_b200 import artifact as A
+    cfg = tiny_config(max_draft_tokens=3)
+    model = OracleModel(orc, cfg, seed=3)
+    path = str(tmp_path / "tiny.ctoxq")
+    A.write_ctoxq(path, model.packed_tensors())
+    art = A.CtoxqArtifact.open(path)
+    be = ctox.B200Backend(0)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        A.load_into_executor(art, ex)
+        ex.warmup()
+        want, _, _ = model.greedy(PROMPT, 10)
+        ex.prefill(PROMPT)
+        tok, got = PROMPT[-1], []
+        while len(got) < 10:
+            blk = ex.decode(tok, mtp_enabled=True)
+            got += blk.emitted
+            tok = blk.token_id
+        assert got[:10] == want
+    finally:
+        ex.unload()
+        be.close()
+        art.close()
