@@ -965,6 +965,12 @@ ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, co
         EX(tp_peer_reduce_add(ctx, o, c.hidden_size, m, h, e->norm_scratch));
     } else {
         EX(group_sum(e, mv, m, &o));
+        if (!fused_norm) {  // residual add, norm and fragments as one cluster kernel
+            const MvIn nin = next ? mv_in(next) : MvIn{};
+            launch_residual_norm_prep(ctx->stream, h, &o, norm_w, c.rms_norm_epsilon, c.hidden_size, m, xn_out,
+                                      next ? &nin : nullptr, e->norm_scratch);
+            return CTOX_OK;
+        }
         launch_residual_add(ctx->stream, h, &o, c.hidden_size, m, e->norm_scratch);
     }
     if (!fused_norm) {
