@@ -36,6 +36,26 @@ class Matrix:
         self.s_out = rng.uniform(0.75, 1.25, rows).astype(np.float16).view(np.uint8)
 
     @classmethod
+    def random_packed(cls, orc, rng, dtype, rows, cols, s_in=None):
+        """Random canonical blocks drawn directly as bytes (codes uniform, f16 block scales
+        exp(N(-4, 0.5))): what the benchmark's synthetic model holds, cheap enough for full-width
+        matrices. One random chunk of a million blocks is repeated with a block-dependent byte added."""
+        m = cls.__new__(cls)
+        m.dtype, m.rows, m.cols = dtype, rows, cols
+        bb = 34 if dtype == orc.Q4B64 else 18
+        blocks = rows * (cols // 64)
+        chunk = min(blocks, 1 << 20)
+        base = np.frombuffer(rng.bytes(chunk * bb), dtype=np.uint8).reshape(chunk, bb)
+        out = np.tile(base, (-(-blocks // chunk), 1))[:blocks].copy()
+        out += ((np.arange(blocks, dtype=np.uint64) // chunk * 37) & 0xff).astype(np.uint8)[:, None]
+        scales = np.exp(rng.standard_normal(blocks, dtype=np.float32) * 0.5 - 4.0).astype(np.float16)
+        out.view(np.uint16).reshape(blocks, bb // 2)[:, 0] = scales.view(np.uint16)
+        m.packed = out.reshape(-1)
+        m.s_in = s_in if s_in is not None else rng.uniform(0.75, 1.25, cols).astype(np.float16).view(np.uint8)
+        m.s_out = rng.uniform(0.75, 1.25, rows).astype(np.float16).view(np.uint8)
+        return m
+
+    @classmethod
     def constant(cls, orc, dtype, rows, cols, value):
         """Every weight equal to `value`, unit recovery scales: the matrices of the reference's
         decoder fixture (decoder.rs:1505-1530 `recovered_matrix`)."""
@@ -86,13 +106,19 @@ def concat(mats):
 
 
 class OracleModel:
-    def __init__(self, orc, cfg, seed=0, loud_tokens=()):
+    def __init__(self, orc, cfg, seed=0, loud_tokens=(), packed_random=False, threads=1, tied_head=False):
         """loud_tokens: lm_head rows whose output scale is raised so far above the rest that the
         greedy token is nearly always one of them; target and MTP drafts then agree often enough
         for natural (unforced) acceptance to be exercised on a random-init model."""
         self.orc, self.cfg = orc, cfg
+        self.threads = threads  # host threads of the oracle's matvec (rows split; same arithmetic per row)
         self.kv_bf16 = cfg.kv_dtype == N.BF16  # the cache stores K and V rounded to bfloat16
         rng = np.random.default_rng(seed)
+        if packed_random:  # full-width models: draw the packed bytes directly instead of quantising floats
+            make = lambda orc_, rng_, dtype, rows, cols, s_in=None, scale=1.0: Matrix.random_packed(
+                orc_, rng_, dtype, rows, cols, s_in)
+        else:
+            make = Matrix
         c = cfg
         H, F = c.hidden_size, c.intermediate_size
         self.qw, self.kvw = c.num_attention_heads * c.head_dim, c.num_key_value_heads * c.head_dim
@@ -101,8 +127,8 @@ class OracleModel:
         self.channels = 2 * self.kw + self.vw
         Q4, Q2 = orc.Q4B64, orc.Q2B64
         norm = lambda n: (rng.standard_normal(n) * 0.1).astype(np.float32)
-        self.embed = Matrix(orc, rng, Q4, c.vocab_size, H, scale=16.0)
-        self.lm_head = Matrix(orc, rng, Q4, c.vocab_size, H, scale=4.0)
+        self.embed = make(orc, rng, Q4, c.vocab_size, H, scale=16.0)
+        self.lm_head = self.embed if tied_head else make(orc, rng, Q4, c.vocab_size, H, scale=4.0)
         if len(loud_tokens):
             so = self.lm_head.s_out.view(np.float16).copy()
             so[list(loud_tokens)] = np.float16(8.0)
@@ -114,28 +140,28 @@ class OracleModel:
             L = {"full": full, "in_ln": norm(H), "post_ln": norm(H)}
             sh = rng.uniform(0.75, 1.25, H).astype(np.float16).view(np.uint8)
             if full:
-                L["q"] = Matrix(orc, rng, Q4, 2 * self.qw, H, sh, 2.0)
-                L["k"] = Matrix(orc, rng, Q4, self.kvw, H, sh, 2.0)
-                L["v"] = Matrix(orc, rng, Q4, self.kvw, H, sh, 2.0)
-                L["o"] = Matrix(orc, rng, Q4, H, self.qw, None, 2.0)
+                L["q"] = make(orc, rng, Q4, 2 * self.qw, H, sh, 2.0)
+                L["k"] = make(orc, rng, Q4, self.kvw, H, sh, 2.0)
+                L["v"] = make(orc, rng, Q4, self.kvw, H, sh, 2.0)
+                L["o"] = make(orc, rng, Q4, H, self.qw, None, 2.0)
                 L["q_norm"], L["k_norm"] = norm(c.head_dim), norm(c.head_dim)
             else:
-                L["qkv"] = Matrix(orc, rng, Q4, self.channels, H, sh, 2.0)
-                L["z"] = Matrix(orc, rng, Q4, self.vw, H, sh, 2.0)
-                L["a"] = Matrix(orc, rng, Q4, c.linear_num_value_heads, H, sh, 2.0)
-                L["b"] = Matrix(orc, rng, Q4, c.linear_num_value_heads, H, sh, 2.0)
-                L["out"] = Matrix(orc, rng, Q4, H, self.vw, None, 2.0)
+                L["qkv"] = make(orc, rng, Q4, self.channels, H, sh, 2.0)
+                L["z"] = make(orc, rng, Q4, self.vw, H, sh, 2.0)
+                L["a"] = make(orc, rng, Q4, c.linear_num_value_heads, H, sh, 2.0)
+                L["b"] = make(orc, rng, Q4, c.linear_num_value_heads, H, sh, 2.0)
+                L["out"] = make(orc, rng, Q4, H, self.vw, None, 2.0)
                 L["conv_w"] = (rng.standard_normal(self.channels * c.linear_conv_kernel_dim) * 0.5).astype(np.float32)
                 L["a_log"] = (rng.standard_normal(c.linear_num_value_heads) * 0.5).astype(np.float32)
                 L["dt_bias"] = (rng.standard_normal(c.linear_num_value_heads) * 0.5).astype(np.float32)
                 L["lin_norm"] = (1.0 + rng.standard_normal(self.vd) * 0.1).astype(np.float32)
             sg = rng.uniform(0.75, 1.25, H).astype(np.float16).view(np.uint8)
-            L["gate"] = Matrix(orc, rng, Q2, F, H, sg, 2.0)
-            L["up"] = Matrix(orc, rng, Q2, F, H, sg, 2.0)
-            L["down"] = Matrix(orc, rng, Q2, H, F, None, 2.0)
+            L["gate"] = make(orc, rng, Q2, F, H, sg, 2.0)
+            L["up"] = make(orc, rng, Q2, F, H, sg, 2.0)
+            L["down"] = make(orc, rng, Q2, H, F, None, 2.0)
             self.layers.append(L)
         if c.mtp_num_hidden_layers:
-            self.mtp_fc = Matrix(orc, rng, Q4, H, 2 * H, None, 2.0)
+            self.mtp_fc = make(orc, rng, Q4, H, 2 * H, None, 2.0)
             self.mtp_norm_e, self.mtp_norm_h, self.mtp_norm = norm(H), norm(H), norm(H)
         self.reset()
 
@@ -252,7 +278,7 @@ class OracleModel:
                                    "rec": np.zeros(c.linear_num_value_heads * self.kd * self.vd, np.float32)})
 
     def proj(self, m, x):
-        return self.orc.fused_matvec(m.op(self.orc, x))
+        return self.orc.fused_matvec(m.op(self.orc, x), threads=self.threads)
 
     def norm(self, x, w):
         return self.orc.rms_norm_1p_weight(x, 1, x.size, w, self.cfg.rms_norm_epsilon)
@@ -405,7 +431,7 @@ def reference_fixture_model(orc, full_layer):
         mtp_num_hidden_layers=1, max_context_tokens=12, kv_page_tokens=16, kv_dtype=N.F32,
         max_draft_tokens=4, draft_vocab=0)
     m = OracleModel.__new__(OracleModel)
-    m.orc, m.cfg, m.kv_bf16 = orc, cfg, False
+    m.orc, m.cfg, m.kv_bf16, m.threads = orc, cfg, False, 1
     m.qw, m.kvw, m.kd, m.vd = 64, 32, 32, 32
     m.kw, m.vw = 32, 64
     m.channels = 2 * m.kw + m.vw

@@ -177,8 +177,9 @@ def test_f16_resident_state_matches_oracle(be, orc):
     assert diff.mean() < 5e-3, diff.mean()  # measured 1.2e-3 after 5 tokens
     a = got_state.view(np.float16).astype(np.float32)
     b = st.view(np.float16).astype(np.float32)
-    # a one-step difference at one token can grow to a few steps over the following tokens
-    assert np.all(np.abs(a - b)[diff] <= np.abs(b[diff]) * 2.0 ** -8 + 2.0 ** -22)
+    # a one-step difference at one token is carried (and rescaled by the decay) through the following
+    # tokens: bound it by one binary16 step at the magnitude of the largest state element
+    assert np.max(np.abs(a - b)) <= np.max(np.abs(b)) * 2.0 ** -10
     assert torch.equal(ds.cpu(), torch.from_numpy(bits.view(np.float16).copy())), "state_in must stay untouched"
     # fp32 state of the same inputs stays close (the drift the reference accepts for this mode)
     _, st32, _ = run_scan(be, q, k, v, g, beta, state, tokens, heads, qk, 128, 128)

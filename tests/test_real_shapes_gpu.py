@@ -130,3 +130,56 @@ def test_config3_lm_head_with_a_depth3_tree(be, orc):
         assert be.device_error() == 0
     finally:
         mv.destroy()
+
+
+def test_config4_shapes_two_layer_model_logits_tokens_and_mtp(orc):
+    """The layer shapes of BASELINE config 4 (hidden 5120, FFN 17408, 24 / 4 heads of 256, 16 / 48 linear
+    heads of 128, vocabulary 248 320, Q4 attention / head and Q2 FFN weights, bf16 KV, 40 000-row draft
+    head) on a model of one linear-attention and one full-attention layer plus the MTP layer, random
+    packed weights as the benchmark's synthetic model holds them: target logits within rel-L2 1e-3
+    and greedy tokens equal for a few steps, then speculative blocks checked like tests/test_mtp_gpu.py
+    (MTP hidden of every pair, drafts, accepted prefix, committed hidden)."""
+    from ctox_llm_b200 import native as N
+    from oracle_model import DeviceChainOracle, OracleModel
+    cfg = ctox.qwen38_27b_config(num_hidden_layers=2, full_attention_interval=2, max_context_tokens=256,
+                                 max_draft_tokens=3, draft_vocab=40_000)
+    model = OracleModel(orc, cfg, seed=11, packed_random=True, threads=THREADS, tied_head=True)
+    ids = (np.arange(cfg.draft_vocab, dtype=np.int64) * (cfg.vocab_size // cfg.draft_vocab))
+    be = ctox.B200Backend(0)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex)
+        ex.load_vector(N.LAYER_GLOBAL, N.T_DRAFT_IDS, ids.astype(np.uint32))
+        ex.warmup()
+        ex.keep_logits(True)
+        prompt = [17, 40_123, 200_001, 5, 99_999, 248_000, 3]
+        want_tokens, want_logits, _ = model.greedy(prompt, 3)
+        ex.prefill(prompt)
+        tok = prompt[-1]
+        for i in range(3):
+            blk = ex.decode(tok, mtp_enabled=False)
+            err = rel_l2(ex.last_logits(0), want_logits[i])
+            assert err <= 1e-3, (i, err)
+            assert blk.token_id == want_tokens[i]
+            tok = blk.token_id
+        dev = DeviceChainOracle(model, cfg.max_draft_tokens, ids)
+        ex.prefill(prompt)
+        dev.prefill(prompt)
+        tok = prompt[-1]
+        for block, force in enumerate((-1, 2, -1)):
+            blk = ex.decode(tok, mtp_enabled=True, force_accept=force)
+            want = dev.decode(tok, force_accept=force, given_drafts=blk.draft_tokens)
+            for j, (g, w) in enumerate(zip(ex.last_mtp_hidden(), want["mtp_hidden"])):
+                assert rel_l2(g, w) <= 1e-3, ("mtp hidden", block, j, rel_l2(g, w))
+            for i in range(cfg.max_draft_tokens):
+                if blk.draft_tokens[i] != want["drafts"][i]:  # only where the oracle's top two are a near-tie
+                    lg = want["draft_logits"][i]
+                    a, b = int(np.searchsorted(ids, blk.draft_tokens[i])), int(np.searchsorted(ids, want["drafts"][i]))
+                    assert abs(float(lg[a]) - float(lg[b])) <= 1e-4 * max(abs(float(lg[a])), abs(float(lg[b])))
+            assert blk.accepted_draft_tokens == want["accepted"] and blk.token_id == want["next_token"], block
+            assert rel_l2(ex.last_hidden(), want["final_hidden"]) <= 1e-3
+            tok = blk.token_id
+        assert be.device_error() == 0
+    finally:
+        ex.unload()
+        be.close()
