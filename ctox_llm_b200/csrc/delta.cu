@@ -62,7 +62,6 @@ __device__ __forceinline__ void delta_scan128_body(
     const int src = head / (heads / qk_heads);  // repeat_heads: decoder.rs:47-65
     __shared__ float qs[kDeltaDim], ks[kDeltaDim];
     __shared__ float red[2][4][kDeltaSlice];
-    __shared__ float norms[2];
 
     float s[32];
     const S *sin_ = state_in + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
@@ -74,8 +73,6 @@ __device__ __forceinline__ void delta_scan128_body(
         const float *qt = q + ((size_t)tok * qk_heads + src) * kDeltaDim;
         const float *kt = k + ((size_t)tok * qk_heads + src) * kDeltaDim;
         const float qv = qt[threadIdx.x], kv = kt[threadIdx.x];
-        qs[threadIdx.x] = qv;
-        ks[threadIdx.x] = kv;
         float q2 = qv * qv, k2 = kv * kv;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -87,22 +84,19 @@ __device__ __forceinline__ void delta_scan128_body(
             red[0][warp][1] = k2;
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            const float sq = red[0][0][0] + red[0][1][0] + red[0][2][0] + red[0][3][0];
-            const float sk = red[0][0][1] + red[0][1][1] + red[0][2][1] + red[0][3][1];
-            norms[0] = 1.0f / sqrtf(sq + kL2Eps);
-            norms[1] = 1.0f / sqrtf(sk + kL2Eps);
-        }
-        __syncthreads();
-        const float q_inv = norms[0], k_inv = norms[1];
+        const float q_inv = 1.0f / sqrtf(red[0][0][0] + red[0][1][0] + red[0][2][0] + red[0][3][0] + kL2Eps);
+        const float k_inv = 1.0f / sqrtf(red[0][0][1] + red[0][1][1] + red[0][2][1] + red[0][3][1] + kL2Eps);
+        ks[threadIdx.x] = kv * k_inv;
+        qs[threadIdx.x] = qv * q_inv * query_scale;
         const float decay = expf(log_decay[(size_t)tok * heads + head]);
         const float b = beta[(size_t)tok * heads + head];
         const float vj = v[((size_t)tok * heads + head) * kDeltaDim + col];
+        __syncthreads();
         float mem = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             s[i] = state_round<S>(s[i] * decay);
-            mem += s[i] * ks[warp * 32 + i] * k_inv;
+            mem += s[i] * ks[warp * 32 + i];
         }
         red[1][warp][lane] = mem;
         __syncthreads();
@@ -110,8 +104,8 @@ __device__ __forceinline__ void delta_scan128_body(
         float o = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            s[i] = state_round<S>(s[i] + ks[warp * 32 + i] * k_inv * delta);
-            o += s[i] * qs[warp * 32 + i] * q_inv * query_scale;
+            s[i] = state_round<S>(s[i] + ks[warp * 32 + i] * delta);
+            o += s[i] * qs[warp * 32 + i];
         }
         red[0][warp][lane] = o;
         __syncthreads();
@@ -254,10 +248,11 @@ constexpr int kLaMaxPos = 8;
 __global__ void __launch_bounds__(512, 1) k_linear_attention(LinearAttnArgs a, int npos) {
     pdl_launch();
     __shared__ float qs[kLaMaxPos][kDeltaDim], ks[kLaMaxPos][kDeltaDim], vs[kLaMaxPos][kDeltaDim];
-    __shared__ float zs[kLaMaxPos][kDeltaDim], core[kLaMaxPos][kDeltaDim];
-    __shared__ float gs[kLaMaxPos], bs[kLaMaxPos], q_inv[kLaMaxPos], k_inv[kLaMaxPos];
-    __shared__ float nred[2][4];
-    __shared__ float red[4][4][kDeltaSlice];  // [slice][row group][column]
+    __shared__ float zs[kLaMaxPos][kDeltaDim];
+    __shared__ float gs[kLaMaxPos], bs[kLaMaxPos];
+    __shared__ float nred[kLaMaxPos][2][4];
+    __shared__ float redm[2][4][4][kDeltaSlice];
+    __shared__ float redo[kLaMaxPos][4][4][kDeltaSlice];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t head = blockIdx.x, rep = a.value_heads / a.qk_heads, khead = head / rep;
     const bool owns_qk = head % rep == 0;
@@ -338,51 +333,57 @@ __global__ void __launch_bounds__(512, 1) k_linear_attention(LinearAttnArgs a, i
         }
     }
     __syncthreads();
-    // L2 norms of q and k per position, with the reduction tree of the stand-alone scan: value d in
-    // lane d % 32 of warp d / 32, butterfly, then the four warp sums in order
-    for (int m = 0; m < npos; ++m) {
-        if (warp < 8) {
+    // L2 norms of q and k for all positions at once, with the reduction tree of the stand-alone scan
+    // (value d in lane d % 32 of warp d / 32, butterfly, then the four warp sums in order); then the
+    // normalised key and the scaled query replace q and k in shared memory, as in the scan
+    if (warp < 8) {
+        for (int m = 0; m < npos; ++m) {
             const float x = warp < 4 ? qs[m][warp * 32 + lane] : ks[m][(warp - 4) * 32 + lane];
             float x2 = x * x;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) x2 += __shfl_xor_sync(0xffffffffu, x2, o);
-            if (lane == 0) nred[warp >> 2][warp & 3] = x2;
+            if (lane == 0) nred[m][warp >> 2][warp & 3] = x2;
         }
-        __syncthreads();
-        if (tid == 0) {
-            q_inv[m] = 1.0f / sqrtf(nred[0][0] + nred[0][1] + nred[0][2] + nred[0][3] + kL2Eps);
-            k_inv[m] = 1.0f / sqrtf(nred[1][0] + nred[1][1] + nred[1][2] + nred[1][3] + kL2Eps);
-        }
-        __syncthreads();
     }
-
-    // ---- 2. recurrence
+    __syncthreads();
     const float query_scale = 1.0f / sqrtf((float)kDeltaDim);
+    if (tid < 256) {  // thread d < 128: q element d of every position; 128..255: k element d - 128
+        const uint32_t d = tid & 127;
+        for (int m = 0; m < npos; ++m) {
+            if (tid < 128) {
+                const float qi = 1.0f / sqrtf(nred[m][0][0] + nred[m][0][1] + nred[m][0][2] + nred[m][0][3] + kL2Eps);
+                qs[m][d] = qs[m][d] * qi * query_scale;
+            } else {
+                const float ki = 1.0f / sqrtf(nred[m][1][0] + nred[m][1][1] + nred[m][1][2] + nred[m][1][3] + kL2Eps);
+                ks[m][d] = ks[m][d] * ki;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- 2. recurrence: one barrier per position (redm double-buffered by parity, the output
+    // partial sums kept per position and added up in phase 3)
     for (int m = 0; m < npos; ++m) {
-        const float qi = q_inv[m], ki = k_inv[m];
         const float decay = expf(gs[m]), b = bs[m], vj = vs[m][col];
         float mem = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
             s[i] *= decay;
-            mem += s[i] * ks[m][rg * 32 + i] * ki;
+            mem += s[i] * ks[m][rg * 32 + i];
         }
-        red[slice][rg][lane] = mem;
+        redm[m & 1][slice][rg][lane] = mem;
         __syncthreads();
-        const float delta = (vj - (red[slice][0][lane] + red[slice][1][lane] + red[slice][2][lane] + red[slice][3][lane])) * b;
-        __syncthreads();
+        const float delta = (vj - (redm[m & 1][slice][0][lane] + redm[m & 1][slice][1][lane] +
+                                   redm[m & 1][slice][2][lane] + redm[m & 1][slice][3][lane])) * b;
         float o = 0.f;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            s[i] += ks[m][rg * 32 + i] * ki * delta;
-            o += s[i] * qs[m][rg * 32 + i] * qi * query_scale;
+            s[i] += ks[m][rg * 32 + i] * delta;
+            o += s[i] * qs[m][rg * 32 + i];
         }
-        red[slice][rg][lane] = o;
-        __syncthreads();
-        if (rg == 0)
-            core[m][col] = red[slice][0][lane] + red[slice][1][lane] + red[slice][2][lane] + red[slice][3][lane];
-        __syncthreads();
+        redo[m][slice][rg][lane] = o;
     }
+    __syncthreads();
     {
         float *sout = a.state_out + ((size_t)head * kDeltaDim + rg * 32) * kDeltaDim + col;
 #pragma unroll
@@ -392,7 +393,16 @@ __global__ void __launch_bounds__(512, 1) k_linear_attention(LinearAttnArgs a, i
     // ---- 3. gated norm and fragments: warp m takes position m, four values per lane
     if (warp < (uint32_t)npos) {
         const int m = warp;
-        const float4 c = *reinterpret_cast<const float4 *>(&core[m][lane * 4]);
+        // columns lane * 4 .. + 3 lie in slice lane / 8; the four row groups in order
+        float4 c = *reinterpret_cast<const float4 *>(&redo[m][lane >> 3][0][(lane & 7) * 4]);
+#pragma unroll
+        for (int r = 1; r < 4; ++r) {
+            const float4 t = *reinterpret_cast<const float4 *>(&redo[m][lane >> 3][r][(lane & 7) * 4]);
+            c.x += t.x;
+            c.y += t.y;
+            c.z += t.z;
+            c.w += t.w;
+        }
         const float4 g = *reinterpret_cast<const float4 *>(&zs[m][lane * 4]);
         float sq = c.x * c.x + c.y * c.y + c.z * c.z + c.w * c.w;
 #pragma unroll

@@ -584,9 +584,10 @@ class DeviceChainOracle:
                 mtp_hidden.append(fh)
         followed = drafts if given_drafts is None else [int(d) for d in given_drafts]
         # verify: the target over [token, drafts...] while the prefix is accepted
-        hiddens, target_tokens, accepted = [], [], []
+        hiddens, target_tokens, accepted, target_logits = [], [], [], []
         hidden, logits = m.decode_target_step(int(token))
         hiddens.append(hidden)
+        target_logits.append(logits)
         target_tokens.append(m.orc.greedy_token(logits))
         for i in range(self.k):
             ok = followed[i] == target_tokens[-1] if force_accept < 0 else i < force_accept
@@ -595,10 +596,11 @@ class DeviceChainOracle:
             accepted.append(followed[i])
             hidden, logits = m.decode_target_step(followed[i])
             hiddens.append(hidden)
+            target_logits.append(logits)
             target_tokens.append(m.orc.greedy_token(logits))
         next_token = target_tokens[-1]
         self.owed = [(accepted[j], hiddens[j]) for j in range(len(accepted))]
         self.last_hidden = hiddens[-1]
         return {"mtp_hidden": mtp_hidden, "draft_logits": draft_logits, "drafts": drafts,
                 "target_tokens": target_tokens, "accepted": accepted, "next_token": next_token,
-                "final_hidden": hiddens[-1]}
+                "final_hidden": hiddens[-1], "target_logits": target_logits}

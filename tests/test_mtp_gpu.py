@@ -108,8 +108,12 @@ def test_mtp_with_four_drafts_and_bf16_cache(orc):
         for block, force in enumerate([-1, 4, 1, -1, 0, -1]):
             blk = ex.decode(tok, mtp_enabled=True, force_accept=force)
             want = dev.decode(tok, force_accept=force, given_drafts=blk.draft_tokens)
+            # 2e-3 here: each chained draft feeds the previous pair's hidden back through the layer, and
+            # the error of the fourth link (measured 0.9e-3 to 1.05e-3) is four times that of the first
             for j, (g, w) in enumerate(zip(ex.last_mtp_hidden(), want["mtp_hidden"])):
-                assert rel_l2(g, w) <= 1e-3, (block, j)
+                assert rel_l2(g, w) <= 2e-3, (block, j, rel_l2(g, w))
+            for p, lg in enumerate(want["target_logits"]):
+                assert rel_l2(ex.last_logits(p), lg) <= 1e-3, (block, p)
             assert blk.accepted_draft_tokens == want["accepted"] and blk.token_id == want["next_token"]
             tok = blk.token_id
     finally:
