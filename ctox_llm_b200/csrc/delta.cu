@@ -288,48 +288,91 @@ __global__ void __launch_bounds__(512, 1) k_linear_attention(LinearAttnArgs a, i
     pdl_wait();
 
     // ---- 1. conv + SiLU, z, decay, beta
-    if (tid < 384) {
-        const uint32_t d = cd;
-        const bool store = part == 2 || owns_qk;
-        for (int m = 0; m < npos; ++m) {
-            const float x = out_of(a.fan, ch, m);
-            if (store) a.conv_in[(size_t)m * channels + ch] = x;
+    {
+        // One row of the input projection per thread: conv threads their channel, the last 128 their
+        // gate column. Where the projection left stream-K pieces (at most eight per value), their
+        // offsets are the same for every position: they are formed once, and the pieces of position
+        // m + 1 are in flight while position m is worked on. Same additions in the same order as out_of.
+        const uint32_t row = tid < 384 ? ch : channels + head * kDeltaDim + (tid - 384);
+        const MvOut &o = a.fan;
+        uint32_t total = 0, off[8];
+        const float *first = nullptr;
+        if (!o.plain && o.warps_per_slice) {
+            const uint32_t n = piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs);
+            total = o.slices * n;
+            first = o.partial + (size_t)(row >> 5) * o.slices * o.max_pieces * 256 + (row & 31);
+            uint32_t sl = 0, q = 0;
 #pragma unroll
-            for (int j = 0; j < 7; ++j)
-                if ((uint32_t)j + 1 < K) st[j] = st[j + 1];
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if ((uint32_t)j + 1 == K) st[j] = x;
-            float sum = 0.f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-                if ((uint32_t)j < K) sum += st[j] * cw[j];
-            const float y = silu_f(sum);
-            if (part == 0) {
-                qs[m][d] = y;
-                if (store) a.q[(size_t)m * a.key_width + khead * kDeltaDim + d] = y;
-            } else if (part == 1) {
-                ks[m][d] = y;
-                if (store) a.k[(size_t)m * a.key_width + khead * kDeltaDim + d] = y;
-            } else {
-                vs[m][d] = y;
-                a.v[(size_t)m * a.value_width + head * kDeltaDim + d] = y;
+            for (int j = 0; j < 8; ++j) {
+                off[j] = (sl * o.max_pieces + q) * 256;
+                if (++q == n) {
+                    q = 0;
+                    ++sl;
+                }
             }
         }
-    } else {
-        const uint32_t d = tid - 384;
-        for (int m = 0; m < npos; ++m) zs[m][d] = out_of(a.fan, channels + head * kDeltaDim + d, m);
-        if (d < (uint32_t)npos) {
-            const float x = out_of(a.fan, channels + a.value_width + head, d) + a.dt_bias[head];
-            const float sp = x > 20.0f ? x : log1pf(expf(x));  // decoder.rs:29-35
-            const float g = -expf(a.a_log[head]) * sp;
-            gs[d] = g;
-            a.log_decay[(size_t)d * a.value_heads + head] = g;
-        } else if (d >= 32 && d < 32 + (uint32_t)npos) {
-            const uint32_t m = d - 32;
-            const float b = 1.0f / (1.0f + expf(-out_of(a.fan, channels + a.value_width + a.value_heads + head, m)));
-            bs[m] = b;
-            a.beta[(size_t)m * a.value_heads + head] = b;
+        const bool pieces = total >= 1 && total <= 8;  // otherwise the general fetch per position
+        const float so = pieces && o.s_out ? o.s_out[row] : 1.0f;
+        float buf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) buf[j] = (pieces && (uint32_t)j < total) ? first[off[j]] : 0.f;
+        const bool store = part == 2 || owns_qk;
+        for (int m = 0; m < npos; ++m) {
+            float x = 0.f;
+            if (pieces) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if ((uint32_t)j < total) x += buf[j];
+                if (o.s_out) x *= so;
+                if (m + 1 < npos) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) buf[j] = (uint32_t)j < total ? first[off[j] + (m + 1) * 32] : 0.f;
+                }
+            } else {
+                x = out_of(o, row, m);
+            }
+            if (tid < 384) {
+                const uint32_t d = cd;
+                if (store) a.conv_in[(size_t)m * channels + ch] = x;
+#pragma unroll
+                for (int j = 0; j < 7; ++j)
+                    if ((uint32_t)j + 1 < K) st[j] = st[j + 1];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if ((uint32_t)j + 1 == K) st[j] = x;
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if ((uint32_t)j < K) sum += st[j] * cw[j];
+                const float y = silu_f(sum);
+                if (part == 0) {
+                    qs[m][d] = y;
+                    if (store) a.q[(size_t)m * a.key_width + khead * kDeltaDim + d] = y;
+                } else if (part == 1) {
+                    ks[m][d] = y;
+                    if (store) a.k[(size_t)m * a.key_width + khead * kDeltaDim + d] = y;
+                } else {
+                    vs[m][d] = y;
+                    a.v[(size_t)m * a.value_width + head * kDeltaDim + d] = y;
+                }
+            } else {
+                zs[m][tid - 384] = x;
+            }
+        }
+        if (tid >= 384) {
+            const uint32_t d = tid - 384;
+            if (d < (uint32_t)npos) {
+                const float x = out_of(a.fan, channels + a.value_width + head, d) + a.dt_bias[head];
+                const float sp = x > 20.0f ? x : log1pf(expf(x));  // decoder.rs:29-35
+                const float g = -expf(a.a_log[head]) * sp;
+                gs[d] = g;
+                a.log_decay[(size_t)d * a.value_heads + head] = g;
+            } else if (d >= 32 && d < 32 + (uint32_t)npos) {
+                const uint32_t m = d - 32;
+                const float b = 1.0f / (1.0f + expf(-out_of(a.fan, channels + a.value_width + a.value_heads + head, m)));
+                bs[m] = b;
+                a.beta[(size_t)m * a.value_heads + head] = b;
+            }
         }
     }
     __syncthreads();
