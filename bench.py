@@ -271,27 +271,6 @@ def decode_config_bytes(cfg, positions):
     return weights, kv, state
 
 
-def launches_per_block(cfg, world=1):
-    """Kernels of this library launched by one speculative block on one GPU, counted from the
-    executor's structure. A pass of m positions: per linear-attention layer 8 (input projection, the
-    layer's one linear-attention kernel, out_proj, residual, gate/up, SwiGLU, down, residual), per
-    full-attention layer 10 (attention pre, attention, split merge instead of the one kernel), plus
-    2 norm kernels per layer when m > 2 (with fewer positions the projections normalise in their
-    prologue); 3 to start and end a pass. Head: 4 (lm_head, statistics, merge, acceptance); commit: 1.
-    An MTP draft pass: that layer plus 11 around it (embedding rows, input norm, fc, residual, final
-    norm, fragments, draft head, finish, 2 argmax). A tensor-parallel group adds nothing: the group
-    sum is the residual kernel."""
-    del world
-    n_full = cfg.num_hidden_layers // cfg.full_attention_interval
-    n_lin = cfg.num_hidden_layers - n_full
-    m = cfg.max_draft_tokens + 1
-    norm = 2 if m > 2 else 0
-    target = n_lin * (8 + norm) + n_full * (10 + norm) + 3 + 4 + 1
-    mtp = cfg.max_draft_tokens * (10 + 11)
-    return target + mtp
-
-
-
 def tp_parity_check(be, local, rank, world, drafts):
     """Outside the timed region: a 4-layer model of the full widths, sharded over the group, against
     the same model unsharded on rank 0 (synthetic tensors are functions of the global index, so the
@@ -391,6 +370,7 @@ def run_decode(args):
         torch.cuda.synchronize()
 
     host_enqueue_ms = [0.0]
+    counted_launches = [0]
 
     def run_blocks(n_blocks, mtp, force, timed):
         """Returns (device ms, wall s, tokens emitted, drafts accepted) for n_blocks decode calls."""
@@ -404,6 +384,7 @@ def run_decode(args):
         enqueue_us = 0.0
         ev0.record(stream)
         t0 = time.perf_counter()
+        launches0 = be.kernel_launches()
         for _ in range(n_blocks):
             # decode + commit_speculative: the two calls of the executor interface per block
             blk = ex.decode(tok, mtp_enabled=mtp, force_accept=force)
@@ -412,6 +393,7 @@ def run_decode(args):
             accepted += len(blk.accepted_draft_tokens)
             enqueue_us += ex.last_enqueue_us()
         host_enqueue_ms[0] = enqueue_us / n_blocks * 1e-3
+        counted_launches[0] = be.kernel_launches() - launches0  # the library's own count of its launches
         wall = time.perf_counter() - t0
         ev1.record(stream)
         barrier()
@@ -421,7 +403,7 @@ def run_decode(args):
     if rank == 0:
         sampler.start()
     ms, wall, emitted, accepted = run_blocks(args.steps, True, -1, True)
-    enqueue_ms = host_enqueue_ms[0]
+    enqueue_ms, timed_launches = host_enqueue_ms[0], counted_launches[0]
     clocks = sampler.stop() if rank == 0 else None
     buckets, plain = {}, None
     if not args.quick:
@@ -507,7 +489,7 @@ def run_decode(args):
                     "h2d_bytes_per_step": 4 + 4 * (emitted / args.steps), "d2h_bytes_per_step": 292 + 4,
                     "note": "decode() + commit_speculative() take a host token and return a host record; "
                             "same calls, wall clock"},
-            "gpu_launches": launches_per_block(cfg, world) * args.steps,
+            "gpu_launches": timed_launches,
             "clocks": clocks,
         }
         line.update(tp_report)
@@ -570,8 +552,10 @@ def run_b200(args):
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         ev0.record(stream)
+        launches0 = be.kernel_launches()
         for i in range(args.steps):
             step(i)
+        timed_launches = be.kernel_launches() - launches0
         ev1.record(stream)
     barrier()
     ms = ev0.elapsed_time(ev1)
@@ -621,7 +605,7 @@ def run_b200(args):
             "e2e": {"value": ALGO_BYTES * e2e_steps * world / e2e_s / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": Q4_COLS * 4, "d2h_bytes_per_step": Q4_ROWS * 4 + 4,
                     "us_per_step": e2e_s / e2e_steps * 1e6},
-            "gpu_launches": 2 * args.steps,
+            "gpu_launches": timed_launches,
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
@@ -657,6 +641,7 @@ def run_micro(args):
     sampler.start()
     line = {"n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic"}
+    launches0 = be.kernel_launches()
     with torch.cuda.stream(stream):
         if args.workload in ("matvec", "q2_matvec"):
             dtype, rows, cols, pos = (("q2", 5120, 17408, 1) if args.workload == "q2_matvec"
@@ -671,7 +656,7 @@ def run_micro(args):
                                   "frac": r["frac"], "peak_kind": r["peak_kind"], "kernel": "k_matvec_stream",
                                   "kernel_us": r["kernel_us"], "frac_pipelined": r["frac_pipelined"],
                                   "traffic": None},
-                        gpu_launches=2 * args.steps * (1 + (pos > 8)))
+                        )
         elif args.workload == "verify_layer":
             sweep = {}
             for m in (1, 2, 4, 8, 16):
@@ -692,8 +677,7 @@ def run_micro(args):
                         sweep=sweep,
                         roofline={"bound": "hbm", "achieved": 130908160 / (ref["kernel_us_per_layer"] * 1e-6) / 1e9,
                                   "peak": peak, "unit": "GB/s", "frac": ref["kernel_frac"],
-                                  "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (M = 4)", "traffic": None},
-                        gpu_launches=0)
+                                  "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (M = 4)", "traffic": None})
         else:  # gated_delta
             heads, qk, layers = 48, 16, 48
             dev = f"cuda:{local}"
@@ -738,8 +722,9 @@ def run_micro(args):
                         sweep=res,
                         roofline={"bound": "hbm", "achieved": res["T4"]["gbs"], "peak": peak, "unit": "GB/s",
                                   "frac": res["T4"]["frac"], "peak_kind": f"of {peak_kind}",
-                                  "kernel": "k_gated_delta_scan128 (48 launches per step)", "traffic": None},
-                        gpu_launches=48 * args.steps * 2)
+                                  "kernel": "k_gated_delta_scan128 (48 launches per step)", "traffic": None})
+    # the library's own count: every launch of this run, warm-up and set-up (weight repacking) included
+    line["gpu_launches"] = be.kernel_launches() - launches0
     line["clocks"] = sampler.stop()
     line["e2e"] = None
     line["cpu_baseline"] = None

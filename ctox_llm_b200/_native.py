@@ -136,6 +136,7 @@ SIGNATURES = {
     "ctox_tp_debug_silent_peers": (C.c_int32, [C.c_void_p, C.c_int32, C.c_uint64]),
     "ctox_ctx_allocated_bytes": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "ctox_ctx_device_error": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "ctox_kernel_launches": (C.c_uint64, []),
     "ctox_ctx_kernel_timing": (C.c_int32, [C.c_void_p, C.c_int32]),
     "ctox_ctx_kernel_timing_read": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double),
                                                 C.POINTER(C.c_uint64)]),

@@ -228,6 +228,10 @@ class B200Backend:
         self._check(self._lib.ctox_ctx_device_error(self._ctx, C.byref(v)))
         return v.value
 
+    def kernel_launches(self) -> int:
+        """Kernels this library has enqueued in this process so far."""
+        return int(self._lib.ctox_kernel_launches())
+
     def kernel_timing(self, enable: bool) -> None:
         self._check(self._lib.ctox_ctx_kernel_timing(self._ctx, int(enable)))
 

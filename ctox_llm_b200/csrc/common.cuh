@@ -97,6 +97,9 @@ void timing_end(ctox_ctx *ctx);
 // pdl_launch() lets the next kernel in the stream be scheduled. CTOX_PDL=0 in the environment
 // turns the early start off (every launch then serialises as usual).
 bool pdl_enabled();
+// Kernels enqueued through launch_pdl / launch_pdl_cluster by this process (every kernel of the
+// decode path goes through them); read by ctox_kernel_launches().
+void count_launch();
 #ifdef __CUDACC__
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
@@ -114,6 +117,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    count_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
@@ -136,6 +140,7 @@ inline cudaError_t launch_pdl_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
+    count_launch();
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 #endif

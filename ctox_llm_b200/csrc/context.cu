@@ -1,4 +1,5 @@
 // Context lifecycle and allocation accounting of libctox_b200.
+#include <atomic>
 #include "common.cuh"
 
 #include <cmath>
@@ -77,7 +78,11 @@ bool pdl_enabled() {
     }();
     return on;
 }
+static std::atomic<uint64_t> g_kernel_launches{0};
+void count_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace ctox
+
+extern "C" uint64_t ctox_kernel_launches(void) { return ctox::g_kernel_launches.load(std::memory_order_relaxed); }
 
 extern "C" {
 

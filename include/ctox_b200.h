@@ -148,6 +148,9 @@ ctox_status ctox_ctx_allocated_bytes(const ctox_ctx *ctx, uint64_t *bytes);
 /* Returns (and clears) the device-side error word: 0 = none. Kernels set it
  * instead of trapping, e.g. when a bounded wait ran out. */
 ctox_status ctox_ctx_device_error(ctox_ctx *ctx, int32_t *code);
+/* Kernels this library has enqueued in this process so far (all contexts): the count behind the
+ * benchmark's `gpu_launches` (difference over the timed region). No counterpart in the reference. */
+uint64_t ctox_kernel_launches(void);
 /* Benchmark support (the reference's verify/bench binaries time dispatches the
  * same way, src/bin/cuda_bench.rs): when enabled, every launch of the dominant
  * kernel (the streaming / row-warp matvec) is bracketed by a CUDA event pair on
