@@ -962,6 +962,13 @@ ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, co
     const ctox_model_config &c = e->cfg;
     MvOut o = mv_out(mv, m);
     if (ctx->tp_peer) {
+        const MvIn nin = next ? mv_in(next) : MvIn{};
+        if (!fused_norm && tp_peer_reduce_add_norm_fits(c.hidden_size, next ? &nin : nullptr)) {
+            // group sum, residual add, norm and fragments as one cluster kernel
+            EX(tp_peer_reduce_add_norm(ctx, o, c.hidden_size, m, h, e->norm_scratch, norm_w, c.rms_norm_epsilon, xn_out,
+                                       next ? &nin : nullptr));
+            return CTOX_OK;
+        }
         EX(tp_peer_reduce_add(ctx, o, c.hidden_size, m, h, e->norm_scratch));
     } else {
         EX(group_sum(e, mv, m, &o));

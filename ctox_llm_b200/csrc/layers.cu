@@ -107,25 +107,14 @@ void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps
                (int)m, xn_out, n, next != nullptr, nblocks);
 }
 
-// Residual add, RMS norm and the next projection's fragments in ONE kernel: the kRnCluster CTAs of
-// a thread-block cluster share a position; each adds its 1024 columns, the partial sums of squares
-// meet through distributed shared memory (one cluster barrier instead of a kernel boundary), then
-// each normalises its columns and writes its sixteen 64-column blocks. Also leaves the 256-column
-// partial sums of squares in `sumsq` like k_residual_add (layers that run next with fewer positions
-// read them). For hidden <= kRnCluster * 1024.
-constexpr int kRnCluster = 5, kRnThreads = 1024;
-
+// Residual add, RMS norm and the next projection's fragments in ONE kernel (the shared part is
+// residual_norm_finish, layers.cuh). For hidden <= kRnCluster * 1024.
 __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
                                                                     uint32_t hidden, const float *__restrict__ w,
                                                                     float eps, int npos, float *__restrict__ xn_out,
                                                                     MvIn next, int has_next, uint32_t nblocks,
                                                                     float *__restrict__ sumsq) {
     pdl_launch();
-    namespace cg = cooperative_groups;
-    cg::cluster_group cluster = cg::this_cluster();
-    __shared__ float red[kRnThreads / 32];
-    __shared__ float part;  // this CTA's sum of squares, read by the whole cluster
-    __shared__ float vals[kRnThreads];
     const uint32_t tid = threadIdx.x, rank = blockIdx.x;  // gridDim.x == cluster size
     const int m = blockIdx.y;
     const uint32_t c = rank * kRnThreads + tid;
@@ -140,43 +129,7 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__r
             h[(size_t)m * hidden + c] = v;
         }
     }
-    float s = v * v;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if ((tid & 31) == 0) red[tid >> 5] = s;
-    __syncthreads();
-    if (tid < 4) {  // the 256-column partition of k_residual_add, four parts per CTA, fixed order
-        float t = 0.f;
-        for (int q = 0; q < 8; ++q) t += red[tid * 8 + q];
-        const uint32_t parts = (hidden + 255) / 256, p = rank * 4 + tid;
-        if (p < parts) sumsq[m * parts + p] = t;
-        red[tid * 8] = t;  // only this thread reads red[tid*8 ..]
-    }
-    __syncthreads();
-    if (tid == 0) part = red[0] + red[8] + red[16] + red[24];
-    cluster.sync();
-    float total = 0.f;
-    for (int r = 0; r < kRnCluster; ++r) total += *cluster.map_shared_rank(&part, r);  // rank order
-    cluster.sync();  // nobody leaves while its `part` may still be read
-    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
-    float xn = 0.f;
-    if (c < hidden) {
-        xn = v * inv * (1.0f + wc);
-        if (xn_out) xn_out[(size_t)m * hidden + c] = xn;
-    }
-    if (!has_next) return;
-    vals[tid] = xn * sc;
-    __syncthreads();
-    if (tid < 256) {  // sixteen groups of 16 lanes, one 64-column block each
-        const int i = tid & 15;
-        const uint32_t grp = tid >> 4, b = rank * 16 + grp;
-        if (b < nblocks) {
-            const float x[4] = {vals[grp * 64 + i * 4], vals[grp * 64 + i * 4 + 1], vals[grp * 64 + i * 4 + 2],
-                                vals[grp * 64 + i * 4 + 3]};
-            const unsigned gmask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
-            prep_block(x, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
-        }
-    }
+    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks, sumsq);
 }
 
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,

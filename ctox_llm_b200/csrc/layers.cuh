@@ -55,6 +55,12 @@ void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps
 // h += sum over the tensor-parallel group of a matvec's output, through peer memory (tp.cu);
 // scratch receives the partial sums of squares like launch_residual_add.
 ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *scratch);
+// The same followed, in the same kernel, by the RMS norm (weight w) and the fragments of `next`
+// (null: xn_out only). False when the shape does not fit the merged kernel (the caller then uses
+// tp_peer_reduce_add + launch_norm_prep).
+bool tp_peer_reduce_add_norm_fits(uint32_t rows, const MvIn *next);
+ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *scratch,
+                                    const float *w, float eps, float *xn_out, const MvIn *next);
 // MTP input: fragments of concat(rmsnorm_1p(embed(tok[m])), rmsnorm_1p(prev_hidden[m])) * s_in.
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,
                     const float *w_hidden, float eps, uint32_t hidden, uint32_t m, const MvIn *next);
@@ -108,6 +114,8 @@ void launch_commit_batch(cudaStream_t st, const CommitLayer *layers_dev, const C
 }  // namespace ctox
 
 #ifdef __CUDACC__
+#include <cooperative_groups.h>
+
 #include "prep.cuh"
 namespace ctox {
 // One output value of an earlier matvec.
@@ -117,6 +125,63 @@ __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t p
         return matvec_output_n(o.partial, piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs), o.slices,
                                o.max_pieces, o.s_out, row, pos);
     return matvec_output(o.partial, o.pieces, o.slices, o.max_pieces, o.s_out, row, pos);
+}
+// The part of the merged residual + norm kernels after this thread's new residual value v of column
+// c = blockIdx.x * kRnThreads + threadIdx.x of position m is known (and stored): the kRnCluster
+// CTAs of a thread-block cluster share a position; the partial sums of squares meet through
+// distributed shared memory (one cluster barrier instead of a kernel boundary), then each CTA
+// normalises its 1024 columns and writes its sixteen 64-column blocks of the next projection's
+// fragments. Also leaves the 256-column partial sums of squares in `sumsq` like k_residual_add
+// (layers that run next with fewer positions read them). wc = norm weight, sc = s_in of column c.
+// Every thread of the cluster must call it.
+constexpr int kRnCluster = 5, kRnThreads = 1024;
+__device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, float wc, float sc, float eps, int m,
+                                                     int npos, float *__restrict__ xn_out, const MvIn &next,
+                                                     int has_next, uint32_t nblocks, float *__restrict__ sumsq) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float red[kRnThreads / 32];
+    __shared__ float part;  // this CTA's sum of squares, read by the whole cluster
+    __shared__ float vals[kRnThreads];
+    const uint32_t tid = threadIdx.x, rank = blockIdx.x;
+    const uint32_t c = rank * kRnThreads + tid;
+    float s = v * v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((tid & 31) == 0) red[tid >> 5] = s;
+    __syncthreads();
+    if (tid < 4) {  // the 256-column partition of k_residual_add, four parts per CTA, fixed order
+        float t = 0.f;
+        for (int q = 0; q < 8; ++q) t += red[tid * 8 + q];
+        const uint32_t parts = (hidden + 255) / 256, p = rank * 4 + tid;
+        if (p < parts) sumsq[m * parts + p] = t;
+        red[tid * 8] = t;  // only this thread reads red[tid*8 ..]
+    }
+    __syncthreads();
+    if (tid == 0) part = red[0] + red[8] + red[16] + red[24];
+    cluster.sync();
+    float total = 0.f;
+    for (int r = 0; r < kRnCluster; ++r) total += *cluster.map_shared_rank(&part, r);  // rank order
+    cluster.sync();  // nobody leaves while its `part` may still be read
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    float xn = 0.f;
+    if (c < hidden) {
+        xn = v * inv * (1.0f + wc);
+        if (xn_out) xn_out[(size_t)m * hidden + c] = xn;
+    }
+    if (!has_next) return;
+    vals[tid] = xn * sc;
+    __syncthreads();
+    if (tid < 256) {  // sixteen groups of 16 lanes, one 64-column block each
+        const int i = tid & 15;
+        const uint32_t grp = tid >> 4, b = rank * 16 + grp;
+        if (b < nblocks) {
+            const float x[4] = {vals[grp * 64 + i * 4], vals[grp * 64 + i * 4 + 1], vals[grp * 64 + i * 4 + 2],
+                                vals[grp * 64 + i * 4 + 3]};
+            const unsigned gmask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
+            prep_block(x, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+        }
+    }
 }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 // Two output values of the same matvec and position with the loads of both issued together

@@ -117,6 +117,46 @@ __device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
 // the same bits the peers receive). Pushes never wait, so two ranks cannot wait on each other
 // without one of them having pushed. Partial sums of squares of the result per 256-column part,
 // like k_residual_add.
+// This thread's (column c, position m): push the rank's own partial value to every peer, collect the
+// peers' values and return h + the sum over the group in rank order (h is rewritten).
+__device__ __forceinline__ float tp_push_collect(const MvOut &o, float *__restrict__ h, const TpPeerPtrs &peers,
+                                                 const uint2 *recv, size_t source_stride, uint32_t rank,
+                                                 uint32_t world, uint32_t seq, uint32_t hidden, uint32_t c, int m,
+                                                 int32_t *error_flag, long long wait_limit) {
+    const float mine = out_of(o, c, m);
+    const size_t at = (size_t)m * hidden + c;
+    // (unrolled with predicates: a run-time index into the by-value pointer table would copy it
+    // to the local-memory stack first)
+#pragma unroll
+    for (uint32_t r = 0; r < kTpMaxWorld; ++r)
+        if (r < world && r != rank) st_word_sys(peers.dst[r] + at, __float_as_uint(mine), seq);
+    float v = h[at];
+    const long long t0 = clock64();
+    // once a wait has run out anywhere (this kernel or an earlier one of the same call), nobody
+    // waits again: the call is lost anyway and the kernels behind it must not each spend the limit
+    bool gave_up = *reinterpret_cast<volatile int32_t *>(error_flag) != 0;
+    for (uint32_t r = 0; r < world; ++r) {
+        if (r == rank) {
+            v += mine;
+            continue;
+        }
+        const uint2 *p = recv + r * source_stride + at;
+        uint2 word = ld_word_sys(p);
+        while (word.y != seq && !gave_up) {
+            if (clock64() - t0 > wait_limit) {  // a peer is gone
+                atomicExch(error_flag, DEV_ERR_WAIT_TIMEOUT);
+                gave_up = true;
+                break;
+            }
+            if (*reinterpret_cast<volatile int32_t *>(error_flag) != 0) gave_up = true;
+            word = ld_word_sys(p);
+        }
+        v += __uint_as_float(word.x);
+    }
+    h[at] = v;
+    return v;
+}
+
 __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float *__restrict__ h, TpPeerPtrs peers,
                                                                const uint2 *recv, size_t source_stride,
                                                                uint32_t rank, uint32_t world, uint32_t seq,
@@ -128,39 +168,8 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
     const int m = blockIdx.y;
     const uint32_t c = blockIdx.x * kTpChunk + threadIdx.x;
     float v = 0.f;
-    if (c < hidden) {
-        const float mine = out_of(o, c, m);
-        const size_t at = (size_t)m * hidden + c;
-        // (unrolled with predicates: a run-time index into the by-value pointer table would copy it
-        // to the local-memory stack first)
-#pragma unroll
-        for (uint32_t r = 0; r < kTpMaxWorld; ++r)
-            if (r < world && r != rank) st_word_sys(peers.dst[r] + at, __float_as_uint(mine), seq);
-        v = h[at];
-        const long long t0 = clock64();
-        // once a wait has run out anywhere (this kernel or an earlier one of the same call), nobody
-        // waits again: the call is lost anyway and the kernels behind it must not each spend the limit
-        bool gave_up = *reinterpret_cast<volatile int32_t *>(error_flag) != 0;
-        for (uint32_t r = 0; r < world; ++r) {
-            if (r == rank) {
-                v += mine;
-                continue;
-            }
-            const uint2 *p = recv + r * source_stride + at;
-            uint2 word = ld_word_sys(p);
-            while (word.y != seq && !gave_up) {
-                if (clock64() - t0 > wait_limit) {  // a peer is gone
-                    atomicExch(error_flag, DEV_ERR_WAIT_TIMEOUT);
-                    gave_up = true;
-                    break;
-                }
-                if (*reinterpret_cast<volatile int32_t *>(error_flag) != 0) gave_up = true;
-                word = ld_word_sys(p);
-            }
-            v += __uint_as_float(word.x);
-        }
-        h[at] = v;
-    }
+    if (c < hidden)
+        v = tp_push_collect(o, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
     float s = v * v;
 #pragma unroll
     for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
@@ -171,6 +180,26 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
         for (unsigned w = 0; w < kTpChunk / 32; ++w) t += red[w];  // fixed order
         sumsq[m * gridDim.x + blockIdx.x] = t;
     }
+}
+
+// The same, then the RMS norm of the new residual and the next projection's fragments without a
+// kernel boundary: a thread-block cluster of kRnCluster CTAs per position (residual_norm_finish).
+// A wait that runs out leaves v undefined but every thread still reaches the cluster barriers.
+__global__ void __launch_bounds__(kRnThreads, 1) k_tp_reduce_residual_norm_prep(
+    MvOut o, float *__restrict__ h, TpPeerPtrs peers, const uint2 *recv, size_t source_stride, uint32_t rank,
+    uint32_t world, uint32_t seq, uint32_t hidden, float *__restrict__ sumsq, int32_t *error_flag, long long wait_limit,
+    const float *__restrict__ w, float eps, int npos, float *__restrict__ xn_out, MvIn next, int has_next,
+    uint32_t nblocks) {
+    pdl_launch();
+    const int m = blockIdx.y;
+    const uint32_t c = blockIdx.x * kRnThreads + threadIdx.x;
+    const float wc = c < hidden ? w[c] : 0.f;  // constants first: they do not depend on earlier kernels
+    const float sc = (has_next && next.s_in && c < hidden) ? next.s_in[c] : 1.0f;
+    pdl_wait();
+    float v = 0.f;
+    if (c < hidden)
+        v = tp_push_collect(o, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
+    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks, sumsq);
 }
 
 ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
@@ -281,6 +310,35 @@ ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uin
     for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
     launch_pdl(k_tp_reduce_residual, dim3(chunks, m), dim3(kTpChunk), 0, ctx->stream, o, h, pp, tp->recv + parity_off,
                tp->elems, tp->rank, tp->world, seq, rows, sumsq, ctx->dev_error, ctx->wait_limit_cycles);
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+bool tp_peer_reduce_add_norm_fits(uint32_t rows, const MvIn *next) {
+    static const bool merged = [] {
+        const char *v = getenv("CTOX_MERGED_NORM");
+        return !(v && v[0] == '0');
+    }();
+    const uint32_t nblocks = next ? next->blocks_padded : (rows + 63) / 64;
+    return merged && rows <= (uint32_t)kRnCluster * kRnThreads && nblocks <= (uint32_t)kRnCluster * 16;
+}
+
+ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *sumsq,
+                                    const float *w, float eps, float *xn_out, const MvIn *next) {
+    TpPeer *tp = ctx->tp_peer;
+    if (!tp) return fail(ctx, CTOX_INVALID_STATE, "tp: peer all-reduce is not set up");
+    if ((size_t)m * rows > tp->elems) return fail(ctx, CTOX_SHAPE, "tp: vector of %u x %u exceeds the peer buffer", m, rows);
+    if (!tp_peer_reduce_add_norm_fits(rows, next)) return fail(ctx, CTOX_SHAPE, "tp: %u rows do not fit the merged kernel", rows);
+    const uint32_t seq = ++tp->seq, parity = seq & 1;
+    if (seq == 0) return fail(ctx, CTOX_INVALID_STATE, "tp: sequence numbers exhausted");
+    const size_t parity_off = (size_t)parity * tp->world * tp->elems;
+    TpPeerPtrs pp{};
+    for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
+    const MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
+    const uint32_t nblocks = next ? next->blocks_padded : (rows + 63) / 64;
+    launch_pdl_cluster(k_tp_reduce_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnThreads), 0, ctx->stream,
+                       kRnCluster, o, h, pp, tp->recv + parity_off, tp->elems, tp->rank, tp->world, seq, rows, sumsq,
+                       ctx->dev_error, ctx->wait_limit_cycles, w, eps, (int)m, xn_out, n, next != nullptr, nblocks);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }
