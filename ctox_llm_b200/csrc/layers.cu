@@ -200,15 +200,16 @@ void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_
 // column (two matvec outputs), then four 16-lane groups write the four 64-column blocks.
 __global__ void __launch_bounds__(256) k_swiglu_prep(MvOut gu, uint32_t inter, int npos, MvIn next) {
     pdl_launch();
-    pdl_wait();
     __shared__ float vals[256];
     const int m = blockIdx.y;
     const uint32_t c = blockIdx.x * 256 + threadIdx.x;
+    const float sc = (next.s_in && c < inter) ? next.s_in[c] : 1.0f;  // a constant: before the wait
+    pdl_wait();
     float v = 0.f;
     if (c < inter) {
         float gate, up;
         out_of2(gu, c, inter + c, m, gate, up);
-        v = silu_f(gate) * up * (next.s_in ? next.s_in[c] : 1.0f);
+        v = silu_f(gate) * up * sc;
     }
     vals[threadIdx.x] = v;
     __syncthreads();
@@ -749,6 +750,12 @@ __global__ void __launch_bounds__(256) k_attn_combine_prep(AttnGeom g, const flo
     const uint32_t kh = hq / G, qi = m * G + hq % G, d = threadIdx.x;  // blockDim.x == head_dim
     const float *base = ws + ((size_t)kh * splits * NQ + qi) * (hd + 2);
     const size_t split_stride = (size_t)NQ * (hd + 2);
+    // this thread's dimension of the first sixteen splits and its gate value: requested before the
+    // weights are formed (they do not depend on them), sixteen loads per trip afterwards
+    float buf[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) buf[j] = (uint32_t)j < splits ? base[j * split_stride + d] : 0.f;
+    const float gt = gate[((size_t)m * g.q_heads + hq) * hd + d];
     if (threadIdx.x < 32) {  // splits <= 64: two per lane
         float ms[2], ls[2];
 #pragma unroll
@@ -774,15 +781,16 @@ __global__ void __launch_bounds__(256) k_attn_combine_prep(AttnGeom g, const flo
     }
     __syncthreads();
     float acc = 0.f;
-    for (uint32_t s0 = 0; s0 < splits; s0 += 8) {
-        float buf[8];
+    for (uint32_t s0 = 0; s0 < splits; s0 += 16) {
+        float nxt[16];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) buf[j] = s0 + j < splits ? base[(s0 + j) * split_stride + d] : 0.f;
+        for (int j = 0; j < 16; ++j) nxt[j] = s0 + 16 + j < splits ? base[(s0 + 16 + j) * split_stride + d] : 0.f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
+        for (int j = 0; j < 16; ++j)
             if (s0 + j < splits) acc += buf[j] * wgt[s0 + j];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) buf[j] = nxt[j];
     }
-    const float gt = gate[((size_t)m * g.q_heads + hq) * hd + d];
     const uint32_t col = hq * hd + d;
     vals[d] = acc * (1.0f / (1.0f + expf(-gt))) * (next.s_in ? next.s_in[col] : 1.0f);
     __syncthreads();
