@@ -285,34 +285,34 @@ __global__ void __launch_bounds__(512, 1) k_linear_attention(LinearAttnArgs a, i
             cw[j] = a.conv_w[(size_t)ch * K + j];
         }
     }
+    // One row of the input projection per thread: conv threads their channel, the last 128 their
+    // gate column. Where the projection left stream-K pieces (at most eight per value), their
+    // offsets are the same for every position: they are formed once, and the pieces of position
+    // m + 1 are in flight while position m is worked on. Same additions in the same order as out_of.
+    const uint32_t row = tid < 384 ? ch : channels + head * kDeltaDim + (tid - 384);
+    const MvOut &o = a.fan;
+    uint32_t total = 0, off[8];
+    const float *first = nullptr;
+    if (!o.plain && o.warps_per_slice) {
+        const uint32_t n = piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs);
+        total = o.slices * n;
+        first = o.partial + (size_t)(row >> 5) * o.slices * o.max_pieces * 256 + (row & 31);
+        uint32_t sl = 0, q = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            off[j] = (sl * o.max_pieces + q) * 256;
+            if (++q == n) {
+                q = 0;
+                ++sl;
+            }
+        }
+    }
+    const bool pieces = total >= 1 && total <= 8;  // otherwise the general fetch per position
+    const float so = pieces && o.s_out ? o.s_out[row] : 1.0f;
     pdl_wait();
 
     // ---- 1. conv + SiLU, z, decay, beta
     {
-        // One row of the input projection per thread: conv threads their channel, the last 128 their
-        // gate column. Where the projection left stream-K pieces (at most eight per value), their
-        // offsets are the same for every position: they are formed once, and the pieces of position
-        // m + 1 are in flight while position m is worked on. Same additions in the same order as out_of.
-        const uint32_t row = tid < 384 ? ch : channels + head * kDeltaDim + (tid - 384);
-        const MvOut &o = a.fan;
-        uint32_t total = 0, off[8];
-        const float *first = nullptr;
-        if (!o.plain && o.warps_per_slice) {
-            const uint32_t n = piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs);
-            total = o.slices * n;
-            first = o.partial + (size_t)(row >> 5) * o.slices * o.max_pieces * 256 + (row & 31);
-            uint32_t sl = 0, q = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                off[j] = (sl * o.max_pieces + q) * 256;
-                if (++q == n) {
-                    q = 0;
-                    ++sl;
-                }
-            }
-        }
-        const bool pieces = total >= 1 && total <= 8;  // otherwise the general fetch per position
-        const float so = pieces && o.s_out ? o.s_out[row] : 1.0f;
         float buf[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) buf[j] = (pieces && (uint32_t)j < total) ? first[off[j]] : 0.f;

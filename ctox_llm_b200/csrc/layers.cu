@@ -120,12 +120,13 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__r
     const uint32_t c = rank * kRnThreads + tid;
     const float wc = c < hidden ? w[c] : 0.f;  // constants first: they do not depend on earlier kernels
     const float sc = (has_next && next.s_in && c < hidden) ? next.s_in[c] : 1.0f;
+    const OutRef ar = (has_add && c < hidden) ? out_ref(add, c) : OutRef{nullptr, 0, 0, 1.0f, false};
     pdl_wait();
     float v = 0.f;
     if (c < hidden) {
         v = h[(size_t)m * hidden + c];
         if (has_add) {
-            v += out_of(add, c, m);
+            v += out_at(add, ar, c, m);
             h[(size_t)m * hidden + c] = v;
         }
     }
@@ -204,11 +205,48 @@ __global__ void __launch_bounds__(256) k_swiglu_prep(MvOut gu, uint32_t inter, i
     const int m = blockIdx.y;
     const uint32_t c = blockIdx.x * 256 + threadIdx.x;
     const float sc = (next.s_in && c < inter) ? next.s_in[c] : 1.0f;  // a constant: before the wait
+    const OutRef gr = c < inter ? out_ref(gu, c) : OutRef{nullptr, 0, 0, 1.0f, false};
+    const OutRef ur = c < inter ? out_ref(gu, inter + c) : OutRef{nullptr, 0, 0, 1.0f, false};
     pdl_wait();
     float v = 0.f;
     if (c < inter) {
         float gate, up;
-        out_of2(gu, c, inter + c, m, gate, up);
+        if (gr.pieces && gr.total <= 8 && ur.total <= 8) {
+            // both values' pieces requested before the first addition (same additions as out_of)
+            float bg[8], bu[8];
+            const float *fg = gr.first + m * 32, *fu = ur.first + m * 32;
+            uint32_t sg = 0, qg = 0, su = 0, qu = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                bg[j] = bu[j] = 0.f;
+                if ((uint32_t)j < gr.total) {
+                    bg[j] = fg[((size_t)sg * gu.max_pieces + qg) * 256];
+                    if (++qg == gr.n) {
+                        qg = 0;
+                        ++sg;
+                    }
+                }
+                if ((uint32_t)j < ur.total) {
+                    bu[j] = fu[((size_t)su * gu.max_pieces + qu) * 256];
+                    if (++qu == ur.n) {
+                        qu = 0;
+                        ++su;
+                    }
+                }
+            }
+            gate = up = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if ((uint32_t)j < gr.total) gate += bg[j];
+                if ((uint32_t)j < ur.total) up += bu[j];
+            }
+            if (gu.s_out) {
+                gate *= gr.so;
+                up *= ur.so;
+            }
+        } else {
+            out_of2(gu, c, inter + c, m, gate, up);
+        }
         v = silu_f(gate) * up * sc;
     }
     vals[threadIdx.x] = v;

@@ -183,6 +183,50 @@ __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, f
         }
     }
 }
+// out_of in two halves for kernels launched ahead of their producer: out_ref is arithmetic on the
+// launch arguments plus the constant s_out[row] and may run BEFORE the dependency wait; out_at does
+// the loads. Same additions in the same order as out_of.
+struct OutRef {
+    const float *first;
+    uint32_t n, total;
+    float so;
+    bool pieces;  // false: out_at falls back to out_of
+};
+__device__ __forceinline__ OutRef out_ref(const MvOut &o, uint32_t row) {
+    OutRef r{nullptr, 0, 0, 1.0f, false};
+    if (!o.plain && o.warps_per_slice) {
+        r.pieces = true;
+        r.n = piece_count(row >> 5, o.kst_s, o.warps_per_slice, o.pairs);
+        r.total = o.slices * r.n;
+        r.first = o.partial + (size_t)(row >> 5) * o.slices * o.max_pieces * 256 + (row & 31);
+        if (o.s_out) r.so = o.s_out[row];
+    }
+    return r;
+}
+__device__ __forceinline__ float out_at(const MvOut &o, const OutRef &r, uint32_t row, uint32_t pos) {
+    if (!r.pieces) return out_of(o, row, pos);
+    const float *first = r.first + pos * 32;
+    float v = 0.f;
+    uint32_t sl = 0, q = 0;
+    for (uint32_t k0 = 0; k0 < r.total; k0 += 8) {
+        float buf[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            buf[j] = 0.f;
+            if (k0 + j < r.total) {
+                buf[j] = first[((size_t)sl * o.max_pieces + q) * 256];
+                if (++q == r.n) {
+                    q = 0;
+                    ++sl;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (k0 + j < r.total) v += buf[j];
+    }
+    return o.s_out ? v * r.so : v;
+}
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 // Two output values of the same matvec and position with the loads of both issued together
 // (each up to four pieces per trip; same order of additions as out_of).

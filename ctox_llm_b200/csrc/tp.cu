@@ -119,11 +119,12 @@ __device__ __forceinline__ uint2 ld_word_sys(const uint2 *p) {
 // like k_residual_add.
 // This thread's (column c, position m): push the rank's own partial value to every peer, collect the
 // peers' values and return h + the sum over the group in rank order (h is rewritten).
-__device__ __forceinline__ float tp_push_collect(const MvOut &o, float *__restrict__ h, const TpPeerPtrs &peers,
+__device__ __forceinline__ float tp_push_collect(const MvOut &o, const OutRef &oref, float *__restrict__ h,
+                                                 const TpPeerPtrs &peers,
                                                  const uint2 *recv, size_t source_stride, uint32_t rank,
                                                  uint32_t world, uint32_t seq, uint32_t hidden, uint32_t c, int m,
                                                  int32_t *error_flag, long long wait_limit) {
-    const float mine = out_of(o, c, m);
+    const float mine = out_at(o, oref, c, m);
     const size_t at = (size_t)m * hidden + c;
     // (unrolled with predicates: a run-time index into the by-value pointer table would copy it
     // to the local-memory stack first)
@@ -163,13 +164,14 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
                                                                uint32_t hidden, float *__restrict__ sumsq,
                                                                int32_t *error_flag, long long wait_limit) {
     pdl_launch();
-    pdl_wait();
     __shared__ float red[kTpChunk / 32];
     const int m = blockIdx.y;
     const uint32_t c = blockIdx.x * kTpChunk + threadIdx.x;
+    const OutRef oref = c < hidden ? out_ref(o, c) : OutRef{nullptr, 0, 0, 1.0f, false};
+    pdl_wait();
     float v = 0.f;
     if (c < hidden)
-        v = tp_push_collect(o, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
+        v = tp_push_collect(o, oref, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
     float s = v * v;
 #pragma unroll
     for (int o2 = 16; o2 > 0; o2 >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o2);
@@ -195,10 +197,11 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_tp_reduce_residual_norm_prep(
     const uint32_t c = blockIdx.x * kRnThreads + threadIdx.x;
     const float wc = c < hidden ? w[c] : 0.f;  // constants first: they do not depend on earlier kernels
     const float sc = (has_next && next.s_in && c < hidden) ? next.s_in[c] : 1.0f;
+    const OutRef oref = c < hidden ? out_ref(o, c) : OutRef{nullptr, 0, 0, 1.0f, false};
     pdl_wait();
     float v = 0.f;
     if (c < hidden)
-        v = tp_push_collect(o, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
+        v = tp_push_collect(o, oref, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
     residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks, sumsq);
 }
 
