@@ -162,26 +162,30 @@ __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, f
     cluster.sync();
     float total = 0.f;
     for (int r = 0; r < kRnCluster; ++r) total += *cluster.map_shared_rank(&part, r);  // rank order
-    cluster.sync();  // nobody leaves while its `part` may still be read
+    // nobody may leave while its `part` can still be read: every thread arrives here and waits for
+    // the others only at the very end, behind its stores
+    cluster.barrier_arrive();
     const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
     float xn = 0.f;
     if (c < hidden) {
         xn = v * inv * (1.0f + wc);
         if (xn_out) xn_out[(size_t)m * hidden + c] = xn;
     }
-    if (!has_next) return;
-    vals[tid] = xn * sc;
-    __syncthreads();
-    if (tid < 256) {  // sixteen groups of 16 lanes, one 64-column block each
-        const int i = tid & 15;
-        const uint32_t grp = tid >> 4, b = rank * 16 + grp;
-        if (b < nblocks) {
-            const float x[4] = {vals[grp * 64 + i * 4], vals[grp * 64 + i * 4 + 1], vals[grp * 64 + i * 4 + 2],
-                                vals[grp * 64 + i * 4 + 3]};
-            const unsigned gmask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
-            prep_block(x, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+    if (has_next) {
+        vals[tid] = xn * sc;
+        __syncthreads();
+        if (tid < 256) {  // sixteen groups of 16 lanes, one 64-column block each
+            const int i = tid & 15;
+            const uint32_t grp = tid >> 4, b = rank * 16 + grp;
+            if (b < nblocks) {
+                const float x[4] = {vals[grp * 64 + i * 4], vals[grp * 64 + i * 4 + 1], vals[grp * 64 + i * 4 + 2],
+                                    vals[grp * 64 + i * 4 + 3]};
+                const unsigned gmask = (tid & 16) ? 0xffff0000u : 0x0000ffffu;
+                prep_block(x, i, gmask, (int)b, m, npos, next.dt, next.xfrag, next.meta);
+            }
         }
     }
+    cluster.barrier_wait();
 }
 // out_of in two halves for kernels launched ahead of their producer: out_ref is arithmetic on the
 // launch arguments plus the constant s_out[row] and may run BEFORE the dependency wait; out_at does
