@@ -51,7 +51,9 @@ template <>
 __device__ __forceinline__ void state_store<__half>(__half *p, float v) { *p = __float2half_rn(v); }
 
 // The scan of one (head, 32-column slice) by one CTA of 128 threads; out may be null (state only).
-template <typename S>
+// kWaitAfterState: the dependency wait comes after the state loads (for a caller whose state_in
+// nothing in flight can write; the inputs of the tokens are read after the wait).
+template <typename S, bool kWaitAfterState = false>
 __device__ __forceinline__ void delta_scan128_body(
     const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
     const float *__restrict__ log_decay, const float *__restrict__ beta,
@@ -67,6 +69,7 @@ __device__ __forceinline__ void delta_scan128_body(
     const S *sin_ = state_in + ((size_t)head * kDeltaDim + warp * 32) * kDeltaDim + col;
 #pragma unroll
     for (int i = 0; i < 32; ++i) s[i] = state_load<S>(sin_ + (size_t)i * kDeltaDim);
+    if (kWaitAfterState) pdl_wait();
 
     const float query_scale = 1.0f / sqrtf((float)kDeltaDim);
     for (int tok = 0; tok < tokens; ++tok) {
@@ -141,25 +144,40 @@ __global__ void __launch_bounds__(128) k_commit_batch(const CommitLayer *__restr
                                                     int rescan, int heads, int qk_heads, uint32_t channels,
                                                     uint32_t conv_kernel) {
     pdl_launch();
-    pdl_wait();
-    const CommitLayer L = layers[blockIdx.y];
+    // The layer table and the committed buffers do not change while a pass is in flight (the state a
+    // re-scan starts from was written by the commit before): pointers and state before the wait.
+    const CommitLayer *L = layers + blockIdx.y;
     const int scan_ctas = heads * 4;
     if ((int)blockIdx.x < scan_ctas) {
         if (!rescan) return;
-        const int c = cur.v[blockIdx.y];
-        delta_scan128_body<float>(L.q, L.k, L.v, L.g, L.beta, L.state[c], L.state[c ^ 1], nullptr, n, heads, qk_heads,
-                                  blockIdx.x >> 2, blockIdx.x & 3);
+        const int c = (int)(((blockIdx.y < 64 ? cur.lo : cur.hi) >> (blockIdx.y & 63)) & 1);
+        const float *sin_ = c ? L->state[1] : L->state[0];
+        float *sout = c ? L->state[0] : L->state[1];
+        delta_scan128_body<float, true>(L->q, L->k, L->v, L->g, L->beta, sin_, sout, nullptr, n, heads, qk_heads,
+                                        blockIdx.x >> 2, blockIdx.x & 3);
         return;
     }
     const uint32_t r = (blockIdx.x - scan_ctas) * blockDim.x + threadIdx.x;
-    if (r >= channels) return;
+    float *cs = L->conv_state;
+    const float *ci = L->conv_in;
+    // taps in registers for any kernel width <= 8 (loops fully unrolled with predicates)
     float st[8];
-    for (uint32_t j = 0; j < conv_kernel; ++j) st[j] = L.conv_state[(size_t)r * conv_kernel + j];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) st[j] = (r < channels && (uint32_t)j < conv_kernel) ? cs[(size_t)r * conv_kernel + j] : 0.f;
+    pdl_wait();
+    if (r >= channels) return;
     for (int m = 0; m < n; ++m) {
-        for (uint32_t j = 0; j + 1 < conv_kernel; ++j) st[j] = st[j + 1];
-        st[conv_kernel - 1] = L.conv_in[(size_t)m * channels + r];
+        const float x = ci[(size_t)m * channels + r];
+#pragma unroll
+        for (int j = 0; j < 7; ++j)
+            if ((uint32_t)j + 1 < conv_kernel) st[j] = st[j + 1];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if ((uint32_t)j + 1 == conv_kernel) st[j] = x;
     }
-    for (uint32_t j = 0; j < conv_kernel; ++j) L.conv_state[(size_t)r * conv_kernel + j] = st[j];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+        if ((uint32_t)j < conv_kernel) cs[(size_t)r * conv_kernel + j] = st[j];
 }
 
 void launch_commit_batch(cudaStream_t st, const CommitLayer *layers_dev, const CommitCur &cur, uint32_t n_layers,

@@ -1062,7 +1062,10 @@ ctox_status commit_positions(ctox_exec *e, uint32_t m, uint32_t n) {
         CommitCur cur{};
         uint32_t j = 0;
         for (uint32_t l = 0; l < e->n_layers; ++l)
-            if (!e->w[l].full) cur.v[j++] = (uint8_t)e->s[l].cur;
+            if (!e->w[l].full) {
+                if (e->s[l].cur) (j < 64 ? cur.lo : cur.hi) |= 1ull << (j & 63);
+                ++j;
+            }
         // partial acceptance: re-scan the recurrence alone from the committed state
         launch_commit_batch(ctx->stream, e->commit_table, cur, e->n_linear, n, n < m, c.linear_num_value_heads,
                             c.linear_num_key_heads, e->channels, c.linear_conv_kernel_dim);

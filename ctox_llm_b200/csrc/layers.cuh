@@ -105,7 +105,7 @@ struct CommitLayer {
     const float *conv_in;
 };
 struct CommitCur {
-    uint8_t v[128];  // per linear layer: index of the committed state buffer
+    uint64_t lo, hi;  // bit j: index (0 / 1) of the committed state buffer of linear layer j < 128
 };
 void launch_commit_batch(cudaStream_t st, const CommitLayer *layers_dev, const CommitCur &cur, uint32_t n_layers,
                          uint32_t n, bool rescan, uint32_t heads, uint32_t qk_heads, uint32_t channels,
