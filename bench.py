@@ -714,6 +714,28 @@ def run_micro(args):
                                    + tokens * heads * 128 * 4)
                 res[f"T{tokens}"] = {"ms_per_48_layers": ms, "us_per_layer": ms * 1e3 / layers, "bytes": nbytes,
                                      "gbs": nbytes / (ms * 1e-3) / 1e9, "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+            # the same 48 scans as ONE launch (the form of the executor's prefix re-scan at commit, where
+            # the layers are independent; inside a decode pass they are not)
+            ql, kl, vl = (x[None].expand(layers, *x.shape).contiguous() for x in (q, k, v))
+            gl, bl = (x[None].expand(layers, *x.shape).contiguous() for x in (gate, beta))
+            for tokens in (4, 1):
+                def one(a, b):
+                    be.gated_delta_scan_layers(ql.data_ptr(), kl.data_ptr(), vl.data_ptr(), gl.data_ptr(), bl.data_ptr(),
+                                               state[a].data_ptr(), state[b].data_ptr(), 0, layers, tokens, heads, qk)
+                for i in range(args.warmup):
+                    one(i & 1, (i & 1) ^ 1)
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record(stream)
+                for i in range(args.steps):
+                    one(i & 1, (i & 1) ^ 1)
+                ev1.record(stream)
+                torch.cuda.synchronize()
+                ms = ev0.elapsed_time(ev1) / args.steps
+                nbytes = layers * (2 * heads * 128 * 128 * 4 + tokens * ((2 * qk + heads) * 128 + 2 * heads) * 4)
+                res[f"T{tokens}_one_launch"] = {"ms_per_48_layers": ms, "bytes": nbytes,
+                                                "gbs": nbytes / (ms * 1e-3) / 1e9,
+                                                "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
             line.update(metric="gated_delta_hbm_gbs", value=res["T4"]["gbs"], unit="GB/s",
                         ms_per_step=res["T4"]["ms_per_48_layers"],
                         config={"workload": "BASELINE config 2: gated-delta recurrence, 16 key / 48 value heads, "

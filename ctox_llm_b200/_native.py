@@ -158,6 +158,7 @@ SIGNATURES = {
     "ctox_matvec_dispatch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                               C.c_uint32]),
     "ctox_gated_delta_scan": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
+    "ctox_gated_delta_scan_layers": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 4),
     "ctox_gated_delta_scan_f16_state": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
     "ctox_gated_delta_prepare": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_uint32] * 2),
     "ctox_argmax_f32": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]),

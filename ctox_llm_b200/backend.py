@@ -172,6 +172,13 @@ class B200Backend:
             self._ctx, *(C.c_void_p(a) for a in (q, k, v, log_decay, beta, state_in, state_out, out)),
             tokens, heads, qk_heads, key_dim, value_dim))
 
+    def gated_delta_scan_layers(self, q: int, k: int, v: int, log_decay: int, beta: int, state_in: int,
+                                state_out: int, out: int, layers: int, tokens: int, heads: int, qk_heads: int) -> None:
+        """`layers` independent scans in one launch (arrays hold the layers back to back; out may be 0)."""
+        self._check(self._lib.ctox_gated_delta_scan_layers(
+            self._ctx, *(C.c_void_p(a) if a else None for a in (q, k, v, log_decay, beta, state_in, state_out, out)),
+            layers, tokens, heads, qk_heads))
+
     def gated_delta_scan_f16_state(self, q: int, k: int, v: int, log_decay: int, beta: int, state_in: int,
                                    state_out: int, out: int, tokens: int, heads: int, qk_heads: int) -> None:
         """recurrent_gated_delta_step_f16_state (reference.rs:299-373) over `tokens` tokens: the state

@@ -136,6 +136,22 @@ __global__ void __launch_bounds__(128) k_gated_delta_scan128(
                           blockIdx.x >> 2, blockIdx.x & 3);
 }
 
+// The scan of `layers` independent layers in one launch (blockIdx.y = layer): every array holds the
+// layers back to back in the layout of the single-layer scan.
+__global__ void __launch_bounds__(128) k_gated_delta_scan128_layers(
+    const float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+    const float *__restrict__ log_decay, const float *__restrict__ beta, const float *__restrict__ state_in,
+    float *__restrict__ state_out, float *__restrict__ out, int tokens, int heads, int qk_heads) {
+    pdl_launch();
+    pdl_wait();
+    const size_t l = blockIdx.y;
+    const size_t qk_n = (size_t)tokens * qk_heads * kDeltaDim, v_n = (size_t)tokens * heads * kDeltaDim;
+    const size_t g_n = (size_t)tokens * heads, s_n = (size_t)heads * kDeltaDim * kDeltaDim;
+    delta_scan128_body<float>(q + l * qk_n, k + l * qk_n, v + l * v_n, log_decay + l * g_n, beta + l * g_n,
+                              state_in + l * s_n, state_out + l * s_n, out ? out + l * v_n : nullptr, tokens, heads,
+                              qk_heads, blockIdx.x >> 2, blockIdx.x & 3);
+}
+
 // Commit of the first n positions of a pass for ALL linear-attention layers in one launch:
 // blockIdx.y = layer; the first heads * 4 CTAs of a layer re-scan the recurrence from the committed
 // state over the kept (q, k, v, g, beta) when only a prefix was accepted, the others shift the first
@@ -510,6 +526,23 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
             q, k, v, log_decay, beta, state_in, state_out, out, (int)tokens, (int)heads, (int)qk_heads,
             (int)key_dim, (int)value_dim);
     }
+    CTOX_CUDA(ctx, cudaGetLastError());
+    return CTOX_OK;
+}
+
+ctox_status ctox_gated_delta_scan_layers(ctox_ctx *ctx, const float *q, const float *k, const float *v,
+                                         const float *log_decay, const float *beta, const float *state_in,
+                                         float *state_out, float *out, uint32_t layers, uint32_t tokens,
+                                         uint32_t heads, uint32_t qk_heads) {
+    if (!ctx) return CTOX_INVALID_STATE;
+    if (!q || !k || !v || !log_decay || !beta || !state_in || !state_out)
+        return fail(ctx, CTOX_SHAPE, "gated delta (layers): null device pointer");
+    if (layers == 0 || layers > 65535 || tokens == 0 || heads == 0 || qk_heads == 0 || heads % qk_heads)
+        return fail(ctx, CTOX_SHAPE, "gated delta (layers): layers %u tokens %u heads %u qk_heads %u", layers, tokens,
+                    heads, qk_heads);
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    launch_pdl(k_gated_delta_scan128_layers, dim3(heads * 4, layers), dim3(128), 0, ctx->stream, q, k, v, log_decay,
+               beta, state_in, state_out, out, (int)tokens, (int)heads, (int)qk_heads);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
 }

@@ -246,6 +246,15 @@ ctox_status ctox_gated_delta_scan(ctox_ctx *ctx, const float *q, const float *k,
                                   const float *log_decay, const float *beta, const float *state_in,
                                   float *state_out, float *out, uint32_t tokens, uint32_t heads,
                                   uint32_t qk_heads, uint32_t key_dim, uint32_t value_dim);
+/* The scan of `layers` independent layers in ONE launch: every array holds the layers back to back
+ * in the single-layer layout above (q, k: [layers][tokens][qk_heads][128], state: [layers][heads][128][128],
+ * ...); out may be NULL (state only). 128 x 128 heads. This is the form in which the executor
+ * re-scans an accepted prefix over all linear-attention layers (the reference replays whole passes
+ * instead, backend/cuda_graph.rs:4962-5003); results equal `layers` calls of ctox_gated_delta_scan. */
+ctox_status ctox_gated_delta_scan_layers(ctox_ctx *ctx, const float *q, const float *k, const float *v,
+                                         const float *log_decay, const float *beta, const float *state_in,
+                                         float *state_out, float *out, uint32_t layers, uint32_t tokens,
+                                         uint32_t heads, uint32_t qk_heads);
 /* The same scan with the FP16-resident state of the reference's CUDA candidate
  * (recurrent_gated_delta_step_f16_state, reference.rs:299-373; backend/cuda_runtime.rs:3514-3900
  * dispatch_gated_delta_f16[_scan]_device): state_in / state_out are [heads][128][128] binary16;

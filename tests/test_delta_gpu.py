@@ -113,6 +113,36 @@ def test_scan_equals_step_by_step_and_layers_back_to_back(be, orc):
             beta[tokens:], st, 1, heads, 128, 128)
         assert rel_l2(o1, eo) <= TIGHT and rel_l2(st1, es) <= TIGHT
 
+def test_layers_in_one_launch_equal_one_launch_per_layer(be):
+    """ctox_gated_delta_scan_layers over 5 layers (the form of the executor's prefix re-scan) gives the
+    bits of 5 single-layer calls, with and without the output array, and leaves state_in untouched."""
+    heads, qk, tokens, layers = 48, 16, 3, 5
+    ins = [config2_inputs(tokens, heads, qk, seed=300 + l) for l in range(layers)]
+    want_out, want_state = [], []
+    for q, k, v, g, beta, state in ins:
+        o, st, _ = run_scan(be, q, k, v, g, beta, state, tokens, heads, qk, 128, 128, in_place=False)
+        want_out.append(o)
+        want_state.append(st)
+    dq, dk, dv, dg, db, ds = (dev(np.stack([x[i] for x in ins])) for i in range(6))
+    dso = torch.full_like(ds, float("nan"))
+    out = torch.full((layers * tokens * heads * 128,), float("nan"), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    be.gated_delta_scan_layers(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), db.data_ptr(),
+                               ds.data_ptr(), dso.data_ptr(), out.data_ptr(), layers, tokens, heads, qk)
+    be.synchronize()
+    assert np.array_equal(out.cpu().numpy().reshape(layers, tokens, heads * 128), np.stack(want_out))
+    assert np.array_equal(dso.cpu().numpy().reshape(layers, -1), np.stack([s.reshape(-1) for s in want_state]))
+    assert np.array_equal(ds.cpu().numpy().reshape(layers, -1), np.stack([x[5].reshape(-1) for x in ins]))
+    dso2 = torch.full_like(ds, float("nan"))
+    be.gated_delta_scan_layers(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), db.data_ptr(),
+                               ds.data_ptr(), dso2.data_ptr(), 0, layers, tokens, heads, qk)
+    be.synchronize()
+    assert torch.equal(dso, dso2)
+    with pytest.raises(ctox.CtoxError) as e:
+        be.gated_delta_scan_layers(dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dg.data_ptr(), db.data_ptr(),
+                                   ds.data_ptr(), dso2.data_ptr(), 0, 0, tokens, heads, qk)
+    assert e.value.kind == "Shape"
+
 
 def test_prepare_matches_oracle(be, orc):
     rng = np.random.default_rng(3)
