@@ -412,6 +412,20 @@ def run_decode(args):
             buckets[f"accept_{force}"] = bem / (bms * 1e-3)
         pms, _, pem, _ = run_blocks(max(args.steps // 8, 8), False, -1, False)
         plain = pem / (pms * 1e-3)
+    # device time per phase of a block (events at the phase boundaries; outside the timed region)
+    phases = None
+    if not args.quick:
+        ex.phase_timing(True)
+        acc = {}
+        ex.prefill_synthetic(context, seed=1)
+        tok = 1
+        for i in range(8):
+            tok = ex.decode(tok, mtp_enabled=True, force_accept=-1).token_id
+            if i >= 3:
+                for name, v in ex.last_phase_ms().items():
+                    acc[name] = acc.get(name, 0.0) + v / 5
+        ex.phase_timing(False)
+        phases = acc
     # dominant kernel (the streaming matvec) alone, event pairs around every launch
     timing_blocks = 1 if args.quick else 4
     be.kernel_timing(True)
@@ -462,6 +476,7 @@ def run_decode(args):
             "mean_accepted_drafts_per_block": accepted / args.steps,
             "tokens_per_s_without_mtp": plain,
             "tokens_per_s_forced_acceptance": buckets,
+            "phase_ms_per_block": phases,
             "host_reads_per_block": 1,
             "host_enqueue_ms_per_block": enqueue_ms,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",

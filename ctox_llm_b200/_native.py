@@ -188,6 +188,8 @@ SIGNATURES = {
                                      C.c_void_p, C.POINTER(ExecStep)]),
     "ctox_exec_commit_speculative": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p]),
     "ctox_exec_session_state": (C.c_int32, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "ctox_exec_phase_timing": (C.c_int32, [C.c_void_p, C.c_int32]),
+    "ctox_exec_last_phase_ms": (C.c_int32, [C.c_void_p, C.POINTER(C.c_float)]),
     "ctox_exec_last_enqueue_us": (C.c_int32, [C.c_void_p, C.POINTER(C.c_double)]),
     "ctox_exec_last_mtp_hidden": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32)]),
     "ctox_exec_last_draft_logits": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint32),

@@ -85,6 +85,12 @@ struct ctox_exec {
     // prefix on the device and leaves the count here until commit_speculative confirms it.
     int32_t pending = -1;
     double last_enqueue_us = 0.0;  // host time the last decode spent enqueuing before it waited for the device
+    // Optional device times of the phases of a decode call (events at the phase boundaries):
+    // drafting, target pass, head + acceptance, commit.
+    bool phase_timing = false;
+    cudaEvent_t phase_ev[6] = {};
+    float phase_ms[4] = {0.f, 0.f, 0.f, 0.f};
+    bool commit_timed = false;
     // A device error or a failed call after work was enqueued leaves the session state undefined:
     // every call fails until reset_session (engine.rs:594-611 invalidates the session the same way).
     bool poisoned = false;
@@ -206,6 +212,8 @@ ctox_status ctox_exec_destroy(ctox_exec *e) {
     ctox_matvec_destroy(e->mtp_fc);
     ctox_matvec_destroy(e->draft_head);
     for (auto &o : e->owned) dev_free(e->ctx, o.first, o.second);
+    for (auto &ev : e->phase_ev)
+        if (ev) cudaEventDestroy(ev);
     delete e;
     return CTOX_OK;
 }
@@ -1203,6 +1211,14 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
     // committed positions or lie beyond them and are rewritten by the next call).
     *began = true;
     EX(upload_u32(e, e->tokens_dev, host_tokens, 1));
+    if (e->phase_timing) {
+        if (e->commit_timed) {  // the commit of the block before: its events have long completed
+            cudaEventSynchronize(e->phase_ev[5]);
+            cudaEventElapsedTime(&e->phase_ms[3], e->phase_ev[4], e->phase_ev[5]);
+            e->commit_timed = false;
+        }
+        cudaEventRecord(e->phase_ev[0], ctx->stream);
+    }
     if (k > 0) {
         // catch-up over the pairs of the last block (true target hiddens), then the chained drafts
         const uint32_t n = e->hist_n;
@@ -1222,7 +1238,9 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
     }
     if (cancelled(cancel)) return fail(ctx, CTOX_CANCELLED, "decode cancelled before the target pass");
     const uint32_t m = k + 1;
+    if (e->phase_timing) cudaEventRecord(e->phase_ev[1], ctx->stream);
     EX(target_pass(e, m, P));
+    if (e->phase_timing) cudaEventRecord(e->phase_ev[2], ctx->stream);
     EX(matvec_stream_prepared(e->lm_head, 0, m));
     int32_t parent[kMaxPass];
     for (uint32_t i = 0; i < m; ++i) parent[i] = (int32_t)i - 1;
@@ -1235,6 +1253,7 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
     EX(head_accept_enqueue(ctx, m, parent, e->tokens_dev, inv_t, seed, step_id,
                            force_accept < 0 ? -1 : (force_accept > (int32_t)k ? (int32_t)k : force_accept),
                            &rec_dev));
+    if (e->phase_timing) cudaEventRecord(e->phase_ev[3], ctx->stream);
     EX(ensure_pinned(ctx, sizeof(ctox_spec_record) + 16));
     CTOX_CUDA(ctx, cudaMemcpyAsync(ctx->pinned, rec_dev, sizeof(ctox_spec_record), cudaMemcpyDeviceToHost,
                                    ctx->stream));
@@ -1242,6 +1261,8 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
                                    cudaMemcpyDeviceToHost, ctx->stream));
     e->last_enqueue_us = std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t_begin).count();
     CTOX_CUDA(ctx, cudaStreamSynchronize(ctx->stream));  // the one host read of the block
+    if (e->phase_timing)
+        for (int i = 0; i < 3; ++i) cudaEventElapsedTime(&e->phase_ms[i], e->phase_ev[i], e->phase_ev[i + 1]);
     ctox_spec_record rec;
     memcpy(&rec, ctx->pinned, sizeof rec);
     int32_t dev_err;
@@ -1258,7 +1279,12 @@ ctox_status decode_impl(ctox_exec *e, uint32_t token, int32_t mtp_enabled, float
     if (rec.n_emitted == 0 || rec.n_emitted > m)
         return fail(ctx, CTOX_INVALID_STATE, "decode: malformed acceptance record");
     const uint32_t n_acc = rec.n_emitted - 1;
+    if (e->phase_timing) cudaEventRecord(e->phase_ev[4], ctx->stream);
     EX(commit_positions(e, m, n_acc + 1));
+    if (e->phase_timing) {
+        cudaEventRecord(e->phase_ev[5], ctx->stream);
+        e->commit_timed = true;
+    }
     for (uint32_t j = 0; j < n_acc; ++j) e->hist_tokens[j] = rec.emitted[j];
     step->proposed_drafts = k;
     step->n_accepted = n_acc;
@@ -1337,6 +1363,29 @@ ctox_status ctox_exec_session_state(const ctox_exec *e, int32_t *pending_accepte
     if (!e) return CTOX_INVALID_STATE;
     if (pending_accepted) *pending_accepted = e->pending;
     if (poisoned) *poisoned = e->poisoned ? 1 : 0;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_phase_timing(ctox_exec *e, int32_t enable) {
+    if (!e) return CTOX_INVALID_STATE;
+    ctox_ctx *ctx = e->ctx;
+    CTOX_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (enable)
+        for (auto &ev : e->phase_ev)
+            if (!ev) CTOX_CUDA(ctx, cudaEventCreate(&ev));
+    e->phase_timing = enable != 0;
+    e->commit_timed = false;
+    return CTOX_OK;
+}
+
+ctox_status ctox_exec_last_phase_ms(ctox_exec *e, float *ms4) {
+    if (!e || !ms4) return CTOX_INVALID_STATE;
+    if (e->commit_timed) {
+        cudaEventSynchronize(e->phase_ev[5]);
+        cudaEventElapsedTime(&e->phase_ms[3], e->phase_ev[4], e->phase_ev[5]);
+        e->commit_timed = false;
+    }
+    for (int i = 0; i < 4; ++i) ms4[i] = e->phase_ms[i];
     return CTOX_OK;
 }
 

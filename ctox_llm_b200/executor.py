@@ -130,6 +130,16 @@ class B200Executor:
         self._b._check(self._lib.ctox_exec_commit_speculative(self._h, accepted_drafts,
                                                               _cancel_ptr(cancellation)))
 
+    def phase_timing(self, enable: bool = True) -> None:
+        """Device events at the phase boundaries of every decode call (off by default)."""
+        self._b._check(self._lib.ctox_exec_phase_timing(self._h, int(enable)))
+
+    def last_phase_ms(self) -> dict:
+        """Device milliseconds of the last decode call's phases (after phase_timing(True))."""
+        v = (C.c_float * 4)()
+        self._b._check(self._lib.ctox_exec_last_phase_ms(self._h, v))
+        return {"drafts": v[0], "target_pass": v[1], "head_and_acceptance": v[2], "commit": v[3]}
+
     def last_enqueue_us(self) -> float:
         """Host microseconds the last decode spent enqueuing kernels before waiting for the device."""
         v = C.c_double()

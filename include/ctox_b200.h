@@ -456,6 +456,13 @@ ctox_status ctox_exec_session_state(const ctox_exec *exec, int32_t *pending_acce
  * waited for the device: the launch path's cost, which bounds a block when the shards are small
  * (the reference bench reports the same split, src/bin/cuda_target_mtp4_graph_bench.rs:36-64). */
 ctox_status ctox_exec_last_enqueue_us(const ctox_exec *exec, double *microseconds);
+/* Device time of the phases of a decode call, measured with events at the phase boundaries when
+ * enabled (off by default: an event between two kernels ends their overlap there): ms4 = {MTP
+ * catch-up + chained drafts, target pass, lm_head + statistics + acceptance, commit of the accepted
+ * prefix} of the last call. The reference's loop bench reports the same split
+ * (src/bin/cuda_target_mtp4_graph_bench.rs:36-64,124-136). */
+ctox_status ctox_exec_phase_timing(ctox_exec *exec, int32_t enable);
+ctox_status ctox_exec_last_phase_ms(ctox_exec *exec, float *ms4);
 ctox_status ctox_exec_position(const ctox_exec *exec, uint64_t *position);
 /* Final hidden state of the last committed position (device -> host), for parity tests. */
 ctox_status ctox_exec_last_hidden(ctox_exec *exec, float *out);

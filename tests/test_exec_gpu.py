@@ -209,6 +209,35 @@ def test_speculative_transaction_and_cancellation(setup):
         ex.prefill(PROMPT, token)
     assert e.value.kind == "Cancelled"
 
+def test_phase_timing_reports_device_time_of_every_phase_and_changes_no_result(setup):
+    """The four phases of a speculative block (drafting, target pass, head + acceptance, commit) get a
+    positive device time each, their sum stays below the call's wall time, and the blocks are the
+    ones the executor resolves without the events."""
+    import time
+    be, ex, model = setup
+    ex.prefill(PROMPT)
+    plain = []
+    tok = PROMPT[-1]
+    for force in (-1, 1, 0):
+        blk = ex.decode(tok, mtp_enabled=True, force_accept=force)
+        plain.append((blk.emitted, blk.draft_tokens))
+        tok = blk.token_id
+    ex.reset_session()
+    ex.prefill(PROMPT)
+    ex.phase_timing(True)
+    tok = PROMPT[-1]
+    for i, force in enumerate((-1, 1, 0)):
+        t0 = time.perf_counter()
+        blk = ex.decode(tok, mtp_enabled=True, force_accept=force)
+        ph = ex.last_phase_ms()
+        wall_ms = (time.perf_counter() - t0) * 1e3
+        assert (blk.emitted, blk.draft_tokens) == plain[i]
+        assert set(ph) == {"drafts", "target_pass", "head_and_acceptance", "commit"}
+        assert all(v > 0.0 for v in ph.values()), ph
+        assert sum(ph.values()) < wall_ms, (ph, wall_ms)
+        tok = blk.token_id
+    ex.phase_timing(False)
+
 
 def test_a_peer_that_never_answers_runs_out_the_bounded_wait_and_poisons_the_session(orc):
     """Failure detection without a fault: rank 0 of a two-rank group whose peer never pushes its
