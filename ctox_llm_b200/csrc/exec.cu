@@ -951,27 +951,19 @@ ctox_status group_sum(ctox_exec *e, ctox_matvec *mv, uint32_t m, MvOut *o) {
     return CTOX_OK;
 }
 
-// Up to this many positions the input norm of a projection runs inside the streaming kernel's
-// prologue; with more positions the prologue (every CTA repeats its slice's fragments for every
-// position) costs more than the separate kernel it replaces (measured on the 5-position verify pass).
-constexpr uint32_t kFuseNormMaxPos = 2;
-
-NormSource norm_of(const ctox_exec *e, const float *h, const float *w) {
-    return NormSource{h, e->norm_scratch, w, residual_parts(e->cfg.hidden_size), e->cfg.hidden_size,
-                      e->cfg.rms_norm_epsilon};
-}
-
 // h += output of a projection back to the hidden width (summed over the tensor-parallel group when
 // there is one: through peer memory, else NCCL), with the partial sums of squares in norm_scratch;
-// then, unless the next projection normalises in its own prologue (`fused_norm`), the norm kernel.
+// then, unless `add_only`, the RMS norm (weight norm_w) into xn_out and / or the fragments of `next`.
+// (The norm used to run inside the next projection's prologue for passes of one or two positions:
+// measured slower than the merged kernel at every position count, and removed.)
 ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, const float *norm_w, float *xn_out,
-                         ctox_matvec *next, bool fused_norm) {
+                         ctox_matvec *next, bool add_only) {
     ctox_ctx *ctx = e->ctx;
     const ctox_model_config &c = e->cfg;
     MvOut o = mv_out(mv, m);
     if (ctx->tp_peer) {
         const MvIn nin = next ? mv_in(next) : MvIn{};
-        if (!fused_norm && tp_peer_reduce_add_norm_fits(c.hidden_size, next ? &nin : nullptr)) {
+        if (!add_only && tp_peer_reduce_add_norm_fits(c.hidden_size, next ? &nin : nullptr)) {
             // group sum, residual add, norm and fragments as one cluster kernel
             EX(tp_peer_reduce_add_norm(ctx, o, c.hidden_size, m, h, e->norm_scratch, norm_w, c.rms_norm_epsilon, xn_out,
                                        next ? &nin : nullptr));
@@ -980,7 +972,7 @@ ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, co
         EX(tp_peer_reduce_add(ctx, o, c.hidden_size, m, h, e->norm_scratch));
     } else {
         EX(group_sum(e, mv, m, &o));
-        if (!fused_norm) {  // residual add, norm and fragments as one cluster kernel
+        if (!add_only) {  // residual add, norm and fragments as one cluster kernel
             const MvIn nin = next ? mv_in(next) : MvIn{};
             launch_residual_norm_prep(ctx->stream, h, &o, norm_w, c.rms_norm_epsilon, c.hidden_size, m, xn_out,
                                       next ? &nin : nullptr, e->norm_scratch);
@@ -988,7 +980,7 @@ ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, co
         }
         launch_residual_add(ctx->stream, h, &o, c.hidden_size, m, e->norm_scratch);
     }
-    if (!fused_norm) {
+    if (!add_only) {
         const MvIn nin = next ? mv_in(next) : MvIn{};
         launch_norm_prep(ctx->stream, h, norm_w, c.rms_norm_epsilon, c.hidden_size, m, xn_out, next ? &nin : nullptr,
                          e->norm_scratch);
@@ -996,11 +988,9 @@ ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, co
     return CTOX_OK;
 }
 
-// One decoder layer for m positions. Up to kFuseNormMaxPos positions the projections normalise h
-// in their own prologue: on entry norm_scratch holds the sums of squares of h, and unless
-// xn_out/next ask for the final norm as a kernel (xn_out receives the normalised vector, `next`
-// its fragments) it holds those of the output on return. With more positions the fragments of the
-// layer's input projection are in place on entry and `next`/next_norm name the next projection.
+// One decoder layer for m positions. The fragments of the layer's input projection are in place on
+// entry; next_norm / next name the norm and projection that follow the layer (xn_out also receives
+// the normalised vector); with neither, the layer ends with the residual add alone.
 ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t rope_pos0, uint64_t slot0,
                        const uint32_t *page_table, const float *next_norm, float *xn_out, ctox_matvec *next) {
     ctox_ctx *ctx = e->ctx;
@@ -1008,9 +998,7 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
     const ctox_model_config &c = e->cfg;
     LayerW &lw = e->w[l];
     LayerS &ls = e->s[l];
-    const bool fuse = m <= kFuseNormMaxPos;
-    const NormSource in_norm = norm_of(e, h, lw.in_ln);
-    EX(matvec_stream_prepared(lw.in_fan, 0, m, fuse ? &in_norm : nullptr));
+    EX(matvec_stream_prepared(lw.in_fan, 0, m));
     const MvOut fan = mv_out(lw.in_fan, m);
     const MvIn out_in = mv_in(lw.out);
     if (!lw.full) {
@@ -1029,9 +1017,8 @@ ctox_status layer_body(ctox_exec *e, uint32_t l, float *h, uint32_t m, uint64_t 
                          c.kv_page_tokens, slot0, m, splits, e->attn_ws, out_in);
     }
     EX(matvec_stream_prepared(lw.out, 0, m));
-    EX(add_and_norm(e, h, lw.out, m, lw.post_ln, nullptr, lw.gate_up, fuse));
-    const NormSource post_norm = norm_of(e, h, lw.post_ln);
-    EX(matvec_stream_prepared(lw.gate_up, 0, m, fuse ? &post_norm : nullptr));
+    EX(add_and_norm(e, h, lw.out, m, lw.post_ln, nullptr, lw.gate_up, false));
+    EX(matvec_stream_prepared(lw.gate_up, 0, m));
     launch_swiglu_prep(st, mv_out(lw.gate_up, m), c.intermediate_size, m, mv_in(lw.down));
     EX(matvec_stream_prepared(lw.down, 0, m));
     EX(add_and_norm(e, h, lw.down, m, next_norm, xn_out, next, !(xn_out || next)));
@@ -1045,18 +1032,13 @@ ctox_status target_pass(ctox_exec *e, uint32_t m, uint64_t pos0) {
     ctox_ctx *ctx = e->ctx;
     const ctox_model_config &c = e->cfg;
     EX(matvec_embed_rows(e->embed, e->tokens_dev, m, e->h));
-    const bool fuse = m <= kFuseNormMaxPos;
-    if (fuse) {
-        launch_residual_add(ctx->stream, e->h, nullptr, c.hidden_size, m, e->norm_scratch);
-    } else {
-        const MvIn first = mv_in(e->w[0].in_fan);
-        launch_residual_norm_prep(ctx->stream, e->h, nullptr, e->w[0].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
-                                  nullptr, &first, e->norm_scratch);
-    }
+    const MvIn first = mv_in(e->w[0].in_fan);
+    launch_residual_norm_prep(ctx->stream, e->h, nullptr, e->w[0].in_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr,
+                              &first, e->norm_scratch);
     for (uint32_t l = 0; l < e->n_layers; ++l) {
         const bool last = l + 1 == e->n_layers;
-        const float *next_norm = last ? e->final_norm : (fuse ? nullptr : e->w[l + 1].in_ln);
-        ctox_matvec *next = last ? e->lm_head : (fuse ? nullptr : e->w[l + 1].in_fan);
+        const float *next_norm = last ? e->final_norm : e->w[l + 1].in_ln;
+        ctox_matvec *next = last ? e->lm_head : e->w[l + 1].in_fan;
         EX(layer_body(e, l, e->h, m, pos0, pos0, e->page_table, next_norm, last ? e->final_hidden : nullptr, next));
     }
     return CTOX_OK;
@@ -1113,13 +1095,9 @@ ctox_status mtp_pass(ctox_exec *e, uint32_t m, uint64_t abs_pos0, const uint32_t
     EX(matvec_stream_prepared(e->mtp_fc, 0, m));
     CTOX_CUDA(ctx, cudaMemsetAsync(e->mtp_h, 0, (size_t)m * c.hidden_size * 4, ctx->stream));
     const MvOut fc = mv_out(e->mtp_fc, m);
-    if (m <= kFuseNormMaxPos) {
-        launch_residual_add(ctx->stream, e->mtp_h, &fc, c.hidden_size, m, e->norm_scratch);
-    } else {
-        const MvIn lin = mv_in(e->w[L].in_fan);
-        launch_residual_norm_prep(ctx->stream, e->mtp_h, &fc, e->w[L].in_ln, c.rms_norm_epsilon, c.hidden_size, m,
-                                  nullptr, &lin, e->norm_scratch);
-    }
+    const MvIn lin = mv_in(e->w[L].in_fan);
+    launch_residual_norm_prep(ctx->stream, e->mtp_h, &fc, e->w[L].in_ln, c.rms_norm_epsilon, c.hidden_size, m, nullptr,
+                              &lin, e->norm_scratch);
     EX(layer_body(e, L, e->mtp_h, m, abs_pos0, abs_pos0 - 1, e->mtp_page_table, e->mtp_norm, e->mtp_hidden,
                   nullptr));
     if (e->keep_logits && e->mtp_trace && e->mtp_trace_n + m <= 2 * kMaxPass) {

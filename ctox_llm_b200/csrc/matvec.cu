@@ -244,14 +244,6 @@ struct StreamParams {
     uint32_t ctas_per_slice;
     uint32_t warps_per_slice;  // warps that take work (<= units per slice)
     uint32_t npos, max_pieces;
-    // When norm_h is set the activations are not read from xfrag/meta: every CTA builds the
-    // fragments of its column slice itself from x = rmsnorm_1p(norm_h) * s_in.
-    const float *norm_h;      // [npos][norm_hidden]
-    const float *norm_sumsq;  // [npos][norm_parts] partial sums of squares of norm_h
-    const float *norm_w;      // [norm_hidden]
-    const float *norm_s_in;   // [norm_hidden] or null
-    uint32_t norm_parts, norm_hidden;
-    float norm_eps;
 };
 
 // Four MMAs of one 16-row x 64-column block; cw = this lane's code vector(s).
@@ -294,7 +286,6 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     uint8_t *ms = xs + xfrag_bytes;
     uint8_t *zero = ms + ((meta_bytes + 15) & ~15u);  // 16 zero bytes for lanes without operands
     uint64_t *bars = reinterpret_cast<uint64_t *>(zero + 16);
-    float *inv_rms = reinterpret_cast<float *>(&bars[WARPS * STAGES + 1]);  // [kMaxPosPerPass]
     const uint32_t xbar = smem_u32(&bars[WARPS * STAGES]);
     const uint32_t my_bars = smem_u32(&bars[warp * STAGES]);
     const uint32_t my_stage = smem_u32(stages + warp * STAGES * kChunkBytes);
@@ -333,66 +324,8 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
     // Everything above touched only this matrix's weights, which nothing in the stream writes.
     // The activations come from the kernels before this one: wait for them here, with the first
     // STAGES chunks of every warp already on their way.
-    // fused norm: the norm weight and s_in of this thread's first block are constants too
-    float4 wv_first = make_float4(0.f, 0.f, 0.f, 0.f), sv_first = make_float4(1.f, 1.f, 1.f, 1.f);
-    if (p.norm_h) {
-        const uint32_t c = (slice * slice_blocks + (threadIdx.x >> 4) / p.npos) * 64 + (threadIdx.x & 15) * 4;
-        if ((threadIdx.x >> 4) < slice_blocks * p.npos && c < p.norm_hidden) {
-            wv_first = *reinterpret_cast<const float4 *>(p.norm_w + c);
-            if (p.norm_s_in) sv_first = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
-        }
-    }
     pdl_wait();
-    if (p.norm_h) {
-        // Fused input norm: xn = h * rsqrt(mean(h^2) + eps) * (1 + w), x = xn * s_in, written as
-        // fragments straight into shared memory while the first weight chunks are in flight.
-        const int i = threadIdx.x & 15;
-        const unsigned gmask = (threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu;
-        const uint32_t first_block = slice * slice_blocks;
-        // tasks = (block, position) pairs, one per 16-lane group and round; the h values of the next
-        // round are requested before this round's fragments are built (one L2 trip in flight), and
-        // those of the first round together with the partial sums of squares
-        const uint32_t n_tasks = slice_blocks * p.npos, stride = (WARPS * 32) >> 4;
-        auto load_h = [&](uint32_t task) {
-            float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (task < n_tasks) {
-                const uint32_t b = task / p.npos, m = task % p.npos;
-                const uint32_t c = (first_block + b) * 64 + i * 4;
-                if (c < p.norm_hidden)  // norm_hidden is a multiple of 64: whole blocks
-                    hv = *reinterpret_cast<const float4 *>(p.norm_h + (size_t)m * p.norm_hidden + c);
-            }
-            return hv;
-        };
-        float4 hv = load_h(threadIdx.x >> 4);
-        if (threadIdx.x < p.npos) {
-            float sq = 0.f;
-            for (uint32_t q = 0; q < p.norm_parts; ++q) sq += p.norm_sumsq[threadIdx.x * p.norm_parts + q];
-            inv_rms[threadIdx.x] = 1.0f / sqrtf(sq / (float)p.norm_hidden + p.norm_eps);
-        }
-        __syncthreads();
-        for (uint32_t task = threadIdx.x >> 4; task < n_tasks; task += stride) {
-            const float4 hn = load_h(task + stride);
-            const uint32_t b = task / p.npos, m = task % p.npos;
-            const uint32_t c = (first_block + b) * 64 + i * 4;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (c < p.norm_hidden) {
-                float4 wv = wv_first, sv = sv_first;
-                if (task != (threadIdx.x >> 4)) {
-                    wv = *reinterpret_cast<const float4 *>(p.norm_w + c);
-                    sv = make_float4(1.f, 1.f, 1.f, 1.f);
-                    if (p.norm_s_in) sv = *reinterpret_cast<const float4 *>(p.norm_s_in + c);
-                }
-                const float inv = inv_rms[m];
-                v[0] = hv.x * inv * (1.0f + wv.x) * sv.x;
-                v[1] = hv.y * inv * (1.0f + wv.y) * sv.y;
-                v[2] = hv.z * inv * (1.0f + wv.z) * sv.z;
-                v[3] = hv.w * inv * (1.0f + wv.w) * sv.w;
-            }
-            prep_block(v, i, gmask, (int)b, (int)m, (int)p.npos, DT, xs, reinterpret_cast<float2 *>(ms));
-            hv = hn;
-        }
-        __syncthreads();
-    } else if (threadIdx.x == 0) {
+    if (threadIdx.x == 0) {
         fence_proxy_async();
         mbar_expect_tx(xbar, xfrag_bytes + meta_bytes);
         const uint8_t *xsrc = p.xfrag + (size_t)slice * xfrag_bytes;
@@ -406,7 +339,7 @@ __global__ void __launch_bounds__(WARPS * 32, 1) k_matvec_stream(const StreamPar
                  meta_bytes, xbar);
     }
     if (!active || nchunks == 0) return;  // warp 0 of every CTA is active and waits for xbar below
-    bool ok = p.norm_h ? true : mbar_wait(xbar, 0);
+    bool ok = mbar_wait(xbar, 0);
 
     // lanes whose B column / position does not exist read zeros with stride 0
     uint32_t b_base[NT], b_stride[NT], b_half[NT], m_base[NT], m_stride[NT];
@@ -795,7 +728,7 @@ size_t stream_smem_bytes(int dt, StreamCfg cfg, uint32_t slice_blocks, uint32_t 
     const size_t stage = (size_t)cfg.warps * cfg.stages * chunk;
     const size_t xfrag = (size_t)slice_blocks * 2 * npos * 128;
     const size_t meta = ((size_t)slice_blocks * npos * 8 + 15) & ~(size_t)15;
-    return stage + xfrag + meta + 16 + ((size_t)cfg.warps * cfg.stages + 1) * 8 + kMaxPosPerPass * 4;
+    return stage + xfrag + meta + 16 + ((size_t)cfg.warps * cfg.stages + 1) * 8;
 }
 
 // The widest launch shape whose shared memory fits; warps == 0 when none does.
@@ -998,8 +931,7 @@ uint32_t matvec_positions_per_pass(ctox_matvec *mv) {
 }
 
 // fragments_of: another matrix of the same fan-out group whose fragment buffers hold the activations.
-ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos, const NormSource *norm,
-                                   const ctox_matvec *fragments_of) {
+ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos, const ctox_matvec *fragments_of) {
     ctox_ctx *ctx = mv->ctx;
     MatvecPart &p = mv->parts[part_index];
     const MatvecPart::Split &split = p.split[npos > 4 ? 1 : 0];
@@ -1023,19 +955,6 @@ ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t 
     sp.warps_per_slice = split.warps_per_slice;
     sp.npos = npos;
     sp.max_pieces = p.max_pieces;
-    sp.norm_h = nullptr;
-    if (norm) {
-        if (norm->hidden != mv->columns || norm->hidden % 64)
-            return fail(ctx, CTOX_SHAPE, "fused norm: %u values for a matrix of %llu columns", norm->hidden,
-                        (unsigned long long)mv->columns);
-        sp.norm_h = norm->h;
-        sp.norm_sumsq = norm->sumsq;
-        sp.norm_w = norm->w;
-        sp.norm_s_in = mv->s_in;
-        sp.norm_parts = norm->parts;
-        sp.norm_hidden = norm->hidden;
-        sp.norm_eps = norm->eps;
-    }
     const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
     const unsigned grid = split.ctas_per_slice * p.slices;
     timing_begin(ctx);
@@ -1337,7 +1256,7 @@ ctox_status ctox_matvec_fanout_dispatch(ctox_matvec *const *mvs, uint64_t n, con
                    (int)first->blocks_padded, (int)npos, first->parts[0].dt, first->xfrag, first->meta);
         for (uint64_t i = 0; i < n; ++i) {
             ctox_matvec *mv = mvs[i];
-            ctox_status rc = matvec_stream_prepared(mv, 0, npos, nullptr, first);
+            ctox_status rc = matvec_stream_prepared(mv, 0, npos, first);
             if (rc) return rc;
             float *y = y_devs[i] + (size_t)m0 * y_strides[i];
             MatvecPart &p = mv->parts[0];
@@ -1630,7 +1549,6 @@ extern "C" ctox_status ctox_matvec_dispatch_static(ctox_matvec *mv, const void *
             sp.warps_per_slice = split.warps_per_slice;
             sp.npos = npos;
             sp.max_pieces = p.max_pieces;
-            sp.norm_h = nullptr;
             const StreamCfg cfg{split.warps, split.stages};
             const size_t smem = stream_smem_bytes(p.dt, cfg, p.kst_s * 4, npos);
             const unsigned grid = split.ctas_per_slice * p.slices;

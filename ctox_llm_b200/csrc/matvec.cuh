@@ -61,19 +61,10 @@ uint32_t matvec_positions_per_pass(ctox_matvec *mv);
 // land in part.partial ([pairs][slices][max_pieces][kMaxPosPerPass][32 rows]); no finish kernel is run.
 ctox_status matvec_stream_pass(ctox_matvec *mv, size_t part_index, const void *x, uint32_t x_dtype,
                                uint32_t npos, uint64_t x_stride);
-// Input of a matvec given as "rmsnorm_1p of h": the streaming kernel normalises and builds the
-// fragments of its column slice in its own prologue (no separate kernel, no round trip).
-struct NormSource {
-    const float *h;      // [npos][hidden]
-    const float *sumsq;  // [npos][parts] partial sums of squares of h (any split; added in order)
-    const float *w;      // [hidden] norm weight (applied as 1 + w)
-    uint32_t parts, hidden;
-    float eps;
-};
-// Same, for activations that are already in fragment form in mv->xfrag / mv->meta, or (norm set)
-// for x = rmsnorm_1p(norm->h) * s_in computed inside the kernel.
+// Same, for activations that are already in fragment form in mv->xfrag / mv->meta (or in those of
+// fragments_of, another matrix of the same fan-out group).
 ctox_status matvec_stream_prepared(ctox_matvec *mv, size_t part_index, uint32_t npos,
-                                   const NormSource *norm = nullptr, const ctox_matvec *fragments_of = nullptr);
+                                   const ctox_matvec *fragments_of = nullptr);
 // Takes ownership of tracked device buffers: canonical bytes, widened s_in [columns], s_out [rows].
 ctox_status matvec_create_device(ctox_ctx *ctx, int dt, uint64_t rows, uint64_t columns, uint8_t *canon,
                                  size_t canon_bytes, float *s_in, float *s_out, uint32_t flags,
