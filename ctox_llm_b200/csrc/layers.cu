@@ -112,8 +112,7 @@ void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps
 __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
                                                                     uint32_t hidden, const float *__restrict__ w,
                                                                     float eps, int npos, float *__restrict__ xn_out,
-                                                                    MvIn next, int has_next, uint32_t nblocks,
-                                                                    float *__restrict__ sumsq) {
+                                                                    MvIn next, int has_next, uint32_t nblocks) {
     pdl_launch();
     const uint32_t tid = threadIdx.x, rank = blockIdx.x;  // gridDim.x == cluster size
     const int m = blockIdx.y;
@@ -130,7 +129,7 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__r
             h[(size_t)m * hidden + c] = v;
         }
     }
-    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks, sumsq);
+    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks);
 }
 
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
@@ -144,7 +143,7 @@ void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, cons
         MvOut a = add ? *add : MvOut{};
         MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
         launch_pdl_cluster(k_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnThreads), 0, st, kRnCluster, h, a,
-                           add != nullptr, hidden, w, eps, (int)m, xn_out, n, next != nullptr, nblocks, scratch);
+                           add != nullptr, hidden, w, eps, (int)m, xn_out, n, next != nullptr, nblocks);
         return;
     }
     launch_residual_add(st, h, add, hidden, m, scratch);

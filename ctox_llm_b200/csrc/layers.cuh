@@ -131,13 +131,11 @@ __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t p
 // CTAs of a thread-block cluster share a position; the partial sums of squares meet through
 // distributed shared memory (one cluster barrier instead of a kernel boundary), then each CTA
 // normalises its 1024 columns and writes its sixteen 64-column blocks of the next projection's
-// fragments. Also leaves the 256-column partial sums of squares in `sumsq` like k_residual_add
-// (layers that run next with fewer positions read them). wc = norm weight, sc = s_in of column c.
-// Every thread of the cluster must call it.
+// fragments. wc = norm weight, sc = s_in of column c. Every thread of the cluster must call it.
 constexpr int kRnCluster = 5, kRnThreads = 1024;
 __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, float wc, float sc, float eps, int m,
                                                      int npos, float *__restrict__ xn_out, const MvIn &next,
-                                                     int has_next, uint32_t nblocks, float *__restrict__ sumsq) {
+                                                     int has_next, uint32_t nblocks) {
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float red[kRnThreads / 32];
@@ -150,15 +148,12 @@ __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, f
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if ((tid & 31) == 0) red[tid >> 5] = s;
     __syncthreads();
-    if (tid < 4) {  // the 256-column partition of k_residual_add, four parts per CTA, fixed order
-        float t = 0.f;
-        for (int q = 0; q < 8; ++q) t += red[tid * 8 + q];
-        const uint32_t parts = (hidden + 255) / 256, p = rank * 4 + tid;
-        if (p < parts) sumsq[m * parts + p] = t;
-        red[tid * 8] = t;  // only this thread reads red[tid*8 ..]
+    if (tid < 32) {  // the 32 warp sums, by one warp (a fixed tree: the same bits in every run)
+        float t = red[tid];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+        if (tid == 0) part = t;
     }
-    __syncthreads();
-    if (tid == 0) part = red[0] + red[8] + red[16] + red[24];
     cluster.sync();
     float total = 0.f;
     for (int r = 0; r < kRnCluster; ++r) total += *cluster.map_shared_rank(&part, r);  // rank order

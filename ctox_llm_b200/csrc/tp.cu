@@ -189,7 +189,7 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
 // A wait that runs out leaves v undefined but every thread still reaches the cluster barriers.
 __global__ void __launch_bounds__(kRnThreads, 1) k_tp_reduce_residual_norm_prep(
     MvOut o, float *__restrict__ h, TpPeerPtrs peers, const uint2 *recv, size_t source_stride, uint32_t rank,
-    uint32_t world, uint32_t seq, uint32_t hidden, float *__restrict__ sumsq, int32_t *error_flag, long long wait_limit,
+    uint32_t world, uint32_t seq, uint32_t hidden, int32_t *error_flag, long long wait_limit,
     const float *__restrict__ w, float eps, int npos, float *__restrict__ xn_out, MvIn next, int has_next,
     uint32_t nblocks) {
     pdl_launch();
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_tp_reduce_residual_norm_prep(
     float v = 0.f;
     if (c < hidden)
         v = tp_push_collect(o, oref, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
-    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks, sumsq);
+    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks);
 }
 
 ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
@@ -340,7 +340,7 @@ ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows
     const MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
     const uint32_t nblocks = next ? next->blocks_padded : (rows + 63) / 64;
     launch_pdl_cluster(k_tp_reduce_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnThreads), 0, ctx->stream,
-                       kRnCluster, o, h, pp, tp->recv + parity_off, tp->elems, tp->rank, tp->world, seq, rows, sumsq,
+                       kRnCluster, o, h, pp, tp->recv + parity_off, tp->elems, tp->rank, tp->world, seq, rows,
                        ctx->dev_error, ctx->wait_limit_cycles, w, eps, (int)m, xn_out, n, next != nullptr, nblocks);
     CTOX_CUDA(ctx, cudaGetLastError());
     return CTOX_OK;
