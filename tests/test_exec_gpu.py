@@ -238,6 +238,41 @@ def test_phase_timing_reports_device_time_of_every_phase_and_changes_no_result(s
         tok = blk.token_id
     ex.phase_timing(False)
 
+def test_context_capacity_is_a_shape_error_and_leaves_the_session_usable(orc):
+    """A prompt that does not fit and a decode past the capacity are refused with Shape before any
+    work is enqueued (the reference refuses both, decoder.rs:1177-1181 and its state-capacity
+    checks); the session is neither advanced nor poisoned, and reset_session starts over."""
+    cfg = tiny_config(max_context_tokens=96)
+    be = ctox.B200Backend(0)
+    model = OracleModel(orc, cfg, seed=3)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex)
+        ex.warmup()
+        with pytest.raises(ctox.CtoxError) as e:
+            ex.prefill(list(range(1, 200)))
+        assert e.value.kind == "Shape" and ex.position() == 0
+        ex.prefill(PROMPT)
+        tok, steps = PROMPT[-1], 0
+        while True:
+            position = ex.position()
+            try:
+                tok = ex.decode(tok, mtp_enabled=True).token_id
+            except ctox.CtoxError as err:
+                assert err.kind == "Shape" and "capacity" in str(err)
+                break
+            steps += 1
+            assert steps < 200
+        assert steps > 10 and ex.position() == position
+        assert ex.session_state() == {"pending_accepted": -1, "poisoned": False}
+        ex.reset_session()
+        ex.prefill(PROMPT)
+        assert ex.decode(PROMPT[-1], mtp_enabled=False).token_id == model.greedy(PROMPT, 1)[0][0]
+    finally:
+        ex.unload()
+        assert be.allocated_bytes() == 0
+        be.close()
+
 
 def test_a_peer_that_never_answers_runs_out_the_bounded_wait_and_poisons_the_session(orc):
     """Failure detection without a fault: rank 0 of a two-rank group whose peer never pushes its
