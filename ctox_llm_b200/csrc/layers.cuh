@@ -46,7 +46,7 @@ struct AttnGeom {
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
                                uint32_t hidden, uint32_t m, float *xn_out, const MvIn *next, float *scratch);
 // h[m] (+= matvec output) and the partial sums of squares of the result: scratch[m][ceil(hidden/256)],
-// the form NormSource takes.
+// the form launch_norm_prep reads.
 void launch_residual_add(cudaStream_t st, float *h, const MvOut *add, uint32_t hidden, uint32_t m, float *scratch);
 inline uint32_t residual_parts(uint32_t hidden) { return (hidden + 255) / 256; }
 // The norm half of launch_residual_norm_prep alone (scratch already holds the sums of squares of h).
