@@ -641,7 +641,8 @@ CONFIG1_LAYER = [  # BASELINE config 1 (q_proj with the interleaved gate rows, a
 def run_micro(args):
     """Single-kernel workloads on one GPU: `matvec` (any shape), `q2_matvec` (BASELINE config 0b),
     `verify_layer` (config 1: the seven projections of one layer at M = 1, 2, 4, 8, 16 positions) and
-    `gated_delta` (config 2: 48 layers, T = 4 then T = 1). Inputs are resident in HBM; weights or
+    `gated_delta` (config 2: 48 layers, T = 4 then T = 1), `kv_pack` (K/V rows of one layer at 32768
+    tokens to Q4 blocks, the Q4 -> Q2 demotion and the decode). Inputs are resident in HBM; weights or
     states are rotated over more than twice the L2."""
     import torch
     import ctox_llm_b200 as ctox
@@ -693,6 +694,43 @@ def run_micro(args):
                         roofline={"bound": "hbm", "achieved": 130908160 / (ref["kernel_us_per_layer"] * 1e-6) / 1e9,
                                   "peak": peak, "unit": "GB/s", "frac": ref["kernel_frac"],
                                   "peak_kind": f"of {peak_kind}", "kernel": "k_matvec_stream (M = 4)", "traffic": None})
+        elif args.workload == "kv_pack":
+            # K and V of one full-attention layer at 32768 tokens: 4 + 4 heads x 256 = 32 blocks per token
+            n_blocks = 32768 * 32
+            dev = f"cuda:{local}"
+            g = torch.Generator(device=dev).manual_seed(3)
+            vals = torch.randn(n_blocks * 64, device=dev, generator=g)
+            q4 = torch.empty(n_blocks * 34, dtype=torch.uint8, device=dev)
+            q2 = torch.empty(n_blocks * 18, dtype=torch.uint8, device=dev)
+            back = torch.empty(n_blocks * 64, device=dev)
+            ops = {"pack_q4": (lambda: be.kv_pack_q4(vals.data_ptr(), n_blocks, q4.data_ptr()), n_blocks * (256 + 34)),
+                   "demote_q4_to_q2": (lambda: be.kv_demote_q4_to_q2(q4.data_ptr(), n_blocks, q2.data_ptr()),
+                                       n_blocks * (34 + 18)),
+                   "unpack_q2": (lambda: be.kv_unpack(ctox.native.Q2B64, q2.data_ptr(), n_blocks, back.data_ptr()),
+                                 n_blocks * (18 + 256))}
+            res = {}
+            for name, (fn, nbytes) in ops.items():
+                for _ in range(args.warmup):
+                    fn()
+                torch.cuda.synchronize()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record(stream)
+                for _ in range(args.steps):
+                    fn()
+                ev1.record(stream)
+                torch.cuda.synchronize()
+                ms = ev0.elapsed_time(ev1) / args.steps
+                res[name] = {"us": ms * 1e3, "bytes": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                             "frac": nbytes / (ms * 1e-3) / 1e9 / peak}
+            line.update(metric="kv_pack_hbm_gbs", value=res["pack_q4"]["gbs"], unit="GB/s",
+                        ms_per_step=res["pack_q4"]["us"] * 1e-3,
+                        config={"workload": "K/V rows of one full-attention layer at 32768 tokens (1 048 576 blocks "
+                                            "of 64 values): f32 -> Q4_B64, Q4_B64 -> Q2_B64, Q2_B64 -> f32",
+                                "l2": "268 MB of values per launch > 2x L2"},
+                        sweep=res,
+                        roofline={"bound": "hbm", "achieved": res["pack_q4"]["gbs"], "peak": peak, "unit": "GB/s",
+                                  "frac": res["pack_q4"]["frac"], "peak_kind": f"of {peak_kind}",
+                                  "kernel": "k_kv_pack_q4", "traffic": None})
         else:  # gated_delta
             heads, qk, layers = 48, 16, 48
             dev = f"cuda:{local}"
@@ -776,7 +814,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode",
-                    choices=["decode", "q4_matvec", "q2_matvec", "matvec", "verify_layer", "gated_delta"])
+                    choices=["decode", "q4_matvec", "q2_matvec", "matvec", "verify_layer", "gated_delta", "kv_pack"])
     ap.add_argument("--dtype", default="q4", choices=["q4", "q2"], help="matvec: code format")
     ap.add_argument("--rows", type=int, default=17408)
     ap.add_argument("--cols", type=int, default=5120)
@@ -795,9 +833,9 @@ def main():
                     help="decode: only the timed region and one kernel-timing block (for launch lists)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"decode": 256, "verify_layer": 400, "gated_delta": 50}.get(args.workload, 2000)
+        args.steps = {"decode": 256, "verify_layer": 400, "gated_delta": 50, "kv_pack": 50}.get(args.workload, 2000)
     if args.warmup is None:
-        args.warmup = {"decode": 4, "gated_delta": 5}.get(args.workload, 50)
+        args.warmup = {"decode": 4, "gated_delta": 5, "kv_pack": 5}.get(args.workload, 50)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode":

@@ -158,6 +158,9 @@ SIGNATURES = {
     "ctox_matvec_dispatch_host": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p,
                                               C.c_uint32]),
     "ctox_gated_delta_scan": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
+    "ctox_kv_pack_q4": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "ctox_kv_demote_q4_to_q2": (C.c_int32, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "ctox_kv_unpack": (C.c_int32, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint64, C.c_void_p]),
     "ctox_gated_delta_scan_layers": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 4),
     "ctox_gated_delta_scan_f16_state": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 8 + [C.c_uint32] * 5),
     "ctox_gated_delta_prepare": (C.c_int32, [C.c_void_p] + [C.c_void_p] * 6 + [C.c_uint32] * 2),

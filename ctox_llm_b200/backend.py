@@ -187,6 +187,20 @@ class B200Backend:
             self._ctx, *(C.c_void_p(a) for a in (q, k, v, log_decay, beta, state_in, state_out, out)),
             tokens, heads, qk_heads, 128, 128))
 
+    # -- K/V rows as packed blocks (kv_cache.rs:22-73) ----------------------------------------
+    def kv_pack_q4(self, values: int, n_blocks: int, q4_bytes: int) -> None:
+        """QuantizedKvToken::quantize(.., Q4) over n_blocks blocks of 64 floats (device addresses)."""
+        self._check(self._lib.ctox_kv_pack_q4(self._ctx, C.c_void_p(values), n_blocks, C.c_void_p(q4_bytes)))
+
+    def kv_demote_q4_to_q2(self, q4_bytes: int, n_blocks: int, q2_bytes: int) -> None:
+        """QuantizedKvToken::requantize(Q2) of Q4 blocks (a page leaving the recent window)."""
+        self._check(self._lib.ctox_kv_demote_q4_to_q2(self._ctx, C.c_void_p(q4_bytes), n_blocks,
+                                                      C.c_void_p(q2_bytes)))
+
+    def kv_unpack(self, dtype: int, packed: int, n_blocks: int, values: int) -> None:
+        """QuantizedKvToken::dequantize."""
+        self._check(self._lib.ctox_kv_unpack(self._ctx, dtype, C.c_void_p(packed), n_blocks, C.c_void_p(values)))
+
     def gated_delta_prepare(self, a: int, b: int, a_log: int, dt_bias: int, log_decay: int,
                             beta: int, tokens: int, heads: int) -> None:
         self._check(self._lib.ctox_gated_delta_prepare(

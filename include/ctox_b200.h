@@ -265,6 +265,20 @@ ctox_status ctox_gated_delta_scan_f16_state(ctox_ctx *ctx, const float *q, const
                                             const void *state_in, void *state_out, float *out,
                                             uint32_t tokens, uint32_t heads, uint32_t qk_heads,
                                             uint32_t key_dim, uint32_t value_dim);
+/* ---- K/V rows as packed blocks: the steps of the reference's paged KV cache (kv_cache.rs:22-73
+ * QuantizedKvToken::quantize / dequantize / requantize over quant.rs:74-105,144-168; reference CUDA
+ * kernels ctox_pack_paged_kv_q4_f32_sm86 and ctox_demote_paged_kv_q4_to_q2_sm86,
+ * kernels/cuda/q2q4_fused_matvec_sm86.cu:1675-1835). All pointers are device memory; values are
+ * [n_blocks][64] floats, blocks the canonical 34-byte Q4_B64 / 18-byte Q2_B64 encodings back to
+ * back. The bytes equal the scalar code's for the same floats. A non-finite value or scale sets the
+ * device error word (ctox_ctx_device_error). The executor's cache does not use these yet (it keeps
+ * bf16 / f32 rows). */
+ctox_status ctox_kv_pack_q4(ctox_ctx *ctx, const float *values, uint64_t n_blocks, uint8_t *q4_bytes);
+/* Every block decoded and re-quantized to Q2_B64: what a page undergoes when it leaves the recent
+ * window (kv_cache.rs:67-73,461-478). */
+ctox_status ctox_kv_demote_q4_to_q2(ctox_ctx *ctx, const uint8_t *q4_bytes, uint64_t n_blocks, uint8_t *q2_bytes);
+/* dtype: CTOX_Q2B64 or CTOX_Q4B64. */
+ctox_status ctox_kv_unpack(ctox_ctx *ctx, uint32_t dtype, const uint8_t *bytes, uint64_t n_blocks, float *values);
 /* beta = sigmoid(b), log_decay = -exp(A_log) * softplus(a + dt_bias)
  * (decoder.rs:29-35,881,897-902). a, b, log_decay, beta: [tokens][heads]. */
 ctox_status ctox_gated_delta_prepare(ctox_ctx *ctx, const float *a, const float *b,
