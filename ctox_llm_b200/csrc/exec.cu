@@ -107,7 +107,7 @@ struct ctox_exec {
     uint32_t *tokens_dev = nullptr;  // [kMaxPass + 1]: verify inputs = [token, drafts...]
     uint32_t *mtp_tokens_dev = nullptr;
     uint32_t *page_table = nullptr, *mtp_page_table = nullptr;
-    uint32_t attn_splits_max = 64;
+    uint32_t attn_splits_max = kAttnMaxSplits;
     uint64_t model_bytes = 0, session_bytes = 0;
     std::vector<std::pair<void *, size_t>> owned;  // tracked raw allocations (vectors, buffers, states)
 };
@@ -188,7 +188,7 @@ ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c_global, c
     // one CTA per (KV head, context split): fill the SMs once
     e->attn_splits_max = (uint32_t)ctx->sm_count / c->num_key_value_heads;
     if (e->attn_splits_max < 1) e->attn_splits_max = 1;
-    if (e->attn_splits_max > 64) e->attn_splits_max = 64;
+    if (e->attn_splits_max > (uint32_t)kAttnMaxSplits) e->attn_splits_max = kAttnMaxSplits;
     const uint32_t total_layers = e->n_layers + c->mtp_num_hidden_layers;
     e->w.resize(total_layers);
     e->s.resize(total_layers);

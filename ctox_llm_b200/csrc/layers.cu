@@ -779,7 +779,7 @@ __global__ void __launch_bounds__(256) k_attn_combine_prep(AttnGeom g, const flo
                                                          MvIn next) {
     pdl_launch();
     pdl_wait();
-    __shared__ float wgt[64];    // per split: exp(max_s - max) / denominator
+    __shared__ float wgt[kAttnMaxSplits];  // per split: exp(max_s - max) / denominator
     __shared__ float vals[256];  // the head's output, gated and scaled
     const uint32_t hd = g.head_dim, G = g.q_heads / g.kv_heads, NQ = G * npos;
     const uint32_t hq = blockIdx.x % g.q_heads;
@@ -793,27 +793,30 @@ __global__ void __launch_bounds__(256) k_attn_combine_prep(AttnGeom g, const flo
 #pragma unroll
     for (int j = 0; j < 16; ++j) buf[j] = (uint32_t)j < splits ? base[j * split_stride + d] : 0.f;
     const float gt = gate[((size_t)m * g.q_heads + hq) * hd + d];
-    if (threadIdx.x < 32) {  // splits <= 64: two per lane
-        float ms[2], ls[2];
+    if (threadIdx.x < 32) {  // splits <= kAttnMaxSplits: up to kPerLane per lane
+        constexpr int kPerLane = kAttnMaxSplits / 32;
+        float ms[kPerLane], ls[kPerLane];
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < kPerLane; ++j) {
             const uint32_t sp = threadIdx.x + 32 * j;
             ms[j] = sp < splits ? base[sp * split_stride + hd] : -INFINITY;
             ls[j] = sp < splits ? base[sp * split_stride + hd + 1] : 0.f;
         }
-        float mx = fmaxf(ms[0], ms[1]);
+        float mx = ms[0];
+#pragma unroll
+        for (int j = 1; j < kPerLane; ++j) mx = fmaxf(mx, ms[j]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        float w[2], den = 0.f;
+        float w[kPerLane], den = 0.f;
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
+        for (int j = 0; j < kPerLane; ++j) {
             w[j] = ms[j] > -INFINITY ? expf(ms[j] - mx) : 0.f;
             den += ls[j] * w[j];
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int j = 0; j < kPerLane; ++j)
             if (threadIdx.x + 32 * j < splits) wgt[threadIdx.x + 32 * j] = w[j] / den;
     }
     __syncthreads();

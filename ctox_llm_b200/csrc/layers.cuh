@@ -36,6 +36,9 @@ struct MvIn {
 MvOut mv_out(ctox_matvec *mv, uint32_t npos);
 MvIn mv_in(ctox_matvec *mv);
 
+// Most context splits a query head's partial outputs can be merged from (k_attn_combine_prep).
+constexpr int kAttnMaxSplits = 160;
+
 struct AttnGeom {
     uint32_t q_heads, kv_heads, head_dim, rotary_dim;
     float theta, eps;
