@@ -444,8 +444,12 @@ def run_decode(args):
     sub = {}
     if rank == 0 and world == 1 and not args.quick:
         # the other half of the headline metric in the same record: BASELINE config 0 (a) and (b)
+        bytes_before_unload = be.allocated_bytes()
         ex.unload()
         ex = None
+        # the reference's loop bench checks bytes freed after drop == bytes before prepare
+        # (src/bin/cuda_target_mtp4_graph_bench.rs:156-161)
+        sub["device_bytes"] = {"model_and_session": bytes_before_unload, "after_unload": be.allocated_bytes()}
         sub["q4_matvec"] = measure_matvec(be, stream, local, "q4", Q4_ROWS, Q4_COLS, 1, 400)
         sub["q2_matvec"] = measure_matvec(be, stream, local, "q2", 5120, 17408, 1, 400)
     traffic_ratio = load_traffic_ratio()
@@ -473,6 +477,7 @@ def run_decode(args):
                                       if world > 1 else "single",
                        "collective": collective,
                        "acceptance": "as measured on random-init weights"},
+            "speculative_blocks_per_s": args.steps / (ms * 1e-3),
             "mean_accepted_drafts_per_block": accepted / args.steps,
             "tokens_per_s_without_mtp": plain,
             "tokens_per_s_forced_acceptance": buckets,
