@@ -157,7 +157,7 @@ def measure_matvec(be, stream, local, dtype, rows, cols, positions, steps, warmu
     from ctox_llm_b200 import synthetic
     dt = ctox.Q4B64 if dtype == "q4" else ctox.Q2B64
     wbytes = rows * (cols // 64) * BLOCK_BYTES[dtype]
-    n_rep = replicas if replicas > 0 else max(2, min(16, -(-300_000_000 // wbytes)))
+    n_rep = replicas if replicas > 0 else max(8, min(16, -(-300_000_000 // wbytes)))
     reps = [be.prepare_fused_matvec(ctox.FusedMatVec(dt, synthetic.packed_weights(dt, rows, cols, seed=100 + r),
                                                      rows, cols, None)) for r in range(n_rep)]
     x = torch.from_numpy(synthetic.activations(cols, 0, positions=positions).reshape(positions, cols)).cuda(local)
