@@ -407,7 +407,7 @@ def run_decode(args):
     clocks = sampler.stop() if rank == 0 else None
     buckets, plain = {}, None
     if not args.quick:
-        for force in sorted({0, min(2, cfg.max_draft_tokens), cfg.max_draft_tokens}):
+        for force in range(cfg.max_draft_tokens + 1):  # every acceptance bucket (docs/ROOFLINE_GATES.md:50)
             bms, _, bem, _ = run_blocks(max(args.steps // 8, 8), True, force, False)
             buckets[f"accept_{force}"] = bem / (bms * 1e-3)
         pms, _, pem, _ = run_blocks(max(args.steps // 8, 8), False, -1, False)
