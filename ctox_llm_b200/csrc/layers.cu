@@ -494,7 +494,13 @@ __global__ void __launch_bounds__(kAttnThreads) k_attention(
 //    accumulator layout, O += P V with P split the same way and V read through ldmatrix.trans;
 //  * no barrier between the four warps of a group inside a tile: each keeps its own running
 //    max / sum / O and the four are merged once at the end, like the context splits.
-constexpr int kFaTile = 64, kFaHd = 256, kFaStride = kFaHd + 8;  // padded rows: conflict-free ldmatrix
+// Q rows are padded (conflict-free ldmatrix). With two query groups the K / V tile rows are 512 bytes
+// with their 16-byte chunks XOR-swizzled by the row (chunk c of row r sits at c ^ (r & 7)):
+// conflict-free too, and three tile buffers fit beside Q. With one group: two buffers of padded rows.
+constexpr int kFaTile = 64, kFaHd = 256, kFaStride = kFaHd + 8;
+// Tile buffers: three (two tiles in flight) for two query groups, two for one (measured: the third
+// buffer costs the 4-warp kernel 5 us per launch).
+__host__ __device__ constexpr int fa_buffers(int groups) { return groups == 2 ? 3 : 2; }
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -532,14 +538,18 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     uint64_t cache_slot, int npos, uint32_t splits, float *__restrict__ ws) {
     pdl_launch();
     extern __shared__ __align__(128) uint8_t smraw[];
-    constexpr int NT = GROUPS * 128;
+    constexpr int NT = GROUPS * 128, kFaBuffers = fa_buffers(GROUPS);
     const uint32_t G = g.q_heads / g.kv_heads, NQ = G * npos;
     const uint32_t kh = blockIdx.x / splits, sp = blockIdx.x % splits;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
     const uint32_t grp = warp >> 2, wg = warp & 3;  // query group, warp inside the group
-    // shared memory: Q [2 terms][32 queries][stride], then 2 buffers of (K tile, V tile)
+    // shared memory: Q [2 terms][32 queries][stride], then kFaBuffers buffers of (K tile, V tile)
     __nv_bfloat16 *q_s = reinterpret_cast<__nv_bfloat16 *>(smraw);
-    constexpr uint32_t kQBytes = 2 * 32 * kFaStride * 2, kTileBytes = kFaTile * kFaStride * 2;
+    // tile rows: swizzled 512-byte rows where three buffers must fit, padded rows otherwise (their
+    // ldmatrix offsets are compile-time constants)
+    constexpr bool kSwz = kFaBuffers == 3;
+    constexpr uint32_t kRowB = kSwz ? kFaHd * 2 : kFaStride * 2;
+    constexpr uint32_t kQBytes = 2 * 32 * kFaStride * 2, kTileBytes = kFaTile * kRowB;
     const uint32_t q_a = (uint32_t)__cvta_generic_to_shared(q_s);
     const uint32_t buf_a = q_a + kQBytes;  // buffer b: K at buf_a + b*2*kTileBytes, V right after
     const uint64_t total = cache_slot + (uint64_t)npos;
@@ -583,7 +593,7 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
 #pragma unroll
         for (int j = 0; j < kRowsPerThread; ++j) {
             const uint32_t r = warp + j * kRowStep;
-            const uint32_t dst = buf_a + b * 2 * kTileBytes + r * kFaStride * 2 + lane * 16;
+            const uint32_t dst = buf_a + b * 2 * kTileBytes + r * kRowB + ((kSwz ? lane ^ (r & 7) : lane) * 16);
             if (slots[j] != kNoSlot) {
                 const size_t off = ((size_t)slots[j] * g.kv_heads + kh) * kFaHd + lane * 8;
                 cp_async16(dst, k_cache + off);
@@ -609,7 +619,7 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
     pdl_wait();
     if (tile_beg < tile_end) {
         issue_tile(0);
-        if (tile_beg + 1 < tile_end) fetch_slots(tile_beg + 1);
+        if (tile_beg + 1 < tile_end) fetch_slots(tile_beg + 1);  // lands while Q is staged below
     }
     {   // Q as bf16 hi + lo: 8 float4 per thread, all loads issued before the first conversion
         constexpr int kQRows = 16 * GROUPS, kVec = kQRows * kFaHd / 4 / NT;
@@ -633,16 +643,37 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
             *reinterpret_cast<uint2 *>(q_s + (32 + qi) * kFaStride + d) = make_uint2(lo[0], lo[1]);
         }
     }
+    if (kFaBuffers == 3 && tile_beg + 1 < tile_end) {  // the second tile in flight before the first is worked on
+        issue_tile(1);
+        if (tile_beg + 2 < tile_end) fetch_slots(tile_beg + 2);
+    }
     for (uint64_t tile = tile_beg; tile < tile_end; ++tile) {
-        const uint32_t b = (uint32_t)(tile - tile_beg) & 1;
-        if (tile + 1 < tile_end) {
-            issue_tile(b ^ 1);
-            if (tile + 2 < tile_end) fetch_slots(tile + 2);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        const uint32_t b = (uint32_t)((tile - tile_beg) % kFaBuffers);
+        if (kFaBuffers == 2) {
+            // two buffers: the next tile is requested before this one is waited for (both in flight
+            // during the wait); a barrier at the end of the iteration frees this buffer
+            if (tile + 1 < tile_end) {
+                issue_tile(b ^ 1);
+                if (tile + 2 < tile_end) fetch_slots(tile + 2);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncthreads();
         } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            // three buffers: this tile's copies have landed (the group issued after it may still be in
+            // flight) for every thread, and every thread is done with the tile before, whose buffer
+            // takes the tile after next: one barrier per tile, two tiles in flight
+            if (tile + 1 < tile_end)
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            if (tile + 2 < tile_end) {
+                issue_tile((b + 2) % kFaBuffers);
+                if (tile + 3 < tile_end) fetch_slots(tile + 3);
+            }
         }
-        __syncthreads();
         const uint32_t k_a = buf_a + b * 2 * kTileBytes, v_a = k_a + kTileBytes;
         const uint32_t tok0 = wg * 16;
         // ---- S = Q K^T for this warp's 16 queries x 16 tokens
@@ -652,8 +683,8 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
         for (int ks = 0; ks < kFaHd / 16; ++ks) {
             uint32_t bk[4], aq[4];
             // K matrices: (tokens 0-7, k 0-7), (tokens 0-7, k 8-15), (tokens 8-15, k 0-7), (tokens 8-15, k 8-15)
-            ldsm_x4(bk, k_a + (tok0 + (lane & 7) + 8 * (lane >> 4)) * kFaStride * 2 +
-                            (ks * 16 + 8 * ((lane >> 3) & 1)) * 2);
+            ldsm_x4(bk, k_a + (tok0 + (lane & 7) + 8 * (lane >> 4)) * kRowB +
+                            ((kSwz ? (ks * 2 + ((lane >> 3) & 1)) ^ (lane & 7) : ks * 2 + ((lane >> 3) & 1)) * 16));
 #pragma unroll
             for (int term = 0; term < 2; ++term) {
                 // Q matrices: (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15)
@@ -711,15 +742,16 @@ __global__ void __launch_bounds__(GROUPS * 128, 1) k_attention_mma(
 #pragma unroll
         for (int dn = 0; dn < kFaHd / 16; ++dn) {
             uint32_t bv[4];
-            ldsm_x4_trans(bv, v_a + (tok0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kFaStride * 2 +
-                                  (dn * 16 + 8 * (lane >> 4)) * 2);
+            ldsm_x4_trans(bv, v_a + (tok0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kRowB +
+                                  ((kSwz ? (dn * 2 + (lane >> 4)) ^ (lane & 7) : dn * 2 + (lane >> 4)) * 16));
             mma_bf16(oacc[2 * dn], p_hi, bv[0], bv[1]);
             mma_bf16(oacc[2 * dn], p_lo, bv[0], bv[1]);
             mma_bf16(oacc[2 * dn + 1], p_hi, bv[2], bv[3]);
             mma_bf16(oacc[2 * dn + 1], p_lo, bv[2], bv[3]);
         }
-        __syncthreads();  // everyone is done with buffer b before it is refilled
+        if (kFaBuffers == 2) __syncthreads();  // everyone is done with buffer b before it is refilled
     }
+    __syncthreads();  // the merge below reuses the tile buffers
     // ---- merge the four warps of each group through shared memory (reusing the tile buffers)
     float *mo = reinterpret_cast<float *>(smraw + kQBytes);  // [warp][16 rows][hd + 2]
     float *mine = mo + (size_t)warp * 16 * (kFaHd + 2);
@@ -873,22 +905,23 @@ void launch_attention(cudaStream_t st, const AttnGeom &g, const float *q, const 
                       const MvIn &next) {
     const uint32_t nq = g.q_heads / g.kv_heads * m;
     if (kv_bf16 && g.head_dim == kFaHd && nq <= 32) {
-        const size_t smem = 2 * 32 * kFaStride * 2 + 4 * (size_t)kFaTile * kFaStride * 2;
+        const size_t smem1 = 2 * 32 * kFaStride * 2 + (size_t)fa_buffers(1) * 2 * kFaTile * kFaStride * 2;
+        const size_t smem2 = 2 * 32 * kFaStride * 2 + (size_t)fa_buffers(2) * 2 * kFaTile * kFaHd * 2;
         static thread_local unsigned long long attr_devices = 0;  // per device, like above
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev < 64 && !(attr_devices >> dev & 1ull) &&
-            cudaFuncSetAttribute(k_attention_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) ==
+            cudaFuncSetAttribute(k_attention_mma<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem1) ==
                 cudaSuccess &&
-            cudaFuncSetAttribute(k_attention_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) ==
+            cudaFuncSetAttribute(k_attention_mma<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2) ==
                 cudaSuccess)
             attr_devices |= 1ull << dev;
         if (nq <= 16)
-            launch_pdl(k_attention_mma<1>, dim3(g.kv_heads * splits), dim3(128), smem, st, 
+            launch_pdl(k_attention_mma<1>, dim3(g.kv_heads * splits), dim3(128), smem1, st, 
                 g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
                 cache_slot, (int)m, splits, workspace);
         else
-            launch_pdl(k_attention_mma<2>, dim3(g.kv_heads * splits), dim3(256), smem, st, 
+            launch_pdl(k_attention_mma<2>, dim3(g.kv_heads * splits), dim3(256), smem2, st, 
                 g, q, (const __nv_bfloat16 *)k_cache, (const __nv_bfloat16 *)v_cache, page_table, page_tokens,
                 cache_slot, (int)m, splits, workspace);
         launch_pdl(k_attn_combine_prep, dim3(m * g.q_heads), dim3(g.head_dim), 0, st, g, workspace, gate, (int)m, splits,
