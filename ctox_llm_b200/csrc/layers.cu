@@ -108,7 +108,7 @@ void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps
 }
 
 // Residual add, RMS norm and the next projection's fragments in ONE kernel (the shared part is
-// residual_norm_finish, layers.cuh). For hidden <= kRnCluster * 1024.
+// residual_norm_finish, layers.cuh). For hidden <= kRnCluster * kRnThreads = 5120.
 __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
                                                                     uint32_t hidden, const float *__restrict__ w,
                                                                     float eps, int npos, float *__restrict__ xn_out,
@@ -139,7 +139,7 @@ void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, cons
         return !(v && v[0] == '0');
     }();
     const uint32_t nblocks = next ? next->blocks_padded : (hidden + 63) / 64;
-    if (merged && hidden <= kRnCluster * kRnThreads && nblocks <= kRnCluster * 16) {
+    if (merged && hidden <= kRnCluster * kRnThreads && nblocks <= kRnCluster * kRnBlocks) {
         MvOut a = add ? *add : MvOut{};
         MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
         launch_pdl_cluster(k_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnThreads), 0, st, kRnCluster, h, a,

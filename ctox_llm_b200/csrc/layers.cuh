@@ -133,9 +133,12 @@ __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t p
 // c = blockIdx.x * kRnThreads + threadIdx.x of position m is known (and stored): the kRnCluster
 // CTAs of a thread-block cluster share a position; the partial sums of squares meet through
 // distributed shared memory (one cluster barrier instead of a kernel boundary), then each CTA
-// normalises its 1024 columns and writes its sixteen 64-column blocks of the next projection's
+// normalises its kRnThreads columns and writes its kRnBlocks 64-column blocks of the next projection's
 // fragments. wc = norm weight, sc = s_in of column c. Every thread of the cluster must call it.
-constexpr int kRnCluster = 5, kRnThreads = 1024;
+// (measured per speculative block: 5 CTAs of 1024 threads 6.24 ms, 8 of 640 6.18, 10 of 512 6.22,
+// 16 of 320 6.24; one CTA of 1024 threads with five columns per thread 7.74)
+constexpr int kRnCluster = 8, kRnThreads = 5120 / kRnCluster, kRnBlocks = kRnThreads / 64;
+static_assert(kRnThreads % 64 == 0 && kRnThreads <= 1024, "whole 64-column blocks per CTA");
 __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, float wc, float sc, float eps, int m,
                                                      int npos, float *__restrict__ xn_out, const MvIn &next,
                                                      int has_next, uint32_t nblocks) {
@@ -152,7 +155,7 @@ __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, f
     if ((tid & 31) == 0) red[tid >> 5] = s;
     __syncthreads();
     if (tid < 32) {  // the 32 warp sums, by one warp (a fixed tree: the same bits in every run)
-        float t = red[tid];
+        float t = tid < kRnThreads / 32 ? red[tid] : 0.f;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
         if (tid == 0) part = t;
@@ -172,9 +175,9 @@ __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, f
     if (has_next) {
         vals[tid] = xn * sc;
         __syncthreads();
-        if (tid < 256) {  // sixteen groups of 16 lanes, one 64-column block each
+        if (tid < kRnBlocks * 16) {  // groups of 16 lanes, one 64-column block each
             const int i = tid & 15;
-            const uint32_t grp = tid >> 4, b = rank * 16 + grp;
+            const uint32_t grp = tid >> 4, b = rank * kRnBlocks + grp;
             if (b < nblocks) {
                 const float x[4] = {vals[grp * 64 + i * 4], vals[grp * 64 + i * 4 + 1], vals[grp * 64 + i * 4 + 2],
                                     vals[grp * 64 + i * 4 + 3]};

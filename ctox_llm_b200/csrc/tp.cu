@@ -323,7 +323,7 @@ bool tp_peer_reduce_add_norm_fits(uint32_t rows, const MvIn *next) {
         return !(v && v[0] == '0');
     }();
     const uint32_t nblocks = next ? next->blocks_padded : (rows + 63) / 64;
-    return merged && rows <= (uint32_t)kRnCluster * kRnThreads && nblocks <= (uint32_t)kRnCluster * 16;
+    return merged && rows <= (uint32_t)kRnCluster * kRnThreads && nblocks <= (uint32_t)kRnCluster * kRnBlocks;
 }
 
 ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *sumsq,
