@@ -189,6 +189,10 @@ ctox_status ctox_exec_create(ctox_ctx *ctx, const ctox_model_config *c_global, c
     e->attn_splits_max = (uint32_t)ctx->sm_count / c->num_key_value_heads;
     if (e->attn_splits_max < 1) e->attn_splits_max = 1;
     if (e->attn_splits_max > (uint32_t)kAttnMaxSplits) e->attn_splits_max = kAttnMaxSplits;
+    if (const char *cap = getenv("CTOX_ATTN_SPLITS_MAX")) {  // fewer, longer splits (tests: many tiles per CTA)
+        const long v = strtol(cap, nullptr, 10);
+        if (v >= 1 && (uint32_t)v < e->attn_splits_max) e->attn_splits_max = (uint32_t)v;
+    }
     const uint32_t total_layers = e->n_layers + c->mtp_num_hidden_layers;
     e->w.resize(total_layers);
     e->s.resize(total_layers);

@@ -151,6 +151,44 @@ def test_bf16_cache_tensor_core_attention_matches_oracle(orc):
         ex.unload()
         be.close()
 
+@pytest.mark.parametrize("drafts", [0, 4])
+def test_attention_over_many_tiles_per_split_matches_oracle(orc, drafts, monkeypatch):
+    """One context split per KV head (CTOX_ATTN_SPLITS_MAX=1), so that a CTA of the tensor-core kernel
+    walks all 64-token tiles of a 330-token context itself: the tile ring wraps around (two buffers
+    with one query group, three with two). Logits of plain decode steps and the first emitted tokens
+    of speculative blocks against the oracle with the same bf16-rounded cache."""
+    monkeypatch.setenv("CTOX_ATTN_SPLITS_MAX", "1")
+    be = ctox.B200Backend(0)
+    cfg = tiny_config(max_draft_tokens=max(drafts, 1), num_attention_heads=4, num_key_value_heads=1, head_dim=256,
+                      rotary_dim=64, kv_dtype=ctox.BF16, max_context_tokens=512, full_attention_interval=2)
+    model = OracleModel(orc, cfg, seed=9)
+    ex = ctox.B200Executor(be, cfg)
+    try:
+        model.load_into(ex)
+        ex.warmup()
+        ex.keep_logits(True)
+        rng = np.random.default_rng(13)
+        prompt = [int(t) for t in rng.integers(0, 1024, 330)]  # 6 tiles of 64 tokens
+        n_new = 4
+        exp_tokens, exp_logits, _ = model.greedy(prompt, n_new)
+        ex.prefill(prompt)
+        if drafts == 0:
+            tok = prompt[-1]
+            for i in range(n_new):
+                blk = ex.decode(tok, mtp_enabled=False)
+                assert rel_l2(ex.last_logits(0), exp_logits[i]) <= 1e-3, i
+                assert blk.token_id == exp_tokens[i]
+                tok = blk.token_id
+        else:  # five verify positions x four query heads: the two-group kernel
+            blk = ex.decode(prompt[-1], mtp_enabled=True)
+            assert rel_l2(ex.last_logits(0), exp_logits[0]) <= 1e-3
+            assert (blk.accepted_draft_tokens + [blk.token_id]) == exp_tokens[:len(blk.emitted)]
+            blk2 = ex.decode(blk.token_id, mtp_enabled=True, force_accept=0)
+            assert blk2.token_id == exp_tokens[len(blk.emitted)]
+    finally:
+        ex.unload()
+        be.close()
+
 
 def test_select_target_token_samples_from_the_kept_logits(setup, orc):
     """ModelExecutor::select_target_token (engine.rs:322-362): the sampler runs on the logits the
