@@ -108,15 +108,16 @@ void launch_norm_prep(cudaStream_t st, const float *h, const float *w, float eps
 }
 
 // Residual add, RMS norm and the next projection's fragments in ONE kernel (the shared part is
-// residual_norm_finish, layers.cuh). For hidden <= kRnCluster * kRnThreads = 5120.
-__global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
+// residual_norm_finish, layers.cuh). For hidden <= kRnColumns.
+template <int CL>
+__global__ void __launch_bounds__(kRnColumns / CL, 1) k_residual_norm_prep(float *__restrict__ h, MvOut add, int has_add,
                                                                     uint32_t hidden, const float *__restrict__ w,
                                                                     float eps, int npos, float *__restrict__ xn_out,
                                                                     MvIn next, int has_next, uint32_t nblocks) {
     pdl_launch();
     const uint32_t tid = threadIdx.x, rank = blockIdx.x;  // gridDim.x == cluster size
     const int m = blockIdx.y;
-    const uint32_t c = rank * kRnThreads + tid;
+    const uint32_t c = rank * (kRnColumns / CL) + tid;
     const float wc = c < hidden ? w[c] : 0.f;  // constants first: they do not depend on earlier kernels
     const float sc = (has_next && next.s_in && c < hidden) ? next.s_in[c] : 1.0f;
     const OutRef ar = (has_add && c < hidden) ? out_ref(add, c) : OutRef{nullptr, 0, 0, 1.0f, false};
@@ -129,7 +130,7 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_residual_norm_prep(float *__r
             h[(size_t)m * hidden + c] = v;
         }
     }
-    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks);
+    residual_norm_finish<CL>(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks);
 }
 
 void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, const float *w, float eps,
@@ -139,11 +140,30 @@ void launch_residual_norm_prep(cudaStream_t st, float *h, const MvOut *add, cons
         return !(v && v[0] == '0');
     }();
     const uint32_t nblocks = next ? next->blocks_padded : (hidden + 63) / 64;
-    if (merged && hidden <= kRnCluster * kRnThreads && nblocks <= kRnCluster * kRnBlocks) {
+    if (merged && hidden <= kRnColumns && nblocks <= kRnColumns / 64) {
         MvOut a = add ? *add : MvOut{};
         MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
-        launch_pdl_cluster(k_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnThreads), 0, st, kRnCluster, h, a,
-                           add != nullptr, hidden, w, eps, (int)m, xn_out, n, next != nullptr, nblocks);
+        // one or two positions: 16 CTAs per cluster (more than the portable size: the kernel opts in,
+        // once per device); more positions: 8
+        static thread_local unsigned long long wide_ok = 0, wide_tried = 0;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (m <= 2 && dev < 64 && !(wide_tried >> dev & 1ull)) {
+            wide_tried |= 1ull << dev;
+            if (cudaFuncSetAttribute(k_residual_norm_prep<kRnClusterWide>, cudaFuncAttributeNonPortableClusterSizeAllowed,
+                                     1) == cudaSuccess)
+                wide_ok |= 1ull << dev;
+            else
+                cudaGetLastError();
+        }
+        if (m <= 2 && dev < 64 && (wide_ok >> dev & 1ull))
+            launch_pdl_cluster(k_residual_norm_prep<kRnClusterWide>, dim3(kRnClusterWide, m),
+                               dim3(kRnColumns / kRnClusterWide), 0, st, kRnClusterWide, h, a, add != nullptr, hidden, w,
+                               eps, (int)m, xn_out, n, next != nullptr, nblocks);
+        else
+            launch_pdl_cluster(k_residual_norm_prep<kRnCluster>, dim3(kRnCluster, m), dim3(kRnColumns / kRnCluster), 0, st,
+                               kRnCluster, h, a, add != nullptr, hidden, w, eps, (int)m, xn_out, n, next != nullptr,
+                               nblocks);
         return;
     }
     launch_residual_add(st, h, add, hidden, m, scratch);

@@ -135,13 +135,16 @@ __device__ __forceinline__ float out_of(const MvOut &o, uint32_t row, uint32_t p
 // distributed shared memory (one cluster barrier instead of a kernel boundary), then each CTA
 // normalises its kRnThreads columns and writes its kRnBlocks 64-column blocks of the next projection's
 // fragments. wc = norm weight, sc = s_in of column c. Every thread of the cluster must call it.
-// (measured per speculative block: 5 CTAs of 1024 threads 6.24 ms, 8 of 640 6.18, 10 of 512 6.22,
-// 16 of 320 6.24; one CTA of 1024 threads with five columns per thread 7.74)
-constexpr int kRnCluster = 8, kRnThreads = 5120 / kRnCluster, kRnBlocks = kRnThreads / 64;
-static_assert(kRnThreads % 64 == 0 && kRnThreads <= 1024, "whole 64-column blocks per CTA");
+// (measured per speculative block of four verify positions: 5 CTAs of 1024 threads 6.24 ms, 8 of 640
+// 6.18, 10 of 512 6.22, 16 of 320 6.24; one CTA of 1024 threads with five columns per thread 7.74. With
+// one position 16 CTAs are the fastest: 196.5 against 194.8 tokens/s of plain decode.)
+constexpr int kRnCluster = 8, kRnClusterWide = 16, kRnColumns = 5120;
+template <int CL>
 __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, float wc, float sc, float eps, int m,
                                                      int npos, float *__restrict__ xn_out, const MvIn &next,
                                                      int has_next, uint32_t nblocks) {
+    constexpr int kRnThreads = kRnColumns / CL, kRnBlocks = kRnThreads / 64;
+    static_assert(kRnThreads % 64 == 0 && kRnThreads <= 1024, "whole 64-column blocks per CTA");
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float red[kRnThreads / 32];
@@ -162,7 +165,7 @@ __device__ __forceinline__ void residual_norm_finish(float v, uint32_t hidden, f
     }
     cluster.sync();
     float total = 0.f;
-    for (int r = 0; r < kRnCluster; ++r) total += *cluster.map_shared_rank(&part, r);  // rank order
+    for (int r = 0; r < CL; ++r) total += *cluster.map_shared_rank(&part, r);  // rank order
     // nobody may leave while its `part` can still be read: every thread arrives here and waits for
     // the others only at the very end, behind its stores
     cluster.barrier_arrive();

@@ -187,14 +187,14 @@ __global__ void __launch_bounds__(kTpChunk) k_tp_reduce_residual(MvOut o, float 
 // The same, then the RMS norm of the new residual and the next projection's fragments without a
 // kernel boundary: a thread-block cluster of kRnCluster CTAs per position (residual_norm_finish).
 // A wait that runs out leaves v undefined but every thread still reaches the cluster barriers.
-__global__ void __launch_bounds__(kRnThreads, 1) k_tp_reduce_residual_norm_prep(
+__global__ void __launch_bounds__(kRnColumns / kRnCluster, 1) k_tp_reduce_residual_norm_prep(
     MvOut o, float *__restrict__ h, TpPeerPtrs peers, const uint2 *recv, size_t source_stride, uint32_t rank,
     uint32_t world, uint32_t seq, uint32_t hidden, int32_t *error_flag, long long wait_limit,
     const float *__restrict__ w, float eps, int npos, float *__restrict__ xn_out, MvIn next, int has_next,
     uint32_t nblocks) {
     pdl_launch();
     const int m = blockIdx.y;
-    const uint32_t c = blockIdx.x * kRnThreads + threadIdx.x;
+    const uint32_t c = blockIdx.x * (kRnColumns / kRnCluster) + threadIdx.x;
     const float wc = c < hidden ? w[c] : 0.f;  // constants first: they do not depend on earlier kernels
     const float sc = (has_next && next.s_in && c < hidden) ? next.s_in[c] : 1.0f;
     const OutRef oref = c < hidden ? out_ref(o, c) : OutRef{nullptr, 0, 0, 1.0f, false};
@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kRnThreads, 1) k_tp_reduce_residual_norm_prep(
     float v = 0.f;
     if (c < hidden)
         v = tp_push_collect(o, oref, h, peers, recv, source_stride, rank, world, seq, hidden, c, m, error_flag, wait_limit);
-    residual_norm_finish(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks);
+    residual_norm_finish<kRnCluster>(v, hidden, wc, sc, eps, m, npos, xn_out, next, has_next, nblocks);
 }
 
 ctox_status tp_peer_init(ctox_ctx *ctx, size_t elems) {
@@ -323,7 +323,7 @@ bool tp_peer_reduce_add_norm_fits(uint32_t rows, const MvIn *next) {
         return !(v && v[0] == '0');
     }();
     const uint32_t nblocks = next ? next->blocks_padded : (rows + 63) / 64;
-    return merged && rows <= (uint32_t)kRnCluster * kRnThreads && nblocks <= (uint32_t)kRnCluster * kRnBlocks;
+    return merged && rows <= (uint32_t)kRnColumns && nblocks <= (uint32_t)kRnColumns / 64;
 }
 
 ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *sumsq,
@@ -339,7 +339,7 @@ ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows
     for (uint32_t r = 0; r < tp->world; ++r) pp.dst[r] = tp->peer_recv[r] + parity_off + (size_t)tp->rank * tp->elems;
     const MvIn n = next ? *next : MvIn{nullptr, nullptr, nullptr, 0, 0, 0};
     const uint32_t nblocks = next ? next->blocks_padded : (rows + 63) / 64;
-    launch_pdl_cluster(k_tp_reduce_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnThreads), 0, ctx->stream,
+    launch_pdl_cluster(k_tp_reduce_residual_norm_prep, dim3(kRnCluster, m), dim3(kRnColumns / kRnCluster), 0, ctx->stream,
                        kRnCluster, o, h, pp, tp->recv + parity_off, tp->elems, tp->rank, tp->world, seq, rows,
                        ctx->dev_error, ctx->wait_limit_cycles, w, eps, (int)m, xn_out, n, next != nullptr, nblocks);
     CTOX_CUDA(ctx, cudaGetLastError());
