@@ -311,6 +311,32 @@ def test_context_capacity_is_a_shape_error_and_leaves_the_session_usable(orc):
         assert be.allocated_bytes() == 0
         be.close()
 
+def test_dependent_launch_overlap_changes_no_bit(tmp_path):
+    """Every kernel may start before the one in front of it has finished and does part of its work
+    ahead of its dependency wait (weights, constants, piece references, committed state). Whatever it
+    reads there must not be written by anything still in flight: the blocks, logits and hidden
+    states of a full-width 8-layer model are the same, bit for bit, with CTOX_PDL=0, which
+    serialises every launch."""
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    outs = []
+    for name, pdl in (("overlapped", None), ("serialised", "0")):
+        env = dict(os.environ)
+        env["PYTHONPATH"] = os.path.dirname(here) + os.pathsep + env.get("PYTHONPATH", "")
+        env.pop("CTOX_PDL", None)
+        if pdl is not None:
+            env["CTOX_PDL"] = pdl
+        path = str(tmp_path / (name + ".npz"))
+        r = subprocess.run([sys.executable, os.path.join(here, "pdl_worker.py"), path], env=env, capture_output=True,
+                           text=True, timeout=900)
+        assert r.returncode == 0, r.stderr[-2000:]
+        outs.append(np.load(path))
+    a, b = outs
+    assert np.array_equal(a["tokens"], b["tokens"])
+    assert np.array_equal(a["logits"], b["logits"]) and np.array_equal(a["hidden"], b["hidden"])
+
 
 def test_a_peer_that_never_answers_runs_out_the_bounded_wait_and_poisons_the_session(orc):
     """Failure detection without a fault: rank 0 of a two-rank group whose peer never pushes its
