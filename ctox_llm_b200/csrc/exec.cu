@@ -969,7 +969,7 @@ ctox_status add_and_norm(ctox_exec *e, float *h, ctox_matvec *mv, uint32_t m, co
         const MvIn nin = next ? mv_in(next) : MvIn{};
         if (!add_only && tp_peer_reduce_add_norm_fits(c.hidden_size, next ? &nin : nullptr)) {
             // group sum, residual add, norm and fragments as one cluster kernel
-            EX(tp_peer_reduce_add_norm(ctx, o, c.hidden_size, m, h, e->norm_scratch, norm_w, c.rms_norm_epsilon, xn_out,
+            EX(tp_peer_reduce_add_norm(ctx, o, c.hidden_size, m, h, norm_w, c.rms_norm_epsilon, xn_out,
                                        next ? &nin : nullptr));
             return CTOX_OK;
         }

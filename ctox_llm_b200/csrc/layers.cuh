@@ -62,7 +62,7 @@ ctox_status tp_peer_reduce_add(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uin
 // (null: xn_out only). False when the shape does not fit the merged kernel (the caller then uses
 // tp_peer_reduce_add + launch_norm_prep).
 bool tp_peer_reduce_add_norm_fits(uint32_t rows, const MvIn *next);
-ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *scratch,
+ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h,
                                     const float *w, float eps, float *xn_out, const MvIn *next);
 // MTP input: fragments of concat(rmsnorm_1p(embed(tok[m])), rmsnorm_1p(prev_hidden[m])) * s_in.
 void launch_mtp_pre(cudaStream_t st, const float *embed_rows, const float *prev_hidden, const float *w_embed,

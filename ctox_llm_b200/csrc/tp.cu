@@ -326,7 +326,7 @@ bool tp_peer_reduce_add_norm_fits(uint32_t rows, const MvIn *next) {
     return merged && rows <= (uint32_t)kRnColumns && nblocks <= (uint32_t)kRnColumns / 64;
 }
 
-ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h, float *sumsq,
+ctox_status tp_peer_reduce_add_norm(ctox_ctx *ctx, const MvOut &o, uint32_t rows, uint32_t m, float *h,
                                     const float *w, float eps, float *xn_out, const MvIn *next) {
     TpPeer *tp = ctx->tp_peer;
     if (!tp) return fail(ctx, CTOX_INVALID_STATE, "tp: peer all-reduce is not set up");
